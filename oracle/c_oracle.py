@@ -1,0 +1,59 @@
+"""ctypes loader for oracle/liboracle.so (TEST INFRASTRUCTURE; see attn_oracle.c)."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+def build():
+    subprocess.check_call(["make", "-s", "-C", _HERE, "liboracle.so"])
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        _LIB = ctypes.CDLL(path)
+        _LIB.oracle_num_threads.restype = ctypes.c_int
+    return _LIB
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p) if a is not None else None
+
+
+def attention(Q, K, V, mask_add=None, scale=0.0, causal=False, seq_lens=None):
+    Q = np.ascontiguousarray(Q, np.float32)
+    K = np.ascontiguousarray(K, np.float32)
+    V = np.ascontiguousarray(V, np.float32)
+    B, H, S, D = Q.shape
+    T = K.shape[2]
+    out = np.empty_like(Q)
+    m = None if mask_add is None else np.ascontiguousarray(mask_add, np.float32)
+    sl = None if seq_lens is None else np.ascontiguousarray(seq_lens, np.int32)
+    lib().oracle_attention_f32(_p(Q), _p(K), _p(V), _p(m), _p(out), B, H, S, T, D,
+                               ctypes.c_float(scale), int(bool(causal)), _p(sl))
+    return out
+
+
+def gqa_decode(q, k_cache, v_cache, cache_lens=None, scale=0.0):
+    q = np.ascontiguousarray(q, np.float32)
+    k_cache = np.ascontiguousarray(k_cache, np.float32)
+    v_cache = np.ascontiguousarray(v_cache, np.float32)
+    B, _, Hq, D = q.shape
+    Tmax, Hkv = k_cache.shape[1], k_cache.shape[2]
+    out = np.empty_like(q)
+    cl = None if cache_lens is None else np.ascontiguousarray(np.broadcast_to(cache_lens, (B,)), np.int32)
+    lib().oracle_gqa_decode_f32(_p(q), _p(k_cache), _p(v_cache), _p(out), B, Hq, Hkv, D, Tmax,
+                                _p(cl), ctypes.c_float(scale))
+    return out
+
+
+def num_threads():
+    return lib().oracle_num_threads()
