@@ -1,0 +1,446 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One JSON line on stdout (rank 0).  Headline metric: prefill attention TFLOP/s on configuration 2
+(FlashAttention-2 + RoPE, causal, batch 4, 32 heads, seq 2048, head_dim 128, bf16 tensor-core
+path); the decode configuration 3 (GQA decode, batch 32, 32/8 heads, KV 4096 -> 4352, 256 steps)
+is measured in the same run and reported under "decode".  Synthetic N(0,1) inputs from a seed.
+
+A step is one pass of the hot path over one batch.  `value` times the kernel with inputs resident
+in HBM (CUDA events on the library's stream); `e2e` times the public Python op
+(grilly_core.flash_attention2 / decode_step) with pinned HOST buffers, copies inside the timed
+region.  With N > 1 (torchrun, one process per GPU) every rank runs the same per-GPU workload on
+its own GPU (weak scaling, no data-path collective); times are the max over ranks.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "grilly-next_b200", "python"))
+
+CFG2 = dict(B=4, H=32, S=2048, D=128, theta=10000.0, seed=1002)
+CFG3 = dict(B=32, Hq=32, Hkv=8, D=128, T0=4096, steps=256, theta=10000.0, seed=1003, page=64)
+
+
+def prefill_flops(c):
+    return 4 * c["D"] * c["B"] * c["H"] * (c["S"] * (c["S"] + 1) // 2)
+
+
+def decode_bytes(c):
+    """Algorithmic bytes of the 256-step run: K+V rows attended (bf16) + q read + O write + append write."""
+    per_pos = 2 * c["B"] * c["Hkv"] * c["D"] * 2
+    kv = sum(per_pos * (c["T0"] + t + 1) for t in range(c["steps"]))
+    other = c["steps"] * (c["B"] * c["Hq"] * c["D"] * (4 + 4) + 2 * c["B"] * c["Hkv"] * c["D"] * 2)
+    return kv + other
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm=d["hbm_gbs"], tf=d["bf16_tflops"], tf_sustained=d.get("bf16_tflops_sustained"), src="measured")
+    return dict(hbm=6650.0, tf=1590.0, tf_sustained=1400.0, src="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------- reference arm
+def run_reference(args):
+    """The reference's CPU implementation of the path: its Vulkan shaders cannot run here (no
+    graphics stack) and its C++ library does not build without the Vulkan SDK, so this arm times
+    the C restatement of its CPU attention (oracle/attn_oracle.c, OpenMP, all host threads)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import c_oracle
+    c = CFG2
+    heads = 32                                   # bounded sample: 32 of the 128 (batch, head) pairs per step
+    rng = np.random.default_rng(c["seed"])
+    Q, K, V = (rng.standard_normal((1, heads, c["S"], c["D"]), dtype=np.float32) for _ in range(3))
+    from oracle import attention_oracle as orc
+    pos = np.arange(c["S"])
+    fl = 4 * c["D"] * heads * (c["S"] * (c["S"] + 1) // 2)
+    for _ in range(max(1, min(args.warmup, 2))):
+        c_oracle.attention(Q, K, V, causal=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        q = orc.rope_interleaved(Q, pos, c["theta"])   # RoPE is part of the path
+        k = orc.rope_interleaved(K, pos, c["theta"])
+        c_oracle.attention(q, k, V, causal=True)
+    dt = time.perf_counter() - t0
+    val = fl * args.steps / dt / 1e12
+    line = {
+        "impl": "reference", "metric": "prefill_attn_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg2: FlashAttention-2+RoPE causal prefill, B4 H32 S2048 D128", "l2": "inputs larger than L2"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": c_oracle.num_threads(), "kind": "port",
+                         "sample": f"{heads} of 128 (batch, head) slices of cfg2 per step, RoPE + causal attention, C/OpenMP"},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------- our arm
+def pinned_array(L, shape, dtype):
+    n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+    p = C.c_void_p()
+    rc = L.grl_host_alloc(n, C.byref(p))
+    if rc != 0:
+        raise RuntimeError(L.grl_last_error().decode())
+    buf = (C.c_char * n).from_address(p.value)
+    return np.frombuffer(buf, dtype=dtype).reshape(shape), p
+
+
+def bench_prefill(dev, cabi, args, dist):
+    c = CFG2
+    B, H, S, D = c["B"], c["H"], c["S"], c["D"]
+    rng = np.random.default_rng(c["seed"] + dist["rank"])
+    n = B * H * S * D
+    q = dev.upload_bf16(rng.standard_normal((B, H, S, D), dtype=np.float32))
+    k = dev.upload_bf16(rng.standard_normal((B, H, S, D), dtype=np.float32))
+    v = dev.upload_bf16(rng.standard_normal((B, H, S, D), dtype=np.float32))
+    o = dev.malloc(n * 4)
+    p = cabi.FlashParams()
+    p.q, p.k, p.v, p.o = q, k, v, o
+    p.in_dtype, p.out_dtype = cabi.BF16, cabi.F32
+    p.batch, p.heads, p.seq_len, p.head_dim = B, H, S, D
+    p.causal, p.rope_mode, p.rope_theta, p.rope_scaling = 1, cabi.ROPE_INTERLEAVED, c["theta"], 1.0
+    p.kernel = cabi.KERNEL_TCGEN05
+    L = dev.L
+
+    def step():
+        cabi.check(L.grl_flash_fwd(dev.h, C.byref(p)))
+
+    for _ in range(args.warmup):
+        step()
+    dev.sync()
+    e0, e1 = dev.event(), dev.event()
+    sampler = ClockSampler(dist["local_rank"])
+    sampler.start()
+    dist["barrier"]()
+    launches0 = L.grl_launch_count()
+    dev.record(e0)
+    for _ in range(args.steps):
+        step()
+    dev.record(e1)
+    dev.sync()
+    ms = dev.elapsed_ms(e0, e1)
+    launches = L.grl_launch_count() - launches0
+    ms = dist["max"](ms)
+    dist["barrier"]()
+    clocks = sampler.stop()
+    for x in (q, k, v, o):
+        dev.free(x)
+    return ms, launches, clocks
+
+
+def bench_prefill_e2e(args, L, steps, dist):
+    """grilly_core.flash_attention2(dtype='bf16') with pinned host arrays: upload, cast, kernel, download."""
+    import grilly_core
+    c = CFG2
+    shape = (c["B"], c["H"], c["S"], c["D"])
+    rng = np.random.default_rng(c["seed"])
+    arrs, ptrs = [], []
+    for _ in range(3):
+        a, pp = pinned_array(L, shape, np.float32)
+        a[...] = rng.standard_normal(shape, dtype=np.float32)
+        arrs.append(a)
+        ptrs.append(pp)
+    ctx = grilly_core.Device()
+    kw = dict(causal=True, rope_theta=c["theta"], dtype="bf16")
+    for _ in range(2):
+        out = grilly_core.flash_attention2(ctx, *arrs, **kw)
+    dist["barrier"]()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        out = grilly_core.flash_attention2(ctx, *arrs, **kw)   # synchronous: returns with the result on the host
+    dt = dist["max"]((time.perf_counter() - t0) / steps)
+    assert np.isfinite(out[0, 0, -1]).all()
+    del ctx
+    for pp in ptrs:
+        L.grl_host_free(pp)
+    nbytes = int(np.prod(shape)) * 4
+    return dt, 3 * nbytes, nbytes
+
+
+def bench_decode(dev, cabi, dist, repeats=3):
+    """cfg3: 256 decode steps (RoPE + append + split-KV attention + merge), graph-replayed."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle import attention_oracle as orc
+    c = CFG3
+    B, Hq, Hkv, D, T0, steps, P = c["B"], c["Hq"], c["Hkv"], c["D"], c["T0"], c["steps"], c["page"]
+    L = dev.L
+    rng = np.random.default_rng(c["seed"] + dist["rank"])
+    max_tokens = T0 + steps
+    max_pages = (max_tokens + P - 1) // P
+    n_pages = max_pages * B
+    page_elems = Hkv * P * D
+    kp, vp = dev.malloc(n_pages * page_elems * 2), dev.malloc(n_pages * page_elems * 2)
+    # iid N(0,1) bf16 in every page (the prefix is "already rotated" keys; layout does not matter for iid data)
+    chunk = rng.standard_normal(32 * page_elems, dtype=np.float32)
+    bits = orc.to_bf16_bits(chunk)
+    for dst in (kp, vp):
+        off = 0
+        total = n_pages * page_elems
+        while off < total:
+            m = min(bits.size, total - off)
+            rolled = np.roll(bits, int(rng.integers(0, bits.size)))[:m]
+            cabi.check(L.grl_memcpy_h2d(dev.h, C.c_void_p(dst.value + off * 2), rolled.ctypes.data_as(C.c_void_p), m * 2))
+            dev.sync()
+            off += m
+    table = dev.upload(np.arange(n_pages, dtype=np.int32).reshape(B, max_pages))
+    lens0 = np.full(B, T0, np.int32)
+    seq_lens = dev.upload(lens0)
+    qs = dev.upload(rng.standard_normal((steps, B, 1, Hq, D), dtype=np.float32))
+    ks = dev.upload(rng.standard_normal((steps, B, 1, Hkv, D), dtype=np.float32))
+    vs = dev.upload(rng.standard_normal((steps, B, 1, Hkv, D), dtype=np.float32))
+    q_rot = dev.malloc(B * Hq * D * 4)
+    out = dev.malloc(steps * B * Hq * D * 4)
+
+    lay = cabi.KVLayout()
+    lay.k_pages, lay.v_pages, lay.cache_dtype = kp, vp, cabi.BF16
+    lay.block_table, lay.seq_lens = table, seq_lens
+    lay.batch, lay.num_kv_heads, lay.head_dim, lay.page_tokens, lay.max_pages = B, Hkv, D, P, max_pages
+    dp = cabi.DecodeParams()
+    dp.kv, dp.num_q_heads, dp.max_seq_len = lay, Hq, max_tokens
+    ns = C.c_int()
+    cabi.check(L.grl_decode_pick_splits(dev.h, C.byref(dp), C.byref(ns)))
+    wb = C.c_size_t()
+    cabi.check(L.grl_decode_workspace_bytes(C.byref(dp), ns.value, C.byref(wb)))
+    ws = dev.malloc(wb.value)
+    dp.n_splits, dp.workspace, dp.workspace_bytes = ns.value, ws, wb.value
+
+    def record_steps():
+        for t in range(steps):
+            ap = cabi.AppendParams()
+            ap.kv = lay
+            ap.k_new = C.c_void_p(ks.value + t * B * Hkv * D * 4)
+            ap.v_new = C.c_void_p(vs.value + t * B * Hkv * D * 4)
+            ap.q_in = C.c_void_p(qs.value + t * B * Hq * D * 4)
+            ap.q_out = q_rot
+            ap.n_new, ap.num_q_heads = 1, Hq
+            ap.rope_mode, ap.rope_theta, ap.rope_scaling, ap.pos_base, ap.update_lens = cabi.ROPE_INTERLEAVED, c["theta"], 1.0, 0, 1
+            cabi.check(L.grl_kv_append(dev.h, C.byref(ap)))
+            dp.q = q_rot
+            dp.out = C.c_void_p(out.value + t * B * Hq * D * 4)
+            cabi.check(L.grl_gqa_decode(dev.h, C.byref(dp)))
+
+    def reset():
+        cabi.check(L.grl_memcpy_h2d(dev.h, seq_lens, lens0.ctypes.data_as(C.c_void_p), lens0.nbytes))
+
+    launches0 = L.grl_launch_count()
+    cabi.check(L.grl_graph_begin(dev.h))
+    record_steps()
+    g = C.c_void_p()
+    cabi.check(L.grl_graph_end(dev.h, C.byref(g)))
+    launches_per_run = L.grl_launch_count() - launches0
+    reset()
+    cabi.check(L.grl_graph_launch(dev.h, g))    # warm-up run
+    dev.sync()
+    best = None
+    e0, e1 = dev.event(), dev.event()
+    for _ in range(repeats):
+        reset()
+        dev.sync()
+        dist["barrier"]()
+        dev.record(e0)
+        cabi.check(L.grl_graph_launch(dev.h, g))
+        dev.record(e1)
+        dev.sync()
+        ms = dist["max"](dev.elapsed_ms(e0, e1))
+        best = ms if best is None else min(best, ms)
+    o_last = dev.download(C.c_void_p(out.value + (steps - 1) * B * Hq * D * 4), (B, Hq, D), np.float32)
+    assert np.isfinite(o_last).all()
+    L.grl_graph_destroy(g)
+    for x in (kp, vp, table, seq_lens, qs, ks, vs, q_rot, out, ws):
+        dev.free(x)
+    return best, launches_per_run, ns.value
+
+
+def bench_decode_e2e(dist, steps=32):
+    """grilly_core.decode_step with host arrays per step (upload q/k/v, append, attend, download)."""
+    import grilly_core
+    c = CFG3
+    B, Hq, Hkv, D, T0 = c["B"], c["Hq"], c["Hkv"], c["D"], c["T0"]
+    rng = np.random.default_rng(c["seed"])
+    ctx = grilly_core.Device()
+    kv = grilly_core.create_kv_cache(ctx, num_heads=Hkv, head_dim=D, compression_ratio=1, max_cache_tokens=T0 + steps + 8,
+                                     use_h2o=False, batch_size=B, page_tokens=c["page"], dtype="bf16")
+    blk = 512
+    for _ in range(T0 // blk):
+        k0 = rng.standard_normal((B, blk, Hkv, D), dtype=np.float32)
+        grilly_core.kv_cache_append(ctx, kv, k0, k0)
+    q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
+    k1 = rng.standard_normal((B, 1, Hkv, D), dtype=np.float32)
+    for _ in range(4):
+        grilly_core.decode_step(ctx, kv, q, k1, k1, rope_theta=c["theta"])
+    dist["barrier"]()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        o = grilly_core.decode_step(ctx, kv, q, k1, k1, rope_theta=c["theta"])
+    dt = dist["max"]((time.perf_counter() - t0) / steps)
+    assert np.isfinite(o).all()
+    grilly_core.destroy_kv_cache(ctx, kv)
+    return dt, (q.nbytes + 2 * k1.nbytes), o.nbytes
+
+
+def cpu_baseline():
+    from oracle import attention_oracle as orc
+    from oracle import c_oracle
+    c = CFG2
+    heads = 32
+    rng = np.random.default_rng(c["seed"])
+    Q, K, V = (rng.standard_normal((1, heads, c["S"], c["D"]), dtype=np.float32) for _ in range(3))
+    pos = np.arange(c["S"])
+    c_oracle.attention(Q[:, :2], K[:, :2], V[:, :2], causal=True)
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < 10.0 and reps < 8:
+        c_oracle.attention(orc.rope_interleaved(Q, pos, c["theta"]), orc.rope_interleaved(K, pos, c["theta"]), V, causal=True)
+        reps += 1
+    dt = time.perf_counter() - t0
+    fl = 4 * c["D"] * heads * (c["S"] * (c["S"] + 1) // 2) * reps
+    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": c_oracle.num_threads(), "kind": "port",
+            "sample": f"{reps} passes over {heads} of 128 (batch, head) slices of cfg2 (RoPE + causal attention), C/OpenMP oracle"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    if args.impl == "reference":
+        return run_reference(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = {"rank": rank, "world": world, "local_rank": local_rank, "barrier": lambda: None, "max": lambda x: x}
+    if world > 1:
+        import torch
+        import torch.distributed as td
+        torch.cuda.set_device(local_rank)
+        td.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+        def _barrier():
+            td.barrier()
+            torch.cuda.synchronize()
+
+        def _max(x):
+            t = torch.tensor([x], dtype=torch.float64, device="cuda")
+            td.all_reduce(t, op=td.ReduceOp.MAX)
+            return float(t.item())
+
+        dist["barrier"], dist["max"] = _barrier, _max
+
+    from grilly_next import cabi
+    dev = cabi.Device(local_rank)          # raises if the CUDA library or the GPU is missing: no fallback
+    L = dev.L
+    pk = peaks()
+
+    ms, launches, clocks = bench_prefill(dev, cabi, args, dist)
+    fl = prefill_flops(CFG2)
+    tflops_gpu = fl * args.steps / (ms * 1e-3) / 1e12
+    value = tflops_gpu * world
+    line = {
+        "metric": "prefill_attn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "cfg2: FlashAttention-2+RoPE causal prefill, B4 H32 S2048 D128, bf16 in / fp32 out, per GPU",
+                   "flops_per_step_per_gpu": fl, "l2": "inputs larger than L2 (320 MiB per step)",
+                   "parallelism": f"replica per GPU x{world}, no collective"},
+        "clocks": clocks, "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": tflops_gpu, "peak": pk["tf"], "unit": "TFLOP/s",
+                     "frac": tflops_gpu / pk["tf"], "traffic": None, "peak_source": pk["src"] + " (burst)",
+                     "frac_of_sustained": tflops_gpu / pk["tf_sustained"] if pk["tf_sustained"] else None,
+                     "frac_of_nominal_2250": tflops_gpu / 2250.0, "kernel": "flash_fwd_sm100_kernel"},
+    }
+
+    if not args.skip_decode:
+        dms, dl, nsplit = bench_decode(dev, cabi, dist)
+        c = CFG3
+        toks = c["B"] * c["steps"] / (dms * 1e-3)
+        gbs = decode_bytes(c) / (dms * 1e-3) / 1e9
+        line["decode"] = {"metric": "decode_tokens_per_s", "value": toks * world, "unit": "tokens/s",
+                          "ms_per_step": dms / c["steps"], "workload": "cfg3: GQA decode B32 Hq32/Hkv8 D128 KV 4096->4352, 256 steps, bf16 paged cache, CUDA-graph replay, per GPU",
+                          "gpu_launches": int(dl), "n_splits": nsplit,
+                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
+                                       "traffic": None, "peak_source": pk["src"], "frac_of_nominal_8000": gbs / 8000.0,
+                                       "kernel": "decode_split_kernel"}}
+
+    if not args.skip_e2e:
+        os.environ["GRILLY_GPU_INDEX"] = str(local_rank)     # the op layer's device selector
+        dt, h2d, d2h = bench_prefill_e2e(args, L, min(args.steps, 5), dist)
+        line["e2e"] = {"value": fl / dt / 1e12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "ms_per_step": dt * 1e3, "api": "grilly_core.flash_attention2(dtype='bf16'), pinned fp32 host arrays"}
+        if not args.skip_decode:
+            ddt, dh2d, dd2h = bench_decode_e2e(dist)
+            line["decode"]["e2e"] = {"value": CFG3["B"] / ddt * world, "unit": "tokens/s", "h2d_bytes_per_step": dh2d,
+                                     "d2h_bytes_per_step": dd2h, "ms_per_step": ddt * 1e3, "api": "grilly_core.decode_step"}
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        line["cpu_baseline"] = cpu_baseline()
+
+    dev.close()
+    if world > 1:
+        import torch.distributed as td
+        td.barrier()
+        td.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

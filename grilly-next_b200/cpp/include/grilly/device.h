@@ -1,0 +1,43 @@
+#pragma once
+// CUDA device context of the op layer.  Same role and accessors as the reference's Vulkan
+// GrillyDevice (cpp/include/grilly/device.h:16-53): picks a GPU, owns the queue (here: a CUDA
+// stream inside the C-ABI handle) and reports capabilities.
+#include <stdexcept>
+#include <string>
+
+#include "grilly_cuda.h"
+
+namespace grilly {
+
+/// Throws std::runtime_error carrying the C-ABI's message when rc != GRL_OK.
+inline void check(int rc, const char* what) {
+    if (rc != GRL_OK)
+        throw std::runtime_error(std::string(what) + ": " + grl_last_error());
+}
+
+class GrillyDevice {
+public:
+    /// Opens the GPU named by the GRILLY_GPU_INDEX environment variable (default 0), the
+    /// counterpart of VK_GPU_INDEX (cpp/src/device.cpp:408-414).
+    GrillyDevice();
+    explicit GrillyDevice(int ordinal);
+    ~GrillyDevice();
+    GrillyDevice(const GrillyDevice&) = delete;
+    GrillyDevice& operator=(const GrillyDevice&) = delete;
+
+    grl_device* handle() const { return dev_; }
+    const std::string& deviceName() const { return name_; }
+    bool hasCooperativeMatrix() const { return true; }  // tcgen05 tensor cores
+    bool hasFloat16() const { return true; }
+    int smCount() const { return info_.sm_count; }
+    int ordinal() const { return info_.ordinal; }
+    const grl_device_info& info() const { return info_; }
+
+private:
+    void open(int ordinal);
+    grl_device* dev_ = nullptr;
+    grl_device_info info_{};
+    std::string name_;
+};
+
+}  // namespace grilly

@@ -1,0 +1,56 @@
+#pragma once
+// Prefill attention ops.  flashAttention2 keeps the reference signature
+// (cpp/include/grilly/ops/attention.h:55-62); flashAttention2Ex adds the implicit masks, RoPE
+// and the bf16 tensor-core path; the *Device forms take HBM-resident buffers.
+#include <cstdint>
+
+#include "grilly/buffer_pool.h"
+#include "grilly/command_batch.h"
+#include "grilly/pipeline_cache.h"
+
+namespace grilly {
+namespace ops {
+
+/// Push-constant block of the reference shader (flash-attention2.glsl:49-61), kept as a public POD.
+struct FlashAttention2Params {
+    uint32_t batchSize, seqLen, numHeads, headDim;
+    float scale;
+    uint32_t tileSizeQ, tileSizeK, passType, hasMask, qTileIdx, kTileIdx;
+};
+
+enum class RopeMode : int { None = GRL_ROPE_NONE, Interleaved = GRL_ROPE_INTERLEAVED, Half = GRL_ROPE_HALF };
+enum class Precision : int { FP32 = 0, BF16 = 1 };
+
+/// Extensions over the reference call: everything defaults to the reference behaviour.
+struct FlashAttention2Options {
+    bool causal = false;
+    const int32_t* seqLens = nullptr;   // host, (batch) valid lengths; rows beyond are zero
+    int maskRank = 4;                   // rank of `mask`: 2 (B,S), 3 (B,S,S), 4 (B,H,S,S)
+    bool maskBroadcastHeads = false;    // rank 4 with a head extent of 1
+    RopeMode ropeMode = RopeMode::None;
+    float ropeTheta = 10000.0f;         // rope_base of flash-attention2-rope.glsl:56-71
+    float ropeScaling = 1.0f;
+    Precision precision = Precision::FP32;  // BF16: inputs rounded to bf16, tcgen05 kernel
+};
+
+/// Host pointers in, host pointer out, synchronous -- the reference contract
+/// (cpp/src/ops/attention.cpp:45-166).  Q,K,V,output: (B,H,S,D) float32 row-major;
+/// mask: nullptr or (B,H,S,S) floats, > 0 keeps.
+void flashAttention2(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* Q, const float* K,
+                     const float* V, const float* mask, float* output, uint32_t batchSize, uint32_t seqLen,
+                     uint32_t numHeads, uint32_t headDim, float scale = 0.0f, uint32_t tileSizeQ = 64,
+                     uint32_t tileSizeK = 64);
+
+void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* Q, const float* K,
+                       const float* V, const float* mask, float* output, uint32_t batchSize, uint32_t seqLen,
+                       uint32_t numHeads, uint32_t headDim, float scale, const FlashAttention2Options& opt);
+
+/// Device-resident form: q,k,v,out are HBM buffers of dtype inDtype/outDtype (GRL_F32 / GRL_BF16),
+/// seqLensDev a device int32 buffer or empty.  Asynchronous on the context stream.
+void flashAttention2Device(CommandBatch& batch, PipelineCache& cache, const GrillyBuffer& q, const GrillyBuffer& k,
+                           const GrillyBuffer& v, GrillyBuffer& out, int inDtype, int outDtype, uint32_t batchSize,
+                           uint32_t seqLen, uint32_t numHeads, uint32_t headDim, float scale, bool causal,
+                           const GrillyBuffer* seqLensDev, RopeMode ropeMode, float ropeTheta, float ropeScaling);
+
+}  // namespace ops
+}  // namespace grilly

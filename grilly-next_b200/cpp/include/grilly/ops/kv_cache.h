@@ -1,0 +1,99 @@
+#pragma once
+// Paged, head-major KV cache and GQA decode.  Keeps the reference's KV-cache op surface
+// (cpp/include/grilly/ops/kv_cache.h:46-65,123-177,232-240) for the uncompressed mode
+// (compressionRatio == 1, no quantisation), in which the reference stores only metadata; here
+// the tokens are stored, in pages [page][Hkv][pageTokens][D] of bf16 (or float32).
+#include <cstdint>
+#include <vector>
+
+#include "grilly/buffer_pool.h"
+#include "grilly/command_batch.h"
+#include "grilly/ops/attention.h"
+#include "grilly/pipeline_cache.h"
+
+namespace grilly {
+namespace ops {
+
+struct KVCacheConfig {
+    // reference fields (kv_cache.h:46-65)
+    uint32_t maxSeqLen = 2048;
+    uint32_t numHeads = 8;            // KV heads
+    uint32_t headDim = 64;
+    uint32_t numLayers = 12;
+    uint32_t compressionRatio = 1;    // only 1 (no MLA) is built
+    uint32_t maxCacheTokens = 2048;   // capacity per sequence
+    bool useAsymmetricQuant = false;  // not built
+    uint32_t valueBits = 4;
+    bool crossLayerSharing = false;
+    bool useH2O = false;              // eviction family: not built on the paged cache
+    bool useSpeculativeEviction = false;
+    float evictionThreshold = 0.1f;
+    // paged-cache additions
+    uint32_t batchSize = 1;           // sequences held
+    uint32_t pageTokens = 64;
+    int dtype = GRL_BF16;             // storage type of the pages
+};
+
+struct KVCache {
+    GrillyBuffer kPages, vPages;      // [numPages][Hkv][pageTokens][D]
+    GrillyBuffer blockTable;          // int32 [B][maxPages]
+    GrillyBuffer seqLens;             // int32 [B]
+    std::vector<int32_t> hostBlockTable;
+    std::vector<int32_t> hostSeqLens; // host mirror (lengths advance deterministically)
+    uint32_t maxPages = 0;            // per sequence
+    uint32_t numPages = 0;            // in the pool
+    uint32_t nextFreePage = 0;        // bump allocator over the pool (no eviction => no free list churn)
+    uint32_t currentLen = 0;          // tokens of sequence 0 (the reference's single-sequence view)
+    uint64_t totalAppended = 0;
+    KVCacheConfig config;
+    grl_kv_layout layout() const;
+};
+
+struct KVCacheStats {
+    uint32_t currentTokens, maxTokens, totalEvicted, totalAppended;
+    float compressionRatio, avgAttentionScore;
+    uint32_t pagesTotal, pagesUsed;
+    uint64_t bytes;
+};
+
+KVCache createKVCache(BufferPool& pool, const KVCacheConfig& config);
+void destroyKVCache(BufferPool& pool, KVCache& cache);
+
+/// Reference form (kv_cache.h:163-166): newKeys/newValues (numNewTokens, numHeads, headDim) host
+/// float32, appended to sequence 0 (batchSize 1) -- or (B, numNewTokens, numHeads, headDim) when
+/// the cache holds B sequences.  No RoPE.
+void kvCacheAppend(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kvCache,
+                   const float* newKeys, const float* newValues, uint32_t numNewTokens);
+
+/// Append with fused RoPE of the new keys (and optionally of the step's queries, rotated in place
+/// into qOut) at position posBase + current length.
+void kvCacheAppendRope(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kvCache,
+                       const float* newKeys, const float* newValues, uint32_t numNewTokens, const float* qIn,
+                       float* qOut, uint32_t numQHeads, RopeMode mode, float theta, float scaling,
+                       int32_t posBase = 0);
+
+/// Reference form (kv_cache.h:175-177): sequence `seq` back as (T, numHeads, headDim) float32.
+void kvCacheDecode(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const KVCache& kvCache,
+                   float* decodedKeys, float* decodedValues, uint32_t seq = 0);
+
+KVCacheStats kvCacheGetStats(const KVCache& kvCache);
+
+/// GQA decode attention over the cache (shaders/gqa-attention.glsl:34-130): q, out (B,1,Hq,D)
+/// host float32, already rotated.
+void gqaAttention(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const KVCache& kvCache,
+                  const float* q, float* out, uint32_t numQHeads, float scale = 0.0f, int nSplits = 0);
+
+/// One decode step: RoPE(q, k) at the current position, append k/v, attend over the cache.
+/// q (B,1,Hq,D), kNew/vNew (B,1,Hkv,D), out (B,1,Hq,D): host float32.
+void decodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kvCache, const float* q,
+                const float* kNew, const float* vNew, float* out, uint32_t numQHeads, RopeMode mode, float theta,
+                float scaling, float scale = 0.0f);
+
+// Eviction family of the reference (kv_cache.h:186-229): not built on the paged cache; each
+// throws std::runtime_error naming itself.
+void kvCacheEvictH2O(CommandBatch&, BufferPool&, PipelineCache&, KVCache&, const float* attentionScores,
+                     uint32_t numEvict = 0);
+void kvCacheCompact(CommandBatch&, BufferPool&, PipelineCache&, KVCache&);
+
+}  // namespace ops
+}  // namespace grilly

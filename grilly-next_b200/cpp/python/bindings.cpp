@@ -1,0 +1,359 @@
+// grilly_core: pybind11 module with the reference's names, keyword arguments and defaults for the
+// attention / KV-cache subset (cpp/python/bindings.cpp:169-206, 416-462, 592-694 of the reference),
+// plus additive keyword arguments for the fused masks, RoPE, the bf16 tensor-core path and decode.
+#include <pybind11/numpy.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <optional>
+#include <string>
+
+#include "grilly/buffer_pool.h"
+#include "grilly/command_batch.h"
+#include "grilly/device.h"
+#include "grilly/ops/attention.h"
+#include "grilly/ops/kv_cache.h"
+#include "grilly/ops/rope.h"
+#include "grilly/pipeline_cache.h"
+
+namespace py = pybind11;
+using namespace grilly;
+using FArr = py::array_t<float, py::array::c_style | py::array::forcecast>;
+using IArr = py::array_t<int32_t, py::array::c_style | py::array::forcecast>;
+
+/// One object holding device -> pool -> cache -> batch, like the reference's GrillyCoreContext.
+struct GrillyCoreContext {
+    GrillyDevice device;
+    BufferPool pool;
+    PipelineCache cache;
+    CommandBatch batch;
+    bool shadersLoaded = false;
+    GrillyCoreContext() : device(), pool(device), cache(device), batch(device) {}
+    /// Kernels are compiled into the library; the call is kept so that callers written for the
+    /// Vulkan backend keep working.
+    void loadShaders(const std::string&) { shadersLoaded = true; }
+};
+
+static ops::RopeMode parseRopeMode(const std::string& m, bool allowNone) {
+    if (m == "interleaved") return ops::RopeMode::Interleaved;
+    if (m == "half" || m == "rotate_half") return ops::RopeMode::Half;
+    if (allowNone && (m == "none" || m.empty())) return ops::RopeMode::None;
+    throw std::runtime_error("rope_mode must be 'interleaved' or 'half'");
+}
+
+static py::array_t<float> flashImpl(GrillyCoreContext& ctx, FArr Q, FArr K, FArr V, std::optional<FArr> mask,
+                                    float scale, bool causal, std::optional<IArr> seqLens, float ropeTheta,
+                                    float ropeScaling, const std::string& ropeMode, const std::string& dtype) {
+    if (Q.ndim() != 4) throw std::runtime_error("Q must be 4D (batch, heads, seq_len, head_dim)");
+    if (K.ndim() != 4 || V.ndim() != 4) throw std::runtime_error("K and V must be 4D (batch, heads, seq_len, head_dim)");
+    for (int i = 0; i < 4; ++i)
+        if (K.shape(i) != Q.shape(i) || V.shape(i) != Q.shape(i))
+            throw std::runtime_error("Q, K and V must have the same shape");
+    const uint32_t B = uint32_t(Q.shape(0)), H = uint32_t(Q.shape(1)), S = uint32_t(Q.shape(2)), D = uint32_t(Q.shape(3));
+    ops::FlashAttention2Options opt;
+    opt.causal = causal;
+    const float* maskPtr = nullptr;
+    if (mask.has_value()) {
+        const auto& m = *mask;
+        const bool ok2 = m.ndim() == 2 && m.shape(0) == B && m.shape(1) == S;
+        const bool ok3 = m.ndim() == 3 && m.shape(0) == B && m.shape(1) == S && m.shape(2) == S;
+        const bool ok4 = m.ndim() == 4 && m.shape(0) == B && (m.shape(1) == H || m.shape(1) == 1) && m.shape(2) == S &&
+                         m.shape(3) == S;
+        if (!ok2 && !ok3 && !ok4)
+            throw std::runtime_error("mask must be (batch, seq), (batch, seq, seq) or (batch, heads|1, seq, seq)");
+        opt.maskRank = int(m.ndim());
+        opt.maskBroadcastHeads = ok4 && m.shape(1) == 1 && H != 1;
+        maskPtr = m.data();
+    }
+    if (seqLens.has_value()) {
+        if (seqLens->ndim() != 1 || seqLens->shape(0) != B) throw std::runtime_error("seq_lens must be (batch,)");
+        opt.seqLens = seqLens->data();
+    }
+    if (ropeTheta != 0.0f) {
+        opt.ropeMode = parseRopeMode(ropeMode, false);
+        opt.ropeTheta = ropeTheta;
+        opt.ropeScaling = ropeScaling;
+    }
+    if (dtype == "bf16") opt.precision = ops::Precision::BF16;
+    else if (dtype != "fp32") throw std::runtime_error("dtype must be 'fp32' or 'bf16'");
+    py::array_t<float> result({py::ssize_t(B), py::ssize_t(H), py::ssize_t(S), py::ssize_t(D)});
+    float* out = result.mutable_data();
+    const float *q = Q.data(), *k = K.data(), *v = V.data();
+    {
+        py::gil_scoped_release nogil;
+        ops::flashAttention2Ex(ctx.batch, ctx.pool, ctx.cache, q, k, v, maskPtr, out, B, S, H, D, scale, opt);
+    }
+    return result;
+}
+
+PYBIND11_MODULE(grilly_core, m) {
+    m.doc() = "grilly C++ backend, CUDA (sm_100a) build of the attention / KV-cache ops";
+    m.attr("BACKEND") = "cuda-sm100a";
+
+    py::class_<GrillyCoreContext>(m, "Device")
+        .def(py::init<>(), "Initialize the CUDA device, buffer pool and kernel-plan cache")
+        .def("load_shaders", &GrillyCoreContext::loadShaders, py::arg("shader_dir"),
+             "Accepted for compatibility; kernels are linked into the library")
+        .def_property_readonly("device_name", [](const GrillyCoreContext& c) { return c.device.deviceName(); })
+        .def_property_readonly("has_cooperative_matrix",
+                               [](const GrillyCoreContext& c) { return c.device.hasCooperativeMatrix(); })
+        .def_property_readonly("has_float16", [](const GrillyCoreContext& c) { return c.device.hasFloat16(); })
+        .def_property_readonly("sm_count", [](const GrillyCoreContext& c) { return c.device.smCount(); })
+        .def("pool_stats",
+             [](const GrillyCoreContext& c) {
+                 auto s = c.pool.stats();
+                 py::dict d;
+                 d["hits"] = s.hits; d["misses"] = s.misses; d["allocations"] = s.allocations;
+                 d["total_acquired"] = s.totalAcquired; d["total_released"] = s.totalReleased;
+                 return d;
+             })
+        .def("cache_stats", [](const GrillyCoreContext& c) {
+            auto s = c.cache.cacheStats();
+            py::dict d;
+            d["hits"] = s.hits; d["misses"] = s.misses; d["evictions"] = s.evictions; d["cached_sets"] = s.cachedSets;
+            return d;
+        });
+
+    // ---- flash attention 2 (reference: bindings.cpp:416-462)
+    m.def(
+        "flash_attention2",
+        [](GrillyCoreContext& ctx, FArr Q, FArr K, FArr V, std::optional<FArr> mask, float scale, uint32_t, uint32_t,
+           bool causal, std::optional<IArr> seqLens, float ropeTheta, float ropeScaling, const std::string& ropeMode,
+           const std::string& dtype) {
+            return flashImpl(ctx, Q, K, V, mask, scale, causal, seqLens, ropeTheta, ropeScaling, ropeMode, dtype);
+        },
+        py::arg("device"), py::arg("Q"), py::arg("K"), py::arg("V"), py::arg("mask") = py::none(),
+        py::arg("scale") = 0.0f, py::arg("tile_size_q") = 64, py::arg("tile_size_k") = 64, py::arg("causal") = false,
+        py::arg("seq_lens") = py::none(), py::arg("rope_theta") = 0.0f, py::arg("rope_scaling") = 1.0f,
+        py::arg("rope_mode") = "interleaved", py::arg("dtype") = "fp32",
+        "GPU Flash Attention 2 with online softmax tiling");
+
+    // ---- flash attention 2 + RoPE (push block of shaders/flash-attention2-rope.glsl:56-71)
+    m.def(
+        "flash_attention2_rope",
+        [](GrillyCoreContext& ctx, FArr Q, FArr K, FArr V, std::optional<FArr> mask, float scale, float ropeBase,
+           float ropeScaling, bool useRope, bool causal, std::optional<IArr> seqLens, const std::string& dtype) {
+            return flashImpl(ctx, Q, K, V, mask, scale, causal, seqLens, useRope ? ropeBase : 0.0f, ropeScaling,
+                             "interleaved", dtype);
+        },
+        py::arg("device"), py::arg("Q"), py::arg("K"), py::arg("V"), py::arg("mask") = py::none(),
+        py::arg("scale") = 0.0f, py::arg("rope_base") = 10000.0f, py::arg("rope_scaling") = 1.0f,
+        py::arg("use_rope") = true, py::arg("causal") = false, py::arg("seq_lens") = py::none(),
+        py::arg("dtype") = "fp32", "Flash Attention 2 with interleaved-pair RoPE applied to Q and K");
+
+    m.def(
+        "rope",
+        [](GrillyCoreContext& ctx, FArr x, float base, float scaling, std::optional<FArr> cosT,
+           std::optional<FArr> sinT, const std::string& mode) {
+            if (x.ndim() != 4) throw std::runtime_error("x must be 4D (batch, seq_len, heads, head_dim)");
+            const uint32_t B = uint32_t(x.shape(0)), S = uint32_t(x.shape(1)), H = uint32_t(x.shape(2)),
+                           D = uint32_t(x.shape(3));
+            if (cosT.has_value() != sinT.has_value()) throw std::runtime_error("cos and sin tables go together");
+            if (cosT.has_value() &&
+                (cosT->ndim() != 2 || cosT->shape(0) < S || cosT->shape(1) != D / 2 || sinT->ndim() != 2 ||
+                 sinT->shape(0) < S || sinT->shape(1) != D / 2))
+                throw std::runtime_error("cos/sin tables must be (>= seq_len, head_dim/2)");
+            py::array_t<float> y({py::ssize_t(B), py::ssize_t(S), py::ssize_t(H), py::ssize_t(D)});
+            ops::rope(ctx.batch, ctx.pool, ctx.cache, x.data(), y.mutable_data(), B, S, H, D, base, scaling,
+                      parseRopeMode(mode, false), cosT ? cosT->data() : nullptr, sinT ? sinT->data() : nullptr);
+            return y;
+        },
+        py::arg("device"), py::arg("x"), py::arg("base") = 10000.0f, py::arg("scaling") = 1.0f,
+        py::arg("cos") = py::none(), py::arg("sin") = py::none(), py::arg("mode") = "half",
+        "RoPE on (batch, seq_len, heads, head_dim)");
+
+    m.def(
+        "attention_mask",
+        [](GrillyCoreContext& ctx, FArr scores, std::optional<FArr> mask, bool causal, float maskValue) {
+            if (scores.ndim() != 4 || scores.shape(2) != scores.shape(3))
+                throw std::runtime_error("scores must be 4D (batch, heads, seq_len, seq_len)");
+            const uint32_t B = uint32_t(scores.shape(0)), H = uint32_t(scores.shape(1)), S = uint32_t(scores.shape(2));
+            if (!causal && !mask.has_value()) throw std::runtime_error("a (batch, seq_len) mask is required unless causal");
+            if (mask.has_value() && (mask->ndim() != 2 || mask->shape(0) != B || mask->shape(1) != S))
+                throw std::runtime_error("mask must be (batch, seq_len)");
+            py::array_t<float> out({py::ssize_t(B), py::ssize_t(H), py::ssize_t(S), py::ssize_t(S)});
+            std::memcpy(out.mutable_data(), scores.data(), size_t(B) * H * S * S * 4);
+            ops::attentionMask(ctx.batch, ctx.pool, ctx.cache, out.mutable_data(), mask ? mask->data() : nullptr, B, H,
+                               S, causal, maskValue);
+            return out;
+        },
+        py::arg("device"), py::arg("scores"), py::arg("mask") = py::none(), py::arg("causal") = false,
+        py::arg("mask_value") = -1e9f, "Causal or key-padding fill on attention scores; returns the masked copy");
+
+    // ---- KV cache (reference: bindings.cpp:592-694)
+    py::class_<ops::KVCache>(m, "KVCache")
+        .def_readonly("current_len", &ops::KVCache::currentLen)
+        .def_property_readonly("seq_lens", [](const ops::KVCache& kv) { return kv.hostSeqLens; })
+        .def("stats", [](const ops::KVCache& kv) {
+            auto s = ops::kvCacheGetStats(kv);
+            py::dict d;
+            d["current_tokens"] = s.currentTokens; d["max_tokens"] = s.maxTokens;
+            d["total_evicted"] = s.totalEvicted; d["total_appended"] = s.totalAppended;
+            d["compression_ratio"] = s.compressionRatio; d["avg_attention_score"] = s.avgAttentionScore;
+            d["pages_total"] = s.pagesTotal; d["pages_used"] = s.pagesUsed; d["bytes"] = s.bytes;
+            return d;
+        });
+
+    m.def(
+        "create_kv_cache",
+        [](GrillyCoreContext& ctx, uint32_t maxSeqLen, uint32_t numHeads, uint32_t headDim, uint32_t numLayers,
+           uint32_t compressionRatio, uint32_t maxCacheTokens, bool useAsymmetricQuant, uint32_t valueBits,
+           bool crossLayerSharing, bool useH2O, bool useSpeculativeEviction, float evictionThreshold,
+           uint32_t batchSize, uint32_t pageTokens, const std::string& dtype) {
+            ops::KVCacheConfig cfg;
+            cfg.maxSeqLen = maxSeqLen; cfg.numHeads = numHeads; cfg.headDim = headDim; cfg.numLayers = numLayers;
+            cfg.compressionRatio = compressionRatio; cfg.maxCacheTokens = maxCacheTokens;
+            cfg.useAsymmetricQuant = useAsymmetricQuant; cfg.valueBits = valueBits;
+            cfg.crossLayerSharing = crossLayerSharing; cfg.useH2O = useH2O;
+            cfg.useSpeculativeEviction = useSpeculativeEviction; cfg.evictionThreshold = evictionThreshold;
+            cfg.batchSize = batchSize; cfg.pageTokens = pageTokens;
+            if (dtype == "bf16") cfg.dtype = GRL_BF16;
+            else if (dtype == "fp32") cfg.dtype = GRL_F32;
+            else throw std::runtime_error("dtype must be 'bf16' or 'fp32'");
+            return ops::createKVCache(ctx.pool, cfg);
+        },
+        py::arg("device"), py::arg("max_seq_len") = 2048, py::arg("num_heads") = 8, py::arg("head_dim") = 64,
+        py::arg("num_layers") = 12, py::arg("compression_ratio") = 4, py::arg("max_cache_tokens") = 2048,
+        py::arg("use_asymmetric_quant") = false, py::arg("value_bits") = 4, py::arg("cross_layer_sharing") = false,
+        py::arg("use_h2o") = true, py::arg("use_speculative_eviction") = false, py::arg("eviction_threshold") = 0.1f,
+        py::arg("batch_size") = 1, py::arg("page_tokens") = 64, py::arg("dtype") = "bf16",
+        "Create a KV cache (compression_ratio=1 selects the paged head-major cache built here)");
+
+    m.def("destroy_kv_cache",
+          [](GrillyCoreContext& ctx, ops::KVCache& kv) { ops::destroyKVCache(ctx.pool, kv); }, py::arg("device"),
+          py::arg("kv_cache"));
+
+    auto checkNew = [](const ops::KVCache& kv, const FArr& a, const char* name, uint32_t heads) -> uint32_t {
+        const auto& c = kv.config;
+        if (a.ndim() == 3) {
+            if (c.batchSize != 1) throw std::runtime_error(std::string(name) + " must be (batch, n, heads, head_dim) for a batched cache");
+            if (a.shape(1) != heads || a.shape(2) != c.headDim)
+                throw std::runtime_error(std::string(name) + " must be (n, heads, head_dim)");
+            return uint32_t(a.shape(0));
+        }
+        if (a.ndim() == 4) {
+            if (a.shape(0) != c.batchSize || a.shape(2) != heads || a.shape(3) != c.headDim)
+                throw std::runtime_error(std::string(name) + " must be (batch, n, heads, head_dim)");
+            return uint32_t(a.shape(1));
+        }
+        throw std::runtime_error(std::string(name) + " must be 3D or 4D");
+    };
+
+    m.def(
+        "kv_cache_append",
+        [checkNew](GrillyCoreContext& ctx, ops::KVCache& kv, FArr newKeys, FArr newValues, float ropeTheta,
+                   float ropeScaling, const std::string& ropeMode) {
+            const uint32_t n = checkNew(kv, newKeys, "new_keys", kv.config.numHeads);
+            if (checkNew(kv, newValues, "new_values", kv.config.numHeads) != n)
+                throw std::runtime_error("new_keys and new_values differ in length");
+            if (ropeTheta != 0.0f)
+                ops::kvCacheAppendRope(ctx.batch, ctx.pool, ctx.cache, kv, newKeys.data(), newValues.data(), n, nullptr,
+                                       nullptr, 0, parseRopeMode(ropeMode, false), ropeTheta, ropeScaling);
+            else
+                ops::kvCacheAppend(ctx.batch, ctx.pool, ctx.cache, kv, newKeys.data(), newValues.data(), n);
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("new_keys"), py::arg("new_values"),
+        py::arg("rope_theta") = 0.0f, py::arg("rope_scaling") = 1.0f, py::arg("rope_mode") = "interleaved",
+        "Append new KV pairs to the cache");
+
+    m.def(
+        "kv_cache_decode",
+        [](GrillyCoreContext& ctx, const ops::KVCache& kv, uint32_t seq) {
+            const auto& c = kv.config;
+            if (seq >= c.batchSize) throw std::runtime_error("seq out of range");
+            const py::ssize_t T = kv.hostSeqLens.empty() ? 0 : kv.hostSeqLens[seq];
+            py::array_t<float> keys({T, py::ssize_t(c.numHeads), py::ssize_t(c.headDim)});
+            py::array_t<float> values({T, py::ssize_t(c.numHeads), py::ssize_t(c.headDim)});
+            ops::kvCacheDecode(ctx.batch, ctx.pool, ctx.cache, kv, keys.mutable_data(), values.mutable_data(), seq);
+            py::dict r;
+            r["keys"] = keys;
+            r["values"] = values;
+            return r;
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("seq") = 0, "Decode KV from the cache as (T, heads, head_dim)");
+
+    m.def(
+        "kv_cache_evict_h2o",
+        [](GrillyCoreContext& ctx, ops::KVCache& kv, std::optional<FArr> scores, uint32_t numEvict) {
+            ops::kvCacheEvictH2O(ctx.batch, ctx.pool, ctx.cache, kv, scores ? scores->data() : nullptr, numEvict);
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("attention_scores") = py::none(), py::arg("num_evict") = 0);
+    m.def("kv_cache_compact",
+          [](GrillyCoreContext& ctx, ops::KVCache& kv) { ops::kvCacheCompact(ctx.batch, ctx.pool, ctx.cache, kv); },
+          py::arg("device"), py::arg("kv_cache"));
+
+    // ---- GQA decode (shaders/gqa-attention.glsl)
+    m.def(
+        "gqa_attention",
+        [](GrillyCoreContext& ctx, FArr q, py::object kvOrK, std::optional<FArr> vCache, std::optional<uint32_t> cacheLen,
+           float scale, int nSplits, const std::string& dtype) {
+            if (q.ndim() != 4 || q.shape(1) != 1) throw std::runtime_error("q must be (batch, 1, num_q_heads, head_dim)");
+            const uint32_t B = uint32_t(q.shape(0)), Hq = uint32_t(q.shape(2)), D = uint32_t(q.shape(3));
+            py::array_t<float> out({py::ssize_t(B), py::ssize_t(1), py::ssize_t(Hq), py::ssize_t(D)});
+            if (py::isinstance<ops::KVCache>(kvOrK)) {
+                auto& kv = kvOrK.cast<ops::KVCache&>();
+                if (kv.config.batchSize != B || kv.config.headDim != D) throw std::runtime_error("q does not match the cache");
+                ops::gqaAttention(ctx.batch, ctx.pool, ctx.cache, kv, q.data(), out.mutable_data(), Hq, scale, nSplits);
+                return out;
+            }
+            // explicit (B,T,Hkv,D) arrays in the reference shader's layout: stage them in a temporary cache
+            FArr kC = kvOrK.cast<FArr>();
+            if (!vCache.has_value()) throw std::runtime_error("v_cache is required with an explicit k_cache");
+            if (kC.ndim() != 4 || vCache->ndim() != 4 || kC.shape(0) != B || kC.shape(3) != D)
+                throw std::runtime_error("k_cache / v_cache must be (batch, cache_len, num_kv_heads, head_dim)");
+            for (int i = 0; i < 4; ++i)
+                if (kC.shape(i) != vCache->shape(i)) throw std::runtime_error("k_cache and v_cache differ in shape");
+            const uint32_t Tmax = uint32_t(kC.shape(1)), Hkv = uint32_t(kC.shape(2));
+            const uint32_t T = cacheLen.value_or(Tmax);
+            if (T == 0 || T > Tmax) throw std::runtime_error("cache_len out of range");
+            if (Hkv == 0 || Hq % Hkv != 0) throw std::runtime_error("num_q_heads must be a multiple of num_kv_heads");
+            ops::KVCacheConfig cfg;
+            cfg.numHeads = Hkv; cfg.headDim = D; cfg.batchSize = B; cfg.maxCacheTokens = T; cfg.maxSeqLen = T;
+            cfg.dtype = dtype == "bf16" ? GRL_BF16 : GRL_F32;
+            ops::KVCache kv = ops::createKVCache(ctx.pool, cfg);
+            try {
+                if (T == Tmax) {
+                    ops::kvCacheAppend(ctx.batch, ctx.pool, ctx.cache, kv, kC.data(), vCache->data(), T);
+                } else {  // keep only the first T tokens of every sequence
+                    std::vector<float> kk(size_t(B) * T * Hkv * D), vv(kk.size());
+                    const size_t row = size_t(Hkv) * D;
+                    for (uint32_t b = 0; b < B; ++b) {
+                        std::memcpy(&kk[size_t(b) * T * row], kC.data() + size_t(b) * Tmax * row, size_t(T) * row * 4);
+                        std::memcpy(&vv[size_t(b) * T * row], vCache->data() + size_t(b) * Tmax * row, size_t(T) * row * 4);
+                    }
+                    ops::kvCacheAppend(ctx.batch, ctx.pool, ctx.cache, kv, kk.data(), vv.data(), T);
+                }
+                ops::gqaAttention(ctx.batch, ctx.pool, ctx.cache, kv, q.data(), out.mutable_data(), Hq, scale, nSplits);
+            } catch (...) {
+                ops::destroyKVCache(ctx.pool, kv);
+                throw;
+            }
+            ops::destroyKVCache(ctx.pool, kv);
+            return out;
+        },
+        py::arg("device"), py::arg("q"), py::arg("k_cache"), py::arg("v_cache") = py::none(),
+        py::arg("cache_len") = py::none(), py::arg("scale") = 0.0f, py::arg("n_splits") = 0, py::arg("dtype") = "fp32",
+        "GQA decode attention: q (B,1,Hq,D) over a KVCache, or over explicit (B,T,Hkv,D) arrays");
+
+    m.def(
+        "decode_step",
+        [](GrillyCoreContext& ctx, ops::KVCache& kv, FArr q, FArr kNew, FArr vNew, float ropeTheta, float ropeScaling,
+           const std::string& ropeMode, float scale) {
+            const auto& c = kv.config;
+            if (q.ndim() != 4 || q.shape(0) != c.batchSize || q.shape(1) != 1 || q.shape(3) != c.headDim)
+                throw std::runtime_error("q must be (batch, 1, num_q_heads, head_dim)");
+            for (const FArr* a : {&kNew, &vNew})
+                if (a->ndim() != 4 || a->shape(0) != c.batchSize || a->shape(1) != 1 || a->shape(2) != c.numHeads ||
+                    a->shape(3) != c.headDim)
+                    throw std::runtime_error("k_new / v_new must be (batch, 1, num_kv_heads, head_dim)");
+            const uint32_t Hq = uint32_t(q.shape(2));
+            py::array_t<float> out({py::ssize_t(c.batchSize), py::ssize_t(1), py::ssize_t(Hq), py::ssize_t(c.headDim)});
+            ops::decodeStep(ctx.batch, ctx.pool, ctx.cache, kv, q.data(), kNew.data(), vNew.data(), out.mutable_data(),
+                            Hq, ropeTheta != 0.0f ? parseRopeMode(ropeMode, false) : ops::RopeMode::None,
+                            ropeTheta != 0.0f ? ropeTheta : 10000.0f, ropeScaling, scale);
+            return out;
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("q"), py::arg("k_new"), py::arg("v_new"),
+        py::arg("rope_theta") = 10000.0f, py::arg("rope_scaling") = 1.0f, py::arg("rope_mode") = "interleaved",
+        py::arg("scale") = 0.0f, "RoPE(q,k) at the current position, append k/v, attend over the cache");
+}

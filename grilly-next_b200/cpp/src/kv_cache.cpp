@@ -1,0 +1,290 @@
+// Host side of the paged KV cache and the GQA decode ops.
+#include <algorithm>
+#include <cstring>
+#include <string>
+
+#include "grilly/ops/kv_cache.h"
+
+namespace grilly {
+namespace ops {
+
+namespace {
+size_t elemSize(int dtype) { return dtype == GRL_BF16 ? 2 : 4; }
+
+struct Recording {
+    CommandBatch& batch;
+    explicit Recording(CommandBatch& b) : batch(b) { batch.begin(); }
+    ~Recording() {
+        if (batch.recording()) batch.submitNoWait();
+    }
+};
+
+// Give every sequence pages for `extra` more tokens; uploads the block table when it changed.
+void reservePages(BufferPool& pool, KVCache& kv, uint32_t extra) {
+    const auto& c = kv.config;
+    bool changed = false;
+    for (uint32_t b = 0; b < c.batchSize; ++b) {
+        const uint32_t need = (uint32_t(kv.hostSeqLens[b]) + extra + c.pageTokens - 1) / c.pageTokens;
+        if (need > kv.maxPages)
+            throw std::runtime_error("kvCacheAppend: sequence would exceed max_cache_tokens (" +
+                                     std::to_string(c.maxCacheTokens) + ")");
+        for (uint32_t i = 0; i < need; ++i) {
+            int32_t& slot = kv.hostBlockTable[size_t(b) * kv.maxPages + i];
+            if (slot < 0) {
+                if (kv.nextFreePage >= kv.numPages) throw std::runtime_error("kvCacheAppend: page pool exhausted");
+                slot = int32_t(kv.nextFreePage++);
+                changed = true;
+            }
+        }
+    }
+    if (changed) {
+        // unassigned entries are uploaded as page 0; they are never read (beyond seq_lens)
+        std::vector<int32_t> tmp(kv.hostBlockTable);
+        for (auto& x : tmp) x = std::max(x, 0);
+        // synchronous: the staging vector dies at scope exit
+        check(grl_memcpy_h2d(pool.device().handle(), kv.blockTable.dptr, tmp.data(), tmp.size() * 4),
+              "kvCache: block table upload");
+        check(grl_sync(pool.device().handle(), 0), "kvCache: block table upload");
+    }
+}
+}  // namespace
+
+grl_kv_layout KVCache::layout() const {
+    grl_kv_layout l{};
+    l.k_pages = kPages.dptr;
+    l.v_pages = vPages.dptr;
+    l.cache_dtype = config.dtype;
+    l.block_table = static_cast<const int32_t*>(blockTable.dptr);
+    l.seq_lens = static_cast<int32_t*>(seqLens.dptr);
+    l.batch = int(config.batchSize);
+    l.num_kv_heads = int(config.numHeads);
+    l.head_dim = int(config.headDim);
+    l.page_tokens = int(config.pageTokens);
+    l.max_pages = int(maxPages);
+    return l;
+}
+
+KVCache createKVCache(BufferPool& pool, const KVCacheConfig& cfg) {
+    if (cfg.compressionRatio != 1 || cfg.useAsymmetricQuant)
+        throw std::runtime_error(
+            "createKVCache: only the uncompressed paged cache is built (compression_ratio=1, "
+            "use_asymmetric_quant=False); MLA latents and FP8/INT4 storage are not");
+    if (cfg.numHeads == 0 || cfg.headDim == 0 || cfg.batchSize == 0 || cfg.pageTokens == 0 || cfg.maxCacheTokens == 0)
+        throw std::runtime_error("createKVCache: empty shape");
+    if (cfg.headDim != 32 && cfg.headDim != 64 && cfg.headDim != 128)
+        throw std::runtime_error("createKVCache: head_dim must be 32, 64 or 128");
+    if (cfg.dtype != GRL_BF16 && cfg.dtype != GRL_F32) throw std::runtime_error("createKVCache: unknown dtype");
+    KVCache kv;
+    kv.config = cfg;
+    kv.maxPages = (cfg.maxCacheTokens + cfg.pageTokens - 1) / cfg.pageTokens;
+    kv.numPages = kv.maxPages * cfg.batchSize;
+    const size_t pageBytes = size_t(cfg.numHeads) * cfg.pageTokens * cfg.headDim * elemSize(cfg.dtype);
+    kv.kPages = pool.acquire(pageBytes * kv.numPages);
+    kv.vPages = pool.acquire(pageBytes * kv.numPages);
+    kv.blockTable = pool.acquire(size_t(kv.maxPages) * cfg.batchSize * 4);
+    kv.seqLens = pool.acquire(size_t(cfg.batchSize) * 4);
+    kv.hostBlockTable.assign(size_t(kv.maxPages) * cfg.batchSize, -1);
+    kv.hostSeqLens.assign(cfg.batchSize, 0);
+    grl_device* dev = pool.device().handle();
+    check(grl_memset(dev, kv.blockTable.dptr, 0, size_t(kv.maxPages) * cfg.batchSize * 4), "createKVCache");
+    check(grl_memset(dev, kv.seqLens.dptr, 0, size_t(cfg.batchSize) * 4), "createKVCache");
+    check(grl_sync(dev, 0), "createKVCache");
+    return kv;
+}
+
+void destroyKVCache(BufferPool& pool, KVCache& kv) {
+    pool.release(kv.kPages);
+    pool.release(kv.vPages);
+    pool.release(kv.blockTable);
+    pool.release(kv.seqLens);
+    kv.hostBlockTable.clear();
+    kv.hostSeqLens.clear();
+    kv.currentLen = 0;
+    kv.nextFreePage = 0;
+}
+
+void kvCacheAppendRope(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kv, const float* newKeys,
+                       const float* newValues, uint32_t n, const float* qIn, float* qOut, uint32_t numQHeads,
+                       RopeMode mode, float theta, float scaling, int32_t posBase) {
+    if (!kv.kPages.valid()) throw std::runtime_error("kvCacheAppend: cache was destroyed");
+    if (!newKeys || !newValues) throw std::runtime_error("kvCacheAppend: null tensor pointer");
+    if (n == 0) return;
+    const auto& c = kv.config;
+    grl_device* dev = pool.device().handle();
+    cache.getOrCreate("kv-append/" + std::to_string(c.headDim));
+    reservePages(pool, kv, n);
+    const size_t kvElems = size_t(c.batchSize) * n * c.numHeads * c.headDim;
+    const size_t qElems = qIn ? size_t(c.batchSize) * n * numQHeads * c.headDim : 0;
+    GrillyBuffer kb = pool.acquire(kvElems * 4), vb = pool.acquire(kvElems * 4), qb, qo;
+    if (qIn) { qb = pool.acquire(qElems * 4); qo = pool.acquire(qElems * 4); }
+    try {
+        Recording rec(batch);
+        pool.upload(kb, newKeys, kvElems * 4);
+        pool.upload(vb, newValues, kvElems * 4);
+        if (qIn) pool.upload(qb, qIn, qElems * 4);
+        grl_append_params p{};
+        p.kv = kv.layout();
+        p.k_new = static_cast<const float*>(kb.dptr);
+        p.v_new = static_cast<const float*>(vb.dptr);
+        p.q_in = static_cast<const float*>(qb.dptr);
+        p.q_out = static_cast<float*>(qo.dptr);
+        p.n_new = int(n); p.num_q_heads = int(numQHeads);
+        p.rope_mode = int(mode); p.rope_theta = theta; p.rope_scaling = scaling;
+        p.pos_base = posBase; p.update_lens = 1;
+        check(grl_kv_append(dev, &p), "kvCacheAppend");
+        if (qIn && qOut) check(grl_memcpy_d2h(dev, qOut, qo.dptr, qElems * 4), "kvCacheAppend: q download");
+        batch.submit();
+    } catch (...) {
+        pool.release(kb); pool.release(vb); pool.release(qb); pool.release(qo);
+        throw;
+    }
+    pool.release(kb); pool.release(vb); pool.release(qb); pool.release(qo);
+    for (auto& l : kv.hostSeqLens) l += int32_t(n);
+    kv.currentLen = uint32_t(kv.hostSeqLens[0]);
+    kv.totalAppended += uint64_t(n) * c.batchSize;
+}
+
+void kvCacheAppend(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kv, const float* newKeys,
+                   const float* newValues, uint32_t numNewTokens) {
+    kvCacheAppendRope(batch, pool, cache, kv, newKeys, newValues, numNewTokens, nullptr, nullptr, 0, RopeMode::None,
+                      10000.0f, 1.0f, 0);
+}
+
+void kvCacheDecode(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const KVCache& kv, float* decodedKeys,
+                   float* decodedValues, uint32_t seq) {
+    if (!kv.kPages.valid()) throw std::runtime_error("kvCacheDecode: cache was destroyed");
+    const auto& c = kv.config;
+    if (seq >= c.batchSize) throw std::runtime_error("kvCacheDecode: sequence index out of range");
+    const uint32_t T = uint32_t(kv.hostSeqLens[seq]);
+    if (T == 0) return;
+    if (!decodedKeys || !decodedValues) throw std::runtime_error("kvCacheDecode: null output");
+    grl_device* dev = pool.device().handle();
+    cache.getOrCreate("kv-gather/" + std::to_string(c.headDim));
+    const size_t n = size_t(T) * c.numHeads * c.headDim;
+    GrillyBuffer kb = pool.acquire(n * 4), vb = pool.acquire(n * 4);
+    try {
+        Recording rec(batch);
+        grl_kv_layout l = kv.layout();
+        check(grl_kv_gather(dev, &l, int(seq), int(T), static_cast<float*>(kb.dptr), static_cast<float*>(vb.dptr)),
+              "kvCacheDecode");
+        check(grl_memcpy_d2h(dev, decodedKeys, kb.dptr, n * 4), "kvCacheDecode: download");
+        check(grl_memcpy_d2h(dev, decodedValues, vb.dptr, n * 4), "kvCacheDecode: download");
+        batch.submit();
+    } catch (...) {
+        pool.release(kb); pool.release(vb);
+        throw;
+    }
+    pool.release(kb); pool.release(vb);
+}
+
+KVCacheStats kvCacheGetStats(const KVCache& kv) {
+    KVCacheStats s{};
+    s.currentTokens = kv.currentLen;
+    s.maxTokens = kv.config.maxCacheTokens;
+    s.totalEvicted = 0;
+    s.totalAppended = uint32_t(kv.totalAppended);
+    s.compressionRatio = kv.config.dtype == GRL_BF16 ? 2.0f : 1.0f;  // bytes saved against float32 storage
+    s.avgAttentionScore = 0.0f;
+    s.pagesTotal = kv.numPages;
+    s.pagesUsed = kv.nextFreePage;
+    s.bytes = uint64_t(kv.kPages.bucketSize) + kv.vPages.bucketSize;
+    return s;
+}
+
+static void launchDecode(grl_device* dev, BufferPool& pool, const KVCache& kv, const float* qDev, float* outDev,
+                         uint32_t numQHeads, float scale, int nSplits, GrillyBuffer& ws) {
+    grl_decode_params p{};
+    p.kv = kv.layout();
+    p.q = qDev; p.out = outDev;
+    p.num_q_heads = int(numQHeads);
+    p.scale = scale; p.n_splits = nSplits;
+    p.max_seq_len = *std::max_element(kv.hostSeqLens.begin(), kv.hostSeqLens.end());
+    int splits = 0;
+    check(grl_decode_pick_splits(dev, &p, &splits), "gqaAttention");
+    size_t bytes = 0;
+    check(grl_decode_workspace_bytes(&p, splits, &bytes), "gqaAttention");
+    ws = pool.acquire(bytes);
+    p.n_splits = splits; p.workspace = ws.dptr; p.workspace_bytes = ws.bucketSize;
+    check(grl_gqa_decode(dev, &p), "gqaAttention");
+}
+
+void gqaAttention(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const KVCache& kv, const float* q,
+                  float* out, uint32_t numQHeads, float scale, int nSplits) {
+    if (!kv.kPages.valid()) throw std::runtime_error("gqaAttention: cache was destroyed");
+    if (!q || !out) throw std::runtime_error("gqaAttention: null tensor pointer");
+    const auto& c = kv.config;
+    if (numQHeads == 0 || numQHeads % c.numHeads != 0)
+        throw std::runtime_error("gqaAttention: num_q_heads must be a positive multiple of num_kv_heads");
+    grl_device* dev = pool.device().handle();
+    cache.getOrCreate("gqa-attention/" + std::to_string(c.headDim));
+    const size_t n = size_t(c.batchSize) * numQHeads * c.headDim;
+    GrillyBuffer qb = pool.acquire(n * 4), ob = pool.acquire(n * 4), ws;
+    try {
+        Recording rec(batch);
+        pool.upload(qb, q, n * 4);
+        launchDecode(dev, pool, kv, static_cast<const float*>(qb.dptr), static_cast<float*>(ob.dptr), numQHeads, scale,
+                     nSplits, ws);
+        check(grl_memcpy_d2h(dev, out, ob.dptr, n * 4), "gqaAttention: download");
+        batch.submit();
+    } catch (...) {
+        pool.release(qb); pool.release(ob); pool.release(ws);
+        throw;
+    }
+    pool.release(qb); pool.release(ob); pool.release(ws);
+}
+
+void decodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kv, const float* q,
+                const float* kNew, const float* vNew, float* out, uint32_t numQHeads, RopeMode mode, float theta,
+                float scaling, float scale) {
+    if (!kv.kPages.valid()) throw std::runtime_error("decodeStep: cache was destroyed");
+    if (!q || !kNew || !vNew || !out) throw std::runtime_error("decodeStep: null tensor pointer");
+    const auto& c = kv.config;
+    if (numQHeads == 0 || numQHeads % c.numHeads != 0)
+        throw std::runtime_error("decodeStep: num_q_heads must be a positive multiple of num_kv_heads");
+    grl_device* dev = pool.device().handle();
+    cache.getOrCreate("decode-step/" + std::to_string(c.headDim));
+    reservePages(pool, kv, 1);
+    const size_t qn = size_t(c.batchSize) * numQHeads * c.headDim, kn = size_t(c.batchSize) * c.numHeads * c.headDim;
+    GrillyBuffer qb = pool.acquire(qn * 4), qr = pool.acquire(qn * 4), ob = pool.acquire(qn * 4),
+                 kb = pool.acquire(kn * 4), vb = pool.acquire(kn * 4), ws;
+    auto releaseAll = [&]() {
+        pool.release(qb); pool.release(qr); pool.release(ob); pool.release(kb); pool.release(vb); pool.release(ws);
+    };
+    try {
+        Recording rec(batch);
+        pool.upload(qb, q, qn * 4);
+        pool.upload(kb, kNew, kn * 4);
+        pool.upload(vb, vNew, kn * 4);
+        grl_append_params ap{};
+        ap.kv = kv.layout();
+        ap.k_new = static_cast<const float*>(kb.dptr);
+        ap.v_new = static_cast<const float*>(vb.dptr);
+        ap.q_in = static_cast<const float*>(qb.dptr);
+        ap.q_out = static_cast<float*>(qr.dptr);
+        ap.n_new = 1; ap.num_q_heads = int(numQHeads);
+        ap.rope_mode = int(mode); ap.rope_theta = theta; ap.rope_scaling = scaling;
+        ap.pos_base = 0; ap.update_lens = 1;
+        check(grl_kv_append(dev, &ap), "decodeStep: append");
+        for (auto& l : kv.hostSeqLens) l += 1;
+        kv.currentLen = uint32_t(kv.hostSeqLens[0]);
+        kv.totalAppended += c.batchSize;
+        launchDecode(dev, pool, kv, static_cast<const float*>(qr.dptr), static_cast<float*>(ob.dptr), numQHeads, scale,
+                     0, ws);
+        check(grl_memcpy_d2h(dev, out, ob.dptr, qn * 4), "decodeStep: download");
+        batch.submit();
+    } catch (...) {
+        releaseAll();
+        throw;
+    }
+    releaseAll();
+}
+
+void kvCacheEvictH2O(CommandBatch&, BufferPool&, PipelineCache&, KVCache&, const float*, uint32_t) {
+    throw std::runtime_error("kvCacheEvictH2O: the eviction family is not built on the paged cache");
+}
+void kvCacheCompact(CommandBatch&, BufferPool&, PipelineCache&, KVCache&) {
+    throw std::runtime_error("kvCacheCompact: the eviction family is not built on the paged cache");
+}
+
+}  // namespace ops
+}  // namespace grilly

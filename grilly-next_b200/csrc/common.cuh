@@ -1,0 +1,116 @@
+// Shared host/device helpers for the C-ABI kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+
+#include "grilly_cuda.h"
+
+struct grl_device {
+    int ordinal = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;   // the stream launches go to (own_stream or an adopted one)
+    cudaDeviceProp prop{};
+    std::mutex mu;
+    // RoPE cos/sin tables, float2 (cos, sin) per (position, pair), keyed by
+    // (positions, head_dim, theta bits, scaling bits).
+    std::map<std::tuple<int, int, uint32_t, uint32_t>, float2*> rope_tables;
+    // Status word written by kernels with bounded waits; read back by grl_sync when dirty.
+    int32_t* d_status = nullptr;   // device int32[4]
+    bool status_dirty = false;
+};
+
+struct grl_event {
+    cudaEvent_t ev = nullptr;
+};
+
+struct grl_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+};
+
+namespace grl {
+
+int set_error(int code, const char* fmt, ...);
+extern std::atomic<long long> g_launches;
+
+#define GRL_CUDA(call)                                                                       \
+    do {                                                                                     \
+        cudaError_t _e = (call);                                                             \
+        if (_e != cudaSuccess)                                                               \
+            return grl::set_error(_e == cudaErrorMemoryAllocation ? GRL_ERR_OOM : GRL_ERR_CUDA, \
+                                  "%s failed: %s", #call, cudaGetErrorString(_e));           \
+    } while (0)
+
+#define GRL_REQUIRE(cond, ...)                                              \
+    do {                                                                    \
+        if (!(cond)) return grl::set_error(GRL_ERR_INVALID, __VA_ARGS__);   \
+    } while (0)
+
+// Call after every kernel launch: counts it and turns a launch error into a status code.
+#define GRL_LAUNCHED(name)                                                                    \
+    do {                                                                                      \
+        grl::g_launches.fetch_add(1, std::memory_order_relaxed);                              \
+        cudaError_t _e = cudaGetLastError();                                                  \
+        if (_e != cudaSuccess)                                                                \
+            return grl::set_error(GRL_ERR_CUDA, "launch of %s failed: %s", name,              \
+                                  cudaGetErrorString(_e));                                    \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int ordinal) {
+        cudaGetDevice(&prev);
+        if (prev != ordinal) cudaSetDevice(ordinal);
+        else prev = -1;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+// inv_freq[i] = theta^(-2i/D) / scaling in double, for i < D/2 <= 128.
+struct RopeFreq {
+    double inv_freq[128];
+};
+RopeFreq make_rope_freq(int head_dim, float theta, float scaling);
+
+// Device table of (cos, sin) for positions [0, n_pos) x pairs [0, D/2); cached per device.
+int get_rope_table(grl_device* dev, int n_pos, int head_dim, float theta, float scaling,
+                   const float2** out);
+
+#ifdef __CUDACC__
+// cos/sin of pos * inv_freq with the product and the 2*pi reduction in double, so that the
+// angle error stays near 1e-7 rad for positions up to 2^24 (a float product alone is off by
+// up to pos * 2^-24 rad).
+__device__ __forceinline__ void rope_sincos(int pos, double inv_freq, float* c, float* s) {
+    double th = (double)pos * inv_freq;
+    double k = rint(th * 0.15915494309189535);  // 1/(2*pi)
+    double r = fma(-k, 6.283185307179586, th);
+    r = fma(-k, 2.4492935982947064e-16, r);     // low part of 2*pi
+    sincosf((float)r, s, c);
+}
+
+__device__ __forceinline__ float bf16_round(float x) {
+    return __bfloat162float(__float2bfloat16_rn(x));
+}
+
+template <typename T> __device__ __forceinline__ float load_as_float(const T* p);
+template <> __device__ __forceinline__ float load_as_float<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float load_as_float<__nv_bfloat16>(const __nv_bfloat16* p) {
+    return __bfloat162float(*p);
+}
+template <typename T> __device__ __forceinline__ void store_from_float(T* p, float v);
+template <> __device__ __forceinline__ void store_from_float<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_from_float<__nv_bfloat16>(__nv_bfloat16* p, float v) {
+    *p = __float2bfloat16_rn(v);
+}
+#endif
+
+}  // namespace grl

@@ -1,0 +1,321 @@
+// GQA decode attention over the paged, head-major KV cache: split-KV partition over SMs plus a
+// log-sum-exp merge.  Replaces shaders/gqa-attention.glsl:34-130 (scores -> softmax -> P.V in
+// three global-memory phases with a (B,Hq,T) scratch) by a single streaming pass: every K and V
+// row is read once with 16-byte loads and shared by all query heads of its KV group.
+#include "common.cuh"
+
+namespace grl {
+
+constexpr float kEmptyMax = -1e30f;  // running max of a part that saw no token (finite on purpose)
+constexpr int kDecodeThreads = 128;
+
+struct DecodeArgs {
+    const void* k_pages;
+    const void* v_pages;
+    const int32_t* block_table;
+    const int32_t* seq_lens;
+    const float* q;
+    float* part;       // [n_splits][rows*(D+2)]
+    float* out;        // direct output when n_splits == 1 and no partial is wanted
+    int B, Hq, Hkv, P, max_pages, n_splits, group, chunks;
+    float scale;
+    int direct;
+};
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    __device__ static void load(const float* p, float* x) {
+        float4 v = __ldg(reinterpret_cast<const float4*>(p));
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    }
+};
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ static void load(const __nv_bfloat16* p, float* x) {
+        uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x[2 * i] = __uint_as_float(w[i] << 16);
+            x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+
+// grid (n_splits, Hkv*chunks, B); GC = query heads handled per CTA (a chunk of the KV group).
+template <typename T, int D, int GC>
+__global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(DecodeArgs a) {
+    constexpr int VEC = Vec16<T>::N;
+    constexpr int LPT = D / VEC;           // lanes per token
+    constexpr int TPW = 32 / LPT;          // tokens per warp iteration
+    constexpr int NWARP = kDecodeThreads / 32;
+    constexpr int NGRP = NWARP * TPW;      // independent online-softmax streams per CTA
+    static_assert(LPT >= 1 && LPT <= 32, "head_dim / vector width");
+
+    __shared__ float sm_m[NGRP][GC], sm_l[NGRP][GC];
+    __shared__ float sm_acc[NGRP][GC][D];
+    __shared__ float sm_w[NGRP][GC];
+
+    const int split = blockIdx.x;
+    const int kvh = blockIdx.y / a.chunks, chunk = blockIdx.y % a.chunks;
+    const int b = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = lane / LPT, li = lane % LPT;
+    const int grp = warp * TPW + sub;
+    const int qh0 = kvh * a.group + chunk * GC;          // first query head of this CTA
+    const int n_heads = min(GC, a.group - chunk * GC);   // live heads in this chunk
+
+    const int len = a.seq_lens[b];
+    const int n_pages = (len + a.P - 1) / a.P;
+    const int pps = (n_pages + a.n_splits - 1) / a.n_splits;  // pages per split
+    const int t_begin = min(len, split * pps * a.P);
+    const int t_end = min(len, (split + 1) * pps * a.P);
+
+    float qv[GC][VEC], acc[GC][VEC], m[GC], l[GC];
+#pragma unroll
+    for (int g = 0; g < GC; ++g) {
+        m[g] = kEmptyMax;
+        l[g] = 0.f;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            acc[g][e] = 0.f;
+            qv[g][e] = (g < n_heads) ? a.q[((size_t)b * a.Hq + qh0 + g) * D + li * VEC + e] * a.scale : 0.f;
+        }
+    }
+
+    const T* kp = reinterpret_cast<const T*>(a.k_pages);
+    const T* vp = reinterpret_cast<const T*>(a.v_pages);
+    const int32_t* bt = a.block_table + (size_t)b * a.max_pages;
+
+    // The trip count is uniform across the warp (the shuffles below need all 32 lanes); a
+    // lane group whose token index runs past the end just skips its update.
+    for (int t0 = t_begin + warp * TPW; t0 < t_end; t0 += NGRP) {
+        const int t = t0 + sub;
+        const bool live = t < t_end;
+        float kx[VEC], vx[VEC];
+        if (live) {
+            const int page = bt[t / a.P], slot = t % a.P;
+            const size_t off = (((size_t)page * a.Hkv + kvh) * a.P + slot) * D + li * VEC;
+            Vec16<T>::load(kp + off, kx);
+            Vec16<T>::load(vp + off, vx);
+        } else {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) { kx[e] = 0.f; vx[e] = 0.f; }
+        }
+        float s[GC];
+#pragma unroll
+        for (int g = 0; g < GC; ++g) {
+            float d = 0.f;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) d = fmaf(qv[g][e], kx[e], d);
+            s[g] = d;
+        }
+#pragma unroll
+        for (int off2 = 1; off2 < LPT; off2 <<= 1)
+#pragma unroll
+            for (int g = 0; g < GC; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off2);
+        if (live) {
+#pragma unroll
+            for (int g = 0; g < GC; ++g) {
+                const float m_new = fmaxf(m[g], s[g]);
+                const float corr = __expf(m[g] - m_new);
+                const float p = __expf(s[g] - m_new);
+                l[g] = l[g] * corr + p;
+                m[g] = m_new;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) acc[g][e] = fmaf(acc[g][e], corr, p * vx[e]);
+            }
+        }
+    }
+
+    // combine the NGRP streams of this CTA
+#pragma unroll
+    for (int g = 0; g < GC; ++g) {
+        if (li == 0) { sm_m[grp][g] = m[g]; sm_l[grp][g] = l[g]; }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) sm_acc[grp][g][li * VEC + e] = acc[g][e];
+    }
+    __syncthreads();
+    __shared__ float sm_mtot[GC], sm_ltot[GC];
+    if (tid < GC) {
+        float mt = kEmptyMax;
+        for (int i = 0; i < NGRP; ++i) mt = fmaxf(mt, sm_m[i][tid]);
+        float lt = 0.f;
+        for (int i = 0; i < NGRP; ++i) {
+            float w = __expf(sm_m[i][tid] - mt);
+            sm_w[i][tid] = w;
+            lt += w * sm_l[i][tid];
+        }
+        sm_mtot[tid] = mt;
+        sm_ltot[tid] = lt;
+    }
+    __syncthreads();
+    const int rows = a.B * a.Hq;
+    for (int idx = tid; idx < n_heads * D; idx += kDecodeThreads) {
+        const int g = idx / D, d = idx % D;
+        float o = 0.f;
+#pragma unroll 4
+        for (int i = 0; i < NGRP; ++i) o = fmaf(sm_w[i][g], sm_acc[i][g][d], o);
+        const int row = b * a.Hq + qh0 + g;
+        if (a.direct) {
+            const float lt = sm_ltot[g];
+            a.out[(size_t)row * D + d] = lt > 0.f ? o / lt : 0.f;
+        } else {
+            float* part = a.part + (size_t)split * rows * (D + 2);
+            part[(size_t)row * D + d] = o;
+            if (d == 0) {
+                part[(size_t)rows * D + row] = sm_mtot[g];
+                part[(size_t)rows * D + rows + row] = sm_ltot[g];
+            }
+        }
+    }
+}
+
+// parts: n_parts x [O (rows*D) | m (rows) | l (rows)].  grid (rows), block 128.
+__global__ void lse_merge_kernel(const float* __restrict__ parts, int n_parts, size_t part_stride, int rows,
+                                 int D, int normalise, float* __restrict__ out) {
+    const int row = blockIdx.x;
+    float mt = kEmptyMax;
+    for (int i = 0; i < n_parts; ++i) mt = fmaxf(mt, parts[i * part_stride + (size_t)rows * D + row]);
+    float lt = 0.f;
+    for (int i = 0; i < n_parts; ++i) {
+        const float* p = parts + i * part_stride + (size_t)rows * D;
+        lt += __expf(p[row] - mt) * p[rows + row];
+    }
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float o = 0.f;
+        for (int i = 0; i < n_parts; ++i) {
+            const float* p = parts + i * part_stride;
+            o = fmaf(__expf(p[(size_t)rows * D + row] - mt), p[(size_t)row * D + d], o);
+        }
+        if (normalise) out[(size_t)row * D + d] = lt > 0.f ? o / lt : 0.f;
+        else out[(size_t)row * D + d] = o;
+    }
+    if (!normalise && threadIdx.x == 0) {
+        out[(size_t)rows * D + row] = mt;
+        out[(size_t)rows * D + rows + row] = lt;
+    }
+}
+
+template <typename T, int D, int GC>
+static int launch_decode(grl_device* dev, const DecodeArgs& a) {
+    dim3 grid(a.n_splits, a.Hkv * a.chunks, a.B);
+    decode_split_kernel<T, D, GC><<<grid, kDecodeThreads, 0, dev->stream>>>(a);
+    GRL_LAUNCHED("decode_split_kernel");
+    return GRL_OK;
+}
+
+template <typename T, int D>
+static int dispatch_gc(grl_device* dev, DecodeArgs& a) {
+    int gc = a.group <= 1 ? 1 : a.group <= 2 ? 2 : a.group <= 4 ? 4 : 8;
+    a.chunks = (a.group + gc - 1) / gc;
+    switch (gc) {
+        case 1: return launch_decode<T, D, 1>(dev, a);
+        case 2: return launch_decode<T, D, 2>(dev, a);
+        case 4: return launch_decode<T, D, 4>(dev, a);
+        default: return launch_decode<T, D, 8>(dev, a);
+    }
+}
+
+template <typename T>
+static int dispatch_decode_d(grl_device* dev, DecodeArgs& a, int D) {
+    switch (D) {
+        case 32: return dispatch_gc<T, 32>(dev, a);
+        case 64: return dispatch_gc<T, 64>(dev, a);
+        case 128: return dispatch_gc<T, 128>(dev, a);
+        default: return set_error(GRL_ERR_UNSUPPORTED, "head_dim %d not supported (32, 64 or 128)", D);
+    }
+}
+
+static int check_decode(const grl_decode_params* p) {
+    GRL_REQUIRE(p, "params is NULL");
+    const grl_kv_layout& kv = p->kv;
+    GRL_REQUIRE(kv.k_pages && kv.v_pages && kv.block_table && kv.seq_lens, "NULL cache pointer");
+    GRL_REQUIRE(kv.batch > 0 && kv.num_kv_heads > 0 && kv.page_tokens > 0 && kv.max_pages > 0, "bad cache shape");
+    GRL_REQUIRE(p->num_q_heads > 0 && p->num_q_heads % kv.num_kv_heads == 0,
+                "num_q_heads (%d) must be a multiple of num_kv_heads (%d)", p->num_q_heads, kv.num_kv_heads);
+    GRL_REQUIRE(kv.cache_dtype == GRL_BF16 || kv.cache_dtype == GRL_F32, "unknown cache dtype");
+    GRL_REQUIRE(p->q, "q is NULL");
+    GRL_REQUIRE(p->out || p->partial_out, "out and partial_out are both NULL");
+    return GRL_OK;
+}
+
+}  // namespace grl
+
+using namespace grl;
+
+extern "C" {
+
+int grl_decode_pick_splits(grl_device* dev, const grl_decode_params* p, int* n_splits) {
+    GRL_REQUIRE(dev && n_splits, "NULL argument");
+    int rc = check_decode(p);
+    if (rc) return rc;
+    if (p->n_splits > 0) {
+        *n_splits = p->n_splits;
+        return GRL_OK;
+    }
+    const grl_kv_layout& kv = p->kv;
+    const int max_len = p->max_seq_len > 0 ? p->max_seq_len : kv.max_pages * kv.page_tokens;
+    const int pages = (max_len + kv.page_tokens - 1) / kv.page_tokens;
+    const int base_ctas = kv.batch * kv.num_kv_heads;
+    const int target = 4 * dev->prop.multiProcessorCount;  // ~4 resident CTAs per SM
+    int s = 1;
+    // grow while it adds parallelism and every split keeps at least 2 pages (128 tokens)
+    while (base_ctas * s < target && pages / (s * 2) >= 2 && s < 256) s *= 2;
+    *n_splits = s;
+    return GRL_OK;
+}
+
+int grl_decode_workspace_bytes(const grl_decode_params* p, int n_splits, size_t* bytes) {
+    GRL_REQUIRE(p && bytes && n_splits > 0, "bad argument");
+    const size_t rows = (size_t)p->kv.batch * p->num_q_heads;
+    *bytes = sizeof(float) * (size_t)n_splits * rows * (p->kv.head_dim + 2);
+    return GRL_OK;
+}
+
+int grl_lse_merge(grl_device* dev, const float* parts, int n_parts, size_t part_stride, int rows,
+                  int head_dim, int normalise, float* out) {
+    GRL_REQUIRE(dev && parts && out, "NULL argument");
+    GRL_REQUIRE(n_parts > 0 && rows > 0 && head_dim > 0, "bad shape");
+    GRL_REQUIRE(part_stride >= (size_t)rows * (head_dim + 2), "part_stride too small");
+    DeviceGuard g(dev->ordinal);
+    lse_merge_kernel<<<rows, 128, 0, dev->stream>>>(parts, n_parts, part_stride, rows, head_dim, normalise, out);
+    GRL_LAUNCHED("lse_merge_kernel");
+    return GRL_OK;
+}
+
+int grl_gqa_decode(grl_device* dev, const grl_decode_params* p) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    int rc = check_decode(p);
+    if (rc) return rc;
+    int n_splits = 0;
+    rc = grl_decode_pick_splits(dev, p, &n_splits);
+    if (rc) return rc;
+    const grl_kv_layout& kv = p->kv;
+    const int D = kv.head_dim;
+    const bool direct = (n_splits == 1) && !p->partial_out;
+    size_t need = 0;
+    grl_decode_workspace_bytes(p, n_splits, &need);
+    if (!direct)
+        GRL_REQUIRE(p->workspace && p->workspace_bytes >= need, "decode workspace too small: %zu < %zu",
+                    p->workspace_bytes, need);
+    DeviceGuard g(dev->ordinal);
+    DecodeArgs a{};
+    a.k_pages = kv.k_pages; a.v_pages = kv.v_pages; a.block_table = kv.block_table; a.seq_lens = kv.seq_lens;
+    a.q = p->q; a.part = (float*)p->workspace; a.out = p->out;
+    a.B = kv.batch; a.Hq = p->num_q_heads; a.Hkv = kv.num_kv_heads; a.P = kv.page_tokens;
+    a.max_pages = kv.max_pages; a.n_splits = n_splits; a.group = p->num_q_heads / kv.num_kv_heads;
+    a.scale = p->scale == 0.f ? 1.f / sqrtf((float)D) : p->scale;
+    a.direct = direct ? 1 : 0;
+    rc = (kv.cache_dtype == GRL_BF16) ? dispatch_decode_d<__nv_bfloat16>(dev, a, D)
+                                      : dispatch_decode_d<float>(dev, a, D);
+    if (rc || direct) return rc;
+    const int rows = kv.batch * p->num_q_heads;
+    const size_t stride = (size_t)rows * (D + 2);
+    if (p->partial_out)
+        return grl_lse_merge(dev, (const float*)p->workspace, n_splits, stride, rows, D, 0, p->partial_out);
+    return grl_lse_merge(dev, (const float*)p->workspace, n_splits, stride, rows, D, 1, p->out);
+}
+
+}  // extern "C"

@@ -1,0 +1,364 @@
+// Device, memory, stream, event and graph entry points of the C ABI, plus small element-wise
+// kernels (cast, RoPE table).  See include/grilly_cuda.h for the reference pieces replaced.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <chrono>
+#include <thread>
+
+#include "common.cuh"
+
+namespace grl {
+
+static thread_local char t_err[512] = "";
+std::atomic<long long> g_launches{0};
+
+int set_error(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_err, sizeof(t_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+RopeFreq make_rope_freq(int head_dim, float theta, float scaling) {
+    RopeFreq f{};
+    double sc = (scaling == 0.0f) ? 1.0 : (double)scaling;
+    for (int i = 0; i < head_dim / 2 && i < 128; ++i)
+        f.inv_freq[i] = pow((double)theta, -2.0 * (double)i / (double)head_dim) / sc;
+    return f;
+}
+
+__global__ void rope_table_kernel(float2* table, int n_pos, int half, RopeFreq f) {
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_pos * half) return;
+    int pos = idx / half, i = idx % half;
+    float c, s;
+    rope_sincos(pos, f.inv_freq[i], &c, &s);
+    table[idx] = make_float2(c, s);
+}
+
+int get_rope_table(grl_device* dev, int n_pos, int head_dim, float theta, float scaling,
+                   const float2** out) {
+    uint32_t tb, sb;
+    memcpy(&tb, &theta, 4);
+    memcpy(&sb, &scaling, 4);
+    auto key = std::make_tuple(n_pos, head_dim, tb, sb);
+    std::lock_guard<std::mutex> lock(dev->mu);
+    auto it = dev->rope_tables.find(key);
+    if (it != dev->rope_tables.end()) {
+        *out = it->second;
+        return GRL_OK;
+    }
+    float2* t = nullptr;
+    int half = head_dim / 2;
+    GRL_CUDA(cudaMalloc(&t, sizeof(float2) * (size_t)n_pos * half));
+    int n = n_pos * half;
+    rope_table_kernel<<<(n + 255) / 256, 256, 0, dev->stream>>>(t, n_pos, half,
+                                                                 make_rope_freq(head_dim, theta, scaling));
+    GRL_LAUNCHED("rope_table_kernel");
+    dev->rope_tables[key] = t;
+    *out = t;
+    return GRL_OK;
+}
+
+template <typename S, typename D>
+__global__ void cast_kernel(const S* __restrict__ src, D* __restrict__ dst, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) store_from_float<D>(dst + i, load_as_float<S>(src + i));
+}
+
+// 8 elements per thread with 16/32-byte accesses; n8 = n / 8.
+__global__ void cast_f32_bf16_vec8(const float4* __restrict__ src, uint4* __restrict__ dst, size_t n8) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n8; i += stride) {
+        float4 a = src[2 * i], b = src[2 * i + 1];
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+        __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+        uint4 o;
+        o.x = *reinterpret_cast<uint32_t*>(&p0);
+        o.y = *reinterpret_cast<uint32_t*>(&p1);
+        o.z = *reinterpret_cast<uint32_t*>(&p2);
+        o.w = *reinterpret_cast<uint32_t*>(&p3);
+        dst[i] = o;
+    }
+}
+
+}  // namespace grl
+
+using namespace grl;
+
+extern "C" {
+
+const char* grl_last_error(void) { return t_err; }
+
+int64_t grl_launch_count(void) { return (int64_t)g_launches.load(); }
+
+int grl_device_count(int* count) {
+    GRL_REQUIRE(count, "count is NULL");
+    cudaError_t e = cudaGetDeviceCount(count);
+    if (e != cudaSuccess) {
+        *count = 0;
+        return set_error(GRL_ERR_CUDA, "cudaGetDeviceCount failed: %s", cudaGetErrorString(e));
+    }
+    return GRL_OK;
+}
+
+int grl_device_open(int ordinal, grl_device** out) {
+    GRL_REQUIRE(out, "out is NULL");
+    int n = 0;
+    GRL_CUDA(cudaGetDeviceCount(&n));
+    GRL_REQUIRE(ordinal >= 0 && ordinal < n, "device ordinal %d out of range (%d devices)", ordinal, n);
+    GRL_CUDA(cudaSetDevice(ordinal));
+    grl_device* d = new grl_device();
+    d->ordinal = ordinal;
+    cudaError_t e = cudaGetDeviceProperties(&d->prop, ordinal);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        delete d;
+        return set_error(GRL_ERR_CUDA, "device open failed: %s", cudaGetErrorString(e));
+    }
+    d->stream = d->own_stream;
+    if (cudaMalloc(&d->d_status, 4 * sizeof(int32_t)) != cudaSuccess ||
+        cudaMemset(d->d_status, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
+        cudaStreamDestroy(d->own_stream);
+        delete d;
+        return set_error(GRL_ERR_OOM, "could not allocate the device status word");
+    }
+    if (d->prop.major != 10) {
+        int maj = d->prop.major, min = d->prop.minor;
+        cudaFree(d->d_status);
+        cudaStreamDestroy(d->own_stream);
+        delete d;
+        return set_error(GRL_ERR_UNSUPPORTED,
+                         "this library is built for sm_100a only; device %d is sm_%d%d", ordinal, maj, min);
+    }
+    *out = d;
+    return GRL_OK;
+}
+
+int grl_device_close(grl_device* dev) {
+    if (!dev) return GRL_OK;
+    DeviceGuard g(dev->ordinal);
+    cudaStreamSynchronize(dev->stream);
+    for (auto& kv : dev->rope_tables) cudaFree(kv.second);
+    cudaFree(dev->d_status);
+    cudaStreamDestroy(dev->own_stream);
+    delete dev;
+    return GRL_OK;
+}
+
+int grl_device_get_info(grl_device* dev, grl_device_info* info) {
+    GRL_REQUIRE(dev && info, "NULL argument");
+    memset(info, 0, sizeof(*info));
+    strncpy(info->name, dev->prop.name, sizeof(info->name) - 1);
+    info->ordinal = dev->ordinal;
+    info->cc_major = dev->prop.major;
+    info->cc_minor = dev->prop.minor;
+    info->sm_count = dev->prop.multiProcessorCount;
+    info->total_mem_bytes = (int64_t)dev->prop.totalGlobalMem;
+    info->l2_bytes = dev->prop.l2CacheSize;
+    info->smem_per_block_optin = (int64_t)dev->prop.sharedMemPerBlockOptin;
+    return GRL_OK;
+}
+
+int grl_device_use_stream(grl_device* dev, void* cuda_stream) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    dev->stream = cuda_stream ? (cudaStream_t)cuda_stream : dev->own_stream;
+    return GRL_OK;
+}
+
+int grl_malloc(grl_device* dev, size_t bytes, void** out) {
+    GRL_REQUIRE(dev && out, "NULL argument");
+    DeviceGuard g(dev->ordinal);
+    *out = nullptr;
+    if (bytes == 0) bytes = 256;
+    GRL_CUDA(cudaMalloc(out, bytes));
+    return GRL_OK;
+}
+
+int grl_free(grl_device* dev, void* ptr) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    if (!ptr) return GRL_OK;
+    DeviceGuard g(dev->ordinal);
+    GRL_CUDA(cudaFree(ptr));
+    return GRL_OK;
+}
+
+int grl_host_alloc(size_t bytes, void** out) {
+    GRL_REQUIRE(out, "out is NULL");
+    GRL_CUDA(cudaMallocHost(out, bytes ? bytes : 16));
+    return GRL_OK;
+}
+
+int grl_host_free(void* ptr) {
+    if (ptr) GRL_CUDA(cudaFreeHost(ptr));
+    return GRL_OK;
+}
+
+int grl_memcpy_h2d(grl_device* dev, void* dst, const void* src_host, size_t bytes) {
+    GRL_REQUIRE(dev && (bytes == 0 || (dst && src_host)), "NULL argument");
+    DeviceGuard g(dev->ordinal);
+    GRL_CUDA(cudaMemcpyAsync(dst, src_host, bytes, cudaMemcpyHostToDevice, dev->stream));
+    return GRL_OK;
+}
+
+int grl_memcpy_d2h(grl_device* dev, void* dst_host, const void* src, size_t bytes) {
+    GRL_REQUIRE(dev && (bytes == 0 || (dst_host && src)), "NULL argument");
+    DeviceGuard g(dev->ordinal);
+    GRL_CUDA(cudaMemcpyAsync(dst_host, src, bytes, cudaMemcpyDeviceToHost, dev->stream));
+    return GRL_OK;
+}
+
+int grl_memcpy_d2d(grl_device* dev, void* dst, const void* src, size_t bytes) {
+    GRL_REQUIRE(dev && (bytes == 0 || (dst && src)), "NULL argument");
+    DeviceGuard g(dev->ordinal);
+    GRL_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, dev->stream));
+    return GRL_OK;
+}
+
+int grl_memset(grl_device* dev, void* dst, int value, size_t bytes) {
+    GRL_REQUIRE(dev && (bytes == 0 || dst), "NULL argument");
+    DeviceGuard g(dev->ordinal);
+    GRL_CUDA(cudaMemsetAsync(dst, value, bytes, dev->stream));
+    return GRL_OK;
+}
+
+// After the stream drained: report (and clear) a failure that a kernel left in the status word.
+static int check_kernel_status(grl_device* dev) {
+    if (!dev->status_dirty) return GRL_OK;
+    dev->status_dirty = false;
+    int32_t st[4] = {0, 0, 0, 0};
+    GRL_CUDA(cudaMemcpyAsync(st, dev->d_status, sizeof(st), cudaMemcpyDeviceToHost, dev->stream));
+    GRL_CUDA(cudaStreamSynchronize(dev->stream));
+    if (st[0] == 0) return GRL_OK;
+    GRL_CUDA(cudaMemsetAsync(dev->d_status, 0, sizeof(st), dev->stream));
+    return set_error(st[0] == GRL_ERR_TIMEOUT ? GRL_ERR_TIMEOUT : GRL_ERR_KERNEL,
+                     "kernel reported failure %d (wait %d, block %d,%d)", st[0], st[1], st[2], st[3]);
+}
+
+int grl_sync(grl_device* dev, uint64_t timeout_ns) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    DeviceGuard g(dev->ordinal);
+    if (timeout_ns == 0) {
+        GRL_CUDA(cudaStreamSynchronize(dev->stream));
+        return check_kernel_status(dev);
+    }
+    auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        cudaError_t e = cudaStreamQuery(dev->stream);
+        if (e == cudaSuccess) return check_kernel_status(dev);
+        if (e != cudaErrorNotReady)
+            return set_error(GRL_ERR_CUDA, "stream failed: %s", cudaGetErrorString(e));
+        auto dt = std::chrono::steady_clock::now() - t0;
+        if ((uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(dt).count() > timeout_ns)
+            return set_error(GRL_ERR_TIMEOUT, "stream did not finish within %llu ns",
+                             (unsigned long long)timeout_ns);
+        std::this_thread::sleep_for(std::chrono::microseconds(20));
+    }
+}
+
+int grl_event_create(grl_event** out) {
+    GRL_REQUIRE(out, "out is NULL");
+    grl_event* e = new grl_event();
+    cudaError_t err = cudaEventCreate(&e->ev);
+    if (err != cudaSuccess) {
+        delete e;
+        return set_error(GRL_ERR_CUDA, "cudaEventCreate failed: %s", cudaGetErrorString(err));
+    }
+    *out = e;
+    return GRL_OK;
+}
+
+int grl_event_destroy(grl_event* ev) {
+    if (ev) {
+        cudaEventDestroy(ev->ev);
+        delete ev;
+    }
+    return GRL_OK;
+}
+
+int grl_event_record(grl_device* dev, grl_event* ev) {
+    GRL_REQUIRE(dev && ev, "NULL argument");
+    DeviceGuard g(dev->ordinal);
+    GRL_CUDA(cudaEventRecord(ev->ev, dev->stream));
+    return GRL_OK;
+}
+
+int grl_event_elapsed_ms(grl_event* start, grl_event* stop, float* ms) {
+    GRL_REQUIRE(start && stop && ms, "NULL argument");
+    GRL_CUDA(cudaEventSynchronize(stop->ev));
+    GRL_CUDA(cudaEventElapsedTime(ms, start->ev, stop->ev));
+    return GRL_OK;
+}
+
+int grl_graph_begin(grl_device* dev) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    DeviceGuard g(dev->ordinal);
+    GRL_CUDA(cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal));
+    return GRL_OK;
+}
+
+int grl_graph_end(grl_device* dev, grl_graph** out) {
+    GRL_REQUIRE(dev && out, "NULL argument");
+    DeviceGuard g(dev->ordinal);
+    grl_graph* gr = new grl_graph();
+    cudaError_t e = cudaStreamEndCapture(dev->stream, &gr->graph);
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&gr->exec, gr->graph, 0);
+    if (e != cudaSuccess) {
+        if (gr->graph) cudaGraphDestroy(gr->graph);
+        delete gr;
+        return set_error(GRL_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+    }
+    *out = gr;
+    return GRL_OK;
+}
+
+int grl_graph_launch(grl_device* dev, grl_graph* gr) {
+    GRL_REQUIRE(dev && gr && gr->exec, "NULL argument");
+    DeviceGuard g(dev->ordinal);
+    GRL_CUDA(cudaGraphLaunch(gr->exec, dev->stream));
+    return GRL_OK;
+}
+
+int grl_graph_destroy(grl_graph* gr) {
+    if (gr) {
+        if (gr->exec) cudaGraphExecDestroy(gr->exec);
+        if (gr->graph) cudaGraphDestroy(gr->graph);
+        delete gr;
+    }
+    return GRL_OK;
+}
+
+int grl_cast(grl_device* dev, const void* src, int src_dtype, void* dst, int dst_dtype, size_t n) {
+    GRL_REQUIRE(dev && (n == 0 || (src && dst)), "NULL argument");
+    if (n == 0) return GRL_OK;
+    DeviceGuard g(dev->ordinal);
+    int blocks = (int)((n + 255) / 256 < (size_t)dev->prop.multiProcessorCount * 16
+                           ? (n + 255) / 256
+                           : (size_t)dev->prop.multiProcessorCount * 16);
+    if (src_dtype == GRL_F32 && dst_dtype == GRL_BF16) {
+        if (n % 8 == 0 && ((uintptr_t)src % 16 == 0) && ((uintptr_t)dst % 16 == 0)) {
+            cast_f32_bf16_vec8<<<blocks, 256, 0, dev->stream>>>((const float4*)src, (uint4*)dst, n / 8);
+        } else {
+            cast_kernel<float, __nv_bfloat16><<<blocks, 256, 0, dev->stream>>>(
+                (const float*)src, (__nv_bfloat16*)dst, n);
+        }
+    } else if (src_dtype == GRL_BF16 && dst_dtype == GRL_F32) {
+        cast_kernel<__nv_bfloat16, float><<<blocks, 256, 0, dev->stream>>>(
+            (const __nv_bfloat16*)src, (float*)dst, n);
+    } else if (src_dtype == dst_dtype && (src_dtype == GRL_F32 || src_dtype == GRL_BF16)) {
+        GRL_CUDA(cudaMemcpyAsync(dst, src, n * (src_dtype == GRL_F32 ? 4 : 2), cudaMemcpyDeviceToDevice,
+                                 dev->stream));
+        return GRL_OK;
+    } else {
+        return set_error(GRL_ERR_INVALID, "unknown dtype pair %d -> %d", src_dtype, dst_dtype);
+    }
+    GRL_LAUNCHED("cast");
+    return GRL_OK;
+}
+
+}  // extern "C"

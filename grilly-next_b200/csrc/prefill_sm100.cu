@@ -1,0 +1,561 @@
+// Blackwell (sm_100a) flash-attention forward for bf16 inputs, head_dim 128.
+//
+// Replaces the S^2/(64*64) dispatch+barrier pairs of ops::flashAttention2
+// (cpp/src/ops/attention.cpp:125-141) and the per-(q,k) thread of flash-attention2-rope.glsl
+// by one launch in which a CTA owns a 128-row query tile of one (batch, head):
+//
+//   warp 4      TMA producer: Q once, then K/V tiles (128 keys x 128 dims, two 64-column boxes,
+//               128-byte swizzle) into a 2-stage shared-memory ring, mbarrier complete_tx.
+//   warps 6-9   RoPE: rotate the Q tile and each K tile in place in shared memory (cos/sin from a
+//               device table), fence.proxy.async, hand the tile to the MMA warp.
+//   warp 5      one thread issues tcgen05.mma: S = Q K^T (A,B from shared memory, K-major) into a
+//               double-buffered TMEM accumulator, then O += P V with P read from TMEM and V as an
+//               MN-major shared-memory operand; tcgen05.commit signals mbarriers.
+//   warps 0-3   one thread per query row: tcgen05.ld of the S row, causal / length predicate,
+//               fp32 online softmax in the exp2 domain, P written back to TMEM as packed bf16,
+//               O rescaled in TMEM only when the row maximum moved by more than 2^8 (the stale
+//               maximum stays the reference, so the result is exact), final O / l to global memory.
+//
+// TMEM columns: S0 [0,128) S1 [128,256) O [256,384); P_j overlays the first 64 columns of S_j.
+// Every mbarrier wait is bounded; on expiry the CTA records an error, drains and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "tmem_ops.cuh"
+
+namespace grl {
+
+namespace sm100 {
+
+constexpr int BM = 128;            // query rows per CTA
+constexpr int BN = 128;            // keys per tile
+constexpr int HD = 128;            // head_dim
+constexpr int NSTAGE = 2;
+constexpr int HALF_BYTES = BM * 64 * 2;     // one 64-column box: 16 KiB
+constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KiB
+constexpr int kThreads = 320;
+constexpr int WARP_TMA = 4, WARP_MMA = 5, WARP_ROT0 = 6;
+constexpr int SMEM_Q = 0;
+constexpr int SMEM_K = SMEM_Q + TILE_BYTES;
+constexpr int SMEM_V = SMEM_K + NSTAGE * TILE_BYTES;
+constexpr int SMEM_BAR = SMEM_V + NSTAGE * TILE_BYTES;
+constexpr int SMEM_TOTAL = SMEM_BAR + 256 + 1024;  // + barrier block + alignment slack
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TMEM_O = 256;
+constexpr long long kWaitLimitCycles = 2000000000LL;  // ~1 s at 2 GHz
+
+enum Bar { Q_FULL = 0, Q_READY, K_FULL, K_READY = K_FULL + NSTAGE, K_EMPTY = K_READY + NSTAGE,
+           V_FULL = K_EMPTY + NSTAGE, V_EMPTY = V_FULL + NSTAGE, S_FULL = V_EMPTY + NSTAGE,
+           P_READY = S_FULL + 2, O_DONE = P_READY + 2, NUM_BARS };
+static_assert(NUM_BARS * 8 + 16 <= 256, "barrier block");
+
+struct Args {
+    void* o;
+    const int32_t* seq_lens;
+    const float2* rope;   // (S, 64) cos/sin, or NULL
+    int32_t* status;      // device int32[4]: [0] error code, [1] barrier id, [2] block x, [3] block y
+    int B, H, S;
+    int causal, rope_mode;
+    float scale_log2;
+};
+
+// kind::f16 instruction descriptor: D=f32 (bit 4), A=B=bf16 (bits 7,10), N>>3 at bit 17, M>>4 at bit 24;
+// bit 16 set = B operand is MN-major (the V tile, whose contiguous dimension is head_dim = N).
+constexpr uint32_t IDESC_BASE = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t IDESC_QK = IDESC_BASE;
+constexpr uint32_t IDESC_PV = IDESC_BASE | (1u << 16);
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
+           ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct Ctx {
+    uint32_t bars;          // shared address of barrier 0
+    volatile int* abort;    // shared abort flag
+    int32_t* status;
+};
+
+// Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out).
+__device__ __forceinline__ bool wait_bar(const Ctx& c, int bar, uint32_t parity) {
+    const uint32_t addr = c.bars + bar * 8;
+    if (mbar_try_wait(addr, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        if (mbar_try_wait(addr, parity)) return true;
+        if (*c.abort) return false;
+        if (clock64() - t0 > kWaitLimitCycles) {
+            *c.abort = 1;
+            if (c.status && atomicCAS(c.status, 0, GRL_ERR_TIMEOUT) == 0) {
+                c.status[1] = bar;
+                c.status[2] = blockIdx.x;
+                c.status[3] = blockIdx.y;
+            }
+            return false;
+        }
+    }
+}
+
+// In-place RoPE of one 128 x 128 bf16 tile held as two 64-column boxes with 128-byte swizzle:
+// element (r, d) lives at box d/64, byte r*128 + ((d%64)/8 ^ (r%8))*16 + (d%8)*2.
+__device__ __forceinline__ void rope_tile(uint8_t* tile, int pos0, int S, const float2* __restrict__ rope, int mode,
+                                          int rt) {
+    if (mode == GRL_ROPE_INTERLEAVED) {
+#pragma unroll 4
+        for (int it = 0; it < 16; ++it) {
+            const int idx = it * 128 + rt, r = idx >> 4, c = idx & 15;
+            if (pos0 + r >= S) continue;
+            uint4* p = reinterpret_cast<uint4*>(tile + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+            uint4 v = *p;
+            const float4* t = reinterpret_cast<const float4*>(rope + (size_t)(pos0 + r) * 64 + c * 4);
+            const float4 t0 = __ldg(t), t1 = __ldg(t + 1);
+            uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            const float cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float x0 = __uint_as_float(w[e] << 16), x1 = __uint_as_float(w[e] & 0xffff0000u);
+                const float y0 = x0 * cs[2 * e] - x1 * cs[2 * e + 1];
+                const float y1 = x0 * cs[2 * e + 1] + x1 * cs[2 * e];
+                __nv_bfloat162 o = __floats2bfloat162_rn(y0, y1);
+                w[e] = *reinterpret_cast<uint32_t*>(&o);
+            }
+            *p = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {  // rotate_half: pairs (d, d+64) sit at the same offset of the two boxes
+#pragma unroll 2
+        for (int it = 0; it < 8; ++it) {
+            const int idx = it * 128 + rt, r = idx >> 3, cc = idx & 7;
+            if (pos0 + r >= S) continue;
+            uint4* p0 = reinterpret_cast<uint4*>(tile + r * 128 + ((cc ^ (r & 7)) << 4));
+            uint4* p1 = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p0) + HALF_BYTES);
+            uint4 a = *p0, b = *p1;
+            uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+            const float4* t = reinterpret_cast<const float4*>(rope + (size_t)(pos0 + r) * 64 + cc * 8);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float4 cs = __ldg(t + e);  // pairs 2e, 2e+1 of this chunk
+                const float a0 = __uint_as_float(wa[e] << 16), a1 = __uint_as_float(wa[e] & 0xffff0000u);
+                const float b0 = __uint_as_float(wb[e] << 16), b1 = __uint_as_float(wb[e] & 0xffff0000u);
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a0 * cs.x - b0 * cs.y, a1 * cs.z - b1 * cs.w);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(b0 * cs.x + a0 * cs.y, b1 * cs.z + a1 * cs.w);
+                wa[e] = *reinterpret_cast<uint32_t*>(&lo);
+                wb[e] = *reinterpret_cast<uint32_t*>(&hi);
+            }
+            *p0 = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+            *p1 = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+        }
+    }
+}
+
+template <typename TOut>
+__device__ __forceinline__ void store_row_chunk(TOut* dst, const uint32_t (&r)[32], float f);
+template <>
+__device__ __forceinline__ void store_row_chunk<float>(float* dst, const uint32_t (&r)[32], float f) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4*>(dst)[i] =
+            make_float4(__uint_as_float(r[4 * i]) * f, __uint_as_float(r[4 * i + 1]) * f,
+                        __uint_as_float(r[4 * i + 2]) * f, __uint_as_float(r[4 * i + 3]) * f);
+}
+template <>
+__device__ __forceinline__ void store_row_chunk<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t (&r)[32], float f) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 o = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 2 * e]) * f,
+                                                     __uint_as_float(r[8 * i + 2 * e + 1]) * f);
+            w[e] = *reinterpret_cast<uint32_t*>(&o);
+        }
+        reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base_addr = (raw_addr + 1023u) & ~1023u;   // swizzled tiles need 1024-byte alignment
+    uint8_t* smem = smem_raw + (base_addr - raw_addr);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n_qt = gridDim.x;
+    const int qt = a.causal ? (n_qt - 1 - (int)blockIdx.x) : (int)blockIdx.x;  // longest tiles first
+    const int bh = blockIdx.y, b = bh / a.H;
+    const int S = a.S;
+    const int q0 = qt * BM;
+    const int len = a.seq_lens ? min(a.seq_lens[b], S) : S;
+    TOut* O = reinterpret_cast<TOut*>(a.o) + (size_t)bh * S * HD;
+
+    if (q0 >= len) {  // padded query rows are defined as zero
+        const int rows = min(BM, S - q0);
+        for (int idx = tid; idx < rows * HD; idx += kThreads) store_from_float<TOut>(O + (size_t)q0 * HD + idx, 0.f);
+        return;
+    }
+    {   // an earlier CTA failed: leave, as a whole CTA
+        const int failed = (tid == 0 && a.status) ? (*reinterpret_cast<volatile int32_t*>(a.status) != 0) : 0;
+        if (__syncthreads_or(failed)) return;
+    }
+
+    const int k_end = a.causal ? min(len, q0 + BM) : len;
+    const int n_kt = (k_end + BN - 1) / BN;
+    const bool use_rope = a.rope_mode != GRL_ROPE_NONE;
+
+    uint64_t* bar_mem = reinterpret_cast<uint64_t*>(smem + SMEM_BAR);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SMEM_BAR + NUM_BARS * 8);
+    int* abort_flag = reinterpret_cast<int*>(smem + SMEM_BAR + NUM_BARS * 8 + 4);
+    Ctx ctx{base_addr + SMEM_BAR, abort_flag, a.status};
+    auto bar = [&](int i) { return ctx.bars + (uint32_t)i * 8u; };
+
+    if (tid == 0) {
+        mbar_init(bar(Q_FULL), 1);
+        mbar_init(bar(Q_READY), 128);
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbar_init(bar(K_FULL + s), 1);
+            mbar_init(bar(K_READY + s), 128);
+            mbar_init(bar(K_EMPTY + s), 1);
+            mbar_init(bar(V_FULL + s), 1);
+            mbar_init(bar(V_EMPTY + s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(S_FULL + s), 1);
+            mbar_init(bar(P_READY + s), 128);
+        }
+        mbar_init(bar(O_DONE), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_async_smem();
+    }
+    if (warp == WARP_MMA) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    if (warp == WARP_TMA) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmQ)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
+            mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
+            tma_load_3d(base_addr + SMEM_Q, &tmQ, 0, q0, bh, bar(Q_FULL));
+            tma_load_3d(base_addr + SMEM_Q + HALF_BYTES, &tmQ, 64, q0, bh, bar(Q_FULL));
+            int issued = 0;
+            bool ok = true;
+            for (int j = 0; j < n_kt && ok; ++j) {
+                const int s = j % NSTAGE, it = j / NSTAGE;
+                if (it > 0) ok = wait_bar(ctx, K_EMPTY + s, (it - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(bar(K_FULL + s), TILE_BYTES);
+                tma_load_3d(base_addr + SMEM_K + s * TILE_BYTES, &tmK, 0, j * BN, bh, bar(K_FULL + s));
+                tma_load_3d(base_addr + SMEM_K + s * TILE_BYTES + HALF_BYTES, &tmK, 64, j * BN, bh, bar(K_FULL + s));
+                if (it > 0) ok = wait_bar(ctx, V_EMPTY + s, (it - 1) & 1);
+                if (!ok) { issued = 2 * j + 1; break; }
+                mbar_expect_tx(bar(V_FULL + s), TILE_BYTES);
+                tma_load_3d(base_addr + SMEM_V + s * TILE_BYTES, &tmV, 0, j * BN, bh, bar(V_FULL + s));
+                tma_load_3d(base_addr + SMEM_V + s * TILE_BYTES + HALF_BYTES, &tmV, 64, j * BN, bh, bar(V_FULL + s));
+                issued = 2 * j + 2;
+            }
+            if (*ctx.abort) {
+                // Drain: copies already issued must land before the CTA's shared memory is released.
+                const long long t0 = clock64();
+                while (!mbar_try_wait(bar(Q_FULL), 0) && clock64() - t0 < kWaitLimitCycles) {}
+                for (int x = max(0, issued - 2 * NSTAGE); x < issued; ++x) {
+                    const int j = x >> 1, s = j % NSTAGE, it = j / NSTAGE;
+                    const uint32_t bb = bar(((x & 1) ? V_FULL : K_FULL) + s);
+                    while (!mbar_try_wait(bb, it & 1) && clock64() - t0 < kWaitLimitCycles) {}
+                }
+            }
+        }
+    } else if (warp == WARP_MMA) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            bool ok = wait_bar(ctx, use_rope ? Q_READY : Q_FULL, 0);
+            tc_fence_after();
+            auto issue_qk = [&](int j) -> bool {
+                const int s = j % NSTAGE, it = j / NSTAGE;
+                if (!wait_bar(ctx, (use_rope ? K_READY : K_FULL) + s, it & 1)) return false;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(j & 1) * BN;
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+                    mma_ss(d_tmem, make_desc(base_addr + SMEM_Q + off, 16, 1024),
+                           make_desc(base_addr + SMEM_K + s * TILE_BYTES + off, 16, 1024), IDESC_QK, ks > 0);
+                }
+                mma_commit(bar(S_FULL + (j & 1)));
+                mma_commit(bar(K_EMPTY + s));
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            for (int j = 0; j < n_kt && ok; ++j) {
+                const int s = j % NSTAGE, it = j / NSTAGE;
+                if (j + 1 < n_kt) ok = issue_qk(j + 1);
+                if (ok) ok = wait_bar(ctx, P_READY + (j & 1), (j >> 1) & 1);
+                if (ok) ok = wait_bar(ctx, V_FULL + s, it & 1);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < BN / 16; ++ks) {
+                    // A: P_j in TMEM, 16 keys = 8 packed columns per step.  B: 16 key rows of V = 2 KiB
+                    // per step; MN-major: 64-column boxes HALF_BYTES apart (LBO), 8-row groups 1 KiB apart (SBO).
+                    mma_ts(tmem_base + TMEM_O, tmem_base + (uint32_t)(j & 1) * BN + ks * 8,
+                           make_desc(base_addr + SMEM_V + s * TILE_BYTES + ks * 2048, HALF_BYTES, 1024), IDESC_PV,
+                           (j > 0 || ks > 0));
+                }
+                mma_commit(bar(V_EMPTY + s));
+                mma_commit(bar(O_DONE));
+            }
+        }
+    } else if (warp >= WARP_ROT0) {
+        // ------------------------------------------------------------------ RoPE on Q and K tiles
+        if (use_rope) {
+            const int rt = tid - WARP_ROT0 * 32;
+            bool ok = wait_bar(ctx, Q_FULL, 0);
+            if (ok) {
+                rope_tile(smem + SMEM_Q, q0, S, a.rope, a.rope_mode, rt);
+                fence_async_smem();
+                mbar_arrive(bar(Q_READY));
+            }
+            for (int j = 0; j < n_kt && ok; ++j) {
+                const int s = j % NSTAGE, it = j / NSTAGE;
+                ok = wait_bar(ctx, K_FULL + s, it & 1);
+                if (!ok) break;
+                rope_tile(smem + SMEM_K + s * TILE_BYTES, j * BN, S, a.rope, a.rope_mode, rt);
+                fence_async_smem();
+                mbar_arrive(bar(K_READY + s));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax / correction / epilogue
+        const int row = tid;                       // TMEM lane == query row of the tile
+        const int row_g = q0 + row;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kt && ok; ++j) {
+            const int buf = j & 1, k0 = j * BN;
+            ok = __all_sync(0xffffffffu, wait_bar(ctx, S_FULL + buf, (j >> 1) & 1));  // leave as a whole warp
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t sr[128];
+            tmem_ld_x128_sync(lane_addr + buf * BN, sr);
+            const bool need_mask = (a.causal && k0 + BN - 1 > q0) || (k0 + BN > len);  // CTA-uniform
+            float mx = -INFINITY;
+            if (need_mask) {
+                const int limit = min(a.causal ? row_g : 0x7fffffff, len - 1) - k0;  // last visible column
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const float v = (c <= limit) ? __uint_as_float(sr[c]) : -INFINITY;
+                    sr[c] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+            }
+            const float m_new = fmaxf(m_ref, mx * a.scale_log2);
+            bool o_waited = false;
+            if (j == 0) {
+                m_ref = (m_new == -INFINITY) ? 0.f : m_new;
+            } else {
+                const bool need = m_new > m_ref + 8.f;
+                if (__any_sync(0xffffffffu, need)) {
+                    ok = __all_sync(0xffffffffu, wait_bar(ctx, O_DONE, (j - 1) & 1));  // PV_{j-1} wrote O
+                    if (!ok) break;
+                    o_waited = true;
+                    tc_fence_after();
+                    const float f = need ? ex2(m_ref - m_new) : 1.f;
+                    if (need) m_ref = m_new;
+                    l *= f;
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint32_t orow[32];
+                        tmem_ld_x32_sync(lane_addr + TMEM_O + ch * 32, orow);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * f);
+                        tmem_st_x32(lane_addr + TMEM_O + ch * 32, orow);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            const float neg_m = -m_ref;
+            float rs = 0.f;
+            uint32_t pk[64];
+#pragma unroll
+            for (int c = 0; c < BN; c += 2) {
+                const float p0 = ex2(fmaf(__uint_as_float(sr[c]), a.scale_log2, neg_m));
+                const float p1 = ex2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, neg_m));
+                rs += p0 + p1;
+                __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);   // key c in the low half
+                pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pp);
+            }
+            l += rs;
+            tmem_st_x64(lane_addr + buf * BN, pk);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(bar(P_READY + buf));
+            if (j >= 1 && !o_waited) ok = wait_bar(ctx, O_DONE, (j - 1) & 1);  // keep the phase in step
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) ok = __all_sync(0xffffffffu, wait_bar(ctx, O_DONE, (n_kt - 1) & 1));
+        if (ok) {
+            tc_fence_after();
+            const bool zero = (row_g >= len) || !(l > 0.f);
+            const float inv = zero ? 0.f : 1.f / l;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t orow[32];
+                tmem_ld_x32_sync(lane_addr + TMEM_O + ch * 32, orow);   // warp-collective: no divergence here
+                if (row_g < S) store_row_chunk<TOut>(O + (size_t)row_g * HD + ch * 32, orow, inv);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == WARP_MMA) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// (B*H, S, 128) bf16 tensor, box = 64 columns x 128 rows x 1, 128-byte swizzle, zero fill out of bounds.
+static int make_map(CUtensorMap* tm, const void* ptr, int BH, int S) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return set_error(GRL_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)S, (cuuint64_t)BH};
+    cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)S * HD * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)BM, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(GRL_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return GRL_OK;
+}
+
+}  // namespace sm100
+
+int flash_fwd_sm100(grl_device* dev, const grl_flash_params* p, float scale, const float2* rope, int32_t* status) {
+    using namespace sm100;
+    GRL_REQUIRE(p->head_dim == HD, "the tcgen05 prefill kernel needs head_dim 128 (got %d)", p->head_dim);
+    GRL_REQUIRE(p->in_dtype == GRL_BF16, "the tcgen05 prefill kernel takes bf16 Q/K/V (cast with grl_cast first)");
+    GRL_REQUIRE(!p->mask, "the tcgen05 prefill kernel takes causal / seq_lens masks only");
+    GRL_REQUIRE(scale > 0.f, "scale must be positive");
+    GRL_REQUIRE(((uintptr_t)p->q % 16 == 0) && ((uintptr_t)p->k % 16 == 0) && ((uintptr_t)p->v % 16 == 0) &&
+                    ((uintptr_t)p->o % 16 == 0),
+                "Q/K/V/O must be 16-byte aligned");
+    const int BH = p->batch * p->heads;
+    CUtensorMap tq, tk, tv;
+    int rc = make_map(&tq, p->q, BH, p->seq_len);
+    if (!rc) rc = make_map(&tk, p->k, BH, p->seq_len);
+    if (!rc) rc = make_map(&tv, p->v, BH, p->seq_len);
+    if (rc) return rc;
+    Args a{};
+    a.o = p->o; a.seq_lens = p->seq_lens; a.rope = rope; a.status = status;
+    a.B = p->batch; a.H = p->heads; a.S = p->seq_len;
+    a.causal = p->causal; a.rope_mode = p->rope_mode;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    dim3 grid((p->seq_len + BM - 1) / BM, BH);
+    if (p->out_dtype == GRL_F32) {
+        auto kern = flash_fwd_sm100_kernel<float>;
+        GRL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        kern<<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
+    } else {
+        auto kern = flash_fwd_sm100_kernel<__nv_bfloat16>;
+        GRL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        kern<<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
+    }
+    GRL_LAUNCHED("flash_fwd_sm100_kernel");
+    return GRL_OK;
+}
+
+}  // namespace grl

@@ -1,0 +1,59 @@
+"""VulkanCompute: the reference's backend class (src/grilly_next/backend/compute.py:28-111),
+attention / KV-cache methods only, dispatching to the CUDA build of grilly_core."""
+from . import _bridge
+
+
+class VulkanCompute:
+    """C++ compute backend. All ops dispatch through grilly_core; there is no Python fallback."""
+
+    def __init__(self, shader_dir: str = None):
+        if not _bridge.NATIVE_AVAILABLE:
+            raise RuntimeError("grilly_core C++ extension not found. Build it with: "
+                               "python grilly-next_b200/build.py")
+        self._device = _bridge.create_device(shader_dir)
+
+    @property
+    def device(self):
+        return self._device
+
+    def cleanup(self):
+        self._device = None
+
+    # ---- prefill
+    def flash_attention2(self, Q, K, V, mask=None, **kwargs):
+        return _bridge.flash_attention2(self._device, Q, K, V, mask, **kwargs)
+
+    def flash_attention2_rope(self, Q, K, V, mask=None, **kwargs):
+        return _bridge.flash_attention2_rope(self._device, Q, K, V, mask, **kwargs)
+
+    def rope(self, x, **kwargs):
+        return _bridge.rope(self._device, x, **kwargs)
+
+    def attention_mask(self, scores, mask=None, **kwargs):
+        return _bridge.attention_mask(self._device, scores, mask, **kwargs)
+
+    # ---- KV cache
+    def create_kv_cache(self, **kwargs):
+        return _bridge.create_kv_cache(self._device, **kwargs)
+
+    def kv_cache_append(self, kv_cache, new_keys, new_values, **kwargs):
+        return _bridge.kv_cache_append(self._device, kv_cache, new_keys, new_values, **kwargs)
+
+    def kv_cache_decode(self, kv_cache, seq=0):
+        return _bridge.kv_cache_decode(self._device, kv_cache, seq)
+
+    def kv_cache_evict_h2o(self, kv_cache, attention_scores=None, num_evict=0):
+        return _bridge.kv_cache_evict_h2o(self._device, kv_cache, attention_scores, num_evict)
+
+    def destroy_kv_cache(self, kv_cache):
+        return _bridge.destroy_kv_cache(self._device, kv_cache)
+
+    def swizzle_kv(self, input, wave_size=32, reverse=False):
+        raise RuntimeError("swizzle_kv is not built in the CUDA backend (Wave32 layout op)")
+
+    # ---- decode
+    def gqa_attention(self, q, k_cache, v_cache=None, **kwargs):
+        return _bridge.gqa_attention(self._device, q, k_cache, v_cache, **kwargs)
+
+    def decode_step(self, kv_cache, q, k_new, v_new, **kwargs):
+        return _bridge.decode_step(self._device, kv_cache, q, k_new, v_new, **kwargs)

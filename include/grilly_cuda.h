@@ -1,0 +1,205 @@
+/* grilly_cuda.h -- C ABI of the B200 (sm_100a) attention path.
+ *
+ * This is the whole boundary between the host-side op layer (namespace grilly::ops, the
+ * grilly_core pybind11 module) and the CUDA kernels.  Plain pointers and sizes only: no C++
+ * types, no PyTorch types, no exceptions.  Every function returns GRL_OK (0) or a negative
+ * GRL_ERR_* code; grl_last_error() gives the message of the calling thread's last failure.
+ *
+ * Each entry point names the piece of the reference (Grillcheese-AI/grilly-next, paths relative
+ * to that project) that it replaces.
+ *
+ * Conventions
+ *  - All data pointers are DEVICE pointers unless a parameter says "host".
+ *  - All launches and copies are asynchronous on the device's stream (grl_device_use_stream
+ *    adopts a caller's stream); grl_sync waits for it.
+ *  - Callers own every buffer (grl_malloc / grl_free); kernels never allocate.  The library
+ *    itself caches only small per-device tables (RoPE cos/sin) that it frees in grl_device_close.
+ */
+#ifndef GRILLY_CUDA_H
+#define GRILLY_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct grl_device grl_device;
+typedef struct grl_event grl_event;
+typedef struct grl_graph grl_graph;
+
+enum {
+    GRL_OK = 0,
+    GRL_ERR_INVALID = -1,     /* bad argument / shape; nothing was launched */
+    GRL_ERR_CUDA = -2,        /* a CUDA runtime/driver call failed */
+    GRL_ERR_UNSUPPORTED = -3, /* valid request that no kernel here covers */
+    GRL_ERR_TIMEOUT = -4,     /* grl_sync host timeout, or a bounded device wait ran out */
+    GRL_ERR_OOM = -5,
+    GRL_ERR_KERNEL = -6       /* a kernel reported a failure through its status word */
+};
+
+enum { GRL_F32 = 0, GRL_BF16 = 1 };
+enum { GRL_ROPE_NONE = 0, GRL_ROPE_INTERLEAVED = 1, GRL_ROPE_HALF = 2 };
+/* Mask conventions of the reference, selected by the shape the caller holds. Values > 0 keep. */
+enum {
+    GRL_MASK_NONE = 0,
+    GRL_MASK_KEY = 1,  /* (B,S) key-padding mask: shaders/flash-attention2.glsl:151-154 */
+    GRL_MASK_BSS = 2,  /* (B,S,S): the size cpp/src/ops/attention.cpp:63-66 uploads; also (B,1,S,S) */
+    GRL_MASK_BHSS = 3  /* (B,H,S,S): tests/test_attention.py:29-30 */
+};
+enum { GRL_KERNEL_AUTO = 0, GRL_KERNEL_SIMT_F32 = 1, GRL_KERNEL_TCGEN05 = 2 };
+
+const char* grl_last_error(void);
+
+/* ---- device, memory, stream: replaces GrillyDevice (cpp/src/device.cpp:103-468), the VMA
+ * BufferPool's allocation/upload/download (cpp/src/buffer_pool.cpp:128-175,453-477) and
+ * CommandBatch submit/wait (cpp/src/command_batch.cpp:69-149). */
+typedef struct {
+    char name[128];
+    int32_t ordinal, cc_major, cc_minor, sm_count;
+    int64_t total_mem_bytes, l2_bytes, smem_per_block_optin;
+} grl_device_info;
+
+int grl_device_count(int* count);
+int grl_device_open(int ordinal, grl_device** out);
+int grl_device_close(grl_device* dev);
+int grl_device_get_info(grl_device* dev, grl_device_info* info);
+/* Launch on the caller's cudaStream_t from now on (NULL restores the device's own stream). */
+int grl_device_use_stream(grl_device* dev, void* cuda_stream);
+int grl_malloc(grl_device* dev, size_t bytes, void** out);
+int grl_free(grl_device* dev, void* ptr);
+int grl_host_alloc(size_t bytes, void** out); /* pinned host memory for staging */
+int grl_host_free(void* ptr);
+int grl_memcpy_h2d(grl_device* dev, void* dst, const void* src_host, size_t bytes);
+int grl_memcpy_d2h(grl_device* dev, void* dst_host, const void* src, size_t bytes);
+int grl_memcpy_d2d(grl_device* dev, void* dst, const void* src, size_t bytes);
+int grl_memset(grl_device* dev, void* dst, int value, size_t bytes);
+/* Wait for the stream.  timeout_ns == 0 waits without limit; otherwise polls and returns
+ * GRL_ERR_TIMEOUT when the limit passes (the 2 s fence timeout of command_batch.cpp:16,145-148). */
+int grl_sync(grl_device* dev, uint64_t timeout_ns);
+
+int grl_event_create(grl_event** out);
+int grl_event_destroy(grl_event* ev);
+int grl_event_record(grl_device* dev, grl_event* ev);
+int grl_event_elapsed_ms(grl_event* start, grl_event* stop, float* ms); /* syncs on stop */
+
+/* Stream capture of a launch sequence (the 256-step decode loop); replaces the record-once /
+ * replay role of CommandBatch + OpGraph for this path. */
+int grl_graph_begin(grl_device* dev);
+int grl_graph_end(grl_device* dev, grl_graph** out);
+int grl_graph_launch(grl_device* dev, grl_graph* g);
+int grl_graph_destroy(grl_graph* g);
+
+/* Number of kernels this library has launched on any device since load (for accounting). */
+int64_t grl_launch_count(void);
+
+/* Element-wise dtype conversion (GRL_F32 <-> GRL_BF16, round-to-nearest-even), n elements. */
+int grl_cast(grl_device* dev, const void* src, int src_dtype, void* dst, int dst_dtype, size_t n);
+
+/* ---- prefill: replaces ops::flashAttention2 (cpp/src/ops/attention.cpp:45-166) together with
+ * shaders/flash-attention2.glsl and shaders/flash-attention2-rope.glsl (push block :56-71).
+ * O = softmax(rope(Q) rope(K)^T * scale, masked) V, forward only. */
+typedef struct {
+    const void* q;      /* (B,H,S,D) contiguous, in_dtype */
+    const void* k;
+    const void* v;
+    void* o;            /* (B,H,S,D) contiguous, out_dtype */
+    int32_t in_dtype;   /* GRL_F32 or GRL_BF16 */
+    int32_t out_dtype;
+    int32_t batch, heads, seq_len, head_dim;
+    float scale;        /* 0 => 1/sqrt(head_dim) (attention.cpp:53-55) */
+    int32_t causal;     /* key k visible to query q iff k <= q */
+    const int32_t* seq_lens; /* (B) valid lengths or NULL; rows q >= len are written as 0 */
+    const float* mask;  /* explicit mask or NULL */
+    int32_t mask_kind;  /* GRL_MASK_* */
+    int32_t rope_mode;  /* GRL_ROPE_*; position = sequence index (flash-attention2-rope.glsl:101-141) */
+    float rope_theta;   /* base, e.g. 10000 */
+    float rope_scaling; /* theta / scaling; 0 is read as 1 */
+    int32_t kernel;     /* GRL_KERNEL_*; AUTO picks tcgen05 for bf16 input with D=128 */
+    int32_t* status;    /* optional device int32[4]; [0] != 0 after a kernel-side failure */
+} grl_flash_params;
+int grl_flash_fwd(grl_device* dev, const grl_flash_params* p);
+
+/* ---- standalone RoPE: replaces shaders/rope.glsl:32-126 (push block :32-40).
+ * x, y: (B,S,H,D) float32, out of place; position = sequence index / scaling;
+ * cos_table/sin_table: optional (>=S, D/2) float32 tables (use_precomputed). */
+int grl_rope(grl_device* dev, const float* x, float* y, int batch, int seq_len, int heads,
+             int head_dim, float base, float scaling, int mode, const float* cos_table,
+             const float* sin_table);
+
+/* ---- standalone mask fill: replaces shaders/attention-mask.glsl:18-55.
+ * scores: (B,H,S,S) float32, in place.  causal != 0: scores[k>q] = mask_value; else key_mask
+ * (B,S): scores[..,k] = mask_value where key_mask[b,k] < 0.5. */
+int grl_attention_mask(grl_device* dev, float* scores, const float* key_mask, int batch,
+                       int heads, int seq_len, int causal, float mask_value);
+
+/* ---- paged KV cache.  Pages are head-major: [page][Hkv][page_tokens][D] of cache_dtype, one
+ * pool for K and one for V; block_table[b][i] = page holding tokens [i*page_tokens, ...) of
+ * sequence b; seq_lens[b] = tokens stored.  Replaces the storage of struct KVCache
+ * (cpp/include/grilly/ops/kv_cache.h:123-144) for the uncompressed mode. */
+typedef struct {
+    void* k_pages;
+    void* v_pages;
+    int32_t cache_dtype;          /* GRL_BF16 (default) or GRL_F32 */
+    const int32_t* block_table;   /* (B, max_pages) */
+    int32_t* seq_lens;            /* (B) */
+    int32_t batch, num_kv_heads, head_dim, page_tokens, max_pages;
+} grl_kv_layout;
+
+/* Append n_new tokens per sequence: replaces ops::kvCacheAppend (cpp/src/ops/kv_cache.cpp:155-419;
+ * signature kv_cache.h:163-166) and fuses the RoPE of the new keys and of the step's queries.
+ * k_new, v_new: (B, n_new, Hkv, D) float32.  q_in/q_out: optional (B, n_new, Hq, D) float32,
+ * rotated at the same positions (position = pos_base + seq_lens[b] + i).  update_lens != 0
+ * adds n_new to seq_lens[b] afterwards. */
+typedef struct {
+    grl_kv_layout kv;
+    const float* k_new;
+    const float* v_new;
+    const float* q_in;
+    float* q_out;
+    int32_t n_new, num_q_heads;
+    int32_t rope_mode;
+    float rope_theta, rope_scaling;
+    int32_t pos_base;
+    int32_t update_lens;
+} grl_append_params;
+int grl_kv_append(grl_device* dev, const grl_append_params* p);
+
+/* Materialise sequence b as token-major float32 (T, Hkv, D): replaces ops::kvCacheDecode
+ * (cpp/src/ops/kv_cache.cpp:435-578; kv_cache.h:175-177). */
+int grl_kv_gather(grl_device* dev, const grl_kv_layout* kv, int b, int n_tokens, float* out_k,
+                  float* out_v);
+
+/* ---- decode attention: replaces shaders/gqa-attention.glsl:34-130 (no host dispatcher exists
+ * in the reference).  q, out: (B,1,Hq,D) float32.  kv_head = q_head / (Hq/Hkv).
+ * The KV range of every sequence is cut into n_splits parts that run on different SMs; each
+ * part leaves (O un-normalised, m, l) in `workspace`, and a merge pass combines them.
+ * If partial_out != NULL the merged result is written there UN-normalised as
+ * [O (B*Hq*D) | m (B*Hq) | l (B*Hq)] floats (one part of a cross-GPU merge) and `out` may be NULL. */
+typedef struct {
+    grl_kv_layout kv;
+    const float* q;
+    float* out;
+    int32_t num_q_heads;
+    float scale;            /* 0 => 1/sqrt(D) */
+    int32_t n_splits;       /* 0 => chosen from max_seq_len and the SM count */
+    int32_t max_seq_len;    /* upper bound of seq_lens (host knowledge; sizes the split) */
+    void* workspace;        /* >= grl_decode_workspace_bytes() */
+    size_t workspace_bytes;
+    float* partial_out;
+} grl_decode_params;
+int grl_decode_pick_splits(grl_device* dev, const grl_decode_params* p, int* n_splits);
+int grl_decode_workspace_bytes(const grl_decode_params* p, int n_splits, size_t* bytes);
+int grl_gqa_decode(grl_device* dev, const grl_decode_params* p);
+
+/* Log-sum-exp merge of n_parts partials laid out as the partial_out of grl_gqa_decode, part i at
+ * parts + i*part_stride floats.  rows = B*Hq.  normalise != 0 writes O/l to out (rows*D);
+ * otherwise writes one combined partial of the same layout to out. */
+int grl_lse_merge(grl_device* dev, const float* parts, int n_parts, size_t part_stride, int rows,
+                  int head_dim, int normalise, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRILLY_CUDA_H */
