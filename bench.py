@@ -209,7 +209,7 @@ def bench_prefill_e2e(args, L, steps, dist):
     return dt, 3 * nbytes, nbytes
 
 
-def bench_decode(dev, cabi, dist, repeats=3):
+def bench_decode(dev, cabi, dist, repeats=3, use_graph=True):
     """cfg3: 256 decode steps (RoPE + append + split-KV attention + merge), graph-replayed."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from oracle import attention_oracle as orc
@@ -275,13 +275,18 @@ def bench_decode(dev, cabi, dist, repeats=3):
         cabi.check(L.grl_memcpy_h2d(dev.h, seq_lens, lens0.ctypes.data_as(C.c_void_p), lens0.nbytes))
 
     launches0 = L.grl_launch_count()
-    cabi.check(L.grl_graph_begin(dev.h))
-    record_steps()
     g = C.c_void_p()
-    cabi.check(L.grl_graph_end(dev.h, C.byref(g)))
+    if use_graph:
+        cabi.check(L.grl_graph_begin(dev.h))
+        record_steps()
+        cabi.check(L.grl_graph_end(dev.h, C.byref(g)))
+        run = lambda: cabi.check(L.grl_graph_launch(dev.h, g))
+    else:
+        run = record_steps
+        record_steps()
     launches_per_run = L.grl_launch_count() - launches0
     reset()
-    cabi.check(L.grl_graph_launch(dev.h, g))    # warm-up run
+    run()                                       # warm-up run
     dev.sync()
     best = None
     e0, e1 = dev.event(), dev.event()
@@ -290,14 +295,15 @@ def bench_decode(dev, cabi, dist, repeats=3):
         dev.sync()
         dist["barrier"]()
         dev.record(e0)
-        cabi.check(L.grl_graph_launch(dev.h, g))
+        run()
         dev.record(e1)
         dev.sync()
         ms = dist["max"](dev.elapsed_ms(e0, e1))
         best = ms if best is None else min(best, ms)
     o_last = dev.download(C.c_void_p(out.value + (steps - 1) * B * Hq * D * 4), (B, Hq, D), np.float32)
     assert np.isfinite(o_last).all()
-    L.grl_graph_destroy(g)
+    if use_graph:
+        L.grl_graph_destroy(g)
     for x in (kp, vp, table, seq_lens, qs, ks, vs, q_rot, out, ws):
         dev.free(x)
     return best, launches_per_run, ns.value
@@ -357,6 +363,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--skip-prefill", action="store_true", help="profiling aid: run the decode workload only")
+    ap.add_argument("--no-graph", action="store_true", help="profiling aid: plain launches instead of graph replay")
+    ap.add_argument("--decode-repeats", type=int, default=3)
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     args = ap.parse_args()
@@ -391,6 +400,11 @@ def main():
     L = dev.L
     pk = peaks()
 
+    if args.skip_prefill:
+        dms, dl, nsplit = bench_decode(dev, cabi, dist, args.decode_repeats, not args.no_graph)
+        print(json.dumps({"decode_ms": dms, "launches": int(dl), "n_splits": nsplit}), flush=True)
+        dev.close()
+        return
     ms, launches, clocks = bench_prefill(dev, cabi, args, dist)
     fl = prefill_flops(CFG2)
     tflops_gpu = fl * args.steps / (ms * 1e-3) / 1e12
@@ -410,7 +424,7 @@ def main():
     }
 
     if not args.skip_decode:
-        dms, dl, nsplit = bench_decode(dev, cabi, dist)
+        dms, dl, nsplit = bench_decode(dev, cabi, dist, args.decode_repeats, not args.no_graph)
         c = CFG3
         toks = c["B"] * c["steps"] / (dms * 1e-3)
         gbs = decode_bytes(c) / (dms * 1e-3) / 1e9

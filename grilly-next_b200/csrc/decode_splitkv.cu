@@ -228,7 +228,7 @@ static int dispatch_decode_d(grl_device* dev, DecodeArgs& a, int D) {
     }
 }
 
-static int check_decode(const grl_decode_params* p) {
+static int check_decode(const grl_decode_params* p, bool need_tensors = true) {
     GRL_REQUIRE(p, "params is NULL");
     const grl_kv_layout& kv = p->kv;
     GRL_REQUIRE(kv.k_pages && kv.v_pages && kv.block_table && kv.seq_lens, "NULL cache pointer");
@@ -236,8 +236,10 @@ static int check_decode(const grl_decode_params* p) {
     GRL_REQUIRE(p->num_q_heads > 0 && p->num_q_heads % kv.num_kv_heads == 0,
                 "num_q_heads (%d) must be a multiple of num_kv_heads (%d)", p->num_q_heads, kv.num_kv_heads);
     GRL_REQUIRE(kv.cache_dtype == GRL_BF16 || kv.cache_dtype == GRL_F32, "unknown cache dtype");
-    GRL_REQUIRE(p->q, "q is NULL");
-    GRL_REQUIRE(p->out || p->partial_out, "out and partial_out are both NULL");
+    if (need_tensors) {
+        GRL_REQUIRE(p->q, "q is NULL");
+        GRL_REQUIRE(p->out || p->partial_out, "out and partial_out are both NULL");
+    }
     return GRL_OK;
 }
 
@@ -249,7 +251,7 @@ extern "C" {
 
 int grl_decode_pick_splits(grl_device* dev, const grl_decode_params* p, int* n_splits) {
     GRL_REQUIRE(dev && n_splits, "NULL argument");
-    int rc = check_decode(p);
+    int rc = check_decode(p, false);
     if (rc) return rc;
     if (p->n_splits > 0) {
         *n_splits = p->n_splits;

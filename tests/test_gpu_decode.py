@@ -153,7 +153,7 @@ def test_append_with_rope_and_pos_base(dev):
     kk = rng.standard_normal((1, 1, 1, 128), dtype=np.float32)
     pc2.append(kk, kk, rope_mode=cabi.ROPE_INTERLEAVED, pos_base=131071)
     gk, _ = pc2.gather(0)
-    np.testing.assert_allclose(gk[0], orc.rope_interleaved(kk[0, 0], [131071])[0:1][0], atol=4e-6, rtol=0)
+    np.testing.assert_allclose(gk[0, 0], orc.rope_interleaved(kk[0, 0], [131071])[0], atol=4e-6, rtol=0)
 
 
 def test_decode_step_loop_matches_oracle(gpu):
