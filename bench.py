@@ -61,11 +61,18 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
+        self.t0 = self.t1 = None
+
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -74,17 +81,19 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append([time.time()] + [x.strip() for x in line.split(",")])
 
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         self.t.join(timeout=2)
-        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        # samples taken while the timed region ran (20 ms of slack for the sampler's own latency)
+        rows = [r[1:] for r in self.rows if len(r) >= 7 and self.t0 is not None and self.t0 <= r[0] <= self.t1 + 0.02]
+        sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[2].replace(".", "").isdigit() for r in [r[1:]]]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i] == "Active" for r in rows)]
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
 
@@ -151,25 +160,31 @@ def bench_prefill(dev, cabi, args, dist):
     p.in_dtype, p.out_dtype = cabi.BF16, cabi.F32
     p.batch, p.heads, p.seq_len, p.head_dim = B, H, S, D
     p.causal, p.rope_mode, p.rope_theta, p.rope_scaling = 1, cabi.ROPE_INTERLEAVED, c["theta"], 1.0
+    if args.variant == "norope":          # profiling aids: not the benchmark configuration
+        p.rope_mode = cabi.ROPE_NONE
+    elif args.variant == "noncausal":
+        p.causal = 0
     p.kernel = cabi.KERNEL_TCGEN05
     L = dev.L
 
     def step():
         cabi.check(L.grl_flash_fwd(dev.h, C.byref(p)))
 
+    sampler = ClockSampler(dist["local_rank"])
+    sampler.start()
     for _ in range(args.warmup):
         step()
     dev.sync()
     e0, e1 = dev.event(), dev.event()
-    sampler = ClockSampler(dist["local_rank"])
-    sampler.start()
     dist["barrier"]()
     launches0 = L.grl_launch_count()
+    sampler.mark_start()
     dev.record(e0)
     for _ in range(args.steps):
         step()
     dev.record(e1)
     dev.sync()
+    sampler.mark_end()
     ms = dev.elapsed_ms(e0, e1)
     launches = L.grl_launch_count() - launches0
     ms = dist["max"](ms)
@@ -359,13 +374,15 @@ def cpu_baseline():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-decode", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true", help="profiling aid: run the decode workload only")
     ap.add_argument("--no-graph", action="store_true", help="profiling aid: plain launches instead of graph replay")
     ap.add_argument("--decode-repeats", type=int, default=3)
+    ap.add_argument("--variant", default="cfg2", choices=["cfg2", "norope", "noncausal"],
+                    help="profiling aid: drop RoPE or the causal mask from the prefill workload")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-cpu", action="store_true")
     args = ap.parse_args()
@@ -407,13 +424,16 @@ def main():
         return
     ms, launches, clocks = bench_prefill(dev, cabi, args, dist)
     fl = prefill_flops(CFG2)
+    if args.variant == "noncausal":
+        fl = 4 * CFG2["D"] * CFG2["B"] * CFG2["H"] * CFG2["S"] * CFG2["S"]
     tflops_gpu = fl * args.steps / (ms * 1e-3) / 1e12
     value = tflops_gpu * world
     line = {
         "metric": "prefill_attn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "cfg2: FlashAttention-2+RoPE causal prefill, B4 H32 S2048 D128, bf16 in / fp32 out, per GPU",
+        "config": {"workload": "cfg2: FlashAttention-2+RoPE causal prefill, B4 H32 S2048 D128, bf16 in / fp32 out, per GPU"
+                   + ("" if args.variant == "cfg2" else f" [variant {args.variant}: NOT the benchmark configuration]"),
                    "flops_per_step_per_gpu": fl, "l2": "inputs larger than L2 (320 MiB per step)",
                    "parallelism": f"replica per GPU x{world}, no collective"},
         "clocks": clocks, "gpu_launches": int(launches),

@@ -4,11 +4,11 @@
 // (cpp/src/ops/attention.cpp:125-141) and the per-(q,k) thread of flash-attention2-rope.glsl
 // by one launch in which a CTA owns a 128-row query tile of one (batch, head):
 //
-//   warp 4      TMA producer: Q once, then K/V tiles (128 keys x 128 dims, two 64-column boxes,
+//   warp 8      TMA producer: Q once, then K/V tiles (128 keys x 128 dims, two 64-column boxes,
 //               128-byte swizzle) into a 2-stage shared-memory ring, mbarrier complete_tx.
-//   warps 6-9   RoPE: rotate the Q tile and each K tile in place in shared memory (cos/sin from a
+//   warps 4-7   RoPE: rotate the Q tile and each K tile in place in shared memory (cos/sin from a
 //               device table), fence.proxy.async, hand the tile to the MMA warp.
-//   warp 5      one thread issues tcgen05.mma: S = Q K^T (A,B from shared memory, K-major) into a
+//   warp 9      one thread issues tcgen05.mma: S = Q K^T (A,B from shared memory, K-major) into a
 //               double-buffered TMEM accumulator, then O += P V with P read from TMEM and V as an
 //               MN-major shared-memory operand; tcgen05.commit signals mbarriers.
 //   warps 0-3   one thread per query row: tcgen05.ld of the S row, causal / length predicate,
@@ -33,8 +33,10 @@ constexpr int HD = 128;            // head_dim
 constexpr int NSTAGE = 2;
 constexpr int HALF_BYTES = BM * 64 * 2;     // one 64-column box: 16 KiB
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KiB
-constexpr int kThreads = 320;
-constexpr int WARP_TMA = 4, WARP_MMA = 5, WARP_ROT0 = 6;
+constexpr int kThreads = 384;   // three warpgroups: softmax | RoPE | TMA + MMA (+2 idle warps)
+constexpr int WARP_ROT0 = 4, WARP_TMA = 8, WARP_MMA = 9;
+// Register budget per warpgroup (setmaxnreg): the softmax threads hold a whole 128-column S row.
+constexpr int REGS_SOFTMAX = 232, REGS_ROPE = 112, REGS_MISC = 48;
 constexpr int SMEM_Q = 0;
 constexpr int SMEM_K = SMEM_Q + TILE_BYTES;
 constexpr int SMEM_V = SMEM_K + NSTAGE * TILE_BYTES;
@@ -125,6 +127,8 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -159,51 +163,85 @@ __device__ __forceinline__ bool wait_bar(const Ctx& c, int bar, uint32_t parity)
 
 // In-place RoPE of one 128 x 128 bf16 tile held as two 64-column boxes with 128-byte swizzle:
 // element (r, d) lives at box d/64, byte r*128 + ((d%64)/8 ^ (r%8))*16 + (d%8)*2.
-__device__ __forceinline__ void rope_tile(uint8_t* tile, int pos0, int S, const float2* __restrict__ rope, int mode,
-                                          int rt) {
+//
+// A thread keeps one 16-byte column chunk and walks down the rows in a fixed stride, so that its
+// rotation frequencies never change: it reads cos/sin of its first row from the table once per tile
+// and advances them by the angle-addition recurrence (c,s) <- (c*cd - s*sd, s*cd + c*sd) with the
+// per-thread step (cd, sd) = cos/sin(stride * inv_freq), read once per kernel from table row `stride`.
+// Rows past the end of the sequence hold zeros (TMA fill) and stay zero under any rotation.
+struct RopeState {
+    float cd[8], sd[8];   // step rotation; 4 pairs (interleaved) or 8 pairs (rotate_half) per thread
+};
+
+__device__ __forceinline__ void rope_init(RopeState& st, const float2* __restrict__ rope, int S, int mode, int rt) {
     if (mode == GRL_ROPE_INTERLEAVED) {
+        const float2* t = rope + (size_t)min(8, S - 1) * 64 + (rt & 15) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 v = __ldg(t + e); st.cd[e] = v.x; st.sd[e] = v.y; }
+    } else {
+        const float2* t = rope + (size_t)min(16, S - 1) * 64 + (rt & 7) * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { const float2 v = __ldg(t + e); st.cd[e] = v.x; st.sd[e] = v.y; }
+    }
+}
+
+__device__ __forceinline__ void rope_tile(uint8_t* tile, int pos0, int S, const float2* __restrict__ rope, int mode,
+                                          int rt, const RopeState& st) {
+    if (mode == GRL_ROPE_INTERLEAVED) {
+        // chunk c = 4 adjacent pairs (2i, 2i+1); rows r0, r0+8, ... : r % 8 == r0, so the swizzle term is fixed
+        const int c = rt & 15, r0 = rt >> 4;
+        uint8_t* p = tile + (c >> 3) * HALF_BYTES + r0 * 128 + (((c & 7) ^ r0) << 4);
+        const float4* t = reinterpret_cast<const float4*>(rope + (size_t)min(pos0 + r0, S - 1) * 64 + c * 4);
+        const float4 t0 = __ldg(t), t1 = __ldg(t + 1);
+        float cs[4] = {t0.x, t0.z, t1.x, t1.z}, sn[4] = {t0.y, t0.w, t1.y, t1.w};
 #pragma unroll 4
-        for (int it = 0; it < 16; ++it) {
-            const int idx = it * 128 + rt, r = idx >> 4, c = idx & 15;
-            if (pos0 + r >= S) continue;
-            uint4* p = reinterpret_cast<uint4*>(tile + (c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4));
-            uint4 v = *p;
-            const float4* t = reinterpret_cast<const float4*>(rope + (size_t)(pos0 + r) * 64 + c * 4);
-            const float4 t0 = __ldg(t), t1 = __ldg(t + 1);
+        for (int k = 0; k < 16; ++k, p += 1024) {
+            uint4 v = *reinterpret_cast<uint4*>(p);
             uint32_t w[4] = {v.x, v.y, v.z, v.w};
-            const float cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float x0 = __uint_as_float(w[e] << 16), x1 = __uint_as_float(w[e] & 0xffff0000u);
-                const float y0 = x0 * cs[2 * e] - x1 * cs[2 * e + 1];
-                const float y1 = x0 * cs[2 * e + 1] + x1 * cs[2 * e];
-                __nv_bfloat162 o = __floats2bfloat162_rn(y0, y1);
+                __nv_bfloat162 o = __floats2bfloat162_rn(x0 * cs[e] - x1 * sn[e], x0 * sn[e] + x1 * cs[e]);
                 w[e] = *reinterpret_cast<uint32_t*>(&o);
+                const float nc = cs[e] * st.cd[e] - sn[e] * st.sd[e];
+                sn[e] = sn[e] * st.cd[e] + cs[e] * st.sd[e];
+                cs[e] = nc;
             }
-            *p = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-    } else {  // rotate_half: pairs (d, d+64) sit at the same offset of the two boxes
+    } else {
+        // rotate_half: pairs (d, d+64) sit at the same offset of the two boxes; rows r0, r0+16, ...
+        const int cc = rt & 7, r0 = rt >> 3;
+        uint8_t* p = tile + r0 * 128 + ((cc ^ (r0 & 7)) << 4);
+        const float4* t = reinterpret_cast<const float4*>(rope + (size_t)min(pos0 + r0, S - 1) * 64 + cc * 8);
+        float cs[8], sn[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float4 v = __ldg(t + e);
+            cs[2 * e] = v.x; sn[2 * e] = v.y; cs[2 * e + 1] = v.z; sn[2 * e + 1] = v.w;
+        }
 #pragma unroll 2
-        for (int it = 0; it < 8; ++it) {
-            const int idx = it * 128 + rt, r = idx >> 3, cc = idx & 7;
-            if (pos0 + r >= S) continue;
-            uint4* p0 = reinterpret_cast<uint4*>(tile + r * 128 + ((cc ^ (r & 7)) << 4));
-            uint4* p1 = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p0) + HALF_BYTES);
-            uint4 a = *p0, b = *p1;
+        for (int k = 0; k < 8; ++k, p += 2048) {
+            uint4 a = *reinterpret_cast<uint4*>(p), b = *reinterpret_cast<uint4*>(p + HALF_BYTES);
             uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
-            const float4* t = reinterpret_cast<const float4*>(rope + (size_t)(pos0 + r) * 64 + cc * 8);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float4 cs = __ldg(t + e);  // pairs 2e, 2e+1 of this chunk
                 const float a0 = __uint_as_float(wa[e] << 16), a1 = __uint_as_float(wa[e] & 0xffff0000u);
                 const float b0 = __uint_as_float(wb[e] << 16), b1 = __uint_as_float(wb[e] & 0xffff0000u);
-                __nv_bfloat162 lo = __floats2bfloat162_rn(a0 * cs.x - b0 * cs.y, a1 * cs.z - b1 * cs.w);
-                __nv_bfloat162 hi = __floats2bfloat162_rn(b0 * cs.x + a0 * cs.y, b1 * cs.z + a1 * cs.w);
+                const float c0 = cs[2 * e], s0 = sn[2 * e], c1 = cs[2 * e + 1], s1 = sn[2 * e + 1];
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a0 * c0 - b0 * s0, a1 * c1 - b1 * s1);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(b0 * c0 + a0 * s0, b1 * c1 + a1 * s1);
                 wa[e] = *reinterpret_cast<uint32_t*>(&lo);
                 wb[e] = *reinterpret_cast<uint32_t*>(&hi);
             }
-            *p0 = make_uint4(wa[0], wa[1], wa[2], wa[3]);
-            *p1 = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float nc = cs[e] * st.cd[e] - sn[e] * st.sd[e];
+                sn[e] = sn[e] * st.cd[e] + cs[e] * st.sd[e];
+                cs[e] = nc;
+            }
+            *reinterpret_cast<uint4*>(p) = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+            *reinterpret_cast<uint4*>(p + HALF_BYTES) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
         }
     }
 }
@@ -300,7 +338,9 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-    if (warp == WARP_TMA) {
+    if (warp >= WARP_TMA) {
+      reg_dec<REGS_MISC>();
+      if (warp == WARP_TMA) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmQ)) : "memory");
@@ -336,7 +376,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
             }
         }
-    } else if (warp == WARP_MMA) {
+      } else if (warp == WARP_MMA) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             bool ok = wait_bar(ctx, use_rope ? Q_READY : Q_FULL, 0);
@@ -376,13 +416,17 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 mma_commit(bar(O_DONE));
             }
         }
+      }
     } else if (warp >= WARP_ROT0) {
         // ------------------------------------------------------------------ RoPE on Q and K tiles
+        reg_dec<REGS_ROPE>();
         if (use_rope) {
             const int rt = tid - WARP_ROT0 * 32;
+            RopeState st;
+            rope_init(st, a.rope, S, a.rope_mode, rt);
             bool ok = wait_bar(ctx, Q_FULL, 0);
             if (ok) {
-                rope_tile(smem + SMEM_Q, q0, S, a.rope, a.rope_mode, rt);
+                rope_tile(smem + SMEM_Q, q0, S, a.rope, a.rope_mode, rt, st);
                 fence_async_smem();
                 mbar_arrive(bar(Q_READY));
             }
@@ -390,13 +434,14 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 const int s = j % NSTAGE, it = j / NSTAGE;
                 ok = wait_bar(ctx, K_FULL + s, it & 1);
                 if (!ok) break;
-                rope_tile(smem + SMEM_K + s * TILE_BYTES, j * BN, S, a.rope, a.rope_mode, rt);
+                rope_tile(smem + SMEM_K + s * TILE_BYTES, j * BN, S, a.rope, a.rope_mode, rt, st);
                 fence_async_smem();
                 mbar_arrive(bar(K_READY + s));
             }
         }
     } else {
         // ------------------------------------------------------------------ softmax / correction / epilogue
+        reg_inc<REGS_SOFTMAX>();
         const int row = tid;                       // TMEM lane == query row of the tile
         const int row_g = q0 + row;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
@@ -450,17 +495,20 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             }
             const float neg_m = -m_ref;
             float rs = 0.f;
-            uint32_t pk[64];
 #pragma unroll
-            for (int c = 0; c < BN; c += 2) {
-                const float p0 = ex2(fmaf(__uint_as_float(sr[c]), a.scale_log2, neg_m));
-                const float p1 = ex2(fmaf(__uint_as_float(sr[c + 1]), a.scale_log2, neg_m));
-                rs += p0 + p1;
-                __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);   // key c in the low half
-                pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pp);
+            for (int ch = 0; ch < 4; ++ch) {      // 32 keys -> 16 packed columns per store
+                uint32_t pk[16];
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const float p0 = ex2(fmaf(__uint_as_float(sr[ch * 32 + c]), a.scale_log2, neg_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(sr[ch * 32 + c + 1]), a.scale_log2, neg_m));
+                    rs += p0 + p1;
+                    __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);   // even key in the low half
+                    pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pp);
+                }
+                tmem_st_x16(lane_addr + buf * BN + ch * 16, pk);
             }
             l += rs;
-            tmem_st_x64(lane_addr + buf * BN, pk);
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(bar(P_READY + buf));
