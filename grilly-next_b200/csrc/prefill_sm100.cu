@@ -2,22 +2,26 @@
 //
 // Replaces the S^2/(64*64) dispatch+barrier pairs of ops::flashAttention2
 // (cpp/src/ops/attention.cpp:125-141) and the per-(q,k) thread of flash-attention2-rope.glsl
-// by one launch in which a CTA owns a 128-row query tile of one (batch, head):
+// by one launch in which a CTA owns TWO 128-row query tiles (256 rows) of one (batch, head) and
+// streams the K/V tiles once for both:
 //
-//   warp 8      TMA producer: Q once, then K/V tiles (128 keys x 128 dims, two 64-column boxes,
-//               128-byte swizzle) into a 2-stage shared-memory ring, mbarrier complete_tx.
-//   warps 4-7   RoPE: rotate the Q tile and each K tile in place in shared memory (cos/sin from a
-//               device table), fence.proxy.async, hand the tile to the MMA warp.
-//   warp 9      one thread issues tcgen05.mma: S = Q K^T (A,B from shared memory, K-major) into a
-//               double-buffered TMEM accumulator, then O += P V with P read from TMEM and V as an
-//               MN-major shared-memory operand; tcgen05.commit signals mbarriers.
-//   warps 0-3   one thread per query row: tcgen05.ld of the S row, causal / length predicate,
-//               fp32 online softmax in the exp2 domain, P written back to TMEM as packed bf16,
-//               O rescaled in TMEM only when the row maximum moved by more than 2^8 (the stale
-//               maximum stays the reference, so the result is exact), final O / l to global memory.
+//   warp 12      TMA producer: both Q tiles once, then K/V tiles (128 keys x 128 dims, two
+//                64-column boxes, 128-byte swizzle) into a 2-stage shared-memory ring.
+//   warps 8-11   RoPE: rotate each K tile in place in shared memory, fence.proxy.async, hand the
+//                tile to the MMA warp.  (Each softmax warpgroup rotates its own Q tile once.)
+//   warp 13      one thread issues tcgen05.mma: S_t = Q_t K^T (A,B from shared memory, K-major)
+//                into TMEM, then O_t += P_t V with P_t read from TMEM and V as an MN-major
+//                shared-memory operand; issue order PV0_j, QK0_j+1, PV1_j, QK1_j+1 so that one
+//                warpgroup's softmax overlaps the other's tensor work.
+//   warps 0-3 / 4-7   softmax warpgroup of query tile 0 / 1, one thread per query row:
+//                tcgen05.ld of the S row, causal / length predicate, fp32 online softmax in the
+//                exp2 domain, P written back to TMEM as packed bf16, O rescaled in TMEM only when
+//                the row maximum moved by more than 2^8 (the stale maximum stays the reference,
+//                so the result is exact), final O / l to global memory.
 //
-// TMEM columns: S0 [0,128) S1 [128,256) O [256,384); P_j overlays the first 64 columns of S_j.
-// Every mbarrier wait is bounded; on expiry the CTA records an error, drains and returns.
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t overlays the first 64
+// columns of S_t.  Every mbarrier wait is bounded; on expiry the CTA records an error, drains
+// its copies and returns.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -27,18 +31,19 @@ namespace grl {
 
 namespace sm100 {
 
-constexpr int BM = 128;            // query rows per CTA
+constexpr int BM = 128;            // query rows per tile (TMEM lanes)
+constexpr int NQ = 2;              // query tiles per CTA
 constexpr int BN = 128;            // keys per tile
 constexpr int HD = 128;            // head_dim
 constexpr int NSTAGE = 2;
 constexpr int HALF_BYTES = BM * 64 * 2;     // one 64-column box: 16 KiB
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KiB
-constexpr int kThreads = 384;   // three warpgroups: softmax | RoPE | TMA + MMA (+2 idle warps)
-constexpr int WARP_ROT0 = 4, WARP_TMA = 8, WARP_MMA = 9;
-// Register budget per warpgroup (setmaxnreg): the softmax threads hold a whole 128-column S row.
-constexpr int REGS_SOFTMAX = 232, REGS_ROPE = 112, REGS_MISC = 48;
+constexpr int kThreads = 512;      // four warpgroups: softmax 0 | softmax 1 | RoPE | TMA + MMA (+2 idle warps)
+constexpr int WARP_ROT0 = 8, WARP_TMA = 12, WARP_MMA = 13;
+// Register budget per warpgroup (setmaxnreg); 2*128*192 + 128*72 + 128*56 = 65536.
+constexpr int REGS_SOFTMAX = 192, REGS_ROPE = 72, REGS_MISC = 56;
 constexpr int SMEM_Q = 0;
-constexpr int SMEM_K = SMEM_Q + TILE_BYTES;
+constexpr int SMEM_K = SMEM_Q + NQ * TILE_BYTES;
 constexpr int SMEM_V = SMEM_K + NSTAGE * TILE_BYTES;
 constexpr int SMEM_BAR = SMEM_V + NSTAGE * TILE_BYTES;
 constexpr int SMEM_TOTAL = SMEM_BAR + 256 + 1024;  // + barrier block + alignment slack
@@ -46,9 +51,9 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TMEM_O = 256;
 constexpr long long kWaitLimitCycles = 2000000000LL;  // ~1 s at 2 GHz
 
-enum Bar { Q_FULL = 0, Q_READY, K_FULL, K_READY = K_FULL + NSTAGE, K_EMPTY = K_READY + NSTAGE,
-           V_FULL = K_EMPTY + NSTAGE, V_EMPTY = V_FULL + NSTAGE, S_FULL = V_EMPTY + NSTAGE,
-           P_READY = S_FULL + 2, O_DONE = P_READY + 2, NUM_BARS };
+enum Bar { Q_FULL = 0, Q_READY = Q_FULL + NQ, K_FULL = Q_READY + NQ, K_READY = K_FULL + NSTAGE,
+           K_EMPTY = K_READY + NSTAGE, V_FULL = K_EMPTY + NSTAGE, V_EMPTY = V_FULL + NSTAGE,
+           S_FULL = V_EMPTY + NSTAGE, P_READY = S_FULL + NQ, O_DONE = P_READY + NQ, NUM_BARS = O_DONE + NQ };
 static_assert(NUM_BARS * 8 + 16 <= 256, "barrier block");
 
 struct Args {
@@ -281,16 +286,16 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     uint8_t* smem = smem_raw + (base_addr - raw_addr);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_qt = gridDim.x;
-    const int qt = a.causal ? (n_qt - 1 - (int)blockIdx.x) : (int)blockIdx.x;  // longest tiles first
+    const int n_qp = gridDim.x;                                                  // query tile pairs
+    const int qp = a.causal ? (n_qp - 1 - (int)blockIdx.x) : (int)blockIdx.x;   // longest first
     const int bh = blockIdx.y, b = bh / a.H;
     const int S = a.S;
-    const int q0 = qt * BM;
+    const int q0 = qp * (NQ * BM);
     const int len = a.seq_lens ? min(a.seq_lens[b], S) : S;
     TOut* O = reinterpret_cast<TOut*>(a.o) + (size_t)bh * S * HD;
 
     if (q0 >= len) {  // padded query rows are defined as zero
-        const int rows = min(BM, S - q0);
+        const int rows = min(NQ * BM, S - q0);
         for (int idx = tid; idx < rows * HD; idx += kThreads) store_from_float<TOut>(O + (size_t)q0 * HD + idx, 0.f);
         return;
     }
@@ -299,19 +304,30 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (__syncthreads_or(failed)) return;
     }
 
-    const int k_end = a.causal ? min(len, q0 + BM) : len;
-    const int n_kt = (k_end + BN - 1) / BN;
+    // kv tiles that query tile t attends to (0 when all of its rows are padding)
+    int n_kt[NQ];
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) {
+        const int qt0 = q0 + t * BM;
+        const int k_end = a.causal ? min(len, qt0 + BM) : len;
+        n_kt[t] = (qt0 < len) ? (k_end + BN - 1) / BN : 0;
+    }
+    const int n_total = max(n_kt[0], n_kt[1]);
     const bool use_rope = a.rope_mode != GRL_ROPE_NONE;
 
-    uint64_t* bar_mem = reinterpret_cast<uint64_t*>(smem + SMEM_BAR);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SMEM_BAR + NUM_BARS * 8);
     int* abort_flag = reinterpret_cast<int*>(smem + SMEM_BAR + NUM_BARS * 8 + 4);
     Ctx ctx{base_addr + SMEM_BAR, abort_flag, a.status};
     auto bar = [&](int i) { return ctx.bars + (uint32_t)i * 8u; };
 
     if (tid == 0) {
-        mbar_init(bar(Q_FULL), 1);
-        mbar_init(bar(Q_READY), 128);
+        for (int t = 0; t < NQ; ++t) {
+            mbar_init(bar(Q_FULL + t), 1);
+            mbar_init(bar(Q_READY + t), 128);
+            mbar_init(bar(S_FULL + t), 1);
+            mbar_init(bar(P_READY + t), 128);
+            mbar_init(bar(O_DONE + t), 1);
+        }
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(bar(K_FULL + s), 1);
             mbar_init(bar(K_READY + s), 128);
@@ -319,11 +335,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             mbar_init(bar(V_FULL + s), 1);
             mbar_init(bar(V_EMPTY + s), 1);
         }
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(bar(S_FULL + s), 1);
-            mbar_init(bar(P_READY + s), 128);
-        }
-        mbar_init(bar(O_DONE), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
@@ -346,29 +357,33 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmQ)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
-            mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
-            tma_load_3d(base_addr + SMEM_Q, &tmQ, 0, q0, bh, bar(Q_FULL));
-            tma_load_3d(base_addr + SMEM_Q + HALF_BYTES, &tmQ, 64, q0, bh, bar(Q_FULL));
-            int issued = 0;
+            auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, int row, int full_bar) {
+                mbar_expect_tx(bar(full_bar), TILE_BYTES);
+                tma_load_3d(dst, tm, 0, row, bh, bar(full_bar));
+                tma_load_3d(dst + HALF_BYTES, tm, 64, row, bh, bar(full_bar));
+            };
+            // first K tile between the two Q tiles: QK(0,0) needs Q0 and K0 only
+            load_tile(base_addr + SMEM_Q, &tmQ, q0, Q_FULL);
+            int issued = 0;       // K/V tile loads issued so far (K_j = 2j, V_j = 2j+1)
             bool ok = true;
-            for (int j = 0; j < n_kt && ok; ++j) {
+            for (int j = 0; j < n_total && ok; ++j) {
                 const int s = j % NSTAGE, it = j / NSTAGE;
                 if (it > 0) ok = wait_bar(ctx, K_EMPTY + s, (it - 1) & 1);
                 if (!ok) break;
-                mbar_expect_tx(bar(K_FULL + s), TILE_BYTES);
-                tma_load_3d(base_addr + SMEM_K + s * TILE_BYTES, &tmK, 0, j * BN, bh, bar(K_FULL + s));
-                tma_load_3d(base_addr + SMEM_K + s * TILE_BYTES + HALF_BYTES, &tmK, 64, j * BN, bh, bar(K_FULL + s));
+                load_tile(base_addr + SMEM_K + s * TILE_BYTES, &tmK, j * BN, K_FULL + s);
+                issued = 2 * j + 1;
+                if (j == 0 && n_kt[1] > 0) load_tile(base_addr + SMEM_Q + TILE_BYTES, &tmQ, q0 + BM, Q_FULL + 1);
                 if (it > 0) ok = wait_bar(ctx, V_EMPTY + s, (it - 1) & 1);
-                if (!ok) { issued = 2 * j + 1; break; }
-                mbar_expect_tx(bar(V_FULL + s), TILE_BYTES);
-                tma_load_3d(base_addr + SMEM_V + s * TILE_BYTES, &tmV, 0, j * BN, bh, bar(V_FULL + s));
-                tma_load_3d(base_addr + SMEM_V + s * TILE_BYTES + HALF_BYTES, &tmV, 64, j * BN, bh, bar(V_FULL + s));
+                if (!ok) break;
+                load_tile(base_addr + SMEM_V + s * TILE_BYTES, &tmV, j * BN, V_FULL + s);
                 issued = 2 * j + 2;
             }
             if (*ctx.abort) {
                 // Drain: copies already issued must land before the CTA's shared memory is released.
                 const long long t0 = clock64();
                 while (!mbar_try_wait(bar(Q_FULL), 0) && clock64() - t0 < kWaitLimitCycles) {}
+                if (issued >= 1 && n_kt[1] > 0)
+                    while (!mbar_try_wait(bar(Q_FULL + 1), 0) && clock64() - t0 < kWaitLimitCycles) {}
                 for (int x = max(0, issued - 2 * NSTAGE); x < issued; ++x) {
                     const int j = x >> 1, s = j % NSTAGE, it = j / NSTAGE;
                     const uint32_t bb = bar(((x & 1) ? V_FULL : K_FULL) + s);
@@ -379,58 +394,62 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       } else if (warp == WARP_MMA) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
-            bool ok = wait_bar(ctx, use_rope ? Q_READY : Q_FULL, 0);
-            tc_fence_after();
-            auto issue_qk = [&](int j) -> bool {
+            bool ok = true;
+            // S_t = Q_t K_j^T; releases the K stage after the last tile that reads it
+            auto issue_qk = [&](int t, int j) -> bool {
                 const int s = j % NSTAGE, it = j / NSTAGE;
                 if (!wait_bar(ctx, (use_rope ? K_READY : K_FULL) + s, it & 1)) return false;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(j & 1) * BN;
+                const uint32_t d_tmem = tmem_base + (uint32_t)t * BN;
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
                     const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-                    mma_ss(d_tmem, make_desc(base_addr + SMEM_Q + off, 16, 1024),
+                    mma_ss(d_tmem, make_desc(base_addr + SMEM_Q + t * TILE_BYTES + off, 16, 1024),
                            make_desc(base_addr + SMEM_K + s * TILE_BYTES + off, 16, 1024), IDESC_QK, ks > 0);
                 }
-                mma_commit(bar(S_FULL + (j & 1)));
-                mma_commit(bar(K_EMPTY + s));
+                mma_commit(bar(S_FULL + t));
+                const bool last_reader = (t == 1) || !(j < n_kt[1]);
+                if (last_reader) mma_commit(bar(K_EMPTY + s));
                 return true;
             };
-            if (ok) ok = issue_qk(0);
-            for (int j = 0; j < n_kt && ok; ++j) {
+            for (int t = 0; t < NQ && ok; ++t) {
+                if (n_kt[t] == 0) continue;
+                ok = wait_bar(ctx, (use_rope ? Q_READY : Q_FULL) + t, 0);
+                if (ok) ok = issue_qk(t, 0);
+            }
+            for (int j = 0; j < n_total && ok; ++j) {
                 const int s = j % NSTAGE, it = j / NSTAGE;
-                if (j + 1 < n_kt) ok = issue_qk(j + 1);
-                if (ok) ok = wait_bar(ctx, P_READY + (j & 1), (j >> 1) & 1);
-                if (ok) ok = wait_bar(ctx, V_FULL + s, it & 1);
-                if (!ok) break;
-                tc_fence_after();
+                for (int t = 0; t < NQ && ok; ++t) {
+                    if (j >= n_kt[t]) continue;
+                    ok = wait_bar(ctx, P_READY + t, j & 1);
+                    if (ok) ok = wait_bar(ctx, V_FULL + s, it & 1);
+                    if (!ok) break;
+                    tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {
-                    // A: P_j in TMEM, 16 keys = 8 packed columns per step.  B: 16 key rows of V = 2 KiB
-                    // per step; MN-major: 64-column boxes HALF_BYTES apart (LBO), 8-row groups 1 KiB apart (SBO).
-                    mma_ts(tmem_base + TMEM_O, tmem_base + (uint32_t)(j & 1) * BN + ks * 8,
-                           make_desc(base_addr + SMEM_V + s * TILE_BYTES + ks * 2048, HALF_BYTES, 1024), IDESC_PV,
-                           (j > 0 || ks > 0));
+                    for (int ks = 0; ks < BN / 16; ++ks) {
+                        // A: P_t in TMEM, 16 keys = 8 packed columns per step.  B: 16 key rows of V = 2 KiB per
+                        // step; MN-major: 64-column boxes HALF_BYTES apart (LBO), 8-row groups 1 KiB apart (SBO).
+                        mma_ts(tmem_base + TMEM_O + (uint32_t)t * HD, tmem_base + (uint32_t)t * BN + ks * 8,
+                               make_desc(base_addr + SMEM_V + s * TILE_BYTES + ks * 2048, HALF_BYTES, 1024), IDESC_PV,
+                               (j > 0 || ks > 0));
+                    }
+                    const bool last_reader = (t == 1) || !(j < n_kt[1]);
+                    if (last_reader) mma_commit(bar(V_EMPTY + s));
+                    mma_commit(bar(O_DONE + t));
+                    if (j + 1 < n_kt[t]) ok = issue_qk(t, j + 1);   // overwrites S_t / P_t: in order after PV(t, j)
                 }
-                mma_commit(bar(V_EMPTY + s));
-                mma_commit(bar(O_DONE));
             }
         }
       }
     } else if (warp >= WARP_ROT0) {
-        // ------------------------------------------------------------------ RoPE on Q and K tiles
+        // ------------------------------------------------------------------ RoPE on the K tiles
         reg_dec<REGS_ROPE>();
         if (use_rope) {
             const int rt = tid - WARP_ROT0 * 32;
             RopeState st;
             rope_init(st, a.rope, S, a.rope_mode, rt);
-            bool ok = wait_bar(ctx, Q_FULL, 0);
-            if (ok) {
-                rope_tile(smem + SMEM_Q, q0, S, a.rope, a.rope_mode, rt, st);
-                fence_async_smem();
-                mbar_arrive(bar(Q_READY));
-            }
-            for (int j = 0; j < n_kt && ok; ++j) {
+            bool ok = true;
+            for (int j = 0; j < n_total && ok; ++j) {
                 const int s = j % NSTAGE, it = j / NSTAGE;
                 ok = wait_bar(ctx, K_FULL + s, it & 1);
                 if (!ok) break;
@@ -442,89 +461,119 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     } else {
         // ------------------------------------------------------------------ softmax / correction / epilogue
         reg_inc<REGS_SOFTMAX>();
-        const int row = tid;                       // TMEM lane == query row of the tile
-        const int row_g = q0 + row;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-        float m_ref = -INFINITY, l = 0.f;
-        bool ok = true;
-        for (int j = 0; j < n_kt && ok; ++j) {
-            const int buf = j & 1, k0 = j * BN;
-            ok = __all_sync(0xffffffffu, wait_bar(ctx, S_FULL + buf, (j >> 1) & 1));  // leave as a whole warp
-            if (!ok) break;
-            tc_fence_after();
-            uint32_t sr[128];
-            tmem_ld_x128_sync(lane_addr + buf * BN, sr);
-            const bool need_mask = (a.causal && k0 + BN - 1 > q0) || (k0 + BN > len);  // CTA-uniform
-            float mx = -INFINITY;
-            if (need_mask) {
-                const int limit = min(a.causal ? row_g : 0x7fffffff, len - 1) - k0;  // last visible column
+        const int t = warp >> 2;                   // query tile of this warpgroup
+        const int row = tid & 127;                 // TMEM lane == query row of the tile
+        const int qt0 = q0 + t * BM;
+        const int row_g = qt0 + row;
+        const int n = n_kt[t];
+        if (n == 0) {
+            // every row of this tile is padding: zeros (rows inside the tensor only)
+            if (row_g < S) {
+                uint32_t z[32];
 #pragma unroll
-                for (int c = 0; c < BN; ++c) {
-                    const float v = (c <= limit) ? __uint_as_float(sr[c]) : -INFINITY;
-                    sr[c] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
-                }
-            } else {
+                for (int i = 0; i < 32; ++i) z[i] = 0u;
 #pragma unroll
-                for (int c = 0; c < BN; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+                for (int ch = 0; ch < 4; ++ch) store_row_chunk<TOut>(O + (size_t)row_g * HD + ch * 32, z, 0.f);
             }
-            const float m_new = fmaxf(m_ref, mx * a.scale_log2);
-            bool o_waited = false;
-            if (j == 0) {
-                m_ref = (m_new == -INFINITY) ? 0.f : m_new;
-            } else {
-                const bool need = m_new > m_ref + 8.f;
-                if (__any_sync(0xffffffffu, need)) {
-                    ok = __all_sync(0xffffffffu, wait_bar(ctx, O_DONE, (j - 1) & 1));  // PV_{j-1} wrote O
-                    if (!ok) break;
-                    o_waited = true;
-                    tc_fence_after();
-                    const float f = need ? ex2(m_ref - m_new) : 1.f;
-                    if (need) m_ref = m_new;
-                    l *= f;
+        } else {
+            const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+            const uint32_t s_addr = lane_addr + (uint32_t)t * BN, o_addr = lane_addr + TMEM_O + (uint32_t)t * HD;
+            bool ok = true;
+            if (use_rope) {   // this warpgroup rotates its own Q tile
+                RopeState st;
+                rope_init(st, a.rope, S, a.rope_mode, row);
+                ok = __all_sync(0xffffffffu, wait_bar(ctx, Q_FULL + t, 0));
+                if (ok) {
+                    rope_tile(smem + SMEM_Q + t * TILE_BYTES, qt0, S, a.rope, a.rope_mode, row, st);
+                    fence_async_smem();
+                    mbar_arrive(bar(Q_READY + t));
+                }
+            }
+            float m_ref = -INFINITY, l = 0.f;
+            for (int j = 0; j < n && ok; ++j) {
+                const int k0 = j * BN;
+                ok = __all_sync(0xffffffffu, wait_bar(ctx, S_FULL + t, j & 1));  // leave as a whole warp
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t sr[128];
+                {   // two 64-column loads: a single x128 load exceeds the kernel-wide register target of a 512-thread CTA
+                    uint32_t (&lo)[64] = *reinterpret_cast<uint32_t(*)[64]>(&sr[0]);
+                    uint32_t (&hi)[64] = *reinterpret_cast<uint32_t(*)[64]>(&sr[64]);
+                    tmem_ld_x64_sync(s_addr, lo);
+                    tmem_ld_x64_sync(s_addr + 64, hi);
+                }
+                const bool need_mask = (a.causal && k0 + BN - 1 > qt0) || (k0 + BN > len);  // warpgroup-uniform
+                if (need_mask) {
+                    const int limit = min(a.causal ? row_g : 0x7fffffff, len - 1) - k0;  // last visible column
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
-                        uint32_t orow[32];
-                        tmem_ld_x32_sync(lane_addr + TMEM_O + ch * 32, orow);
+                    for (int c = 0; c < BN; ++c)
+                        if (c > limit) sr[c] = 0xff800000u;   // -inf
+                }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * f);
-                        tmem_st_x32(lane_addr + TMEM_O + ch * 32, orow);
+                for (int c = 0; c < BN; c += 4) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(sr[c + e]));
+                }
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                const float m_new = fmaxf(m_ref, mx * a.scale_log2);
+                bool o_waited = false;
+                if (j == 0) {
+                    m_ref = (m_new == -INFINITY) ? 0.f : m_new;
+                } else {
+                    const bool need = m_new > m_ref + 8.f;
+                    if (__any_sync(0xffffffffu, need)) {
+                        ok = __all_sync(0xffffffffu, wait_bar(ctx, O_DONE + t, (j - 1) & 1));  // PV(t, j-1) wrote O
+                        if (!ok) break;
+                        o_waited = true;
+                        tc_fence_after();
+                        const float f = need ? ex2(m_ref - m_new) : 1.f;
+                        if (need) m_ref = m_new;
+                        l *= f;
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {
+                            uint32_t orow[32];
+                            tmem_ld_x32_sync(o_addr + ch * 32, orow);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * f);
+                            tmem_st_x32(o_addr + ch * 32, orow);
+                        }
+                        tmem_st_wait();
                     }
-                    tmem_st_wait();
                 }
-            }
-            const float neg_m = -m_ref;
-            float rs = 0.f;
+                const float neg_m = -m_ref;
+                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {      // 32 keys -> 16 packed columns per store
-                uint32_t pk[16];
+                for (int ch = 0; ch < 4; ++ch) {      // 32 keys -> 16 packed columns per store
+                    uint32_t pk[16];
 #pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    const float p0 = ex2(fmaf(__uint_as_float(sr[ch * 32 + c]), a.scale_log2, neg_m));
-                    const float p1 = ex2(fmaf(__uint_as_float(sr[ch * 32 + c + 1]), a.scale_log2, neg_m));
-                    rs += p0 + p1;
-                    __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);   // even key in the low half
-                    pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pp);
+                    for (int c = 0; c < 32; c += 2) {
+                        const float p0 = ex2(fmaf(__uint_as_float(sr[ch * 32 + c]), a.scale_log2, neg_m));
+                        const float p1 = ex2(fmaf(__uint_as_float(sr[ch * 32 + c + 1]), a.scale_log2, neg_m));
+                        rs4[(c >> 1) & 3] += p0 + p1;
+                        __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);   // even key in the low half
+                        pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pp);
+                    }
+                    tmem_st_x16(s_addr + ch * 16, pk);
                 }
-                tmem_st_x16(lane_addr + buf * BN + ch * 16, pk);
+                l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(bar(P_READY + t));
+                if (j >= 1 && !o_waited) ok = wait_bar(ctx, O_DONE + t, (j - 1) & 1);  // keep the phase in step
+                ok = __all_sync(0xffffffffu, ok);
             }
-            l += rs;
-            tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(bar(P_READY + buf));
-            if (j >= 1 && !o_waited) ok = wait_bar(ctx, O_DONE, (j - 1) & 1);  // keep the phase in step
-            ok = __all_sync(0xffffffffu, ok);
-        }
-        if (ok) ok = __all_sync(0xffffffffu, wait_bar(ctx, O_DONE, (n_kt - 1) & 1));
-        if (ok) {
-            tc_fence_after();
-            const bool zero = (row_g >= len) || !(l > 0.f);
-            const float inv = zero ? 0.f : 1.f / l;
+            if (ok) ok = __all_sync(0xffffffffu, wait_bar(ctx, O_DONE + t, (n - 1) & 1));
+            if (ok) {
+                tc_fence_after();
+                const bool zero = (row_g >= len) || !(l > 0.f);
+                const float inv = zero ? 0.f : 1.f / l;
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-                uint32_t orow[32];
-                tmem_ld_x32_sync(lane_addr + TMEM_O + ch * 32, orow);   // warp-collective: no divergence here
-                if (row_g < S) store_row_chunk<TOut>(O + (size_t)row_g * HD + ch * 32, orow, inv);
+                for (int ch = 0; ch < 4; ++ch) {
+                    uint32_t orow[32];
+                    tmem_ld_x32_sync(o_addr + ch * 32, orow);   // warp-collective: no divergence here
+                    if (row_g < S) store_row_chunk<TOut>(O + (size_t)row_g * HD + ch * 32, orow, inv);
+                }
             }
         }
     }
@@ -592,7 +641,7 @@ int flash_fwd_sm100(grl_device* dev, const grl_flash_params* p, float scale, con
     a.B = p->batch; a.H = p->heads; a.S = p->seq_len;
     a.causal = p->causal; a.rope_mode = p->rope_mode;
     a.scale_log2 = scale * 1.4426950408889634f;
-    dim3 grid((p->seq_len + BM - 1) / BM, BH);
+    dim3 grid((p->seq_len + NQ * BM - 1) / (NQ * BM), BH);
     if (p->out_dtype == GRL_F32) {
         auto kern = flash_fwd_sm100_kernel<float>;
         GRL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
