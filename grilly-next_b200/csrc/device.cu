@@ -237,7 +237,7 @@ static int check_kernel_status(grl_device* dev) {
     if (st[0] == 0) return GRL_OK;
     GRL_CUDA(cudaMemsetAsync(dev->d_status, 0, sizeof(st), dev->stream));
     return set_error(st[0] == GRL_ERR_TIMEOUT ? GRL_ERR_TIMEOUT : GRL_ERR_KERNEL,
-                     "kernel reported failure %d (wait %d, block %d,%d)", st[0], st[1], st[2], st[3]);
+                     "kernel reported failure %d (stuck barrier mask 0x%x, first block %d,%d)", st[0], st[1], st[2], st[3]);
 }
 
 int grl_sync(grl_device* dev, uint64_t timeout_ns) {

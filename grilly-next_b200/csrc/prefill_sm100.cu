@@ -5,15 +5,15 @@
 // by one launch in which a CTA owns TWO 128-row query tiles (256 rows) of one (batch, head) and
 // streams the K/V tiles once for both:
 //
-//   warp 12      TMA producer: both Q tiles once, then K/V tiles (128 keys x 128 dims, two
+//   warp 1       TMA producer: both Q tiles once, then K/V tiles (128 keys x 128 dims, two
 //                64-column boxes, 128-byte swizzle) into a 2-stage shared-memory ring.
-//   warps 8-11   RoPE: rotate each K tile in place in shared memory, fence.proxy.async, hand the
+//   warps 12-15  RoPE: rotate each K tile in place in shared memory, fence.proxy.async, hand the
 //                tile to the MMA warp.  (Each softmax warpgroup rotates its own Q tile once.)
-//   warp 13      one thread issues tcgen05.mma: S_t = Q_t K^T (A,B from shared memory, K-major)
+//   warp 0       one thread issues tcgen05.mma: S_t = Q_t K^T (A,B from shared memory, K-major)
 //                into TMEM, then O_t += P_t V with P_t read from TMEM and V as an MN-major
 //                shared-memory operand; issue order PV0_j, QK0_j+1, PV1_j, QK1_j+1 so that one
 //                warpgroup's softmax overlaps the other's tensor work.
-//   warps 0-3 / 4-7   softmax warpgroup of query tile 0 / 1, one thread per query row:
+//   warps 4-7 / 8-11  softmax warpgroup of query tile 0 / 1, one thread per query row:
 //                tcgen05.ld of the S row, causal / length predicate, fp32 online softmax in the
 //                exp2 domain, P written back to TMEM as packed bf16, O rescaled in TMEM only when
 //                the row maximum moved by more than 2^8 (the stale maximum stays the reference,
@@ -38,8 +38,8 @@ constexpr int HD = 128;            // head_dim
 constexpr int NSTAGE = 2;
 constexpr int HALF_BYTES = BM * 64 * 2;     // one 64-column box: 16 KiB
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KiB
-constexpr int kThreads = 512;      // four warpgroups: softmax 0 | softmax 1 | RoPE | TMA + MMA (+2 idle warps)
-constexpr int WARP_ROT0 = 8, WARP_TMA = 12, WARP_MMA = 13;
+constexpr int kThreads = 512;      // four warpgroups: MMA + TMA (+2 idle warps) | softmax 0 | softmax 1 | RoPE
+constexpr int WARP_MMA = 0, WARP_TMA = 1, WARP_SOFTMAX0 = 4, WARP_ROT0 = 12;   // warps 2-3 idle
 // Register budget per warpgroup (setmaxnreg); 2*128*192 + 128*72 + 128*56 = 65536.
 constexpr int REGS_SOFTMAX = 192, REGS_ROPE = 72, REGS_MISC = 56;
 constexpr int SMEM_Q = 0;
@@ -60,7 +60,7 @@ struct Args {
     void* o;
     const int32_t* seq_lens;
     const float2* rope;   // (S, 64) cos/sin, or NULL
-    int32_t* status;      // device int32[4]: [0] error code, [1] barrier id, [2] block x, [3] block y
+    int32_t* status;      // device int32[4]: [0] error code, [1] mask of stuck barriers, [2] block x, [3] block y
     int B, H, S;
     int causal, rope_mode;
     float scale_log2;
@@ -126,6 +126,34 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Descriptor halves: the high word (stride offset, version, swizzle) is constant per operand kind and
+// the low word is (address >> 4) | (leading offset >> 4) << 16, so stepping through a tile is one
+// 32-bit add.  The single issuing thread must spend only a few instructions per MMA: a 128x128x16
+// MMA occupies the tensor pipe for 64 cycles, and descriptor arithmetic done per instruction in
+// 64-bit was measured to hold the pipe at less than half rate.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
+}
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1 KiB, version 1, 128-byte swizzle
+template <bool ACC>
+__device__ __forceinline__ void mma_ss2(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "n"(ACC ? 1 : 0)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ts2(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -134,11 +162,32 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+
+// Optional in-kernel timeline (compile with -DGRL_TIMELINE): one thread per role of CTA (0,0)
+// stamps clock64() at its pipeline events; read back with grl_debug_timeline().
+#ifdef GRL_TIMELINE
+constexpr int TL_ROLES = 5, TL_SLOTS = 512;   // roles: 0 softmax0, 1 softmax1, 2 rope, 3 tma, 4 mma
+__device__ unsigned long long g_timeline[TL_ROLES * TL_SLOTS];
+__device__ unsigned int g_timeline_n[TL_ROLES];
+__device__ int g_dbg_flags;   // experiment switches: 1 = softmax skips its math, 2 = softmax skips only the exp/pack/store phase
+#define DBG_FLAG(x) (g_dbg_flags & (x))
+#define TL_DECL(role, active) const int tl_role = (role); const bool tl_on = (active) && blockIdx.x == GRL_TIMELINE && blockIdx.y == 0; int tl_i = 0;
+#define TL(tag) do { if (tl_on && tl_i < TL_SLOTS) { g_timeline[tl_role * TL_SLOTS + tl_i] = ((unsigned long long)(tag) << 48) | (clock64() & 0xffffffffffffULL); ++tl_i; g_timeline_n[tl_role] = tl_i; } } while (0)
+#else
+#define DBG_FLAG(x) 0
+#define TL_DECL(role, active)
+#define TL(tag) do {} while (0)
+#endif
 
 struct Ctx {
     uint32_t bars;          // shared address of barrier 0
@@ -147,19 +196,29 @@ struct Ctx {
 };
 
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out).
+// The inner polls are back to back (a hop through an mbarrier is on the critical path of every
+// tile); the abort flag and the clock are looked at once per 32 polls.
 __device__ __forceinline__ bool wait_bar(const Ctx& c, int bar, uint32_t parity) {
     const uint32_t addr = c.bars + bar * 8;
     if (mbar_try_wait(addr, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-        if (mbar_try_wait(addr, parity)) return true;
-        if (*c.abort) return false;
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(addr, parity)) return true;
+        if (*c.abort) {
+            if (c.status) atomicOr(reinterpret_cast<unsigned int*>(c.status) + 1, 1u << bar);
+            return false;
+        }
         if (clock64() - t0 > kWaitLimitCycles) {
             *c.abort = 1;
-            if (c.status && atomicCAS(c.status, 0, GRL_ERR_TIMEOUT) == 0) {
-                c.status[1] = bar;
-                c.status[2] = blockIdx.x;
-                c.status[3] = blockIdx.y;
+            if (c.status) {
+                // [0] error code, [1] bit mask of the barriers that were being waited on, [2],[3] first CTA
+                atomicOr(reinterpret_cast<unsigned int*>(c.status) + 1, 1u << bar);
+                if (atomicCAS(c.status, 0, GRL_ERR_TIMEOUT) == 0) {
+                    c.status[2] = blockIdx.x | (parity << 16) | (threadIdx.x << 20);
+                    c.status[3] = blockIdx.y;
+                }
             }
             return false;
         }
@@ -198,19 +257,29 @@ __device__ __forceinline__ void rope_tile(uint8_t* tile, int pos0, int S, const 
         uint8_t* p = tile + (c >> 3) * HALF_BYTES + r0 * 128 + (((c & 7) ^ r0) << 4);
         const float4* t = reinterpret_cast<const float4*>(rope + (size_t)min(pos0 + r0, S - 1) * 64 + c * 4);
         const float4 t0 = __ldg(t), t1 = __ldg(t + 1);
-        float cs[4] = {t0.x, t0.z, t1.x, t1.z}, sn[4] = {t0.y, t0.w, t1.y, t1.w};
+        // two pairs per packed operation: C = (c_e, c_e+1), S = (s_e, s_e+1)
+        float2 C[2] = {make_float2(t0.x, t0.z), make_float2(t1.x, t1.z)};
+        float2 Sn[2] = {make_float2(t0.y, t0.w), make_float2(t1.y, t1.w)};
+        const float2 Cd[2] = {make_float2(st.cd[0], st.cd[1]), make_float2(st.cd[2], st.cd[3])};
+        const float2 Sd[2] = {make_float2(st.sd[0], st.sd[1]), make_float2(st.sd[2], st.sd[3])};
+        const float2 Sdn[2] = {make_float2(-st.sd[0], -st.sd[1]), make_float2(-st.sd[2], -st.sd[3])};
 #pragma unroll 4
         for (int k = 0; k < 16; ++k, p += 1024) {
             uint4 v = *reinterpret_cast<uint4*>(p);
             uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float x0 = __uint_as_float(w[e] << 16), x1 = __uint_as_float(w[e] & 0xffff0000u);
-                __nv_bfloat162 o = __floats2bfloat162_rn(x0 * cs[e] - x1 * sn[e], x0 * sn[e] + x1 * cs[e]);
-                w[e] = *reinterpret_cast<uint32_t*>(&o);
-                const float nc = cs[e] * st.cd[e] - sn[e] * st.sd[e];
-                sn[e] = sn[e] * st.cd[e] + cs[e] * st.sd[e];
-                cs[e] = nc;
+            for (int h = 0; h < 2; ++h) {
+                const float2 X0 = make_float2(__uint_as_float(w[2 * h] << 16), __uint_as_float(w[2 * h + 1] << 16));
+                const float2 X1 = make_float2(__uint_as_float(w[2 * h] & 0xffff0000u), __uint_as_float(w[2 * h + 1] & 0xffff0000u));
+                const float2 Snn = make_float2(-Sn[h].x, -Sn[h].y);
+                const float2 Y0 = __ffma2_rn(X1, Snn, __fmul2_rn(X0, C[h]));      // x0 c - x1 s
+                const float2 Y1 = __ffma2_rn(X1, C[h], __fmul2_rn(X0, Sn[h]));    // x0 s + x1 c
+                __nv_bfloat162 o0 = __floats2bfloat162_rn(Y0.x, Y1.x), o1 = __floats2bfloat162_rn(Y0.y, Y1.y);
+                w[2 * h] = *reinterpret_cast<uint32_t*>(&o0);
+                w[2 * h + 1] = *reinterpret_cast<uint32_t*>(&o1);
+                const float2 nC = __ffma2_rn(Sn[h], Sdn[h], __fmul2_rn(C[h], Cd[h]));   // c cd - s sd
+                Sn[h] = __ffma2_rn(C[h], Sd[h], __fmul2_rn(Sn[h], Cd[h]));             // s cd + c sd
+                C[h] = nC;
             }
             *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
         }
@@ -349,7 +418,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-    if (warp >= WARP_TMA) {
+    if (warp < WARP_SOFTMAX0) {
       reg_dec<REGS_MISC>();
       if (warp == WARP_TMA) {
         // ------------------------------------------------------------------ TMA producer
@@ -362,6 +431,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 tma_load_3d(dst, tm, 0, row, bh, bar(full_bar));
                 tma_load_3d(dst + HALF_BYTES, tm, 64, row, bh, bar(full_bar));
             };
+            TL_DECL(3, true)
+            TL(1);
             // first K tile between the two Q tiles: QK(0,0) needs Q0 and K0 only
             load_tile(base_addr + SMEM_Q, &tmQ, q0, Q_FULL);
             int issued = 0;       // K/V tile loads issued so far (K_j = 2j, V_j = 2j+1)
@@ -371,11 +442,13 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 if (it > 0) ok = wait_bar(ctx, K_EMPTY + s, (it - 1) & 1);
                 if (!ok) break;
                 load_tile(base_addr + SMEM_K + s * TILE_BYTES, &tmK, j * BN, K_FULL + s);
+                TL(2);
                 issued = 2 * j + 1;
                 if (j == 0 && n_kt[1] > 0) load_tile(base_addr + SMEM_Q + TILE_BYTES, &tmQ, q0 + BM, Q_FULL + 1);
                 if (it > 0) ok = wait_bar(ctx, V_EMPTY + s, (it - 1) & 1);
                 if (!ok) break;
                 load_tile(base_addr + SMEM_V + s * TILE_BYTES, &tmV, j * BN, V_FULL + s);
+                TL(3);
                 issued = 2 * j + 2;
             }
             if (*ctx.abort) {
@@ -395,21 +468,30 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             bool ok = true;
+            TL_DECL(4, true)
+            TL(1);
+            const uint32_t q_lo = desc_lo(base_addr + SMEM_Q, 16), k_lo = desc_lo(base_addr + SMEM_K, 16);
+            const uint32_t v_lo = desc_lo(base_addr + SMEM_V, HALF_BYTES);
             // S_t = Q_t K_j^T; releases the K stage after the last tile that reads it
             auto issue_qk = [&](int t, int j) -> bool {
                 const int s = j % NSTAGE, it = j / NSTAGE;
                 if (!wait_bar(ctx, (use_rope ? K_READY : K_FULL) + s, it & 1)) return false;
+                TL(10 + t);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)t * BN;
+                const uint32_t qa = q_lo + (uint32_t)t * (TILE_BYTES >> 4), kb = k_lo + (uint32_t)s * (TILE_BYTES >> 4);
+                mma_ss2<false>(d_tmem, qa, kb, IDESC_QK);
+                TL(16);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-                    mma_ss(d_tmem, make_desc(base_addr + SMEM_Q + t * TILE_BYTES + off, 16, 1024),
-                           make_desc(base_addr + SMEM_K + s * TILE_BYTES + off, 16, 1024), IDESC_QK, ks > 0);
+                for (int ks = 1; ks < HD / 16; ++ks) {
+                    const uint32_t off = (uint32_t)(((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4);
+                    mma_ss2<true>(d_tmem, qa + off, kb + off, IDESC_QK);
                 }
+                TL(17);
                 mma_commit(bar(S_FULL + t));
                 const bool last_reader = (t == 1) || !(j < n_kt[1]);
                 if (last_reader) mma_commit(bar(K_EMPTY + s));
+                TL(12 + t);
                 return true;
             };
             for (int t = 0; t < NQ && ok; ++t) {
@@ -422,20 +504,25 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 for (int t = 0; t < NQ && ok; ++t) {
                     if (j >= n_kt[t]) continue;
                     ok = wait_bar(ctx, P_READY + t, j & 1);
+                    TL(20 + t);
                     if (ok) ok = wait_bar(ctx, V_FULL + s, it & 1);
                     if (!ok) break;
+                    TL(22 + t);
                     tc_fence_after();
+                    // A: P_t in TMEM, 16 keys = 8 packed columns per step.  B: 16 key rows of V = 2 KiB per
+                    // step; MN-major: 64-column boxes HALF_BYTES apart (LBO), 8-row groups 1 KiB apart (SBO).
+                    const uint32_t o_tmem = tmem_base + TMEM_O + (uint32_t)t * HD, p_tmem = tmem_base + (uint32_t)t * BN;
+                    const uint32_t vb = v_lo + (uint32_t)s * (TILE_BYTES >> 4);
+                    mma_ts2(o_tmem, p_tmem, vb, IDESC_PV, j > 0);
+                    TL(26);
 #pragma unroll
-                    for (int ks = 0; ks < BN / 16; ++ks) {
-                        // A: P_t in TMEM, 16 keys = 8 packed columns per step.  B: 16 key rows of V = 2 KiB per
-                        // step; MN-major: 64-column boxes HALF_BYTES apart (LBO), 8-row groups 1 KiB apart (SBO).
-                        mma_ts(tmem_base + TMEM_O + (uint32_t)t * HD, tmem_base + (uint32_t)t * BN + ks * 8,
-                               make_desc(base_addr + SMEM_V + s * TILE_BYTES + ks * 2048, HALF_BYTES, 1024), IDESC_PV,
-                               (j > 0 || ks > 0));
-                    }
+                    for (int ks = 1; ks < BN / 16; ++ks)
+                        mma_ts2(o_tmem, p_tmem + ks * 8, vb + (uint32_t)ks * (2048 >> 4), IDESC_PV, 1u);
+                    TL(27);
                     const bool last_reader = (t == 1) || !(j < n_kt[1]);
                     if (last_reader) mma_commit(bar(V_EMPTY + s));
                     mma_commit(bar(O_DONE + t));
+                    TL(24 + t);
                     if (j + 1 < n_kt[t]) ok = issue_qk(t, j + 1);   // overwrites S_t / P_t: in order after PV(t, j)
                 }
             }
@@ -449,19 +536,23 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             RopeState st;
             rope_init(st, a.rope, S, a.rope_mode, rt);
             bool ok = true;
+            TL_DECL(2, rt == 0)
+            TL(1);
             for (int j = 0; j < n_total && ok; ++j) {
                 const int s = j % NSTAGE, it = j / NSTAGE;
                 ok = wait_bar(ctx, K_FULL + s, it & 1);
                 if (!ok) break;
+                TL(2);
                 rope_tile(smem + SMEM_K + s * TILE_BYTES, j * BN, S, a.rope, a.rope_mode, rt, st);
                 fence_async_smem();
                 mbar_arrive(bar(K_READY + s));
+                TL(3);
             }
         }
     } else {
         // ------------------------------------------------------------------ softmax / correction / epilogue
         reg_inc<REGS_SOFTMAX>();
-        const int t = warp >> 2;                   // query tile of this warpgroup
+        const int t = (warp - WARP_SOFTMAX0) >> 2;  // query tile of this warpgroup
         const int row = tid & 127;                 // TMEM lane == query row of the tile
         const int qt0 = q0 + t * BM;
         const int row_g = qt0 + row;
@@ -479,6 +570,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
             const uint32_t s_addr = lane_addr + (uint32_t)t * BN, o_addr = lane_addr + TMEM_O + (uint32_t)t * HD;
             bool ok = true;
+            TL_DECL(t, row == 0)
+            TL(1);
             if (use_rope) {   // this warpgroup rotates its own Q tile
                 RopeState st;
                 rope_init(st, a.rope, S, a.rope_mode, row);
@@ -490,11 +583,26 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
             }
             float m_ref = -INFINITY, l = 0.f;
+            TL(2);
             for (int j = 0; j < n && ok; ++j) {
                 const int k0 = j * BN;
                 ok = __all_sync(0xffffffffu, wait_bar(ctx, S_FULL + t, j & 1));  // leave as a whole warp
                 if (!ok) break;
+                // PV(t, j-1) ran before QK(t, j) on the in-order tensor pipe, so its completion barrier has
+                // already flipped: this wait only consumes the phase.  It must come BEFORE this thread's
+                // P_READY arrival: afterwards PV(t, j) may complete too, and a waiter that then looks for the
+                // parity of phase j-1 would see the barrier two phases ahead and never return.
+                if (j >= 1) {
+                    ok = __all_sync(0xffffffffu, wait_bar(ctx, O_DONE + t, (j - 1) & 1));
+                    if (!ok) break;
+                }
+                TL(3);
                 tc_fence_after();
+                if (DBG_FLAG(1)) {
+                    tc_fence_before();
+                    mbar_arrive(bar(P_READY + t));
+                    continue;
+                }
                 uint32_t sr[128];
                 {   // two 64-column loads: a single x128 load exceeds the kernel-wide register target of a 512-thread CTA
                     uint32_t (&lo)[64] = *reinterpret_cast<uint32_t(*)[64]>(&sr[0]);
@@ -509,24 +617,21 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     for (int c = 0; c < BN; ++c)
                         if (c > limit) sr[c] = 0xff800000u;   // -inf
                 }
-                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains, 3-input max
 #pragma unroll
-                for (int c = 0; c < BN; c += 4) {
+                for (int c = 0; c < BN; c += 8) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(sr[c + e]));
+                    for (int e = 0; e < 4; ++e)
+                        mx4[e] = max3(mx4[e], __uint_as_float(sr[c + 2 * e]), __uint_as_float(sr[c + 2 * e + 1]));
                 }
                 const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+                TL(4);
                 const float m_new = fmaxf(m_ref, mx * a.scale_log2);
-                bool o_waited = false;
                 if (j == 0) {
                     m_ref = (m_new == -INFINITY) ? 0.f : m_new;
                 } else {
                     const bool need = m_new > m_ref + 8.f;
-                    if (__any_sync(0xffffffffu, need)) {
-                        ok = __all_sync(0xffffffffu, wait_bar(ctx, O_DONE + t, (j - 1) & 1));  // PV(t, j-1) wrote O
-                        if (!ok) break;
-                        o_waited = true;
-                        tc_fence_after();
+                    if (__any_sync(0xffffffffu, need)) {   // PV(t, j-1) has written O (waited above)
                         const float f = need ? ex2(m_ref - m_new) : 1.f;
                         if (need) m_ref = m_new;
                         l *= f;
@@ -541,29 +646,32 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         tmem_st_wait();
                     }
                 }
-                const float neg_m = -m_ref;
-                float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+                // p = exp2(s * scale_log2 - m_ref): packed two-wide FMA and add, scalar ex2 (MUFU)
+                const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), nm2 = make_float2(-m_ref, -m_ref);
+                float2 rs4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {      // 32 keys -> 16 packed columns per store
                     uint32_t pk[16];
 #pragma unroll
                     for (int c = 0; c < 32; c += 2) {
-                        const float p0 = ex2(fmaf(__uint_as_float(sr[ch * 32 + c]), a.scale_log2, neg_m));
-                        const float p1 = ex2(fmaf(__uint_as_float(sr[ch * 32 + c + 1]), a.scale_log2, neg_m));
-                        rs4[(c >> 1) & 3] += p0 + p1;
-                        __nv_bfloat162 pp = __floats2bfloat162_rn(p0, p1);   // even key in the low half
+                        float2 x = make_float2(__uint_as_float(sr[ch * 32 + c]), __uint_as_float(sr[ch * 32 + c + 1]));
+                        x = __ffma2_rn(x, sc2, nm2);
+                        const float2 pe = make_float2(ex2(x.x), ex2(x.y));
+                        rs4[(c >> 1) & 3] = __fadd2_rn(rs4[(c >> 1) & 3], pe);
+                        __nv_bfloat162 pp = __floats2bfloat162_rn(pe.x, pe.y);   // even key in the low half
                         pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pp);
                     }
                     tmem_st_x16(s_addr + ch * 16, pk);
                 }
-                l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+                l += ((rs4[0].x + rs4[0].y) + (rs4[1].x + rs4[1].y)) + ((rs4[2].x + rs4[2].y) + (rs4[3].x + rs4[3].y));
+                TL(5);
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(bar(P_READY + t));
-                if (j >= 1 && !o_waited) ok = wait_bar(ctx, O_DONE + t, (j - 1) & 1);  // keep the phase in step
-                ok = __all_sync(0xffffffffu, ok);
+                TL(6);
             }
             if (ok) ok = __all_sync(0xffffffffu, wait_bar(ctx, O_DONE + t, (n - 1) & 1));
+            TL(7);
             if (ok) {
                 tc_fence_after();
                 const bool zero = (row_g >= len) || !(l > 0.f);
@@ -575,6 +683,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     if (row_g < S) store_row_chunk<TOut>(O + (size_t)row_g * HD + ch * 32, orow, inv);
                 }
             }
+            TL(8);
         }
     }
 
@@ -620,6 +729,19 @@ static int make_map(CUtensorMap* tm, const void* ptr, int BH, int S) {
 }
 
 }  // namespace sm100
+
+#ifdef GRL_TIMELINE
+// Copies the timeline of the last launch to the host: counts[5], then 5 x 512 stamps (tag << 48 | clock).
+extern "C" int grl_debug_flags(int flags) {
+    return (int)cudaMemcpyToSymbol(sm100::g_dbg_flags, &flags, sizeof(int));
+}
+extern "C" int grl_debug_timeline(unsigned int* counts, unsigned long long* stamps) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(counts, sm100::g_timeline_n, sizeof(unsigned int) * sm100::TL_ROLES);
+    cudaMemcpyFromSymbol(stamps, sm100::g_timeline, sizeof(unsigned long long) * sm100::TL_ROLES * sm100::TL_SLOTS);
+    return 0;
+}
+#endif
 
 int flash_fwd_sm100(grl_device* dev, const grl_flash_params* p, float scale, const float2* rope, int32_t* status) {
     using namespace sm100;
