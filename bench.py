@@ -413,6 +413,8 @@ def main():
         dist["barrier"], dist["max"] = _barrier, _max
 
     from grilly_next import cabi
+    if os.environ.get("GRL_LIB_OVERRIDE"):      # profiling aid: try an experimental build of the library
+        cabi.LIB_PATH = os.environ["GRL_LIB_OVERRIDE"]
     dev = cabi.Device(local_rank)          # raises if the CUDA library or the GPU is missing: no fallback
     L = dev.L
     pk = peaks()
