@@ -224,7 +224,7 @@ def bench_prefill_e2e(args, L, steps, dist):
     return dt, 3 * nbytes, nbytes
 
 
-def bench_decode(dev, cabi, dist, repeats=3, use_graph=True):
+def bench_decode(dev, cabi, dist, repeats=3, use_graph=True, force_splits=0):
     """cfg3: 256 decode steps (RoPE + append + split-KV attention + merge), graph-replayed."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from oracle import attention_oracle as orc
@@ -262,8 +262,10 @@ def bench_decode(dev, cabi, dist, repeats=3, use_graph=True):
     lay.k_pages, lay.v_pages, lay.cache_dtype = kp, vp, cabi.BF16
     lay.block_table, lay.seq_lens = table, seq_lens
     lay.batch, lay.num_kv_heads, lay.head_dim, lay.page_tokens, lay.max_pages = B, Hkv, D, P, max_pages
+    lay.num_pages = n_pages
     dp = cabi.DecodeParams()
     dp.kv, dp.num_q_heads, dp.max_seq_len = lay, Hq, max_tokens
+    dp.n_splits = force_splits
     ns = C.c_int()
     cabi.check(L.grl_decode_pick_splits(dev.h, C.byref(dp), C.byref(ns)))
     wb = C.c_size_t()
@@ -381,6 +383,7 @@ def main():
     ap.add_argument("--skip-prefill", action="store_true", help="profiling aid: run the decode workload only")
     ap.add_argument("--no-graph", action="store_true", help="profiling aid: plain launches instead of graph replay")
     ap.add_argument("--decode-repeats", type=int, default=3)
+    ap.add_argument("--decode-splits", type=int, default=0, help="profiling aid: force the split-KV count (0 = library choice)")
     ap.add_argument("--variant", default="cfg2", choices=["cfg2", "norope", "noncausal"],
                     help="profiling aid: drop RoPE or the causal mask from the prefill workload")
     ap.add_argument("--skip-e2e", action="store_true")
@@ -420,7 +423,7 @@ def main():
     pk = peaks()
 
     if args.skip_prefill:
-        dms, dl, nsplit = bench_decode(dev, cabi, dist, args.decode_repeats, not args.no_graph)
+        dms, dl, nsplit = bench_decode(dev, cabi, dist, args.decode_repeats, not args.no_graph, args.decode_splits)
         print(json.dumps({"decode_ms": dms, "launches": int(dl), "n_splits": nsplit}), flush=True)
         dev.close()
         return
@@ -446,7 +449,7 @@ def main():
     }
 
     if not args.skip_decode:
-        dms, dl, nsplit = bench_decode(dev, cabi, dist, args.decode_repeats, not args.no_graph)
+        dms, dl, nsplit = bench_decode(dev, cabi, dist, args.decode_repeats, not args.no_graph, args.decode_splits)
         c = CFG3
         toks = c["B"] * c["steps"] / (dms * 1e-3)
         gbs = decode_bytes(c) / (dms * 1e-3) / 1e9
@@ -455,7 +458,7 @@ def main():
                           "gpu_launches": int(dl), "n_splits": nsplit,
                           "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
                                        "traffic": None, "peak_source": pk["src"], "frac_of_nominal_8000": gbs / 8000.0,
-                                       "kernel": "decode_split_kernel"}}
+                                       "kernel": "decode_mma_kernel"}}
 
     if not args.skip_e2e:
         os.environ["GRILLY_GPU_INDEX"] = str(local_rank)     # the op layer's device selector

@@ -61,6 +61,7 @@ grl_kv_layout KVCache::layout() const {
     l.head_dim = int(config.headDim);
     l.page_tokens = int(config.pageTokens);
     l.max_pages = int(maxPages);
+    l.num_pages = int(numPages);
     return l;
 }
 

@@ -1,0 +1,381 @@
+// GQA decode over the paged bf16 cache, head_dim 128, 64-token pages: the fast path.
+//
+// Replaces shaders/gqa-attention.glsl:34-130 like decode_splitkv.cu, for the geometry of the
+// benchmark configurations.  One CTA owns (split, kv head, sequence); a producer warp streams
+// whole (page, kv head) slabs -- 16 KiB of K and 16 KiB of V, each contiguous in HBM -- into a
+// 3-stage shared-memory ring with TMA (128-byte swizzle, mbarrier complete_tx); four compute
+// warps each take 16 of the page's 64 tokens and run QK^T and PV on tensor cores
+// (mma.sync m16n8k16, the group's query heads padded to the 16-row operand, q split into
+// bf16 hi+lo so that its fp32 precision survives), with a private fp32 online softmax in the
+// exp2 domain.  K and V cross HBM -> SM exactly once; the four warps' partials are merged in
+// shared memory and leave the CTA as (O un-normalised, m, l), the layout lse_merge_kernel reads.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace grl {
+namespace dmma {
+
+constexpr int P = 64;               // tokens per page
+constexpr int D = 128;              // head_dim
+constexpr int NST = 3;              // ring stages
+constexpr int SLAB = P * D * 2;     // 16 KiB: one page of K (or V) for one kv head
+constexpr int STAGE = 2 * SLAB;     // K then V
+constexpr int kThreads = 160;       // 4 compute warps + 1 producer warp
+constexpr int SMEM_BAR = NST * STAGE;
+constexpr int SMEM_TOTAL = SMEM_BAR + 128 + 1024;
+constexpr long long kWaitLimitCycles = 2000000000LL;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kEmpty = -1e30f;
+
+struct Args {
+    const int32_t* block_table;
+    const int32_t* seq_lens;
+    const float* q;
+    float* part;
+    float* out;
+    int32_t* status;
+    int B, Hq, Hkv, max_pages, n_splits, group;
+    float scale;
+    int direct;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D += A * B with A rows 8..15 all zero (a1 = a3 = 0): the query heads of one GQA group fill rows 0..7.
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+struct Ctx {
+    uint32_t bars;
+    volatile int* abort;
+    int32_t* status;
+};
+__device__ __forceinline__ bool wait_bar(const Ctx& c, int bar, uint32_t parity) {
+    const uint32_t addr = c.bars + bar * 8;
+    if (mbar_try_wait(addr, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        if (mbar_try_wait(addr, parity)) return true;
+        if (*c.abort) return false;
+        if (clock64() - t0 > kWaitLimitCycles) {
+            *c.abort = 1;
+            if (c.status && atomicCAS(c.status, 0, GRL_ERR_TIMEOUT) == 0) {
+                c.status[1] = 0x100 | bar;
+                c.status[2] = blockIdx.x;
+                c.status[3] = blockIdx.y | (blockIdx.z << 16);
+            }
+            return false;
+        }
+    }
+}
+
+// byte offset inside a slab of element (token row, column d): two 64-column halves, 128-byte swizzle
+__device__ __forceinline__ uint32_t slab_off(int row, int d) {
+    return (uint32_t)((d >> 6) * (P * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4));
+}
+
+__global__ void __launch_bounds__(kThreads, 2)
+decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (base - raw_addr);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int len = a.seq_lens[b];
+    const int n_pages = (len + P - 1) / P;
+    const int pps = (n_pages + a.n_splits - 1) / a.n_splits;
+    const int p_begin = min(n_pages, split * pps), p_end = min(n_pages, (split + 1) * pps);
+    const int32_t* bt = a.block_table + (size_t)b * a.max_pages;
+
+    int* abort_flag = reinterpret_cast<int*>(smem + SMEM_BAR + 2 * NST * 8);
+    Ctx ctx{base + SMEM_BAR, abort_flag, a.status};
+    auto full = [&](int s) { return ctx.bars + (uint32_t)s * 8u; };
+    auto empty = [&](int s) { return ctx.bars + (uint32_t)(NST + s) * 8u; };
+    if (tid == 0) {
+        for (int s = 0; s < NST; ++s) { mbar_init(full(s), 1); mbar_init(empty(s), 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    const int g = lane >> 2, t4 = lane & 3;      // mma row / column-pair index of this lane
+    float o[16][4];
+    float m_run = kEmpty, l_run = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
+            int issued = 0;
+            for (int p = p_begin; p < p_end; ++p) {
+                const int i = p - p_begin, s = i % NST, it = i / NST;
+                if (it > 0 && !wait_bar(ctx, NST + s, (it - 1) & 1)) break;
+                const int row0 = (bt[p] * a.Hkv + kvh) * P;
+                const uint32_t dst = base + (uint32_t)s * STAGE;
+                mbar_expect_tx(full(s), STAGE);
+                tma_load_2d(dst, &tmK, 0, row0, full(s));
+                tma_load_2d(dst + SLAB / 2, &tmK, 64, row0, full(s));
+                tma_load_2d(dst + SLAB, &tmV, 0, row0, full(s));
+                tma_load_2d(dst + SLAB + SLAB / 2, &tmV, 64, row0, full(s));
+                issued = i + 1;
+            }
+            if (*ctx.abort) {   // copies already issued must land before the shared memory is released
+                const long long t0 = clock64();
+                for (int i = max(0, issued - NST); i < issued; ++i)
+                    while (!mbar_try_wait(full(i % NST), (i / NST) & 1) && clock64() - t0 < kWaitLimitCycles) {}
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ compute: tokens [16*warp, 16*warp+16) of every page
+        const int qh0 = kvh * a.group;
+        // A fragments of q (rows = heads of the group, zero beyond), pre-scaled into the exp2 domain, hi + lo bf16
+        uint32_t qhi[8][2], qlo[8][2];
+        {
+            const float sc = a.scale * kLog2e;
+            const float* qrow = a.q + ((size_t)b * a.Hq + qh0 + g) * D;
+            const bool live = g < a.group;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int d = 16 * ks + 8 * h + 2 * t4;
+                    float x0 = 0.f, x1 = 0.f;
+                    if (live) { const float2 v = *reinterpret_cast<const float2*>(qrow + d); x0 = v.x * sc; x1 = v.y * sc; }
+                    const float h0 = __bfloat162float(__float2bfloat16_rn(x0)), h1 = __bfloat162float(__float2bfloat16_rn(x1));
+                    qhi[ks][h] = pack_bf16(h0, h1);
+                    qlo[ks][h] = pack_bf16(x0 - h0, x1 - h1);
+                }
+            }
+        }
+        bool ok = true;
+        for (int p = p_begin; p < p_end && ok; ++p) {
+            const int i = p - p_begin, s = i % NST, it = i / NST;
+            ok = __all_sync(0xffffffffu, wait_bar(ctx, s, it & 1));
+            if (!ok) break;
+            const uint32_t kbase = base + (uint32_t)s * STAGE, vbase = kbase + SLAB;
+            const int tok0 = p * P + 16 * warp;                 // first token of this warp's slice
+            if (tok0 < len) {
+                if (tok0 + 16 > len) {
+                    // rows past the end of the sequence hold whatever the page held: zero them in V
+                    // (their probabilities are zero, but 0 * NaN is not)
+                    for (int c = lane; c < 16 * 16; c += 32) {
+                        const int r = 16 * warp + (c >> 4), ch = c & 15;
+                        if (p * P + r >= len)
+                            *reinterpret_cast<uint4*>(smem + s * STAGE + SLAB + slab_off(r, ch * 8)) = make_uint4(0, 0, 0, 0);
+                    }
+                    __syncwarp();
+                }
+                // ---- S = q K^T for 16 tokens: two 8-token n-tiles
+                float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                const int mat = lane >> 3;
+                {
+                    const int row = 16 * warp + (lane & 7) + ((mat >> 1) << 3);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        uint32_t kb[4];
+                        ldmatrix_x4(kbase + slab_off(row, 16 * ks + ((mat & 1) << 3)), kb);
+                        mma_16816(sacc[0], qhi[ks][0], qhi[ks][1], kb[0], kb[1]);
+                        mma_16816(sacc[1], qhi[ks][0], qhi[ks][1], kb[2], kb[3]);
+                        mma_16816(sacc[0], qlo[ks][0], qlo[ks][1], kb[0], kb[1]);
+                        mma_16816(sacc[1], qlo[ks][0], qlo[ks][1], kb[2], kb[3]);
+                    }
+                }
+                // ---- online softmax for head row g (lanes with the same g share the row)
+                float mx = kEmpty;
+                bool valid[2][2];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        valid[nt][e] = tok0 + nt * 8 + 2 * t4 + e < len;
+                        if (valid[nt][e]) mx = fmaxf(mx, sacc[nt][e]);
+                    }
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_new = fmaxf(m_run, mx);
+                const float corr = ex2(m_run - m_new);
+                float pv[2][2], ps = 0.f;
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        pv[nt][e] = valid[nt][e] ? ex2(sacc[nt][e] - m_new) : 0.f;
+                        ps += pv[nt][e];
+                    }
+                l_run = l_run * corr + ps;
+                m_run = m_new;
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+                    for (int n = 0; n < 16; ++n) { o[n][0] *= corr; o[n][1] *= corr; }
+                }
+                const uint32_t pa0 = pack_bf16(pv[0][0], pv[0][1]), pa2 = pack_bf16(pv[1][0], pv[1][1]);
+                // ---- O += P V: 16 tokens x 128 dims, two 8-wide d n-tiles per ldmatrix
+                {
+                    const int row = 16 * warp + (lane & 7) + ((mat & 1) << 3);
+#pragma unroll
+                    for (int dn = 0; dn < 8; ++dn) {
+                        uint32_t vb[4];
+                        ldmatrix_x4_trans(vbase + slab_off(row, 16 * dn + ((mat >> 1) << 3)), vb);
+                        mma_16816(o[2 * dn], pa0, pa2, vb[0], vb[1]);
+                        mma_16816(o[2 * dn + 1], pa0, pa2, vb[2], vb[3]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty(s));
+        }
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    }
+
+    // ---- merge the four warps' partials (the ring is idle now: reuse it)
+    __syncthreads();
+    float* sm_o = reinterpret_cast<float*>(smem);                 // [4 warps][8 heads][128]
+    float* sm_m = sm_o + 4 * 8 * D;                               // [4][8]
+    float* sm_l = sm_m + 32;
+    if (warp < 4) {
+#pragma unroll
+        for (int n = 0; n < 16; ++n)
+            *reinterpret_cast<float2*>(&sm_o[(warp * 8 + g) * D + n * 8 + 2 * t4]) = make_float2(o[n][0], o[n][1]);
+        if (t4 == 0) { sm_m[warp * 8 + g] = m_run; sm_l[warp * 8 + g] = l_run; }
+    }
+    __syncthreads();
+    const int rows = a.B * a.Hq;
+    for (int idx = tid; idx < a.group * D; idx += kThreads) {
+        const int h = idx / D, d = idx % D;
+        float mt = kEmpty;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mt = fmaxf(mt, sm_m[w * 8 + h]);
+        float ov = 0.f, lt = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float wgt = ex2(sm_m[w * 8 + h] - mt);
+            ov = fmaf(wgt, sm_o[(w * 8 + h) * D + d], ov);
+            lt = fmaf(wgt, sm_l[w * 8 + h], lt);
+        }
+        const int row = b * a.Hq + kvh * a.group + h;
+        if (a.direct) {
+            a.out[(size_t)row * D + d] = lt > 0.f ? ov / lt : 0.f;
+        } else {
+            float* part = a.part + (size_t)split * rows * (D + 2);
+            part[(size_t)row * D + d] = ov;
+            if (d == 0) {
+                part[(size_t)rows * D + row] = mt * 0.6931471805599453f;   // back to the natural-log domain
+                part[(size_t)rows * D + rows + row] = lt;
+            }
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int make_pool_map(CUtensorMap* tm, const void* pool, uint64_t rows) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return set_error(GRL_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)D, rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)P};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(GRL_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return GRL_OK;
+}
+
+}  // namespace dmma
+
+bool decode_mma_supported(const grl_decode_params* p) {
+    const grl_kv_layout& kv = p->kv;
+    const int group = p->num_q_heads / kv.num_kv_heads;
+    return kv.cache_dtype == GRL_BF16 && kv.head_dim == dmma::D && kv.page_tokens == dmma::P && group >= 1 && group <= 8 &&
+           ((uintptr_t)kv.k_pages % 16 == 0) && ((uintptr_t)kv.v_pages % 16 == 0) && ((uintptr_t)p->q % 8 == 0);
+}
+
+int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits, float scale, bool direct) {
+    using namespace dmma;
+    const grl_kv_layout& kv = p->kv;
+    const uint64_t pages = kv.num_pages > 0 ? (uint64_t)kv.num_pages : (uint64_t)kv.batch * kv.max_pages;
+    const uint64_t rows = pages * kv.num_kv_heads * P;
+    CUtensorMap tk, tv;
+    int rc = make_pool_map(&tk, kv.k_pages, rows);
+    if (!rc) rc = make_pool_map(&tv, kv.v_pages, rows);
+    if (rc) return rc;
+    Args a{};
+    a.block_table = kv.block_table; a.seq_lens = kv.seq_lens; a.q = p->q;
+    a.part = (float*)p->workspace; a.out = p->out; a.status = dev->d_status;
+    a.B = kv.batch; a.Hq = p->num_q_heads; a.Hkv = kv.num_kv_heads; a.max_pages = kv.max_pages;
+    a.n_splits = n_splits; a.group = p->num_q_heads / kv.num_kv_heads;
+    a.scale = scale; a.direct = direct ? 1 : 0;
+    dev->status_dirty = true;
+    static bool attr_set = false;
+    if (!attr_set) {
+        GRL_CUDA(cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        attr_set = true;
+    }
+    dim3 grid(n_splits, kv.num_kv_heads, kv.batch);
+    decode_mma_kernel<<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tk, tv, a);
+    GRL_LAUNCHED("decode_mma_kernel");
+    return GRL_OK;
+}
+
+}  // namespace grl

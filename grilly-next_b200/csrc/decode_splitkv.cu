@@ -6,6 +6,9 @@
 
 namespace grl {
 
+bool decode_mma_supported(const grl_decode_params* p);
+int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits, float scale, bool direct);
+
 constexpr float kEmptyMax = -1e30f;  // running max of a part that saw no token (finite on purpose)
 constexpr int kDecodeThreads = 128;
 
@@ -310,8 +313,11 @@ int grl_gqa_decode(grl_device* dev, const grl_decode_params* p) {
     a.max_pages = kv.max_pages; a.n_splits = n_splits; a.group = p->num_q_heads / kv.num_kv_heads;
     a.scale = p->scale == 0.f ? 1.f / sqrtf((float)D) : p->scale;
     a.direct = direct ? 1 : 0;
-    rc = (kv.cache_dtype == GRL_BF16) ? dispatch_decode_d<__nv_bfloat16>(dev, a, D)
-                                      : dispatch_decode_d<float>(dev, a, D);
+    if (decode_mma_supported(p) && !p->force_simt)
+        rc = decode_mma_launch(dev, p, n_splits, a.scale, direct);
+    else
+        rc = (kv.cache_dtype == GRL_BF16) ? dispatch_decode_d<__nv_bfloat16>(dev, a, D)
+                                          : dispatch_decode_d<float>(dev, a, D);
     if (rc || direct) return rc;
     const int rows = kv.batch * p->num_q_heads;
     const size_t stride = (size_t)rows * (D + 2);

@@ -47,7 +47,7 @@ class KVLayout(C.Structure):
     _fields_ = [("k_pages", C.c_void_p), ("v_pages", C.c_void_p), ("cache_dtype", C.c_int32),
                 ("block_table", C.c_void_p), ("seq_lens", C.c_void_p),
                 ("batch", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
-                ("page_tokens", C.c_int32), ("max_pages", C.c_int32)]
+                ("page_tokens", C.c_int32), ("max_pages", C.c_int32), ("num_pages", C.c_int32)]
 
 
 class AppendParams(C.Structure):
@@ -60,7 +60,8 @@ class AppendParams(C.Structure):
 class DecodeParams(C.Structure):
     _fields_ = [("kv", KVLayout), ("q", C.c_void_p), ("out", C.c_void_p), ("num_q_heads", C.c_int32),
                 ("scale", C.c_float), ("n_splits", C.c_int32), ("max_seq_len", C.c_int32),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("partial_out", C.c_void_p)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("partial_out", C.c_void_p),
+                ("force_simt", C.c_int32)]
 
 
 class GrlError(RuntimeError):

@@ -145,6 +145,7 @@ typedef struct {
     const int32_t* block_table;   /* (B, max_pages) */
     int32_t* seq_lens;            /* (B) */
     int32_t batch, num_kv_heads, head_dim, page_tokens, max_pages;
+    int32_t num_pages;            /* pages in each pool; 0 is read as batch * max_pages */
 } grl_kv_layout;
 
 /* Append n_new tokens per sequence: replaces ops::kvCacheAppend (cpp/src/ops/kv_cache.cpp:155-419;
@@ -188,6 +189,7 @@ typedef struct {
     void* workspace;        /* >= grl_decode_workspace_bytes() */
     size_t workspace_bytes;
     float* partial_out;
+    int32_t force_simt;     /* != 0: use the generic SIMT kernel even where the tensor-core path applies */
 } grl_decode_params;
 int grl_decode_pick_splits(grl_device* dev, const grl_decode_params* p, int* n_splits);
 int grl_decode_workspace_bytes(const grl_decode_params* p, int n_splits, size_t* bytes);

@@ -64,6 +64,7 @@ class PagedCache:
         l.k_pages, l.v_pages, l.cache_dtype = self.k_pages, self.v_pages, self.dtype
         l.block_table, l.seq_lens = self.block_table, self.seq_lens
         l.batch, l.num_kv_heads, l.head_dim, l.page_tokens, l.max_pages = self.B, self.Hkv, self.D, self.P, self.max_pages
+        l.num_pages = self.max_pages * self.B
         return l
 
     def append(self, k_new, v_new, q=None, rope_mode=cabi.ROPE_NONE, theta=10000.0, scaling=1.0, pos_base=0):
@@ -102,7 +103,7 @@ class PagedCache:
         dev.free(ok); dev.free(ov)
         return k, v
 
-    def decode(self, q, n_splits=0, scale=0.0, partial=False):
+    def decode(self, q, n_splits=0, scale=0.0, partial=False, force_simt=False):
         dev = self.dev
         B, _, Hq, D = q.shape
         qd = dev.upload(q.astype(np.float32))
@@ -111,6 +112,7 @@ class PagedCache:
         p.kv = self.layout()
         p.q, p.out, p.num_q_heads, p.scale, p.n_splits = qd, od, Hq, scale, n_splits
         p.max_seq_len = int(self.lens.max())
+        p.force_simt = int(force_simt)
         ns = C.c_int()
         cabi.check(dev.L.grl_decode_pick_splits(dev.h, C.byref(p), C.byref(ns)))
         wb = C.c_size_t()
