@@ -20,9 +20,11 @@ struct AppendArgs {
     RopeFreq freq;
 };
 
-// grid (chunks, B).  A work item is (token i, pair j): one cos/sin serves every K head and
-// every query head at that position.  With update_lens the grid has ONE chunk per sequence, so
-// that the length read at entry cannot race with the write at exit.
+// grid (chunks, B).  A work item is (token i, head slot, pair j), head slots being the Hkv key/value
+// heads followed by the Hq query heads, so that a one-token decode step spreads its (Hkv+Hq)*D/2
+// pairs over the whole CTA instead of walking the heads serially behind dependent loads.  With
+// update_lens the grid has ONE chunk per sequence, so that the length read at entry cannot race
+// with the write at exit.
 template <typename T>
 __global__ void __launch_bounds__(256) kv_append_kernel(AppendArgs a) {
     const int b = blockIdx.y;
@@ -30,32 +32,33 @@ __global__ void __launch_bounds__(256) kv_append_kernel(AppendArgs a) {
     const int len0 = a.seq_lens[b];
     T* kp = reinterpret_cast<T*>(a.k_pages);
     T* vp = reinterpret_cast<T*>(a.v_pages);
-    const int items = a.n_new * half;
+    const int slots = a.Hkv + (a.q_in ? a.Hq : 0);
+    const int items = a.n_new * slots * half;
     for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < items; idx += gridDim.x * blockDim.x) {
-        const int i = idx / half, j = idx % half;
+        const int j = idx % half;
+        const int hs = (idx / half) % slots;
+        const int i = idx / (half * slots);
         const int slot_pos = len0 + i;
-        const int page = a.block_table[(size_t)b * a.max_pages + slot_pos / a.P];
-        const int slot = slot_pos % a.P;
         float c = 1.f, s = 0.f;
         int d0 = 2 * j, d1 = 2 * j + 1;
         if (a.rope_mode == GRL_ROPE_HALF) { d0 = j; d1 = j + half; }
         if (a.rope_mode != GRL_ROPE_NONE) rope_sincos(a.pos_base + slot_pos, a.freq.inv_freq[j], &c, &s);
-        for (int h = 0; h < a.Hkv; ++h) {
-            const size_t src = (((size_t)b * a.n_new + i) * a.Hkv + h) * a.D;
-            const size_t dst = (((size_t)page * a.Hkv + h) * a.P + slot) * a.D;
+        if (hs < a.Hkv) {
+            const int page = a.block_table[(size_t)b * a.max_pages + slot_pos / a.P];
+            const int slot = slot_pos % a.P;
+            const size_t src = (((size_t)b * a.n_new + i) * a.Hkv + hs) * a.D;
+            const size_t dst = (((size_t)page * a.Hkv + hs) * a.P + slot) * a.D;
             const float k0 = a.k_new[src + d0], k1 = a.k_new[src + d1];
+            const float v0 = a.v_new[src + d0], v1 = a.v_new[src + d1];
             store_from_float<T>(kp + dst + d0, k0 * c - k1 * s);
             store_from_float<T>(kp + dst + d1, k0 * s + k1 * c);
-            store_from_float<T>(vp + dst + d0, a.v_new[src + d0]);
-            store_from_float<T>(vp + dst + d1, a.v_new[src + d1]);
-        }
-        if (a.q_in) {
-            for (int h = 0; h < a.Hq; ++h) {
-                const size_t qo = (((size_t)b * a.n_new + i) * a.Hq + h) * a.D;
-                const float q0 = a.q_in[qo + d0], q1 = a.q_in[qo + d1];
-                a.q_out[qo + d0] = q0 * c - q1 * s;
-                a.q_out[qo + d1] = q0 * s + q1 * c;
-            }
+            store_from_float<T>(vp + dst + d0, v0);
+            store_from_float<T>(vp + dst + d1, v1);
+        } else {
+            const size_t qo = (((size_t)b * a.n_new + i) * a.Hq + (hs - a.Hkv)) * a.D;
+            const float q0 = a.q_in[qo + d0], q1 = a.q_in[qo + d1];
+            a.q_out[qo + d0] = q0 * c - q1 * s;
+            a.q_out[qo + d1] = q0 * s + q1 * c;
         }
     }
     if (a.update_lens) {  // gridDim.x == 1 here
@@ -117,9 +120,10 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p) {
     a.max_pages = kv.max_pages; a.n_new = p->n_new;
     a.rope_mode = p->rope_mode; a.pos_base = p->pos_base;
     if (p->rope_mode != GRL_ROPE_NONE) a.freq = make_rope_freq(kv.head_dim, p->rope_theta, p->rope_scaling);
-    const int items = p->n_new * (kv.head_dim / 2);
-    int chunks = (items + 255) / 256;
-    if (chunks > 64) chunks = 64;
+    const long long items = (long long)p->n_new * (kv.num_kv_heads + (p->q_in ? p->num_q_heads : 0)) * (kv.head_dim / 2);
+    // one CTA per sequence while a CTA has at most 16 items per thread (a decode step), more for bulk appends
+    int chunks = (int)((items + 4095) / 4096);
+    if (chunks > 128) chunks = 128;
     const bool fused_update = p->update_lens && chunks == 1;
     a.update_lens = fused_update ? 1 : 0;
     dim3 grid(chunks, kv.batch);
