@@ -30,6 +30,7 @@ sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "grilly-next_b200", "python"))
 
 CFG2 = dict(B=4, H=32, S=2048, D=128, theta=10000.0, seed=1002)
+CFG4 = dict(Hq=32, Hkv=8, D=128, T=131072, seed=1004)
 CFG3 = dict(B=32, Hq=32, Hkv=8, D=128, T0=4096, steps=256, theta=10000.0, seed=1003, page=64)
 
 
@@ -353,6 +354,78 @@ def bench_decode_e2e(dist, steps=32):
     return dt, (q.nbytes + 2 * k1.nbytes), o.nbytes
 
 
+def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
+    """cfg4: B=1, Hq32/Hkv8, D128, KV length 131072 split in contiguous shards over the ranks; per step
+    every rank decodes its shard to one partial, NCCL all-gathers the partials, every rank merges."""
+    import torch
+    import torch.distributed as td
+    from grilly_next.parallel import CudaShardOps, ShardedDecoder, shard_range
+    from oracle import attention_oracle as orc
+    c = CFG4
+    B, Hq, Hkv, D, T, P = 1, c["Hq"], c["Hkv"], c["D"], c["T"], 64
+    world, rank = dist["world"], dist["rank"]
+    lo, hi = shard_range(T, world, rank)
+    Tg = hi - lo
+    L = dev.L
+    cabi.check(L.grl_device_use_stream(dev.h, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    n_pages = (Tg + P - 1) // P
+    page_elems = Hkv * P * D
+    shard_bytes = 2 * n_pages * page_elems * 2
+    nbuf = max(1, -(-(512 << 20) // shard_bytes))        # rotate buffers so that a shard never sits in L2
+    rng = np.random.default_rng(c["seed"] + rank)
+    bits = orc.to_bf16_bits(rng.standard_normal(32 * page_elems, dtype=np.float32))
+    pools = []
+    for _ in range(nbuf):
+        pair = []
+        for _kv in range(2):
+            t = torch.empty(n_pages * page_elems, dtype=torch.int16, device="cuda")
+            src = torch.from_numpy(np.roll(bits, int(rng.integers(0, bits.size))).view(np.int16)).cuda()
+            reps = -(-t.numel() // src.numel())
+            t.copy_(src.repeat(reps)[: t.numel()])
+            pair.append(t)
+        pools.append(pair)
+    table = torch.arange(n_pages, dtype=torch.int32, device="cuda").reshape(B, n_pages)
+    lens = torch.full((B,), Tg, dtype=torch.int32, device="cuda")
+    q = torch.from_numpy(rng.standard_normal((B, 1, Hq, D), dtype=np.float32)).cuda()
+    if world > 1:
+        td.broadcast(q, src=0)
+
+    def layout(i):
+        l = cabi.KVLayout()
+        l.k_pages, l.v_pages, l.cache_dtype = pools[i][0].data_ptr(), pools[i][1].data_ptr(), cabi.BF16
+        l.block_table, l.seq_lens = table.data_ptr(), lens.data_ptr()
+        l.batch, l.num_kv_heads, l.head_dim, l.page_tokens, l.max_pages, l.num_pages = B, Hkv, D, P, n_pages, n_pages
+        return l
+
+    ops = CudaShardOps(cabi, dev, layout(0), Hq, Tg, torch)
+    dec = ShardedDecoder(td if world > 1 else _NoDist(), ops, lambda n, m: torch.empty((n, m), dtype=torch.float32, device="cuda"))
+    layouts = [layout(i) for i in range(nbuf)]
+    for i in range(5):
+        ops.set_layout(layouts[i % nbuf]); out = dec.step(q)
+    torch.cuda.synchronize()
+    best = None
+    e0, e1 = dev.event(), dev.event()
+    launches0 = L.grl_launch_count()
+    for _ in range(repeats):
+        dist["barrier"]()
+        dev.record(e0)
+        for i in range(steps):
+            ops.set_layout(layouts[i % nbuf]); out = dec.step(q)
+        dev.record(e1)
+        torch.cuda.synchronize()
+        ms = dist["max"](dev.elapsed_ms(e0, e1))
+        best = ms if best is None else min(best, ms)
+    launches = (L.grl_launch_count() - launches0) // repeats
+    assert bool(torch.isfinite(out).all())
+    cabi.check(L.grl_device_use_stream(dev.h, None))
+    return best / steps, launches // steps, ops.p.n_splits, nbuf
+
+
+class _NoDist:
+    def is_initialized(self):
+        return False
+
+
 def cpu_baseline():
     from oracle import attention_oracle as orc
     from oracle import c_oracle
@@ -376,7 +449,7 @@ def cpu_baseline():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-decode", action="store_true")
@@ -387,6 +460,7 @@ def main():
     ap.add_argument("--variant", default="cfg2", choices=["cfg2", "norope", "noncausal"],
                     help="profiling aid: drop RoPE or the causal mask from the prefill workload")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-long", action="store_true", help="skip the long-context (cfg4) decode leg")
     ap.add_argument("--skip-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -415,6 +489,9 @@ def main():
 
         dist["barrier"], dist["max"] = _barrier, _max
 
+    if world == 1 and not (args.skip_decode or args.skip_long):
+        import torch
+        torch.cuda.set_device(local_rank)
     from grilly_next import cabi
     if os.environ.get("GRL_LIB_OVERRIDE"):      # profiling aid: try an experimental build of the library
         cabi.LIB_PATH = os.environ["GRL_LIB_OVERRIDE"]
@@ -460,6 +537,17 @@ def main():
                                        "traffic": None, "peak_source": pk["src"], "frac_of_nominal_8000": gbs / 8000.0,
                                        "kernel": "decode_mma_kernel"}}
 
+    if not args.skip_decode and not args.skip_long:
+        lms, ll, lsplit, nbuf = bench_long_decode(dev, cabi, dist)
+        kv_bytes = 2 * CFG4["Hkv"] * CFG4["D"] * 2 * CFG4["T"]
+        gbs = kv_bytes / (lms * 1e-3) / 1e9
+        line["decode_long"] = {"metric": "decode_long_tokens_per_s", "value": 1.0 / (lms * 1e-3), "unit": "tokens/s",
+                               "ms_per_step": lms, "scaling": "strong",
+                               "workload": f"cfg4: GQA decode B1 Hq32/Hkv8 D128 KV 131072 bf16 split over {world} GPU(s); "
+                                           f"per-GPU partial + NCCL all-gather (16,640 B/rank) + LSE merge; {nbuf} rotating KV buffers (L2)",
+                               "gpu_launches_per_step": int(ll), "n_splits": lsplit,
+                               "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"] * world, "unit": "GB/s",
+                                            "frac": gbs / (pk["hbm"] * world), "peak_source": pk["src"] + f" x{world}"}}
     if not args.skip_e2e:
         os.environ["GRILLY_GPU_INDEX"] = str(local_rank)     # the op layer's device selector
         dt, h2d, d2h = bench_prefill_e2e(args, L, min(args.steps, 5), dist)
