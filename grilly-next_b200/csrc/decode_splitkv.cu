@@ -176,26 +176,54 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(DecodeArgs
 }
 
 // parts: n_parts x [O (rows*D) | m (rows) | l (rows)].  grid (rows), block 128.
-__global__ void lse_merge_kernel(const float* __restrict__ parts, int n_parts, size_t part_stride, int rows,
-                                 int D, int normalise, float* __restrict__ out) {
-    const int row = blockIdx.x;
-    float mt = kEmptyMax;
-    for (int i = 0; i < n_parts; ++i) mt = fmaxf(mt, parts[i * part_stride + (size_t)rows * D + row]);
-    float lt = 0.f;
-    for (int i = 0; i < n_parts; ++i) {
-        const float* p = parts + i * part_stride + (size_t)rows * D;
-        lt += __expf(p[row] - mt) * p[rows + row];
+// Stage 1: the block finds the common maximum and the weights e^{m_i - m} of up to 1024 parts
+// (kept in shared memory); stage 2: each thread owns output columns and sums the parts with four
+// independent accumulators, so that the loads of different parts are in flight together.
+constexpr int kMaxMergeParts = 1024;
+__global__ void __launch_bounds__(128) lse_merge_kernel(const float* __restrict__ parts, int n_parts,
+                                                         size_t part_stride, int rows, int D, int normalise,
+                                                         float* __restrict__ out) {
+    __shared__ float sm_w[kMaxMergeParts];
+    __shared__ float sm_red[4];
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* ml = parts + (size_t)rows * D;
+    float mloc = kEmptyMax;
+    for (int i = tid; i < n_parts; i += 128) {
+        const float m = ml[i * part_stride + row];
+        sm_w[i] = m;
+        mloc = fmaxf(mloc, m);
     }
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float o = 0.f;
-        for (int i = 0; i < n_parts; ++i) {
-            const float* p = parts + i * part_stride;
-            o = fmaf(__expf(p[(size_t)rows * D + row] - mt), p[(size_t)row * D + d], o);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, off));
+    if (lane == 0) sm_red[warp] = mloc;
+    __syncthreads();
+    const float mt = fmaxf(fmaxf(sm_red[0], sm_red[1]), fmaxf(sm_red[2], sm_red[3]));
+    __syncthreads();
+    float lloc = 0.f;
+    for (int i = tid; i < n_parts; i += 128) {
+        const float w = __expf(sm_w[i] - mt);
+        sm_w[i] = w;
+        lloc = fmaf(w, ml[i * part_stride + rows + row], lloc);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, off);
+    if (lane == 0) sm_red[warp] = lloc;
+    __syncthreads();
+    const float lt = (sm_red[0] + sm_red[1]) + (sm_red[2] + sm_red[3]);
+    for (int d = tid; d < D; d += 128) {
+        const float* p = parts + (size_t)row * D + d;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        int i = 0;
+        for (; i + 4 <= n_parts; i += 4) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = fmaf(sm_w[i + e], p[(size_t)(i + e) * part_stride], acc[e]);
         }
+        for (; i < n_parts; ++i) acc[0] = fmaf(sm_w[i], p[(size_t)i * part_stride], acc[0]);
+        const float o = (acc[0] + acc[1]) + (acc[2] + acc[3]);
         if (normalise) out[(size_t)row * D + d] = lt > 0.f ? o / lt : 0.f;
         else out[(size_t)row * D + d] = o;
     }
-    if (!normalise && threadIdx.x == 0) {
+    if (!normalise && tid == 0) {
         out[(size_t)rows * D + row] = mt;
         out[(size_t)rows * D + rows + row] = lt;
     }
@@ -264,7 +292,7 @@ int grl_decode_pick_splits(grl_device* dev, const grl_decode_params* p, int* n_s
     const int max_len = p->max_seq_len > 0 ? p->max_seq_len : kv.max_pages * kv.page_tokens;
     const int pages = (max_len + kv.page_tokens - 1) / kv.page_tokens;
     const int base_ctas = kv.batch * kv.num_kv_heads;
-    const int target = 4 * dev->prop.multiProcessorCount;  // ~4 resident CTAs per SM
+    const int target = 2 * dev->prop.multiProcessorCount;  // two resident CTAs per SM
     int s = 1;
     // grow while it adds parallelism and every split keeps at least 2 pages (128 tokens)
     while (base_ctas * s < target && pages / (s * 2) >= 2 && s < 256) s *= 2;
@@ -283,6 +311,7 @@ int grl_lse_merge(grl_device* dev, const float* parts, int n_parts, size_t part_
                   int head_dim, int normalise, float* out) {
     GRL_REQUIRE(dev && parts && out, "NULL argument");
     GRL_REQUIRE(n_parts > 0 && rows > 0 && head_dim > 0, "bad shape");
+    GRL_REQUIRE(n_parts <= kMaxMergeParts, "at most %d parts can be merged in one call", kMaxMergeParts);
     GRL_REQUIRE(part_stride >= (size_t)rows * (head_dim + 2), "part_stride too small");
     DeviceGuard g(dev->ordinal);
     lse_merge_kernel<<<rows, 128, 0, dev->stream>>>(parts, n_parts, part_stride, rows, head_dim, normalise, out);

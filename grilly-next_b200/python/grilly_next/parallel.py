@@ -48,6 +48,8 @@ class ShardedDecoder:
         self._gather = None
 
     def step(self, q):
+        if self.world == 1 and hasattr(self.ops, "full"):
+            return self.ops.full(q)          # one GPU holds everything: normalised output directly
         part = self.ops.partial(q)
         if self.world == 1:
             return self.ops.merge(part.reshape(1, -1), 1)
@@ -87,6 +89,11 @@ class CudaShardOps:
         self.p.q, self.p.out, self.p.partial_out = q.data_ptr(), None, self.part.data_ptr()
         self.cabi.check(self.dev.L.grl_gqa_decode(self.dev.h, C.byref(self.p)))
         return self.part
+
+    def full(self, q):
+        self.p.q, self.p.out, self.p.partial_out = q.data_ptr(), self.out.data_ptr(), None
+        self.cabi.check(self.dev.L.grl_gqa_decode(self.dev.h, C.byref(self.p)))
+        return self.out
 
     def merge(self, gathered, n_parts):
         self.cabi.check(self.dev.L.grl_lse_merge(self.dev.h, gathered.data_ptr(), n_parts,
