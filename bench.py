@@ -107,6 +107,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count())   # torchrun pins it to 1; this arm may use every host thread
     from oracle import c_oracle
     c = CFG2
     heads = 32                                   # bounded sample: 32 of the 128 (batch, head) pairs per step
@@ -427,6 +428,7 @@ class _NoDist:
 
 
 def cpu_baseline():
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count())
     from oracle import attention_oracle as orc
     from oracle import c_oracle
     c = CFG2

@@ -355,4 +355,51 @@ int grl_gqa_decode(grl_device* dev, const grl_decode_params* p) {
     return grl_lse_merge(dev, (const float*)p->workspace, n_splits, stride, rows, D, 1, p->out);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode without any allocation by anyone.
+//
+// Some hosts of this library cannot give the decode step a workspace: a serving process that
+// hands every byte of device memory to its own arena at start-up and treats a later cudaMalloc
+// as a bug (it synchronises the device and can fail when the arena already owns the memory), or
+// a plugin loaded into such a process that is only ever given its input and output tensors.
+// For them the split-KV partials live in the array below, which is part of the library's image:
+// every GPU that loads the library holds these 4 MiB until the process exits.
+constexpr size_t kStaticScratchFloats = 1u << 20;   // 4 MiB
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+static float* g_decode_scratch_addr[64];            // per device ordinal: device address of the array
+static std::mutex g_decode_scratch_mu;
+
+int grl_gqa_decode_static(grl_device* dev, const grl_decode_params* p) {
+    GRL_REQUIRE(dev && p, "NULL argument");
+    GRL_REQUIRE(dev->ordinal >= 0 && dev->ordinal < 64, "device ordinal %d out of range", dev->ordinal);
+    int n_splits = 0;
+    int rc = grl_decode_pick_splits(dev, p, &n_splits);
+    if (rc) return rc;
+    size_t need = 0;
+    rc = grl_decode_workspace_bytes(p, n_splits, &need);
+    if (rc) return rc;
+    if (need > kStaticScratchFloats * sizeof(float))
+        return set_error(GRL_ERR_INVALID,
+                         "grl_gqa_decode_static: %d splits x %d rows need %zu bytes of scratch, the built-in array holds "
+                         "%zu; pass fewer splits (n_splits) or use grl_gqa_decode with a caller workspace",
+                         n_splits, p->kv.batch * p->num_q_heads, need, kStaticScratchFloats * sizeof(float));
+    float* scratch = nullptr;
+    {
+        // In host code the array's name is only a stand-in; the kernels need its device address on
+        // THIS device, asked for once per device with that device current.
+        std::lock_guard<std::mutex> lock(g_decode_scratch_mu);
+        scratch = g_decode_scratch_addr[dev->ordinal];
+        if (!scratch) {
+            DeviceGuard g(dev->ordinal);
+            GRL_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_decode_scratch));
+            g_decode_scratch_addr[dev->ordinal] = scratch;
+        }
+    }
+    grl_decode_params q = *p;
+    q.n_splits = n_splits;
+    q.workspace = scratch;
+    q.workspace_bytes = kStaticScratchFloats * sizeof(float);
+    return grl_gqa_decode(dev, &q);
+}
+
 }  // extern "C"

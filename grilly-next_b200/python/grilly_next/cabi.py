@@ -23,7 +23,7 @@ SYMBOLS = [
     "grl_event_record", "grl_event_elapsed_ms", "grl_graph_begin", "grl_graph_end", "grl_graph_launch",
     "grl_graph_destroy", "grl_launch_count", "grl_cast", "grl_flash_fwd", "grl_rope", "grl_attention_mask",
     "grl_kv_append", "grl_kv_gather", "grl_decode_pick_splits", "grl_decode_workspace_bytes", "grl_gqa_decode",
-    "grl_lse_merge",
+    "grl_gqa_decode_static", "grl_lse_merge",
 ]
 
 
@@ -103,6 +103,7 @@ def lib():
         _lib.grl_flash_fwd.argtypes = [C.c_void_p, C.POINTER(FlashParams)]
         _lib.grl_kv_append.argtypes = [C.c_void_p, C.POINTER(AppendParams)]
         _lib.grl_gqa_decode.argtypes = [C.c_void_p, C.POINTER(DecodeParams)]
+        _lib.grl_gqa_decode_static.argtypes = [C.c_void_p, C.POINTER(DecodeParams)]
         _lib.grl_decode_pick_splits.argtypes = [C.c_void_p, C.POINTER(DecodeParams), C.POINTER(C.c_int)]
         _lib.grl_decode_workspace_bytes.argtypes = [C.POINTER(DecodeParams), C.c_int, C.POINTER(C.c_size_t)]
         _lib.grl_kv_gather.argtypes = [C.c_void_p, C.POINTER(KVLayout), C.c_int, C.c_int, C.c_void_p, C.c_void_p]

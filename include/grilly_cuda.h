@@ -195,6 +195,20 @@ int grl_decode_pick_splits(grl_device* dev, const grl_decode_params* p, int* n_s
 int grl_decode_workspace_bytes(const grl_decode_params* p, int n_splits, size_t* bytes);
 int grl_gqa_decode(grl_device* dev, const grl_decode_params* p);
 
+/* The same decode step for callers that cannot allocate device memory and cannot pass a workspace
+ * (a process whose own arena owns all device memory after start-up, a plugin that only ever
+ * receives its input and output tensors).  This entry point has no counterpart in the reference.
+ * The split-KV partials go to a 4 MiB array that is part of the library's device image (each GPU
+ * that loads the library holds it until exit); p->workspace / workspace_bytes are ignored.
+ * Returns GRL_ERR_INVALID, launching nothing, when n_splits * batch * num_q_heads * (head_dim + 2)
+ * floats exceed 4 MiB.  No cudaMalloc / cudaFree / allocating routine is called.
+ * - The first call on a device looks up the array's device address; make that call before any
+ *   stream capture.
+ * - All calls share the one array, which keeps the previous call's contents.  Nothing in it has to
+ *   start at zero (every partial is fully written before it is read), but two calls that overlap
+ *   on the GPU (different streams, different devices' handles on one GPU) race on it. */
+int grl_gqa_decode_static(grl_device* dev, const grl_decode_params* p);
+
 /* Log-sum-exp merge of n_parts partials laid out as the partial_out of grl_gqa_decode, part i at
  * parts + i*part_stride floats.  rows = B*Hq.  normalise != 0 writes O/l to out (rows*D);
  * otherwise writes one combined partial of the same layout to out. */
