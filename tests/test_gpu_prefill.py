@@ -215,6 +215,34 @@ def test_tcgen05_cfg2_full_size(dev):
     assert np.abs(ones - 1.0).max() <= 1e-2
 
 
+def test_tcgen05_cfg5_padded_batch_full_size(dev):
+    """Configuration 5 at full size: batch 8, 32 heads, max seq 4096, per-sequence lengths uniform in
+    [512, 4096] from a seed, causal + padding, RoPE.  Sampled (batch, head) slices against the C oracle
+    on the unrounded fp32 inputs; padded query rows must be exactly zero."""
+    from grilly_next import cabi
+    from gpu_helpers import flash_cabi
+    from oracle import c_oracle
+    rng = np.random.default_rng(1005)
+    B, H, S, D = 8, 32, 4096, 128
+    lens = rng.integers(512, 4097, size=B).astype(np.int32)
+    Q = rng.standard_normal((B, H, S, D), dtype=np.float32)
+    K = rng.standard_normal((B, H, S, D), dtype=np.float32)
+    V = rng.standard_normal((B, H, S, D), dtype=np.float32)
+    out = flash_cabi(dev, Q, K, V, causal=True, seq_lens=lens, rope_mode=cabi.ROPE_INTERLEAVED, rope_theta=10000.0,
+                     bf16=True, kernel=cabi.KERNEL_TCGEN05)
+    assert np.all(np.isfinite(out))
+    pos = np.arange(S)
+    pick = [(int(np.argmin(lens)), 0), (int(np.argmax(lens)), 31), (3, 7), (6, 20)]
+    for (b, h) in pick:
+        q = orc.rope_interleaved(Q[b:b + 1, h:h + 1], pos)
+        k = orc.rope_interleaved(K[b:b + 1, h:h + 1], pos)
+        want = c_oracle.attention(q, k, V[b:b + 1, h:h + 1], causal=True, seq_lens=lens[b:b + 1])
+        err = np.abs(out[b, h] - want[0, 0]).max()
+        assert err <= TOL_BF16, f"cfg5 ({b},{h}) len {lens[b]}: max-abs {err:.3e}"
+    for b in range(B):
+        assert np.all(out[b, :, lens[b]:] == 0)
+
+
 def test_python_op_bf16_path(gpu):
     c = cases.PREFILL_CASES["cfg2_small"]
     Q, K, V = cases.prefill_inputs(c)
