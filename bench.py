@@ -210,7 +210,9 @@ def bench_prefill_e2e(args, L, steps, dist):
         arrs.append(a)
         ptrs.append(pp)
     ctx = grilly_core.Device()
-    kw = dict(causal=True, rope_theta=c["theta"], dtype="bf16")
+    out_arr, out_ptr = pinned_array(L, shape, np.float32)
+    ptrs.append(out_ptr)
+    kw = dict(causal=True, rope_theta=c["theta"], dtype="bf16", out=out_arr)
     for _ in range(2):
         out = grilly_core.flash_attention2(ctx, *arrs, **kw)
     dist["barrier"]()
@@ -554,7 +556,7 @@ def main():
         os.environ["GRILLY_GPU_INDEX"] = str(local_rank)     # the op layer's device selector
         dt, h2d, d2h = bench_prefill_e2e(args, L, min(args.steps, 5), dist)
         line["e2e"] = {"value": fl / dt / 1e12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                       "ms_per_step": dt * 1e3, "api": "grilly_core.flash_attention2(dtype='bf16'), pinned fp32 host arrays"}
+                       "ms_per_step": dt * 1e3, "api": "grilly_core.flash_attention2(dtype='bf16', out=pinned), pinned fp32 host arrays in and out"}
         if not args.skip_decode:
             ddt, dh2d, dd2h = bench_decode_e2e(dist)
             line["decode"]["e2e"] = {"value": CFG3["B"] / ddt * world, "unit": "tokens/s", "h2d_bytes_per_step": dh2d,

@@ -43,7 +43,8 @@ static ops::RopeMode parseRopeMode(const std::string& m, bool allowNone) {
 
 static py::array_t<float> flashImpl(GrillyCoreContext& ctx, FArr Q, FArr K, FArr V, std::optional<FArr> mask,
                                     float scale, bool causal, std::optional<IArr> seqLens, float ropeTheta,
-                                    float ropeScaling, const std::string& ropeMode, const std::string& dtype) {
+                                    float ropeScaling, const std::string& ropeMode, const std::string& dtype,
+                                    std::optional<py::array_t<float>> outArr = std::nullopt) {
     if (Q.ndim() != 4) throw std::runtime_error("Q must be 4D (batch, heads, seq_len, head_dim)");
     if (K.ndim() != 4 || V.ndim() != 4) throw std::runtime_error("K and V must be 4D (batch, heads, seq_len, head_dim)");
     for (int i = 0; i < 4; ++i)
@@ -76,7 +77,17 @@ static py::array_t<float> flashImpl(GrillyCoreContext& ctx, FArr Q, FArr K, FArr
     }
     if (dtype == "bf16") opt.precision = ops::Precision::BF16;
     else if (dtype != "fp32") throw std::runtime_error("dtype must be 'fp32' or 'bf16'");
-    py::array_t<float> result({py::ssize_t(B), py::ssize_t(H), py::ssize_t(S), py::ssize_t(D)});
+    // out=: write into the caller's array (numpy style); a pinned host array there lets the download run
+    // at the full PCIe rate and saves the first-touch page faults of a fresh 100+ MiB result
+    py::array_t<float> result;
+    if (outArr.has_value()) {
+        result = *outArr;
+        if (result.ndim() != 4 || result.shape(0) != B || result.shape(1) != H || result.shape(2) != S ||
+            result.shape(3) != D || !(result.flags() & py::array::c_style) || !result.writeable())
+            throw std::runtime_error("out must be a writable C-contiguous float32 array of Q's shape");
+    } else {
+        result = py::array_t<float>({py::ssize_t(B), py::ssize_t(H), py::ssize_t(S), py::ssize_t(D)});
+    }
     float* out = result.mutable_data();
     const float *q = Q.data(), *k = K.data(), *v = V.data();
     {
@@ -119,13 +130,13 @@ PYBIND11_MODULE(grilly_core, m) {
         "flash_attention2",
         [](GrillyCoreContext& ctx, FArr Q, FArr K, FArr V, std::optional<FArr> mask, float scale, uint32_t, uint32_t,
            bool causal, std::optional<IArr> seqLens, float ropeTheta, float ropeScaling, const std::string& ropeMode,
-           const std::string& dtype) {
-            return flashImpl(ctx, Q, K, V, mask, scale, causal, seqLens, ropeTheta, ropeScaling, ropeMode, dtype);
+           const std::string& dtype, std::optional<py::array_t<float>> out) {
+            return flashImpl(ctx, Q, K, V, mask, scale, causal, seqLens, ropeTheta, ropeScaling, ropeMode, dtype, out);
         },
         py::arg("device"), py::arg("Q"), py::arg("K"), py::arg("V"), py::arg("mask") = py::none(),
         py::arg("scale") = 0.0f, py::arg("tile_size_q") = 64, py::arg("tile_size_k") = 64, py::arg("causal") = false,
         py::arg("seq_lens") = py::none(), py::arg("rope_theta") = 0.0f, py::arg("rope_scaling") = 1.0f,
-        py::arg("rope_mode") = "interleaved", py::arg("dtype") = "fp32",
+        py::arg("rope_mode") = "interleaved", py::arg("dtype") = "fp32", py::arg("out") = py::none(),
         "GPU Flash Attention 2 with online softmax tiling");
 
     // ---- flash attention 2 + RoPE (push block of shaders/flash-attention2-rope.glsl:56-71)

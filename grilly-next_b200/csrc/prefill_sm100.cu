@@ -9,18 +9,19 @@
 //                64-column boxes, 128-byte swizzle) into a 2-stage shared-memory ring.
 //   warps 12-15  RoPE: rotate each K tile in place in shared memory, fence.proxy.async, hand the
 //                tile to the MMA warp.  (Each softmax warpgroup rotates its own Q tile once.)
-//   warp 0       one thread issues tcgen05.mma: S_t = Q_t K^T (A,B from shared memory, K-major)
+//   warps 0, 2   one thread per query tile issues tcgen05.mma: S_t = Q_t K^T (A,B from shared memory, K-major)
 //                into TMEM, then O_t += P_t V with P_t read from TMEM and V as an MN-major
-//                shared-memory operand; issue order PV0_j, QK0_j+1, PV1_j, QK1_j+1 so that one
-//                warpgroup's softmax overlaps the other's tensor work.
+//                shared-memory operand; per 64-key step i the issue order is PV0_i, QK0_i+2, PV1_i, QK1_i+2.
 //   warps 4-7 / 8-11  softmax warpgroup of query tile 0 / 1, one thread per query row:
 //                tcgen05.ld of the S row, causal / length predicate, fp32 online softmax in the
 //                exp2 domain, P written back to TMEM as packed bf16, O rescaled in TMEM only when
 //                the row maximum moved by more than 2^8 (the stale maximum stays the reference,
 //                so the result is exact), final O / l to global memory.
 //
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t overlays the first 64
-// columns of S_t.  Every mbarrier wait is bounded; on expiry the CTA records an error, drains
+// S is produced in 64-key halves into two TMEM buffers per tile, so that QK^T of step i+1 and i+2
+// runs while the softmax of step i is still busy and P.V of step i does not gate the next scores.
+// TMEM columns of tile t: S halves at t*256 + {0, 64} (P overlays the first 32 columns of its
+// half), O at t*256 + 128.  Every mbarrier wait is bounded; on expiry the CTA records an error, drains
 // its copies and returns.
 #include <cuda.h>
 
@@ -39,7 +40,7 @@ constexpr int NSTAGE = 2;
 constexpr int HALF_BYTES = BM * 64 * 2;     // one 64-column box: 16 KiB
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KiB
 constexpr int kThreads = 512;      // four warpgroups: MMA + TMA (+2 idle warps) | softmax 0 | softmax 1 | RoPE
-constexpr int WARP_MMA = 0, WARP_TMA = 1, WARP_SOFTMAX0 = 4, WARP_ROT0 = 12;   // warps 2-3 idle
+constexpr int WARP_MMA = 0, WARP_TMA = 1, WARP_MMA1 = 2, WARP_SOFTMAX0 = 4, WARP_ROT0 = 12;   // warp 3 idle
 // Register budget per warpgroup (setmaxnreg); 2*128*192 + 128*72 + 128*56 = 65536.
 constexpr int REGS_SOFTMAX = 192, REGS_ROPE = 72, REGS_MISC = 56;
 constexpr int SMEM_Q = 0;
@@ -47,13 +48,18 @@ constexpr int SMEM_K = SMEM_Q + NQ * TILE_BYTES;
 constexpr int SMEM_V = SMEM_K + NSTAGE * TILE_BYTES;
 constexpr int SMEM_BAR = SMEM_V + NSTAGE * TILE_BYTES;
 constexpr int SMEM_TOTAL = SMEM_BAR + 256 + 1024;  // + barrier block + alignment slack
+constexpr int BH = 64;              // keys per softmax step: S is computed in 64-key halves, double-buffered
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_O = 256;
+// TMEM columns of query tile t: S half-buffer b at t*256 + b*64 (P overlays its first 32 columns),
+// O at t*256 + 128.
+constexpr uint32_t TMEM_TILE = 256, TMEM_O = 128;
 constexpr long long kWaitLimitCycles = 2000000000LL;  // ~1 s at 2 GHz
 
 enum Bar { Q_FULL = 0, Q_READY = Q_FULL + NQ, K_FULL = Q_READY + NQ, K_READY = K_FULL + NSTAGE,
            K_EMPTY = K_READY + NSTAGE, V_FULL = K_EMPTY + NSTAGE, V_EMPTY = V_FULL + NSTAGE,
-           S_FULL = V_EMPTY + NSTAGE, P_READY = S_FULL + NQ, O_DONE = P_READY + NQ, NUM_BARS = O_DONE + NQ };
+           S_FULL = V_EMPTY + NSTAGE, P_READY = S_FULL + 2 * NQ, O_DONE = P_READY + 2 * NQ, NUM_BARS = O_DONE + NQ };
+// S_FULL / P_READY are indexed [t * 2 + buffer]: a barrier per S half-buffer, so that a waiter can
+// never fall two phases behind (the next use of a buffer needs this waiter's own arrival first).
 static_assert(NUM_BARS * 8 + 16 <= 256, "barrier block");
 
 struct Args {
@@ -70,8 +76,8 @@ struct Args {
 // bit 16 set = B operand is MN-major (the V tile, whose contiguous dimension is head_dim = N).
 constexpr uint32_t IDESC_BASE = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                 ((uint32_t)(BM >> 4) << 24);
-constexpr uint32_t IDESC_QK = IDESC_BASE;
-constexpr uint32_t IDESC_PV = IDESC_BASE | (1u << 16);
+constexpr uint32_t IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);  // N = 64 keys
+constexpr uint32_t IDESC_PV = IDESC_BASE | (1u << 16);                                                                         // N = 128 dims
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -385,6 +391,14 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const int k_end = a.causal ? min(len, qt0 + BM) : len;
         n_kt[t] = (qt0 < len) ? (k_end + BN - 1) / BN : 0;
     }
+    // 64-key softmax steps of tile t (the second half of its last K tile may be wholly invisible)
+    int n_half[NQ];
+#pragma unroll
+    for (int t = 0; t < NQ; ++t) {
+        const int qt0 = q0 + t * BM;
+        const int k_end = a.causal ? min(len, qt0 + BM) : len;
+        n_half[t] = (qt0 < len) ? (k_end + BH - 1) / BH : 0;
+    }
     const int n_total = max(n_kt[0], n_kt[1]);
     const bool use_rope = a.rope_mode != GRL_ROPE_NONE;
 
@@ -397,16 +411,18 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         for (int t = 0; t < NQ; ++t) {
             mbar_init(bar(Q_FULL + t), 1);
             mbar_init(bar(Q_READY + t), 128);
-            mbar_init(bar(S_FULL + t), 1);
-            mbar_init(bar(P_READY + t), 128);
+            for (int bf = 0; bf < 2; ++bf) {
+                mbar_init(bar(S_FULL + 2 * t + bf), 1);
+                mbar_init(bar(P_READY + 2 * t + bf), 128);
+            }
             mbar_init(bar(O_DONE + t), 1);
         }
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(bar(K_FULL + s), 1);
             mbar_init(bar(K_READY + s), 128);
-            mbar_init(bar(K_EMPTY + s), 1);
+            mbar_init(bar(K_EMPTY + s), 2);   // one arrival per reading query tile (twice from a lone reader)
             mbar_init(bar(V_FULL + s), 1);
-            mbar_init(bar(V_EMPTY + s), 1);
+            mbar_init(bar(V_EMPTY + s), 2);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -468,67 +484,66 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
             }
         }
-      } else if (warp == WARP_MMA) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+      } else if (warp == WARP_MMA || warp == WARP_MMA1) {
+        // ------------------------------------------------------------------ MMA issuers: one thread per query tile
+        // Each tile has its own in-order chain  wait P -> P.V(i) -> Q.K^T(i+2)  issued by its own thread, so that
+        // one tile's softmax never holds up the other tile's tensor work; the tensor pipe interleaves the two.
+        const int t = (warp == WARP_MMA) ? 0 : 1;
+        if (lane == 0 && n_half[t] > 0) {
             bool ok = true;
-            TL_DECL(4, true)
+            TL_DECL(4, t == 0)
             TL(1);
-            const uint32_t q_lo = desc_lo(base_addr + SMEM_Q, 16), k_lo = desc_lo(base_addr + SMEM_K, 16);
-            const uint32_t v_lo = desc_lo(base_addr + SMEM_V, HALF_BYTES);
-            // S_t = Q_t K_j^T; releases the K stage after the last tile that reads it
-            auto issue_qk = [&](int t, int j) -> bool {
-                const int s = j % NSTAGE, it = j / NSTAGE;
+            const uint32_t qa = desc_lo(base_addr + SMEM_Q + t * TILE_BYTES, 16);
+            const uint32_t k_lo = desc_lo(base_addr + SMEM_K, 16), v_lo = desc_lo(base_addr + SMEM_V, HALF_BYTES);
+            const int nh = n_half[t], other_tiles = n_kt[t ^ 1];
+            const uint32_t s_tmem = tmem_base + (uint32_t)t * TMEM_TILE, o_tmem = s_tmem + TMEM_O;
+            // A K or V tile (two 64-key steps) is released once per reading tile: the K_EMPTY / V_EMPTY barriers
+            // count two arrivals, and a tile that reads a K/V tile alone arrives twice.
+            auto release = [&](int bar_id, int j) {
+                mma_commit(bar(bar_id));
+                if (j >= other_tiles) mma_commit(bar(bar_id));
+            };
+            // S_t[i & 1] = Q_t K[64 keys of step i]^T
+            auto issue_qk = [&](int i) -> bool {
+                const int j = i >> 1, s = j % NSTAGE, it = j / NSTAGE;
                 if (!wait_bar(ctx, (use_rope ? K_READY : K_FULL) + s, it & 1)) return false;
-                TL(10 + t);
+                TL(10);
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)t * BN;
-                const uint32_t qa = q_lo + (uint32_t)t * (TILE_BYTES >> 4), kb = k_lo + (uint32_t)s * (TILE_BYTES >> 4);
+                const uint32_t d_tmem = s_tmem + (uint32_t)(i & 1) * BH;
+                const uint32_t kb = k_lo + (uint32_t)s * (TILE_BYTES >> 4) + (uint32_t)(i & 1) * ((BH * 128) >> 4);  // rows 64.. of each box
                 mma_ss2<false>(d_tmem, qa, kb, IDESC_QK);
-                TL(16);
 #pragma unroll
                 for (int ks = 1; ks < HD / 16; ++ks) {
                     const uint32_t off = (uint32_t)(((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4);
                     mma_ss2<true>(d_tmem, qa + off, kb + off, IDESC_QK);
                 }
-                TL(17);
-                mma_commit(bar(S_FULL + t));
-                const bool last_reader = (t == 1) || !(j < n_kt[1]);
-                if (last_reader) mma_commit(bar(K_EMPTY + s));
-                TL(12 + t);
+                mma_commit(bar(S_FULL + 2 * t + (i & 1)));
+                if ((i & 1) || i + 1 >= nh) release(K_EMPTY + s, j);   // last step of this tile on K tile j
+                TL(12);
                 return true;
             };
-            for (int t = 0; t < NQ && ok; ++t) {
-                if (n_kt[t] == 0) continue;
-                ok = wait_bar(ctx, (use_rope ? Q_READY : Q_FULL) + t, 0);
-                if (ok) ok = issue_qk(t, 0);
-            }
-            for (int j = 0; j < n_total && ok; ++j) {
-                const int s = j % NSTAGE, it = j / NSTAGE;
-                for (int t = 0; t < NQ && ok; ++t) {
-                    if (j >= n_kt[t]) continue;
-                    ok = wait_bar(ctx, P_READY + t, j & 1);
-                    TL(20 + t);
-                    if (ok) ok = wait_bar(ctx, V_FULL + s, it & 1);
-                    if (!ok) break;
-                    TL(22 + t);
-                    tc_fence_after();
-                    // A: P_t in TMEM, 16 keys = 8 packed columns per step.  B: 16 key rows of V = 2 KiB per
-                    // step; MN-major: 64-column boxes HALF_BYTES apart (LBO), 8-row groups 1 KiB apart (SBO).
-                    const uint32_t o_tmem = tmem_base + TMEM_O + (uint32_t)t * HD, p_tmem = tmem_base + (uint32_t)t * BN;
-                    const uint32_t vb = v_lo + (uint32_t)s * (TILE_BYTES >> 4);
-                    mma_ts2(o_tmem, p_tmem, vb, IDESC_PV, j > 0);
-                    TL(26);
+            ok = wait_bar(ctx, (use_rope ? Q_READY : Q_FULL) + t, 0);
+            for (int i = 0; i < 2 && i < nh && ok; ++i) ok = issue_qk(i);   // two steps of S ahead of the softmax
+            for (int i = 0; i < nh && ok; ++i) {
+                const int j = i >> 1, s = j % NSTAGE, it = j / NSTAGE;
+                ok = wait_bar(ctx, P_READY + 2 * t + (i & 1), (i >> 1) & 1);
+                TL(20);
+                if (ok) ok = wait_bar(ctx, V_FULL + s, it & 1);
+                if (!ok) break;
+                tc_fence_after();
+                // O_t += P_t[step i] V[64 keys]: A = P in TMEM (16 keys = 8 packed columns per k-step), B = 16 key
+                // rows of V = 2 KiB per k-step, MN-major (64-column boxes HALF_BYTES apart = LBO, 8-row groups
+                // 1 KiB apart = SBO).
+                const uint32_t p_tmem = s_tmem + (uint32_t)(i & 1) * BH;
+                const uint32_t vb = v_lo + (uint32_t)s * (TILE_BYTES >> 4) + (uint32_t)(i & 1) * ((BH * 128) >> 4);
+                mma_ts2(o_tmem, p_tmem, vb, IDESC_PV, i > 0);
 #pragma unroll
-                    for (int ks = 1; ks < BN / 16; ++ks)
-                        mma_ts2(o_tmem, p_tmem + ks * 8, vb + (uint32_t)ks * (2048 >> 4), IDESC_PV, 1u);
-                    TL(27);
-                    const bool last_reader = (t == 1) || !(j < n_kt[1]);
-                    if (last_reader) mma_commit(bar(V_EMPTY + s));
-                    mma_commit(bar(O_DONE + t));
-                    TL(24 + t);
-                    if (j + 1 < n_kt[t]) ok = issue_qk(t, j + 1);   // overwrites S_t / P_t: in order after PV(t, j)
-                }
+                for (int ks = 1; ks < BH / 16; ++ks)
+                    mma_ts2(o_tmem, p_tmem + ks * 8, vb + (uint32_t)ks * (2048 >> 4), IDESC_PV, 1u);
+                mma_commit(bar(O_DONE + t));
+                if ((i & 1) || i + 1 >= nh) release(V_EMPTY + s, j);
+                TL(24);
+                if (i + 2 < nh) ok = issue_qk(i + 2);   // reuses buffer i & 1: in order after PV(t, i)
             }
         }
       }
@@ -572,7 +587,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             }
         } else {
             const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-            const uint32_t s_addr = lane_addr + (uint32_t)t * BN, o_addr = lane_addr + TMEM_O + (uint32_t)t * HD;
+            const uint32_t s_addr = lane_addr + (uint32_t)t * TMEM_TILE, o_addr = s_addr + TMEM_O;
             bool ok = true;
             TL_DECL(t, row == 0)
             TL(1);
@@ -588,42 +603,25 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             }
             float m_ref = -INFINITY, l = 0.f;
             TL(2);
-            for (int j = 0; j < n && ok; ++j) {
-                const int k0 = j * BN;
-                ok = wait_bar_warp(ctx, S_FULL + t, j & 1);  // leave as a whole warp
+            const int nh = n_half[t];
+            for (int i = 0; i < nh && ok; ++i) {
+                const int bf = i & 1, k0 = i * BH;
+                ok = wait_bar_warp(ctx, S_FULL + 2 * t + bf, (i >> 1) & 1);
                 if (!ok) break;
-                // PV(t, j-1) ran before QK(t, j) on the in-order tensor pipe, so its completion barrier has
-                // already flipped: this wait only consumes the phase.  It must come BEFORE this thread's
-                // P_READY arrival: afterwards PV(t, j) may complete too, and a waiter that then looks for the
-                // parity of phase j-1 would see the barrier two phases ahead and never return.
-                if (j >= 1) {
-                    ok = wait_bar_warp(ctx, O_DONE + t, (j - 1) & 1);
-                    if (!ok) break;
-                }
                 TL(3);
                 tc_fence_after();
-                if (DBG_FLAG(1)) {
-                    tc_fence_before();
-                    mbar_arrive(bar(P_READY + t));
-                    continue;
-                }
-                uint32_t sr[128];
-                {   // two 64-column loads: a single x128 load exceeds the kernel-wide register target of a 512-thread CTA
-                    uint32_t (&lo)[64] = *reinterpret_cast<uint32_t(*)[64]>(&sr[0]);
-                    uint32_t (&hi)[64] = *reinterpret_cast<uint32_t(*)[64]>(&sr[64]);
-                    tmem_ld_x64_sync(s_addr, lo);
-                    tmem_ld_x64_sync(s_addr + 64, hi);
-                }
-                const bool need_mask = (a.causal && k0 + BN - 1 > qt0) || (k0 + BN > len);  // warpgroup-uniform
+                uint32_t sr[BH];
+                tmem_ld_x64_sync(s_addr + bf * BH, sr);
+                const bool need_mask = (a.causal && k0 + BH - 1 > qt0) || (k0 + BH > len);  // warpgroup-uniform
                 if (need_mask) {
                     const int limit = min(a.causal ? row_g : 0x7fffffff, len - 1) - k0;  // last visible column
 #pragma unroll
-                    for (int c = 0; c < BN; ++c)
+                    for (int c = 0; c < BH; ++c)
                         if (c > limit) sr[c] = 0xff800000u;   // -inf
                 }
                 float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // independent chains, 3-input max
 #pragma unroll
-                for (int c = 0; c < BN; c += 8) {
+                for (int c = 0; c < BH; c += 8) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e)
                         mx4[e] = max3(mx4[e], __uint_as_float(sr[c + 2 * e]), __uint_as_float(sr[c + 2 * e + 1]));
@@ -631,11 +629,16 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                 TL(4);
                 const float m_new = fmaxf(m_ref, mx * a.scale_log2);
-                if (j == 0) {
+                bool o_waited = false;
+                if (i == 0) {
                     m_ref = (m_new == -INFINITY) ? 0.f : m_new;
                 } else {
                     const bool need = m_new > m_ref + 8.f;
-                    if (__any_sync(0xffffffffu, need)) {   // PV(t, j-1) has written O (waited above)
+                    if (__any_sync(0xffffffffu, need)) {
+                        ok = wait_bar_warp(ctx, O_DONE + t, (i - 1) & 1);   // PV(t, i-1) has written O
+                        if (!ok) break;
+                        o_waited = true;
+                        tc_fence_after();
                         const float f = need ? ex2(m_ref - m_new) : 1.f;
                         if (need) m_ref = m_new;
                         l *= f;
@@ -644,7 +647,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                             uint32_t orow[32];
                             tmem_ld_x32_sync(o_addr + ch * 32, orow);
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * f);
+                            for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * f);
                             tmem_st_x32(o_addr + ch * 32, orow);
                         }
                         tmem_st_wait();
@@ -654,7 +657,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), nm2 = make_float2(-m_ref, -m_ref);
                 float2 rs4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {      // 32 keys -> 16 packed columns per store
+                for (int ch = 0; ch < BH / 32; ++ch) {      // 32 keys -> 16 packed columns per store
                     uint32_t pk[16];
 #pragma unroll
                     for (int c = 0; c < 32; c += 2) {
@@ -665,15 +668,23 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         __nv_bfloat162 pp = __floats2bfloat162_rn(pe.x, pe.y);   // even key in the low half
                         pk[c >> 1] = *reinterpret_cast<uint32_t*>(&pp);
                     }
-                    tmem_st_x16(s_addr + ch * 16, pk);
+                    tmem_st_x16(s_addr + bf * BH + ch * 16, pk);
                 }
                 l += ((rs4[0].x + rs4[0].y) + (rs4[1].x + rs4[1].y)) + ((rs4[2].x + rs4[2].y) + (rs4[3].x + rs4[3].y));
                 TL(5);
                 tmem_st_wait();
+                // Consume the phase of PV(t, i-1) BEFORE arriving: after the arrival PV(t, i) may complete too,
+                // and a waiter that then looks for the parity of phase i-1 would find the barrier two phases
+                // ahead and never return.  PV(t, i-1) was issued a whole softmax step ago: no stall here.
+                if (i >= 1 && !o_waited) {
+                    ok = wait_bar_warp(ctx, O_DONE + t, (i - 1) & 1);
+                    if (!ok) break;
+                }
                 tc_fence_before();
-                mbar_arrive(bar(P_READY + t));
+                mbar_arrive(bar(P_READY + 2 * t + bf));
                 TL(6);
             }
+            const int n = nh;
             if (ok) ok = wait_bar_warp(ctx, O_DONE + t, (n - 1) & 1);
             TL(7);
             if (ok) {

@@ -248,3 +248,10 @@ def test_python_op_bf16_path(gpu):
     Q, K, V = cases.prefill_inputs(c)
     out = gpu.flash_attention2(Q, K, V, causal=True, rope_theta=c["rope"], dtype="bf16")
     _check_case(out, "cfg2_small", c, TOL_BF16)
+    # out=: the result lands in the caller's array
+    buf = np.empty_like(Q)
+    ret = gpu.flash_attention2(Q, K, V, causal=True, rope_theta=c["rope"], dtype="bf16", out=buf)
+    assert ret is buf or np.shares_memory(ret, buf)
+    assert np.array_equal(buf, out)
+    with pytest.raises(RuntimeError, match="out must be"):
+        gpu.flash_attention2(Q, K, V, out=np.empty((1, 2, 3, 4), np.float32))
