@@ -259,14 +259,31 @@ __device__ __forceinline__ void rope_init(RopeState& st, const float2* __restric
     }
 }
 
-__device__ __forceinline__ void rope_tile(uint8_t* tile, int pos0, int S, const float2* __restrict__ rope, int mode,
-                                          int rt, const RopeState& st) {
+// cos/sin of a thread's first row of a tile: fetched ahead of the tile itself (the table read is an L2
+// round trip that would otherwise sit between the tile's arrival and its rotation).
+struct RopeStart {
+    float4 v[4];
+};
+__device__ __forceinline__ RopeStart rope_load_start(int pos0, int S, const float2* __restrict__ rope, int mode, int rt) {
+    RopeStart r;
+    if (mode == GRL_ROPE_INTERLEAVED) {
+        const float4* t = reinterpret_cast<const float4*>(rope + (size_t)min(pos0 + (rt >> 4), S - 1) * 64 + (rt & 15) * 4);
+        r.v[0] = __ldg(t); r.v[1] = __ldg(t + 1);
+        r.v[2] = r.v[3] = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+        const float4* t = reinterpret_cast<const float4*>(rope + (size_t)min(pos0 + (rt >> 3), S - 1) * 64 + (rt & 7) * 8);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) r.v[e] = __ldg(t + e);
+    }
+    return r;
+}
+
+__device__ __forceinline__ void rope_tile(uint8_t* tile, const RopeStart& start, int mode, int rt, const RopeState& st) {
     if (mode == GRL_ROPE_INTERLEAVED) {
         // chunk c = 4 adjacent pairs (2i, 2i+1); rows r0, r0+8, ... : r % 8 == r0, so the swizzle term is fixed
         const int c = rt & 15, r0 = rt >> 4;
         uint8_t* p = tile + (c >> 3) * HALF_BYTES + r0 * 128 + (((c & 7) ^ r0) << 4);
-        const float4* t = reinterpret_cast<const float4*>(rope + (size_t)min(pos0 + r0, S - 1) * 64 + c * 4);
-        const float4 t0 = __ldg(t), t1 = __ldg(t + 1);
+        const float4 t0 = start.v[0], t1 = start.v[1];
         // two pairs per packed operation: C = (c_e, c_e+1), S = (s_e, s_e+1)
         float2 C[2] = {make_float2(t0.x, t0.z), make_float2(t1.x, t1.z)};
         float2 Sn[2] = {make_float2(t0.y, t0.w), make_float2(t1.y, t1.w)};
@@ -297,11 +314,10 @@ __device__ __forceinline__ void rope_tile(uint8_t* tile, int pos0, int S, const 
         // rotate_half: pairs (d, d+64) sit at the same offset of the two boxes; rows r0, r0+16, ...
         const int cc = rt & 7, r0 = rt >> 3;
         uint8_t* p = tile + r0 * 128 + ((cc ^ (r0 & 7)) << 4);
-        const float4* t = reinterpret_cast<const float4*>(rope + (size_t)min(pos0 + r0, S - 1) * 64 + cc * 8);
         float cs[8], sn[8];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float4 v = __ldg(t + e);
+            const float4 v = start.v[e];
             cs[2 * e] = v.x; sn[2 * e] = v.y; cs[2 * e + 1] = v.z; sn[2 * e + 1] = v.w;
         }
 #pragma unroll 2
@@ -407,7 +423,15 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     Ctx ctx{base_addr + SMEM_BAR, abort_flag, a.status};
     auto bar = [&](int i) { return ctx.bars + (uint32_t)i * 8u; };
 
-    if (tid == 0) {
+    auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, int row, int full_bar) {
+        mbar_expect_tx(bar(full_bar), TILE_BYTES);
+        tma_load_3d(dst, tm, 0, row, bh, bar(full_bar));
+        tma_load_3d(dst + HALF_BYTES, tm, 64, row, bh, bar(full_bar));
+    };
+    if (warp == WARP_TMA && lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmQ)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
         for (int t = 0; t < NQ; ++t) {
             mbar_init(bar(Q_FULL + t), 1);
             mbar_init(bar(Q_READY + t), 128);
@@ -427,6 +451,16 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_async_smem();
+        // The first loads need no "empty" wait: put them in flight now, behind nothing but the barrier
+        // initialisation, while the other warps are still setting up.  QK(0,0) needs Q0 and K0 first.
+        load_tile(base_addr + SMEM_Q, &tmQ, q0, Q_FULL);
+        load_tile(base_addr + SMEM_K, &tmK, 0, K_FULL);
+        if (n_kt[1] > 0) load_tile(base_addr + SMEM_Q + TILE_BYTES, &tmQ, q0 + BM, Q_FULL + 1);
+        load_tile(base_addr + SMEM_V, &tmV, 0, V_FULL);
+        if (n_total > 1) {
+            load_tile(base_addr + SMEM_K + TILE_BYTES, &tmK, BN, K_FULL + 1);
+            load_tile(base_addr + SMEM_V + TILE_BYTES, &tmV, BN, V_FULL + 1);
+        }
     }
     if (warp == WARP_MMA) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -443,29 +477,18 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (warp == WARP_TMA) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmQ)) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmK)) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmV)) : "memory");
-            auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, int row, int full_bar) {
-                mbar_expect_tx(bar(full_bar), TILE_BYTES);
-                tma_load_3d(dst, tm, 0, row, bh, bar(full_bar));
-                tma_load_3d(dst + HALF_BYTES, tm, 64, row, bh, bar(full_bar));
-            };
             TL_DECL(3, true)
             TL(1);
-            // first K tile between the two Q tiles: QK(0,0) needs Q0 and K0 only
-            load_tile(base_addr + SMEM_Q, &tmQ, q0, Q_FULL);
-            int issued = 0;       // K/V tile loads issued so far (K_j = 2j, V_j = 2j+1)
+            int issued = 2 * min(n_total, NSTAGE);   // K/V tile loads in flight (K_j = 2j, V_j = 2j+1): the first stages
             bool ok = true;
-            for (int j = 0; j < n_total && ok; ++j) {
+            for (int j = NSTAGE; j < n_total && ok; ++j) {
                 const int s = j % NSTAGE, it = j / NSTAGE;
-                if (it > 0) ok = wait_bar(ctx, K_EMPTY + s, (it - 1) & 1);
+                ok = wait_bar(ctx, K_EMPTY + s, (it - 1) & 1);
                 if (!ok) break;
                 load_tile(base_addr + SMEM_K + s * TILE_BYTES, &tmK, j * BN, K_FULL + s);
                 TL(2);
                 issued = 2 * j + 1;
-                if (j == 0 && n_kt[1] > 0) load_tile(base_addr + SMEM_Q + TILE_BYTES, &tmQ, q0 + BM, Q_FULL + 1);
-                if (it > 0) ok = wait_bar(ctx, V_EMPTY + s, (it - 1) & 1);
+                ok = wait_bar(ctx, V_EMPTY + s, (it - 1) & 1);
                 if (!ok) break;
                 load_tile(base_addr + SMEM_V + s * TILE_BYTES, &tmV, j * BN, V_FULL + s);
                 TL(3);
@@ -475,7 +498,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 // Drain: copies already issued must land before the CTA's shared memory is released.
                 const long long t0 = clock64();
                 while (!mbar_try_wait(bar(Q_FULL), 0) && clock64() - t0 < kWaitLimitCycles) {}
-                if (issued >= 1 && n_kt[1] > 0)
+                if (n_kt[1] > 0)
                     while (!mbar_try_wait(bar(Q_FULL + 1), 0) && clock64() - t0 < kWaitLimitCycles) {}
                 for (int x = max(0, issued - 2 * NSTAGE); x < issued; ++x) {
                     const int j = x >> 1, s = j % NSTAGE, it = j / NSTAGE;
@@ -557,12 +580,15 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             bool ok = true;
             TL_DECL(2, rt == 0)
             TL(1);
+            RopeStart cur = rope_load_start(0, S, a.rope, a.rope_mode, rt);
             for (int j = 0; j < n_total && ok; ++j) {
                 const int s = j % NSTAGE, it = j / NSTAGE;
+                const RopeStart nxt = rope_load_start((j + 1) * BN, S, a.rope, a.rope_mode, rt);   // for the next tile
                 ok = wait_bar_warp(ctx, K_FULL + s, it & 1);
                 if (!ok) break;
                 TL(2);
-                rope_tile(smem + SMEM_K + s * TILE_BYTES, j * BN, S, a.rope, a.rope_mode, rt, st);
+                rope_tile(smem + SMEM_K + s * TILE_BYTES, cur, a.rope_mode, rt, st);
+                cur = nxt;
                 fence_async_smem();
                 mbar_arrive(bar(K_READY + s));
                 TL(3);
@@ -594,9 +620,10 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             if (use_rope) {   // this warpgroup rotates its own Q tile
                 RopeState st;
                 rope_init(st, a.rope, S, a.rope_mode, row);
+                const RopeStart start = rope_load_start(qt0, S, a.rope, a.rope_mode, row);
                 ok = wait_bar_warp(ctx, Q_FULL + t, 0);
                 if (ok) {
-                    rope_tile(smem + SMEM_Q + t * TILE_BYTES, qt0, S, a.rope, a.rope_mode, row, st);
+                    rope_tile(smem + SMEM_Q + t * TILE_BYTES, start, a.rope_mode, row, st);
                     fence_async_smem();
                     mbar_arrive(bar(Q_READY + t));
                 }
@@ -691,11 +718,44 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 tc_fence_after();
                 const bool zero = (row_g >= len) || !(l > 0.f);
                 const float inv = zero ? 0.f : 1.f / l;
+                if constexpr (sizeof(TOut) == 4) {
+                    // Each thread holds one 512-byte output row; written directly, a warp store would touch 32
+                    // rows.  Transpose through shared memory instead (this tile's Q buffer is dead: all of its
+                    // QK^T have completed): 32 rows x 64 columns per pass, 16-byte chunks XOR-swizzled by row, then
+                    // every warp store writes 256 contiguous bytes of one row.
+                    uint8_t* stage = smem + SMEM_Q + t * TILE_BYTES + (warp & 3) * 8192;
+                    const int row_w0 = qt0 + (warp & 3) * 32;
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t orow[32];
-                    tmem_ld_x32_sync(o_addr + ch * 32, orow);   // warp-collective: no divergence here
-                    if (row_g < S) store_row_chunk<TOut>(O + (size_t)row_g * HD + ch * 32, orow, inv);
+                    for (int pass = 0; pass < 2; ++pass) {
+#pragma unroll
+                        for (int ch = 0; ch < 2; ++ch) {
+                            uint32_t orow[32];
+                            tmem_ld_x32_sync(o_addr + pass * 64 + ch * 32, orow);
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) {
+                                const int chunk = ch * 8 + c;
+                                *reinterpret_cast<float4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) =
+                                    make_float4(__uint_as_float(orow[4 * c]) * inv, __uint_as_float(orow[4 * c + 1]) * inv,
+                                                __uint_as_float(orow[4 * c + 2]) * inv, __uint_as_float(orow[4 * c + 3]) * inv);
+                            }
+                        }
+                        __syncwarp();
+#pragma unroll 8
+                        for (int rr = 0; rr < 32; ++rr) {
+                            const float2 v = *reinterpret_cast<const float2*>(stage + rr * 256 + (((lane >> 1) ^ (rr & 15)) << 4) +
+                                                                              (lane & 1) * 8);
+                            if (row_w0 + rr < S)
+                                *reinterpret_cast<float2*>(reinterpret_cast<float*>(O) + (size_t)(row_w0 + rr) * HD + pass * 64 + 2 * lane) = v;
+                        }
+                        __syncwarp();
+                    }
+                } else {
+#pragma unroll
+                    for (int ch = 0; ch < 4; ++ch) {
+                        uint32_t orow[32];
+                        tmem_ld_x32_sync(o_addr + ch * 32, orow);   // warp-collective: no divergence here
+                        if (row_g < S) store_row_chunk<TOut>(O + (size_t)row_g * HD + ch * 32, orow, inv);
+                    }
                 }
             }
             TL(8);
