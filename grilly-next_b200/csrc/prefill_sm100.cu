@@ -168,6 +168,20 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+// explicit shared-space accesses (32-bit addresses): the generic-pointer forms cost an address-space check
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -278,11 +292,11 @@ __device__ __forceinline__ RopeStart rope_load_start(int pos0, int S, const floa
     return r;
 }
 
-__device__ __forceinline__ void rope_tile(uint8_t* tile, const RopeStart& start, int mode, int rt, const RopeState& st) {
+__device__ __forceinline__ void rope_tile(uint32_t tile, const RopeStart& start, int mode, int rt, const RopeState& st) {
     if (mode == GRL_ROPE_INTERLEAVED) {
         // chunk c = 4 adjacent pairs (2i, 2i+1); rows r0, r0+8, ... : r % 8 == r0, so the swizzle term is fixed
         const int c = rt & 15, r0 = rt >> 4;
-        uint8_t* p = tile + (c >> 3) * HALF_BYTES + r0 * 128 + (((c & 7) ^ r0) << 4);
+        uint32_t p = tile + (c >> 3) * HALF_BYTES + r0 * 128 + (((c & 7) ^ r0) << 4);
         const float4 t0 = start.v[0], t1 = start.v[1];
         // two pairs per packed operation: C = (c_e, c_e+1), S = (s_e, s_e+1)
         float2 C[2] = {make_float2(t0.x, t0.z), make_float2(t1.x, t1.z)};
@@ -292,7 +306,7 @@ __device__ __forceinline__ void rope_tile(uint8_t* tile, const RopeStart& start,
         const float2 Sdn[2] = {make_float2(-st.sd[0], -st.sd[1]), make_float2(-st.sd[2], -st.sd[3])};
 #pragma unroll 4
         for (int k = 0; k < 16; ++k, p += 1024) {
-            uint4 v = *reinterpret_cast<uint4*>(p);
+            uint4 v = lds128(p);
             uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -308,12 +322,12 @@ __device__ __forceinline__ void rope_tile(uint8_t* tile, const RopeStart& start,
                 Sn[h] = __ffma2_rn(C[h], Sd[h], __fmul2_rn(Sn[h], Cd[h]));             // s cd + c sd
                 C[h] = nC;
             }
-            *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+            sts128(p, make_uint4(w[0], w[1], w[2], w[3]));
         }
     } else {
         // rotate_half: pairs (d, d+64) sit at the same offset of the two boxes; rows r0, r0+16, ...
         const int cc = rt & 7, r0 = rt >> 3;
-        uint8_t* p = tile + r0 * 128 + ((cc ^ (r0 & 7)) << 4);
+        uint32_t p = tile + r0 * 128 + ((cc ^ (r0 & 7)) << 4);
         float cs[8], sn[8];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -322,7 +336,7 @@ __device__ __forceinline__ void rope_tile(uint8_t* tile, const RopeStart& start,
         }
 #pragma unroll 2
         for (int k = 0; k < 8; ++k, p += 2048) {
-            uint4 a = *reinterpret_cast<uint4*>(p), b = *reinterpret_cast<uint4*>(p + HALF_BYTES);
+            uint4 a = lds128(p), b = lds128(p + HALF_BYTES);
             uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -340,8 +354,8 @@ __device__ __forceinline__ void rope_tile(uint8_t* tile, const RopeStart& start,
                 sn[e] = sn[e] * st.cd[e] + cs[e] * st.sd[e];
                 cs[e] = nc;
             }
-            *reinterpret_cast<uint4*>(p) = make_uint4(wa[0], wa[1], wa[2], wa[3]);
-            *reinterpret_cast<uint4*>(p + HALF_BYTES) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+            sts128(p, make_uint4(wa[0], wa[1], wa[2], wa[3]));
+            sts128(p + HALF_BYTES, make_uint4(wb[0], wb[1], wb[2], wb[3]));
         }
     }
 }
@@ -587,7 +601,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 ok = wait_bar_warp(ctx, K_FULL + s, it & 1);
                 if (!ok) break;
                 TL(2);
-                rope_tile(smem + SMEM_K + s * TILE_BYTES, cur, a.rope_mode, rt, st);
+                rope_tile(base_addr + SMEM_K + s * TILE_BYTES, cur, a.rope_mode, rt, st);
                 cur = nxt;
                 fence_async_smem();
                 mbar_arrive(bar(K_READY + s));
@@ -623,7 +637,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 const RopeStart start = rope_load_start(qt0, S, a.rope, a.rope_mode, row);
                 ok = wait_bar_warp(ctx, Q_FULL + t, 0);
                 if (ok) {
-                    rope_tile(smem + SMEM_Q + t * TILE_BYTES, start, a.rope_mode, row, st);
+                    rope_tile(base_addr + SMEM_Q + t * TILE_BYTES, start, a.rope_mode, row, st);
                     fence_async_smem();
                     mbar_arrive(bar(Q_READY + t));
                 }
@@ -723,7 +737,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     // rows.  Transpose through shared memory instead (this tile's Q buffer is dead: all of its
                     // QK^T have completed): 32 rows x 64 columns per pass, 16-byte chunks XOR-swizzled by row, then
                     // every warp store writes 256 contiguous bytes of one row.
-                    uint8_t* stage = smem + SMEM_Q + t * TILE_BYTES + (warp & 3) * 8192;
+                    const uint32_t stage = base_addr + SMEM_Q + t * TILE_BYTES + (warp & 3) * 8192;
                     const int row_w0 = qt0 + (warp & 3) * 32;
 #pragma unroll
                     for (int pass = 0; pass < 2; ++pass) {
@@ -734,16 +748,17 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll
                             for (int c = 0; c < 8; ++c) {
                                 const int chunk = ch * 8 + c;
-                                *reinterpret_cast<float4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) =
-                                    make_float4(__uint_as_float(orow[4 * c]) * inv, __uint_as_float(orow[4 * c + 1]) * inv,
-                                                __uint_as_float(orow[4 * c + 2]) * inv, __uint_as_float(orow[4 * c + 3]) * inv);
+                                sts128(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4),
+                                       make_uint4(__float_as_uint(__uint_as_float(orow[4 * c]) * inv),
+                                                  __float_as_uint(__uint_as_float(orow[4 * c + 1]) * inv),
+                                                  __float_as_uint(__uint_as_float(orow[4 * c + 2]) * inv),
+                                                  __float_as_uint(__uint_as_float(orow[4 * c + 3]) * inv)));
                             }
                         }
                         __syncwarp();
 #pragma unroll 8
                         for (int rr = 0; rr < 32; ++rr) {
-                            const float2 v = *reinterpret_cast<const float2*>(stage + rr * 256 + (((lane >> 1) ^ (rr & 15)) << 4) +
-                                                                              (lane & 1) * 8);
+                            const float2 v = lds64f(stage + rr * 256 + (((lane >> 1) ^ (rr & 15)) << 4) + (lane & 1) * 8);
                             if (row_w0 + rr < S)
                                 *reinterpret_cast<float2*>(reinterpret_cast<float*>(O) + (size_t)(row_w0 + rr) * HD + pass * 64 + 2 * lane) = v;
                         }
