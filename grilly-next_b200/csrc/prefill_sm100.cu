@@ -41,8 +41,8 @@ constexpr int HALF_BYTES = BM * 64 * 2;     // one 64-column box: 16 KiB
 constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KiB
 constexpr int kThreads = 512;      // four warpgroups: MMA + TMA (+2 idle warps) | softmax 0 | softmax 1 | RoPE
 constexpr int WARP_MMA = 0, WARP_TMA = 1, WARP_MMA1 = 2, WARP_SOFTMAX0 = 4, WARP_ROT0 = 12;   // warp 3 idle
-// Register budget per warpgroup (setmaxnreg); 2*128*192 + 128*72 + 128*56 = 65536.
-constexpr int REGS_SOFTMAX = 192, REGS_ROPE = 72, REGS_MISC = 56;
+// Register budget per warpgroup (setmaxnreg); 2*128*160 + 128*112 + 128*80 = 65536.
+constexpr int REGS_SOFTMAX = 160, REGS_ROPE = 112, REGS_MISC = 80;
 constexpr int SMEM_Q = 0;
 constexpr int SMEM_K = SMEM_Q + NQ * TILE_BYTES;
 constexpr int SMEM_V = SMEM_K + NSTAGE * TILE_BYTES;
@@ -57,7 +57,8 @@ constexpr long long kWaitLimitCycles = 2000000000LL;  // ~1 s at 2 GHz
 
 enum Bar { Q_FULL = 0, Q_READY = Q_FULL + NQ, K_FULL = Q_READY + NQ, K_READY = K_FULL + NSTAGE,
            K_EMPTY = K_READY + NSTAGE, V_FULL = K_EMPTY + NSTAGE, V_EMPTY = V_FULL + NSTAGE,
-           S_FULL = V_EMPTY + NSTAGE, P_READY = S_FULL + 2 * NQ, O_DONE = P_READY + 2 * NQ, NUM_BARS = O_DONE + NQ };
+           S_FULL = V_EMPTY + NSTAGE, P_READY = S_FULL + 2 * NQ, O_DONE = P_READY + 2 * NQ, EXP_TURN = O_DONE + NQ,
+           NUM_BARS = EXP_TURN + NQ };
 // S_FULL / P_READY are indexed [t * 2 + buffer]: a barrier per S half-buffer, so that a waiter can
 // never fall two phases behind (the next use of a buffer needs this waiter's own arrival first).
 static_assert(NUM_BARS * 8 + 16 <= 256, "barrier block");
@@ -454,6 +455,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 mbar_init(bar(P_READY + 2 * t + bf), 128);
             }
             mbar_init(bar(O_DONE + t), 1);
+            mbar_init(bar(EXP_TURN + t), 128);
         }
         for (int s = 0; s < NSTAGE; ++s) {
             mbar_init(bar(K_FULL + s), 1);
@@ -645,6 +647,12 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             float m_ref = -INFINITY, l = 0.f;
             TL(2);
             const int nh = n_half[t];
+            // The two softmax warpgroups take turns in the exponential phase (it saturates the MUFU unit they
+            // share): a warpgroup starts its exponentials when the other has finished its own, and spends its
+            // loads, maxima, stores and barrier hops while the other one exponentiates.  Only for the steps that
+            // both tiles have.
+            const int nc = min(n_half[0], n_half[1]);
+            if (t == 1 && nc > 0) mbar_arrive(bar(EXP_TURN + 0));   // tile 0 goes first
             for (int i = 0; i < nh && ok; ++i) {
                 const int bf = i & 1, k0 = i * BH;
                 ok = wait_bar_warp(ctx, S_FULL + 2 * t + bf, (i >> 1) & 1);
@@ -694,6 +702,10 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         tmem_st_wait();
                     }
                 }
+                if (i < nc) {
+                    ok = wait_bar_warp(ctx, EXP_TURN + t, i & 1);
+                    if (!ok) break;
+                }
                 // p = exp2(s * scale_log2 - m_ref): packed two-wide FMA and add, scalar ex2 (MUFU)
                 const float2 sc2 = make_float2(a.scale_log2, a.scale_log2), nm2 = make_float2(-m_ref, -m_ref);
                 float2 rs4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
@@ -711,6 +723,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     }
                     tmem_st_x16(s_addr + bf * BH + ch * 16, pk);
                 }
+                if (t == 0 ? (i < nc) : (i + 1 < nc)) mbar_arrive(bar(EXP_TURN + (t ^ 1)));   // the other tile's turn
                 l += ((rs4[0].x + rs4[0].y) + (rs4[1].x + rs4[1].y)) + ((rs4[2].x + rs4[2].y) + (rs4[3].x + rs4[3].y));
                 TL(5);
                 tmem_st_wait();
