@@ -13,7 +13,6 @@ extern "C" int grl_flash_fwd(grl_device* dev, const grl_flash_params* p) {
     GRL_REQUIRE(p->q && p->k && p->v && p->o, "NULL tensor pointer");
     GRL_REQUIRE(p->batch > 0 && p->heads > 0 && p->seq_len > 0 && p->head_dim > 0, "bad shape (%d,%d,%d,%d)",
                 p->batch, p->heads, p->seq_len, p->head_dim);
-    GRL_REQUIRE((int64_t)p->batch * p->heads <= 65535, "batch*heads above 65535");
     GRL_REQUIRE(p->in_dtype == GRL_F32 || p->in_dtype == GRL_BF16, "unknown in_dtype");
     GRL_REQUIRE(p->out_dtype == GRL_F32 || p->out_dtype == GRL_BF16, "unknown out_dtype");
     GRL_REQUIRE(p->rope_mode >= GRL_ROPE_NONE && p->rope_mode <= GRL_ROPE_HALF, "unknown rope mode");

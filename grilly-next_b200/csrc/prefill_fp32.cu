@@ -231,6 +231,7 @@ static int dispatch_d(grl_device* dev, const FlashF32Args& a) {
 }
 
 int flash_fwd_simt(grl_device* dev, const grl_flash_params* p, float scale, const float2* rope) {
+    GRL_REQUIRE((int64_t)p->batch * p->heads <= 65535, "batch*heads above 65535 (grid y dimension of the fp32 kernel)");
     FlashF32Args a{p->q, p->k, p->v, p->o, p->batch, p->heads, p->seq_len, p->head_dim, scale,
                    p->causal, p->seq_lens, p->mask, p->mask ? p->mask_kind : GRL_MASK_NONE,
                    p->rope_mode, rope};

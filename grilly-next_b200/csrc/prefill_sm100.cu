@@ -68,7 +68,7 @@ struct Args {
     const int32_t* seq_lens;
     const float2* rope;   // (S, 64) cos/sin, or NULL
     int32_t* status;      // device int32[4]: [0] error code, [1] mask of stuck barriers, [2] block x, [3] block y
-    int B, H, S;
+    int B, H, S, n_qp;
     int causal, rope_mode;
     float scale_log2;
 };
@@ -202,7 +202,7 @@ __device__ unsigned long long g_timeline[TL_ROLES * TL_SLOTS];
 __device__ unsigned int g_timeline_n[TL_ROLES];
 __device__ int g_dbg_flags;   // experiment switches: 1 = softmax skips its math, 2 = softmax skips only the exp/pack/store phase
 #define DBG_FLAG(x) (g_dbg_flags & (x))
-#define TL_DECL(role, active) const int tl_role = (role); const bool tl_on = (active) && blockIdx.x == GRL_TIMELINE && blockIdx.y == 0; int tl_i = 0;
+#define TL_DECL(role, active) const int tl_role = (role); const bool tl_on = (active) && blockIdx.x == GRL_TIMELINE; int tl_i = 0;
 #define TL(tag) do { if (tl_on && tl_i < TL_SLOTS) { g_timeline[tl_role * TL_SLOTS + tl_i] = ((unsigned long long)(tag) << 48) | (clock64() & 0xffffffffffffULL); ++tl_i; g_timeline_n[tl_role] = tl_i; } } while (0)
 #else
 #define DBG_FLAG(x) 0
@@ -235,8 +235,8 @@ __device__ __forceinline__ bool wait_bar(const Ctx& c, int bar, uint32_t parity)
                 // [0] error code, [1] bit mask of the barriers that were being waited on, [2],[3] first CTA
                 atomicOr(reinterpret_cast<unsigned int*>(c.status) + 1, 1u << bar);
                 if (atomicCAS(c.status, 0, GRL_ERR_TIMEOUT) == 0) {
-                    c.status[2] = blockIdx.x | (parity << 16) | (threadIdx.x << 20);
-                    c.status[3] = blockIdx.y;
+                    c.status[2] = (parity << 16) | (threadIdx.x << 20);
+                    c.status[3] = blockIdx.x;
                 }
             }
             return false;
@@ -396,9 +396,13 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     uint8_t* smem = smem_raw + (base_addr - raw_addr);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n_qp = gridDim.x;                                                  // query tile pairs
-    const int qp = a.causal ? (n_qp - 1 - (int)blockIdx.x) : (int)blockIdx.x;   // longest first
-    const int bh = blockIdx.y, b = bh / a.H;
+    // 1-D grid over (batch*heads) x (query tile pairs).  Causal: the work of a tile pair grows with its index,
+    // so CTAs are handed out longest pair first across ALL heads and the shortest ones form the tail of the
+    // launch.  Otherwise all pairs cost the same and the pairs of one head stay adjacent (they share K/V in L2).
+    const int n_qp = a.n_qp, n_bh = a.B * a.H;
+    const int qp = a.causal ? (n_qp - 1 - (int)blockIdx.x / n_bh) : (int)blockIdx.x % n_qp;
+    const int bh = a.causal ? (int)blockIdx.x % n_bh : (int)blockIdx.x / n_qp;
+    const int b = bh / a.H;
     const int S = a.S;
     const int q0 = qp * (NQ * BM);
     const int len = a.seq_lens ? min(a.seq_lens[b], S) : S;
@@ -866,7 +870,8 @@ int flash_fwd_sm100(grl_device* dev, const grl_flash_params* p, float scale, con
     a.B = p->batch; a.H = p->heads; a.S = p->seq_len;
     a.causal = p->causal; a.rope_mode = p->rope_mode;
     a.scale_log2 = scale * 1.4426950408889634f;
-    dim3 grid((p->seq_len + NQ * BM - 1) / (NQ * BM), BH);
+    a.n_qp = (p->seq_len + NQ * BM - 1) / (NQ * BM);
+    dim3 grid((unsigned)BH * a.n_qp);
     if (p->out_dtype == GRL_F32) {
         auto kern = flash_fwd_sm100_kernel<float>;
         GRL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
