@@ -48,6 +48,7 @@ constexpr int SMEM_K = SMEM_Q + NQ * TILE_BYTES;
 constexpr int SMEM_V = SMEM_K + NSTAGE * TILE_BYTES;
 constexpr int SMEM_BAR = SMEM_V + NSTAGE * TILE_BYTES;
 constexpr int SMEM_TOTAL = SMEM_BAR + 256 + 1024;  // + barrier block + alignment slack
+constexpr int kHeadGroup = 32;      // (batch, head) slices scheduled together under a causal mask
 constexpr int BH = 64;              // keys per softmax step: S is computed in 64-key halves, double-buffered
 constexpr uint32_t TMEM_COLS = 512;
 // TMEM columns of query tile t: S half-buffer b at t*256 + b*64 (P overlays its first 32 columns),
@@ -397,11 +398,22 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     // 1-D grid over (batch*heads) x (query tile pairs).  Causal: the work of a tile pair grows with its index,
-    // so CTAs are handed out longest pair first across ALL heads and the shortest ones form the tail of the
-    // launch.  Otherwise all pairs cost the same and the pairs of one head stay adjacent (they share K/V in L2).
+    // so within a group of kHeadGroup heads CTAs are handed out longest pair first and the shortest ones form
+    // the tail; groups follow one another so that the K/V of the heads in flight (1 MiB per head at S=2048) stay
+    // in L2 between the pairs that share them.  Otherwise all pairs cost the same and the pairs of one head
+    // stay adjacent.
     const int n_qp = a.n_qp, n_bh = a.B * a.H;
-    const int qp = a.causal ? (n_qp - 1 - (int)blockIdx.x / n_bh) : (int)blockIdx.x % n_qp;
-    const int bh = a.causal ? (int)blockIdx.x % n_bh : (int)blockIdx.x / n_qp;
+    int qp, bh;
+    if (a.causal) {
+        const int per_group = kHeadGroup * n_qp;
+        const int g = (int)blockIdx.x / per_group, r = (int)blockIdx.x % per_group;
+        const int gsize = min(kHeadGroup, n_bh - g * kHeadGroup);
+        qp = n_qp - 1 - r / gsize;
+        bh = g * kHeadGroup + r % gsize;
+    } else {
+        qp = (int)blockIdx.x % n_qp;
+        bh = (int)blockIdx.x / n_qp;
+    }
     const int b = bh / a.H;
     const int S = a.S;
     const int q0 = qp * (NQ * BM);
