@@ -46,6 +46,23 @@ def decode_bytes(c):
     return kv + other
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one flash_fwd_sm100_kernel launch on cfg2 (ncu, see profiles/)
+PREFILL_TRAFFIC_BYTES = 208.9e6 + 103.1e6
+DECODE_TRAFFIC_BYTES = 546.1e6 + 11.0e6     # one decode_mma_kernel launch at cache length ~4117 (ncu, see profiles/)
+
+
+def prefill_roofline(tflops_gpu, timed_ms, pk):
+    """The prefill kernel against the measured cuBLAS bf16 rate: the burst figure when the timed region is
+    short (clocks still at boost), the sustained one when it runs long enough to sit under the power cap."""
+    long_run = timed_ms > 100.0 and pk["tf_sustained"]
+    peak = pk["tf_sustained"] if long_run else pk["tf"]
+    return {"bound": "tensor", "achieved": tflops_gpu, "peak": peak, "unit": "TFLOP/s", "frac": tflops_gpu / peak,
+            "traffic": PREFILL_TRAFFIC_BYTES, "peak_source": pk["src"] + (" (sustained: timed region > 100 ms)" if long_run else " (burst)"),
+            "frac_of_burst": tflops_gpu / pk["tf"],
+            "frac_of_sustained": tflops_gpu / pk["tf_sustained"] if pk["tf_sustained"] else None,
+            "frac_of_nominal_2250": tflops_gpu / 2250.0, "kernel": "flash_fwd_sm100_kernel"}
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -453,7 +470,7 @@ def cpu_baseline():
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-decode", action="store_true")
@@ -523,10 +540,7 @@ def main():
                    "flops_per_step_per_gpu": fl, "l2": "inputs larger than L2 (320 MiB per step)",
                    "parallelism": f"replica per GPU x{world}, no collective"},
         "clocks": clocks, "gpu_launches": int(launches),
-        "roofline": {"bound": "tensor", "achieved": tflops_gpu, "peak": pk["tf"], "unit": "TFLOP/s",
-                     "frac": tflops_gpu / pk["tf"], "traffic": None, "peak_source": pk["src"] + " (burst)",
-                     "frac_of_sustained": tflops_gpu / pk["tf_sustained"] if pk["tf_sustained"] else None,
-                     "frac_of_nominal_2250": tflops_gpu / 2250.0, "kernel": "flash_fwd_sm100_kernel"},
+        "roofline": prefill_roofline(tflops_gpu, ms, pk),
     }
 
     if not args.skip_decode:
@@ -538,7 +552,8 @@ def main():
                           "ms_per_step": dms / c["steps"], "workload": "cfg3: GQA decode B32 Hq32/Hkv8 D128 KV 4096->4352, 256 steps, bf16 paged cache, CUDA-graph replay, per GPU",
                           "gpu_launches": int(dl), "n_splits": nsplit,
                           "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
-                                       "traffic": None, "peak_source": pk["src"], "frac_of_nominal_8000": gbs / 8000.0,
+                                       "traffic": DECODE_TRAFFIC_BYTES, "peak_source": pk["src"], "frac_of_nominal_8000": gbs / 8000.0,
+                                       "note": "achieved = algorithmic bytes of the 256-step run / its time (append + decode + merge per step)",
                                        "kernel": "decode_mma_kernel"}}
 
     if not args.skip_decode and not args.skip_long:
