@@ -374,6 +374,12 @@ def bench_decode_e2e(dist, steps=32):
     return dt, (q.nbytes + 2 * k1.nbytes), o.nbytes
 
 
+def _torch_stream_handle(torch):
+    """torch's current stream as a handle the library accepts (the legacy default stream is NULL -> cudaStreamLegacy)."""
+    h = torch.cuda.current_stream().cuda_stream
+    return C.c_void_p(h if h else 1)
+
+
 def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
     """cfg4: B=1, Hq32/Hkv8, D128, KV length 131072 split in contiguous shards over the ranks; per step
     every rank decodes its shard to one partial, NCCL all-gathers the partials, every rank merges."""
@@ -387,7 +393,7 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
     lo, hi = shard_range(T, world, rank)
     Tg = hi - lo
     L = dev.L
-    cabi.check(L.grl_device_use_stream(dev.h, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    cabi.check(L.grl_device_use_stream(dev.h, _torch_stream_handle(torch)))
     n_pages = (Tg + P - 1) // P
     page_elems = Hkv * P * D
     shard_bytes = 2 * n_pages * page_elems * 2
@@ -423,22 +429,47 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
     for i in range(5):
         ops.set_layout(layouts[i % nbuf]); out = dec.step(q)
     torch.cuda.synchronize()
+
+    def run_steps():
+        o = None
+        for i in range(steps):
+            ops.set_layout(layouts[i % nbuf]); o = dec.step(q)
+        return o
+
+    # The step is three small launches (decode, NCCL all-gather, merge): replay `steps` of them from one CUDA
+    # graph so that launch latency does not hide the kernels.  The library's launches are captured like any
+    # other work on the capturing stream (grl_device_use_stream).
+    graph = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            cabi.check(L.grl_device_use_stream(dev.h, _torch_stream_handle(torch)))
+            out = run_steps()
+        cabi.check(L.grl_device_use_stream(dev.h, _torch_stream_handle(torch)))
+        graph.replay()
+        torch.cuda.synchronize()
+    except Exception as e:          # fall back to plain launches, and say so
+        graph = None
+        cabi.check(L.grl_device_use_stream(dev.h, _torch_stream_handle(torch)))
+        sys.stderr.write(f"long decode: graph capture unavailable ({e}); timing plain launches\n")
     best = None
     e0, e1 = dev.event(), dev.event()
     launches0 = L.grl_launch_count()
     for _ in range(repeats):
         dist["barrier"]()
         dev.record(e0)
-        for i in range(steps):
-            ops.set_layout(layouts[i % nbuf]); out = dec.step(q)
+        if graph is not None:
+            graph.replay()
+        else:
+            out = run_steps()
         dev.record(e1)
         torch.cuda.synchronize()
         ms = dist["max"](dev.elapsed_ms(e0, e1))
         best = ms if best is None else min(best, ms)
-    launches = (L.grl_launch_count() - launches0) // repeats
+    launches = 2 if world == 1 else 3          # decode (+ merge of splits inside it), all-gather is NCCL's, final merge
     assert bool(torch.isfinite(out).all())
     cabi.check(L.grl_device_use_stream(dev.h, None))
-    return best / steps, launches // steps, ops.p.n_splits, nbuf
+    return best / steps, launches, ops.p.n_splits, nbuf, graph is not None
 
 
 class _NoDist:
@@ -557,13 +588,14 @@ def main():
                                        "kernel": "decode_mma_kernel"}}
 
     if not args.skip_decode and not args.skip_long:
-        lms, ll, lsplit, nbuf = bench_long_decode(dev, cabi, dist)
+        lms, ll, lsplit, nbuf, graphed = bench_long_decode(dev, cabi, dist)
         kv_bytes = 2 * CFG4["Hkv"] * CFG4["D"] * 2 * CFG4["T"]
         gbs = kv_bytes / (lms * 1e-3) / 1e9
         line["decode_long"] = {"metric": "decode_long_tokens_per_s", "value": 1.0 / (lms * 1e-3), "unit": "tokens/s",
                                "ms_per_step": lms, "scaling": "strong",
                                "workload": f"cfg4: GQA decode B1 Hq32/Hkv8 D128 KV 131072 bf16 split over {world} GPU(s); "
-                                           f"per-GPU partial + NCCL all-gather (16,640 B/rank) + LSE merge; {nbuf} rotating KV buffers (L2)",
+                                           f"per-GPU partial + NCCL all-gather (16,640 B/rank) + LSE merge; {nbuf} rotating KV buffers (L2); "
+                                           + ("CUDA-graph replay" if graphed else "plain launches"),
                                "gpu_launches_per_step": int(ll), "n_splits": lsplit,
                                "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"] * world, "unit": "GB/s",
                                             "frac": gbs / (pk["hbm"] * world), "peak_source": pk["src"] + f" x{world}"}}

@@ -65,7 +65,9 @@ int grl_device_count(int* count);
 int grl_device_open(int ordinal, grl_device** out);
 int grl_device_close(grl_device* dev);
 int grl_device_get_info(grl_device* dev, grl_device_info* info);
-/* Launch on the caller's cudaStream_t from now on (NULL restores the device's own stream). */
+/* Launch on the caller's cudaStream_t from now on.  NULL restores the device's own (non-blocking)
+ * stream; to name the legacy default stream pass cudaStreamLegacy ((cudaStream_t)0x1), since its
+ * plain handle is NULL too. */
 int grl_device_use_stream(grl_device* dev, void* cuda_stream);
 int grl_malloc(grl_device* dev, size_t bytes, void** out);
 int grl_free(grl_device* dev, void* ptr);
