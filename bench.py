@@ -374,18 +374,12 @@ def bench_decode_e2e(dist, steps=32):
     return dt, (q.nbytes + 2 * k1.nbytes), o.nbytes
 
 
-def _torch_stream_handle(torch):
-    """torch's current stream as a handle the library accepts (the legacy default stream is NULL -> cudaStreamLegacy)."""
-    h = torch.cuda.current_stream().cuda_stream
-    return C.c_void_p(h if h else 1)
-
-
 def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
     """cfg4: B=1, Hq32/Hkv8, D128, KV length 131072 split in contiguous shards over the ranks; per step
     every rank decodes its shard to one partial, NCCL all-gathers the partials, every rank merges."""
     import torch
     import torch.distributed as td
-    from grilly_next.parallel import CudaShardOps, ShardedDecoder, shard_range
+    from grilly_next.parallel import CudaShardOps, ShardedDecoder, shard_range, torch_stream_handle
     from oracle import attention_oracle as orc
     c = CFG4
     B, Hq, Hkv, D, T, P = 1, c["Hq"], c["Hkv"], c["D"], c["T"], 64
@@ -393,7 +387,7 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
     lo, hi = shard_range(T, world, rank)
     Tg = hi - lo
     L = dev.L
-    cabi.check(L.grl_device_use_stream(dev.h, _torch_stream_handle(torch)))
+    cabi.check(L.grl_device_use_stream(dev.h, torch_stream_handle(torch)))
     n_pages = (Tg + P - 1) // P
     page_elems = Hkv * P * D
     shard_bytes = 2 * n_pages * page_elems * 2
@@ -443,14 +437,14 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
     try:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            cabi.check(L.grl_device_use_stream(dev.h, _torch_stream_handle(torch)))
+            cabi.check(L.grl_device_use_stream(dev.h, torch_stream_handle(torch)))
             out = run_steps()
-        cabi.check(L.grl_device_use_stream(dev.h, _torch_stream_handle(torch)))
+        cabi.check(L.grl_device_use_stream(dev.h, torch_stream_handle(torch)))
         graph.replay()
         torch.cuda.synchronize()
     except Exception as e:          # fall back to plain launches, and say so
         graph = None
-        cabi.check(L.grl_device_use_stream(dev.h, _torch_stream_handle(torch)))
+        cabi.check(L.grl_device_use_stream(dev.h, torch_stream_handle(torch)))
         sys.stderr.write(f"long decode: graph capture unavailable ({e}); timing plain launches\n")
     best = None
     e0, e1 = dev.event(), dev.event()

@@ -30,6 +30,13 @@ def owner_of_new_token(world: int) -> int:
     return world - 1
 
 
+def torch_stream_handle(torch):
+    """torch's current CUDA stream as a handle for grl_device_use_stream.  The legacy default stream's
+    handle is NULL, which the library reads as "back to your own stream": name it as cudaStreamLegacy."""
+    h = torch.cuda.current_stream().cuda_stream
+    return C.c_void_p(h if h else 1)
+
+
 def partial_floats(rows: int, head_dim: int) -> int:
     return rows * (head_dim + 2)
 
@@ -62,7 +69,8 @@ class ShardedDecoder:
 class CudaShardOps:
     """The two kernels of a step through the C ABI, on torch's current CUDA stream.
 
-    `dev` is a cabi.Device whose stream was set with grl_device_use_stream(torch stream); `layout`
+    `dev` is a cabi.Device whose stream was set with grl_device_use_stream(torch_stream_handle(torch)), so that
+    the kernels are ordered with torch's NCCL calls; `layout`
     the grl_kv_layout of this rank's shard; q / outputs are torch CUDA float32 tensors.
     """
 
