@@ -43,6 +43,10 @@ constexpr int kThreads = 512;      // four warpgroups: MMA + TMA (+2 idle warps)
 constexpr int WARP_MMA = 0, WARP_TMA = 1, WARP_MMA1 = 2, WARP_SOFTMAX0 = 4, WARP_ROT0 = 12;   // warp 3 idle
 // Register budget per warpgroup (setmaxnreg); 2*128*160 + 128*112 + 128*80 = 65536.
 constexpr int REGS_SOFTMAX = 160, REGS_ROPE = 112, REGS_MISC = 80;
+// setmaxnreg.inc is served only from what setmaxnreg.dec of the SAME CTA released (never from the SM's
+// unallocated registers): if the budgets exceeded threads x launch-bound registers, the increase would wait
+// forever.
+static_assert(2 * REGS_SOFTMAX + REGS_ROPE + REGS_MISC <= 4 * 128, "setmaxnreg budgets exceed the CTA's register allocation");
 constexpr int SMEM_Q = 0;
 constexpr int SMEM_K = SMEM_Q + NQ * TILE_BYTES;
 constexpr int SMEM_V = SMEM_K + NSTAGE * TILE_BYTES;
