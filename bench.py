@@ -418,6 +418,9 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
         return l
 
     ops = CudaShardOps(cabi, dev, layout(0), Hq, Tg, torch)
+    fused = False
+    if world > 1 and not os.environ.get("GRILLY_NO_P2P"):
+        fused = ops.setup_p2p(td)          # peers' inboxes over CUDA IPC; NCCL all-gather is the fallback
     dec = ShardedDecoder(td if world > 1 else _NoDist(), ops, lambda n, m: torch.empty((n, m), dtype=torch.float32, device="cuda"))
     layouts = [layout(i) for i in range(nbuf)]
     for i in range(5):
@@ -463,7 +466,7 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
     launches = 2 if world == 1 else 3          # decode (+ merge of splits inside it), all-gather is NCCL's, final merge
     assert bool(torch.isfinite(out).all())
     cabi.check(L.grl_device_use_stream(dev.h, None))
-    return best / steps, launches, ops.p.n_splits, nbuf, graph is not None
+    return best / steps, launches, ops.p.n_splits, nbuf, graph is not None, fused
 
 
 class _NoDist:
@@ -582,13 +585,15 @@ def main():
                                        "kernel": "decode_mma_kernel"}}
 
     if not args.skip_decode and not args.skip_long:
-        lms, ll, lsplit, nbuf, graphed = bench_long_decode(dev, cabi, dist)
+        lms, ll, lsplit, nbuf, graphed, fused = bench_long_decode(dev, cabi, dist)
         kv_bytes = 2 * CFG4["Hkv"] * CFG4["D"] * 2 * CFG4["T"]
         gbs = kv_bytes / (lms * 1e-3) / 1e9
         line["decode_long"] = {"metric": "decode_long_tokens_per_s", "value": 1.0 / (lms * 1e-3), "unit": "tokens/s",
                                "ms_per_step": lms, "scaling": "strong",
                                "workload": f"cfg4: GQA decode B1 Hq32/Hkv8 D128 KV 131072 bf16 split over {world} GPU(s); "
-                                           f"per-GPU partial + NCCL all-gather (16,640 B/rank) + LSE merge; {nbuf} rotating KV buffers (L2); "
+                                           f"per-GPU partial (16,640 B/rank) + "
+                                           + ("exchange over NVLink peer stores fused with the LSE merge" if fused else "NCCL all-gather + LSE merge")
+                                           + f"; {nbuf} rotating KV buffers (L2); "
                                            + ("CUDA-graph replay" if graphed else "plain launches"),
                                "gpu_launches_per_step": int(ll), "n_splits": lsplit,
                                "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"] * world, "unit": "GB/s",

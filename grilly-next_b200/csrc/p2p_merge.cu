@@ -1,0 +1,158 @@
+// Cross-GPU log-sum-exp merge over NVLink peer memory: the exchange step of the KV-sharded
+// long-context decode, fused with the merge.
+//
+// Every rank holds one un-normalised partial [O (rows*D) | m (rows) | l (rows)] of its KV shard.
+// Instead of an all-gather followed by a merge, ONE kernel per rank (a) stores the local partial
+// straight into every peer's inbox (plain st.global through NVLink, then a system-scope fence and
+// a flag with the step's sequence number), (b) waits -- bounded -- for the peers' flags in its own
+// inbox, and (c) merges.  The reference has no multi-GPU code; the merge arithmetic is that of
+// lse_merge_kernel.  Inboxes are double-buffered by step parity: a rank can be at most one step
+// ahead of a peer (it needs that peer's partial to finish a step), so the slot it overwrites was
+// consumed two steps ago.  No TMA, no multicast, no multimem: ordinary peer loads/stores only.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace grl {
+
+constexpr long long kPeerWaitLimitCycles = 1000000000LL;   // ~0.5 s: a missing peer ends in an error code, not a hang
+constexpr int kMaxPeers = 16;
+
+struct ExchangeArgs {
+    const float* local_part;       // this rank's partial (n floats)
+    float* inbox;                  // local: [2][world][n]
+    unsigned int* flags;           // local: [2][world]
+    float* peer_inbox[kMaxPeers];  // peers' inbox base pointers (peer address space mapped here)
+    unsigned int* peer_flags[kMaxPeers];
+    const unsigned int* seq;       // local step counter (already bumped for this step)
+    float* out;                    // (rows, D)
+    int32_t* status;
+    int rank, world, rows, D;
+};
+
+__global__ void bump_seq_kernel(unsigned int* seq) { *seq += 1; }
+
+// grid = rows CTAs of 128 threads.  CTA p < world, p != rank, first pushes to peer p.
+__global__ void __launch_bounds__(128) exchange_merge_kernel(ExchangeArgs a) {
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const unsigned int e = *a.seq;
+    const int par = e & 1;
+    const size_t n = (size_t)a.rows * (a.D + 2);
+    if (row < a.world && row != a.rank) {
+        float* dst = a.peer_inbox[row] + ((size_t)par * a.world + a.rank) * n;
+        const float4* src4 = reinterpret_cast<const float4*>(a.local_part);
+        float4* dst4 = reinterpret_cast<float4*>(dst);
+        for (size_t i = tid; i < n / 4; i += 128) dst4[i] = src4[i];
+        for (size_t i = (n / 4) * 4 + tid; i < n; i += 128) dst[i] = a.local_part[i];
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            volatile unsigned int* f = a.peer_flags[row] + par * a.world + a.rank;
+            *f = e;
+            __threadfence_system();
+        }
+    }
+    // wait for every peer's partial of this step
+    __shared__ int s_ok;
+    if (tid == 0) {
+        int ok = 1;
+        const long long t0 = clock64();
+        for (int r = 0; r < a.world && ok; ++r) {
+            if (r == a.rank) continue;
+            volatile unsigned int* f = a.flags + par * a.world + r;
+            while (*f != e) {
+                if (clock64() - t0 > kPeerWaitLimitCycles) {
+                    ok = 0;
+                    if (a.status && atomicCAS(a.status, 0, GRL_ERR_TIMEOUT) == 0) {
+                        a.status[1] = 0x200 | r;
+                        a.status[2] = (int)e;
+                        a.status[3] = a.rank;
+                    }
+                    break;
+                }
+            }
+        }
+        __threadfence_system();
+        s_ok = ok;
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    if (row >= a.rows) return;
+    // merge (same arithmetic as lse_merge_kernel); the local part is read in place
+    auto part = [&](int r) -> const float* {
+        return r == a.rank ? a.local_part : a.inbox + ((size_t)par * a.world + r) * n;
+    };
+    float mt = -1e30f;
+    for (int r = 0; r < a.world; ++r) mt = fmaxf(mt, __ldcv(part(r) + (size_t)a.rows * a.D + row));
+    float w[kMaxPeers], lt = 0.f;
+    for (int r = 0; r < a.world; ++r) {
+        const float* p = part(r) + (size_t)a.rows * a.D;
+        w[r] = __expf(__ldcv(p + row) - mt);
+        lt = fmaf(w[r], __ldcv(p + a.rows + row), lt);
+    }
+    for (int d = tid; d < a.D; d += 128) {
+        float o = 0.f;
+        for (int r = 0; r < a.world; ++r) o = fmaf(w[r], __ldcv(part(r) + (size_t)row * a.D + d), o);
+        a.out[(size_t)row * a.D + d] = lt > 0.f ? o / lt : 0.f;
+    }
+}
+
+}  // namespace grl
+
+using namespace grl;
+
+extern "C" {
+
+int grl_ipc_export(grl_device* dev, void* ptr, void* handle_out) {
+    GRL_REQUIRE(dev && ptr && handle_out, "NULL argument");
+    DeviceGuard g(dev->ordinal);
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    GRL_CUDA(cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(handle_out), ptr));
+    return GRL_OK;
+}
+
+int grl_ipc_import(grl_device* dev, const void* handle, void** ptr_out) {
+    GRL_REQUIRE(dev && handle && ptr_out, "NULL argument");
+    DeviceGuard g(dev->ordinal);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    GRL_CUDA(cudaIpcOpenMemHandle(ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+    return GRL_OK;
+}
+
+int grl_ipc_release(grl_device* dev, void* ptr) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    if (!ptr) return GRL_OK;
+    DeviceGuard g(dev->ordinal);
+    GRL_CUDA(cudaIpcCloseMemHandle(ptr));
+    return GRL_OK;
+}
+
+int grl_exchange_merge(grl_device* dev, const grl_exchange_params* p) {
+    GRL_REQUIRE(dev && p, "NULL argument");
+    GRL_REQUIRE(p->world >= 1 && p->world <= kMaxPeers && p->rank >= 0 && p->rank < p->world, "bad rank / world");
+    GRL_REQUIRE(p->rows > 0 && p->head_dim > 0, "bad shape");
+    GRL_REQUIRE(p->local_partial && p->inbox && p->flags && p->seq && p->out, "NULL buffer");
+    GRL_REQUIRE(p->peer_inbox && p->peer_flags, "NULL peer tables");
+    GRL_REQUIRE(((uintptr_t)p->local_partial % 16 == 0) && ((uintptr_t)p->inbox % 16 == 0) &&
+                    (((size_t)p->rows * (p->head_dim + 2) * 4) % 16 == 0),
+                "partials must be 16-byte aligned and a multiple of 16 bytes");
+    DeviceGuard g(dev->ordinal);
+    ExchangeArgs a{};
+    a.local_part = p->local_partial; a.inbox = p->inbox; a.flags = p->flags; a.seq = p->seq; a.out = p->out;
+    a.status = dev->d_status; a.rank = p->rank; a.world = p->world; a.rows = p->rows; a.D = p->head_dim;
+    for (int r = 0; r < p->world; ++r) {
+        GRL_REQUIRE(r == p->rank || (p->peer_inbox[r] && p->peer_flags[r]), "peer %d has no inbox", r);
+        a.peer_inbox[r] = p->peer_inbox[r];
+        a.peer_flags[r] = p->peer_flags[r];
+    }
+    dev->status_dirty = true;
+    bump_seq_kernel<<<1, 1, 0, dev->stream>>>(p->seq);
+    GRL_LAUNCHED("bump_seq_kernel");
+    const int ctas = p->rows > p->world ? p->rows : p->world;
+    exchange_merge_kernel<<<ctas, 128, 0, dev->stream>>>(a);
+    GRL_LAUNCHED("exchange_merge_kernel");
+    return GRL_OK;
+}
+
+}  // extern "C"

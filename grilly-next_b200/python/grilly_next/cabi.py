@@ -23,7 +23,8 @@ SYMBOLS = [
     "grl_event_record", "grl_event_elapsed_ms", "grl_graph_begin", "grl_graph_end", "grl_graph_launch",
     "grl_graph_destroy", "grl_launch_count", "grl_cast", "grl_flash_fwd", "grl_rope", "grl_attention_mask",
     "grl_kv_append", "grl_kv_gather", "grl_decode_pick_splits", "grl_decode_workspace_bytes", "grl_gqa_decode",
-    "grl_gqa_decode_static", "grl_lse_merge",
+    "grl_gqa_decode_static", "grl_lse_merge", "grl_ipc_export", "grl_ipc_import", "grl_ipc_release",
+    "grl_exchange_merge",
 ]
 
 
@@ -62,6 +63,13 @@ class DecodeParams(C.Structure):
                 ("scale", C.c_float), ("n_splits", C.c_int32), ("max_seq_len", C.c_int32),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("partial_out", C.c_void_p),
                 ("force_simt", C.c_int32)]
+
+
+class ExchangeParams(C.Structure):
+    _fields_ = [("local_partial", C.c_void_p), ("inbox", C.c_void_p), ("flags", C.c_void_p),
+                ("peer_inbox", C.POINTER(C.c_void_p)), ("peer_flags", C.POINTER(C.c_void_p)),
+                ("seq", C.c_void_p), ("out", C.c_void_p),
+                ("rank", C.c_int32), ("world", C.c_int32), ("rows", C.c_int32), ("head_dim", C.c_int32)]
 
 
 class GrlError(RuntimeError):
@@ -104,6 +112,10 @@ def lib():
         _lib.grl_kv_append.argtypes = [C.c_void_p, C.POINTER(AppendParams)]
         _lib.grl_gqa_decode.argtypes = [C.c_void_p, C.POINTER(DecodeParams)]
         _lib.grl_gqa_decode_static.argtypes = [C.c_void_p, C.POINTER(DecodeParams)]
+        _lib.grl_ipc_export.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+        _lib.grl_ipc_import.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]
+        _lib.grl_ipc_release.argtypes = [C.c_void_p, C.c_void_p]
+        _lib.grl_exchange_merge.argtypes = [C.c_void_p, C.POINTER(ExchangeParams)]
         _lib.grl_decode_pick_splits.argtypes = [C.c_void_p, C.POINTER(DecodeParams), C.POINTER(C.c_int)]
         _lib.grl_decode_workspace_bytes.argtypes = [C.POINTER(DecodeParams), C.c_int, C.POINTER(C.c_size_t)]
         _lib.grl_kv_gather.argtypes = [C.c_void_p, C.POINTER(KVLayout), C.c_int, C.c_int, C.c_void_p, C.c_void_p]

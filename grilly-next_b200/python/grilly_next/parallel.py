@@ -60,6 +60,8 @@ class ShardedDecoder:
         part = self.ops.partial(q)
         if self.world == 1:
             return self.ops.merge(part.reshape(1, -1), 1)
+        if getattr(self.ops, "p2p_ready", False):
+            return self.ops.exchange_merge()     # partials cross NVLink inside the merge kernel, no collective call
         if self._gather is None or self._gather.shape[1] != part.numel():
             self._gather = self.empty(self.world, part.numel())
         self.dist.all_gather_into_tensor(self._gather.reshape(-1), part)
@@ -89,6 +91,54 @@ class CudaShardOps:
         self.p = p
         self.part = torch.empty(partial_floats(self.rows, self.D), dtype=torch.float32, device="cuda")
         self.out = torch.empty((self.B, 1, self.Hq, self.D), dtype=torch.float32, device="cuda")
+
+    def setup_p2p(self, dist):
+        """Map every peer's inbox into this process (CUDA IPC) for the fused exchange + merge kernel.
+        Collective: every rank calls it once.  Falls back silently (p2p_ready stays False) if the
+        handles cannot be opened, e.g. without peer access between the GPUs."""
+        cabi, dev, L = self.cabi, self.dev, self.dev.L
+        world, rank = dist.get_world_size(), dist.get_rank()
+        n = partial_floats(self.rows, self.D)
+        self._inbox = dev.malloc(2 * world * n * 4)
+        self._flags = dev.malloc(2 * world * 4 + 64)
+        self._seq = dev.malloc(64)
+        for p_, nb in ((self._inbox, 2 * world * n * 4), (self._flags, 2 * world * 4 + 64), (self._seq, 64)):
+            cabi.check(L.grl_memset(dev.h, p_, 0, nb))
+        dev.sync()
+        hi, hf = (C.c_char * 64)(), (C.c_char * 64)()
+        cabi.check(L.grl_ipc_export(dev.h, self._inbox, hi))
+        cabi.check(L.grl_ipc_export(dev.h, self._flags, hf))
+        mine = (bytes(hi), bytes(hf))
+        handles = [None] * world
+        dist.all_gather_object(handles, mine)
+        self._peer_inbox = (C.c_void_p * world)()
+        self._peer_flags = (C.c_void_p * world)()
+        ok = True
+        for r in range(world):
+            if r == rank:
+                continue
+            for raw, table in ((handles[r][0], self._peer_inbox), (handles[r][1], self._peer_flags)):
+                ptr = C.c_void_p()
+                if L.grl_ipc_import(dev.h, C.create_string_buffer(raw, 64), C.byref(ptr)) != 0:
+                    ok = False
+                table[r] = ptr.value
+        flags = [ok]
+        all_ok = [None] * world
+        dist.all_gather_object(all_ok, ok)
+        dist.barrier()            # nobody stores into an inbox before everybody has zeroed and exported it
+        self.p2p_ready = all(all_ok)
+        e = cabi.ExchangeParams()
+        e.local_partial, e.inbox, e.flags = self.part.data_ptr(), self._inbox, self._flags
+        e.peer_inbox = C.cast(self._peer_inbox, C.POINTER(C.c_void_p))
+        e.peer_flags = C.cast(self._peer_flags, C.POINTER(C.c_void_p))
+        e.seq, e.out = self._seq, self.out.data_ptr()
+        e.rank, e.world, e.rows, e.head_dim = rank, world, self.rows, self.D
+        self._exchange = e
+        return self.p2p_ready
+
+    def exchange_merge(self):
+        self.cabi.check(self.dev.L.grl_exchange_merge(self.dev.h, C.byref(self._exchange)))
+        return self.out
 
     def set_layout(self, layout):
         self.p.kv = layout

@@ -217,6 +217,33 @@ int grl_gqa_decode_static(grl_device* dev, const grl_decode_params* p);
 int grl_lse_merge(grl_device* dev, const float* parts, int n_parts, size_t part_stride, int rows,
                   int head_dim, int normalise, float* out);
 
+/* ---- cross-GPU merge over NVLink peer memory (one process per GPU).  No counterpart in the
+ * reference, which has no multi-GPU code; it is the exchange step of the KV-sharded decode.
+ * grl_ipc_export / grl_ipc_import / grl_ipc_release wrap the CUDA IPC handle (64 bytes) of a
+ * grl_malloc'ed buffer so that ranks can map one another's inboxes.
+ * grl_exchange_merge: stores this rank's partial (layout of grl_gqa_decode's partial_out, n =
+ * rows*(head_dim+2) floats) into every peer's inbox, waits -- at most ~0.5 s, then GRL_ERR_TIMEOUT
+ * through grl_sync -- for the peers' partials of the same step, and writes the normalised merge to
+ * out.  inbox: local float[2][world][n]; flags: local uint32[2][world], zero before the first step;
+ * seq: local uint32 step counter, zero before the first step (the call increments it on the
+ * device, so a captured CUDA graph can be replayed); peer_inbox / peer_flags: HOST arrays of
+ * `world` device pointers (imported; the entry of this rank is ignored).  Every rank must make the
+ * same sequence of calls. */
+typedef struct {
+    const float* local_partial;
+    float* inbox;
+    uint32_t* flags;
+    float* const* peer_inbox;
+    uint32_t* const* peer_flags;
+    uint32_t* seq;
+    float* out;
+    int32_t rank, world, rows, head_dim;
+} grl_exchange_params;
+int grl_ipc_export(grl_device* dev, void* ptr, void* handle_out_64_bytes);
+int grl_ipc_import(grl_device* dev, const void* handle_64_bytes, void** ptr_out);
+int grl_ipc_release(grl_device* dev, void* ptr);
+int grl_exchange_merge(grl_device* dev, const grl_exchange_params* p);
+
 #ifdef __cplusplus
 }
 #endif
