@@ -374,7 +374,7 @@ def bench_decode_e2e(dist, steps=32):
     return dt, (q.nbytes + 2 * k1.nbytes), o.nbytes
 
 
-def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
+def bench_long_decode(dev, cabi, dist, steps=50, repeats=3, n_splits=0):
     """cfg4: B=1, Hq32/Hkv8, D128, KV length 131072 split in contiguous shards over the ranks; per step
     every rank decodes its shard to one partial, NCCL all-gathers the partials, every rank merges."""
     import torch
@@ -417,7 +417,7 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
         l.batch, l.num_kv_heads, l.head_dim, l.page_tokens, l.max_pages, l.num_pages = B, Hkv, D, P, n_pages, n_pages
         return l
 
-    ops = CudaShardOps(cabi, dev, layout(0), Hq, Tg, torch)
+    ops = CudaShardOps(cabi, dev, layout(0), Hq, Tg, torch, n_splits=n_splits)
     fused = False
     if world > 1 and not os.environ.get("GRILLY_NO_P2P"):
         fused = ops.setup_p2p(td)          # peers' inboxes over CUDA IPC; NCCL all-gather is the fallback
