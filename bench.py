@@ -418,9 +418,12 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3, n_splits=0):
         return l
 
     ops = CudaShardOps(cabi, dev, layout(0), Hq, Tg, torch, n_splits=n_splits)
-    fused = False
-    if world > 1 and not os.environ.get("GRILLY_NO_P2P"):
-        fused = ops.setup_p2p(td)          # peers' inboxes over CUDA IPC; NCCL all-gather is the fallback
+    fused = ""
+    mode = os.environ.get("GRILLY_EXCHANGE", "decode")     # profiling aid: "nccl" | "merge" | "decode"
+    if world > 1 and mode != "nccl":
+        # peers' inboxes over CUDA IPC; NCCL all-gather is the fallback
+        if ops.setup_p2p(td, one_launch=(mode == "decode")):
+            fused = "decode" if ops.one_launch else "merge"
     dec = ShardedDecoder(td if world > 1 else _NoDist(), ops, lambda n, m: torch.empty((n, m), dtype=torch.float32, device="cuda"))
     layouts = [layout(i) for i in range(nbuf)]
     for i in range(5):
@@ -592,7 +595,9 @@ def main():
                                "ms_per_step": lms, "scaling": "strong",
                                "workload": f"cfg4: GQA decode B1 Hq32/Hkv8 D128 KV 131072 bf16 split over {world} GPU(s); "
                                            f"per-GPU partial (16,640 B/rank) + "
-                                           + ("exchange over NVLink peer stores fused with the LSE merge" if fused else "NCCL all-gather + LSE merge")
+                                           + {"decode": "exchange over NVLink peer stores and LSE merge inside the decode kernel (one launch per step)",
+                                              "merge": "exchange over NVLink peer stores fused with the LSE merge",
+                                              "": "NCCL all-gather + LSE merge" if world > 1 else "LSE merge"}[fused]
                                            + f"; {nbuf} rotating KV buffers (L2); "
                                            + ("CUDA-graph replay" if graphed else "plain launches"),
                                "gpu_launches_per_step": int(ll), "n_splits": lsplit,

@@ -22,8 +22,12 @@ struct grl_device {
     // (positions, head_dim, theta bits, scaling bits).
     std::map<std::tuple<int, int, uint32_t, uint32_t>, float2*> rope_tables;
     // Status word written by kernels with bounded waits; read back by grl_sync when dirty.
-    int32_t* d_status = nullptr;   // device int32[4]
+    int32_t* d_status = nullptr;   // device int32[4], followed by the arrival counters below
     bool status_dirty = false;
+    // Arrival counters of the split-KV decode (one per (sequence, kv head), zero between launches: the
+    // CTA that brings a counter to its final value resets it) and, last, the count of finished heads.
+    static constexpr int kCounterSlots = 4096;
+    int32_t* d_counters = nullptr;   // = d_status + 4, int32[kCounterSlots + 1]
 };
 
 struct grl_event {
@@ -38,6 +42,19 @@ struct grl_graph {
 namespace grl {
 
 int set_error(int code, const char* fmt, ...);
+
+// Peer inboxes of the cross-GPU merge, by value in kernel parameters (filled from grl_exchange_params).
+constexpr int kMaxPeers = 16;
+constexpr long long kPeerWaitLimitCycles = 1000000000LL;   // ~0.5 s: a missing peer ends in an error code, not a hang
+struct PeerExchange {
+    float* inbox;                        // local: [2][world][n]
+    unsigned int* flags;                 // local: [2][world][flag_slots]
+    float* peer_inbox[kMaxPeers];        // the peers' inboxes mapped into this process
+    unsigned int* peer_flags[kMaxPeers];
+    unsigned int* seq;                   // local step counter
+    int rank, world, flag_slots;
+};
+int fill_peer_exchange(const grl_exchange_params* p, PeerExchange* x);
 extern std::atomic<long long> g_launches;
 
 #define GRL_CUDA(call)                                                                       \

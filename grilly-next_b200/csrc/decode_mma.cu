@@ -38,7 +38,14 @@ struct Args {
     int B, Hq, Hkv, max_pages, n_splits, group;
     float scale;
     int direct;
+    // fused merge: the last CTA of a (sequence, kv head) to arrive merges the head's splits
+    int fuse;               // 0: leave the splits to lse_merge_kernel
+    int32_t* counters;      // arrival counters, zero between launches; [kDoneSlot] counts finished heads
+    float* partial_out;     // != NULL: merged rows leave un-normalised as [O | m | l]
+    PeerExchange x;         // x.world > 1: the merged rows are exchanged with the peers and merged again
 };
+constexpr int kDoneSlot = grl_device::kCounterSlots;
+constexpr int kMaxFusedSplits = 256;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -315,6 +322,155 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             }
         }
     }
+    if (a.direct || !a.fuse) return;
+
+    // ---- fused merge: whoever arrives last for this (sequence, kv head) combines its splits
+    __threadfence();
+    __syncthreads();
+    int* s_flag = reinterpret_cast<int*>(smem + SMEM_BAR + 2 * NST * 8 + 8);
+    const int slot = b * a.Hkv + kvh;
+    if (tid == 0) {
+        const int t = atomicAdd(&a.counters[slot], 1);
+        const int last = (t == a.n_splits - 1);
+        if (last) a.counters[slot] = 0;          // nobody else touches the slot before the next launch
+        *s_flag = last;
+    }
+    __syncthreads();
+    if (!*s_flag) return;
+    __threadfence();
+    float* sm_w = reinterpret_cast<float*>(smem);              // [8 heads][256 splits]: m, then the weights
+    float* sm_ls = sm_w + 8 * kMaxFusedSplits;                 // [8][256]: l of every split
+    float* sm_mt = sm_ls + 8 * kMaxFusedSplits;                // [8] max (natural log), [8] l
+    float* sm_res = sm_mt + 16;                                // [8][128] merged un-normalised rows
+    const size_t pstride = (size_t)rows * (D + 2);
+    const int row0 = b * a.Hq + kvh * a.group;
+    for (int idx = tid; idx < a.group * a.n_splits; idx += kThreads) {
+        const int h = idx / a.n_splits, s = idx % a.n_splits;
+        const float* ml = a.part + (size_t)s * pstride + (size_t)rows * D + row0 + h;
+        sm_w[h * kMaxFusedSplits + s] = __ldcg(ml);
+        sm_ls[h * kMaxFusedSplits + s] = __ldcg(ml + rows);
+    }
+    __syncthreads();
+    for (int h = warp; h < a.group; h += kThreads / 32) {
+        float mt = kEmpty;
+        for (int s = lane; s < a.n_splits; s += 32) mt = fmaxf(mt, sm_w[h * kMaxFusedSplits + s]);
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, sh));
+        float lt = 0.f;
+        for (int s = lane; s < a.n_splits; s += 32) {
+            const float w = __expf(sm_w[h * kMaxFusedSplits + s] - mt);
+            sm_w[h * kMaxFusedSplits + s] = w;
+            lt = fmaf(w, sm_ls[h * kMaxFusedSplits + s], lt);
+        }
+#pragma unroll
+        for (int sh = 16; sh > 0; sh >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, sh);
+        if (lane == 0) { sm_mt[h] = mt; sm_mt[8 + h] = lt; }
+    }
+    __syncthreads();
+    const PeerExchange& x = a.x;
+    const bool exchange = x.world > 1;
+    unsigned int e = 0;
+    int par = 0;
+    if (exchange) { e = *x.seq + 1; par = e & 1; }
+    for (int idx = tid; idx < a.group * D; idx += kThreads) {
+        const int h = idx / D, d = idx % D;
+        float ov = 0.f;
+        const float* col = a.part + (size_t)(row0 + h) * D + d;
+        int s = 0;
+        for (; s + 8 <= a.n_splits; s += 8) {       // eight loads in flight: the chain is latency, not bandwidth
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __ldcg(col + (size_t)(s + j) * pstride);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ov = fmaf(sm_w[h * kMaxFusedSplits + s + j], v[j], ov);
+        }
+        for (; s < a.n_splits; ++s) ov = fmaf(sm_w[h * kMaxFusedSplits + s], __ldcg(col + (size_t)s * pstride), ov);
+        const float lt = sm_mt[8 + h];
+        if (exchange) {
+            sm_res[idx] = ov;
+            for (int r = 0; r < x.world; ++r)
+                if (r != x.rank) x.peer_inbox[r][((size_t)par * x.world + x.rank) * pstride + (size_t)(row0 + h) * D + d] = ov;
+        } else if (a.partial_out) {
+            a.partial_out[(size_t)(row0 + h) * D + d] = ov;
+        } else {
+            a.out[(size_t)(row0 + h) * D + d] = lt > 0.f ? ov / lt : 0.f;
+        }
+    }
+    if (!exchange) {
+        if (a.partial_out && tid < a.group) {
+            a.partial_out[(size_t)rows * D + row0 + tid] = sm_mt[tid];
+            a.partial_out[(size_t)rows * D + rows + row0 + tid] = sm_mt[8 + tid];
+        }
+        return;
+    }
+
+    // ---- cross-GPU exchange of this head's rows: plain stores into the peers' inboxes, then a flag
+    if (tid < a.group) {
+        for (int r = 0; r < x.world; ++r) {
+            if (r == x.rank) continue;
+            float* dst = x.peer_inbox[r] + ((size_t)par * x.world + x.rank) * pstride + (size_t)rows * D;
+            dst[row0 + tid] = sm_mt[tid];
+            dst[rows + row0 + tid] = sm_mt[8 + tid];
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < x.world && tid != x.rank) {
+        __threadfence_system();
+        volatile unsigned int* f = x.peer_flags[tid] + (size_t)(par * x.world + x.rank) * x.flag_slots + slot;
+        *f = e;
+    }
+    if (tid == 0) {
+        int ok = 1;
+        const long long t0 = clock64();
+        for (int r = 0; r < x.world && ok; ++r) {
+            if (r == x.rank) continue;
+            volatile unsigned int* f = x.flags + (size_t)(par * x.world + r) * x.flag_slots + slot;
+            while (*f != e) {
+                if (clock64() - t0 > kPeerWaitLimitCycles) {
+                    ok = 0;
+                    if (a.status && atomicCAS(a.status, 0, GRL_ERR_TIMEOUT) == 0) {
+                        a.status[1] = 0x200 | r;
+                        a.status[2] = (int)e;
+                        a.status[3] = x.rank;
+                    }
+                    break;
+                }
+            }
+        }
+        __threadfence_system();
+        *s_flag = ok;
+    }
+    __syncthreads();
+    if (*s_flag) {
+        for (int idx = tid; idx < a.group * D; idx += kThreads) {
+            const int h = idx / D, d = idx % D;
+            auto m_of = [&](int r) {
+                return r == x.rank ? sm_mt[h]
+                                   : __ldcv(x.inbox + ((size_t)par * x.world + r) * pstride + (size_t)rows * D + row0 + h);
+            };
+            float mt = sm_mt[h];
+            for (int r = 0; r < x.world; ++r) mt = fmaxf(mt, m_of(r));
+            float ov = 0.f, lt = 0.f;
+            for (int r = 0; r < x.world; ++r) {
+                const float w = __expf(m_of(r) - mt);
+                const float* in = x.inbox + ((size_t)par * x.world + r) * pstride;
+                const float orow = r == x.rank ? sm_res[idx] : __ldcv(in + (size_t)(row0 + h) * D + d);
+                const float lrow = r == x.rank ? sm_mt[8 + h] : __ldcv(in + (size_t)rows * D + rows + row0 + h);
+                ov = fmaf(w, orow, ov);
+                lt = fmaf(w, lrow, lt);
+            }
+            a.out[(size_t)(row0 + h) * D + d] = lt > 0.f ? ov / lt : 0.f;
+        }
+    }
+    // the head that finishes last advances the step counter for the next launch (every head has read it by then)
+    if (tid == 0 && *s_flag) {
+        const int heads = a.B * a.Hkv;
+        if (atomicAdd(&a.counters[kDoneSlot], 1) == heads - 1) {
+            a.counters[kDoneSlot] = 0;
+            *x.seq = e;
+        }
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -351,7 +507,7 @@ bool decode_mma_supported(const grl_decode_params* p) {
            ((uintptr_t)kv.k_pages % 16 == 0) && ((uintptr_t)kv.v_pages % 16 == 0) && ((uintptr_t)p->q % 8 == 0);
 }
 
-int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits, float scale, bool direct) {
+int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits, float scale, bool direct, bool fuse) {
     using namespace dmma;
     const grl_kv_layout& kv = p->kv;
     const uint64_t pages = kv.num_pages > 0 ? (uint64_t)kv.num_pages : (uint64_t)kv.batch * kv.max_pages;
@@ -366,11 +522,24 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
     a.B = kv.batch; a.Hq = p->num_q_heads; a.Hkv = kv.num_kv_heads; a.max_pages = kv.max_pages;
     a.n_splits = n_splits; a.group = p->num_q_heads / kv.num_kv_heads;
     a.scale = scale; a.direct = direct ? 1 : 0;
+    a.fuse = fuse ? 1 : 0; a.counters = dev->d_counters; a.partial_out = p->partial_out;
+    a.x.world = 1;
+    if (p->exchange) {
+        GRL_REQUIRE(fuse && !direct, "the fused cross-GPU merge needs the split-KV path");
+        rc = fill_peer_exchange(p->exchange, &a.x);
+        if (rc) return rc;
+        const int heads = kv.batch * kv.num_kv_heads;
+        GRL_REQUIRE(heads <= dev->prop.multiProcessorCount,
+                    "fused cross-GPU merge: B*Hkv = %d exceeds the %d SMs (waiting CTAs must leave room for the rest)",
+                    heads, dev->prop.multiProcessorCount);
+        GRL_REQUIRE(a.x.flag_slots >= heads, "fused cross-GPU merge: flag_slots %d < B*Hkv %d", a.x.flag_slots, heads);
+        GRL_REQUIRE(p->out, "out is NULL");
+    }
     dev->status_dirty = true;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[64] = {};
+    if (!attr_set[dev->ordinal & 63]) {      // a function attribute belongs to the device that was current
         GRL_CUDA(cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
-        attr_set = true;
+        attr_set[dev->ordinal & 63] = true;
     }
     dim3 grid(n_splits, kv.num_kv_heads, kv.batch);
     decode_mma_kernel<<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tk, tv, a);

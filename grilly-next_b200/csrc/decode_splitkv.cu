@@ -7,7 +7,7 @@
 namespace grl {
 
 bool decode_mma_supported(const grl_decode_params* p);
-int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits, float scale, bool direct);
+int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits, float scale, bool direct, bool fuse);
 
 constexpr float kEmptyMax = -1e30f;  // running max of a part that saw no token (finite on purpose)
 constexpr int kDecodeThreads = 128;
@@ -333,7 +333,7 @@ int grl_gqa_decode(grl_device* dev, const grl_decode_params* p) {
     if (rc) return rc;
     const grl_kv_layout& kv = p->kv;
     const int D = kv.head_dim;
-    const bool direct = (n_splits == 1) && !p->partial_out;
+    const bool direct = (n_splits == 1) && !p->partial_out && !p->exchange;
     size_t need = 0;
     grl_decode_workspace_bytes(p, n_splits, &need);
     if (!direct)
@@ -347,12 +347,18 @@ int grl_gqa_decode(grl_device* dev, const grl_decode_params* p) {
     a.max_pages = kv.max_pages; a.n_splits = n_splits; a.group = p->num_q_heads / kv.num_kv_heads;
     a.scale = p->scale == 0.f ? 1.f / sqrtf((float)D) : p->scale;
     a.direct = direct ? 1 : 0;
-    if (decode_mma_supported(p) && !p->force_simt)
-        rc = decode_mma_launch(dev, p, n_splits, a.scale, direct);
+    const bool mma = decode_mma_supported(p) && !p->force_simt;
+    // the tensor-core kernel merges its own splits (last CTA of a head to arrive) when its counters can hold the heads
+    const bool fused = mma && !direct && n_splits <= 256 && kv.batch * kv.num_kv_heads <= grl_device::kCounterSlots;
+    GRL_REQUIRE(!p->exchange || fused,
+                "the cross-GPU merge inside the decode needs the tensor-core geometry (bf16 cache, head_dim 128, "
+                "64-token pages); use partial_out and grl_exchange_merge instead");
+    if (mma)
+        rc = decode_mma_launch(dev, p, n_splits, a.scale, direct, fused);
     else
         rc = (kv.cache_dtype == GRL_BF16) ? dispatch_decode_d<__nv_bfloat16>(dev, a, D)
                                           : dispatch_decode_d<float>(dev, a, D);
-    if (rc || direct) return rc;
+    if (rc || direct || fused) return rc;
     const int rows = kv.batch * p->num_q_heads;
     const size_t stride = (size_t)rows * (D + 2);
     if (p->partial_out)

@@ -122,8 +122,9 @@ int grl_device_open(int ordinal, grl_device** out) {
         return set_error(GRL_ERR_CUDA, "device open failed: %s", cudaGetErrorString(e));
     }
     d->stream = d->own_stream;
-    if (cudaMalloc(&d->d_status, 4 * sizeof(int32_t)) != cudaSuccess ||
-        cudaMemset(d->d_status, 0, 4 * sizeof(int32_t)) != cudaSuccess) {
+    const size_t status_bytes = (4 + grl_device::kCounterSlots + 1) * sizeof(int32_t);
+    if (cudaMalloc(&d->d_status, status_bytes) != cudaSuccess ||
+        cudaMemset(d->d_status, 0, status_bytes) != cudaSuccess) {
         cudaStreamDestroy(d->own_stream);
         delete d;
         return set_error(GRL_ERR_OOM, "could not allocate the device status word");
@@ -136,6 +137,7 @@ int grl_device_open(int ordinal, grl_device** out) {
         return set_error(GRL_ERR_UNSUPPORTED,
                          "this library is built for sm_100a only; device %d is sm_%d%d", ordinal, maj, min);
     }
+    d->d_counters = d->d_status + 4;
     *out = d;
     return GRL_OK;
 }
@@ -235,7 +237,8 @@ static int check_kernel_status(grl_device* dev) {
     GRL_CUDA(cudaMemcpyAsync(st, dev->d_status, sizeof(st), cudaMemcpyDeviceToHost, dev->stream));
     GRL_CUDA(cudaStreamSynchronize(dev->stream));
     if (st[0] == 0) return GRL_OK;
-    GRL_CUDA(cudaMemsetAsync(dev->d_status, 0, sizeof(st), dev->stream));
+    // a kernel that gave up may have left arrival counters half-way: clear them with the status
+    GRL_CUDA(cudaMemsetAsync(dev->d_status, 0, (4 + grl_device::kCounterSlots + 1) * sizeof(int32_t), dev->stream));
     return set_error(st[0] == GRL_ERR_TIMEOUT ? GRL_ERR_TIMEOUT : GRL_ERR_KERNEL,
                      "kernel reported failure %d (stuck barrier mask 0x%x, first block %d,%d)", st[0], st[1], st[2], st[3]);
 }

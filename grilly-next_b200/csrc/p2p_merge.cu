@@ -15,31 +15,40 @@
 
 namespace grl {
 
-constexpr long long kPeerWaitLimitCycles = 1000000000LL;   // ~0.5 s: a missing peer ends in an error code, not a hang
-constexpr int kMaxPeers = 16;
-
 struct ExchangeArgs {
     const float* local_part;       // this rank's partial (n floats)
-    float* inbox;                  // local: [2][world][n]
-    unsigned int* flags;           // local: [2][world]
-    float* peer_inbox[kMaxPeers];  // peers' inbox base pointers (peer address space mapped here)
-    unsigned int* peer_flags[kMaxPeers];
-    const unsigned int* seq;       // local step counter (already bumped for this step)
+    PeerExchange x;                // seq already bumped for this step
     float* out;                    // (rows, D)
     int32_t* status;
-    int rank, world, rows, D;
+    int rows, D;
 };
+
+int fill_peer_exchange(const grl_exchange_params* p, PeerExchange* x) {
+    GRL_REQUIRE(p->world >= 1 && p->world <= kMaxPeers && p->rank >= 0 && p->rank < p->world, "bad rank / world");
+    GRL_REQUIRE(p->inbox && p->flags && p->seq, "NULL buffer");
+    GRL_REQUIRE(p->peer_inbox && p->peer_flags, "NULL peer tables");
+    GRL_REQUIRE((uintptr_t)p->inbox % 16 == 0, "inbox must be 16-byte aligned");
+    x->inbox = p->inbox; x->flags = p->flags; x->seq = p->seq;
+    x->rank = p->rank; x->world = p->world; x->flag_slots = p->flag_slots > 0 ? p->flag_slots : 1;
+    for (int r = 0; r < p->world; ++r) {
+        GRL_REQUIRE(r == p->rank || (p->peer_inbox[r] && p->peer_flags[r]), "peer %d has no inbox", r);
+        x->peer_inbox[r] = p->peer_inbox[r];
+        x->peer_flags[r] = p->peer_flags[r];
+    }
+    return GRL_OK;
+}
 
 __global__ void bump_seq_kernel(unsigned int* seq) { *seq += 1; }
 
 // grid = rows CTAs of 128 threads.  CTA p < world, p != rank, first pushes to peer p.
 __global__ void __launch_bounds__(128) exchange_merge_kernel(ExchangeArgs a) {
     const int row = blockIdx.x, tid = threadIdx.x;
-    const unsigned int e = *a.seq;
+    const PeerExchange& x = a.x;
+    const unsigned int e = *x.seq;
     const int par = e & 1;
     const size_t n = (size_t)a.rows * (a.D + 2);
-    if (row < a.world && row != a.rank) {
-        float* dst = a.peer_inbox[row] + ((size_t)par * a.world + a.rank) * n;
+    if (row < x.world && row != x.rank) {
+        float* dst = x.peer_inbox[row] + ((size_t)par * x.world + x.rank) * n;
         const float4* src4 = reinterpret_cast<const float4*>(a.local_part);
         float4* dst4 = reinterpret_cast<float4*>(dst);
         for (size_t i = tid; i < n / 4; i += 128) dst4[i] = src4[i];
@@ -47,7 +56,7 @@ __global__ void __launch_bounds__(128) exchange_merge_kernel(ExchangeArgs a) {
         __threadfence_system();
         __syncthreads();
         if (tid == 0) {
-            volatile unsigned int* f = a.peer_flags[row] + par * a.world + a.rank;
+            volatile unsigned int* f = x.peer_flags[row] + (size_t)(par * x.world + x.rank) * x.flag_slots;
             *f = e;
             __threadfence_system();
         }
@@ -57,16 +66,16 @@ __global__ void __launch_bounds__(128) exchange_merge_kernel(ExchangeArgs a) {
     if (tid == 0) {
         int ok = 1;
         const long long t0 = clock64();
-        for (int r = 0; r < a.world && ok; ++r) {
-            if (r == a.rank) continue;
-            volatile unsigned int* f = a.flags + par * a.world + r;
+        for (int r = 0; r < x.world && ok; ++r) {
+            if (r == x.rank) continue;
+            volatile unsigned int* f = x.flags + (size_t)(par * x.world + r) * x.flag_slots;
             while (*f != e) {
                 if (clock64() - t0 > kPeerWaitLimitCycles) {
                     ok = 0;
                     if (a.status && atomicCAS(a.status, 0, GRL_ERR_TIMEOUT) == 0) {
                         a.status[1] = 0x200 | r;
                         a.status[2] = (int)e;
-                        a.status[3] = a.rank;
+                        a.status[3] = x.rank;
                     }
                     break;
                 }
@@ -80,19 +89,19 @@ __global__ void __launch_bounds__(128) exchange_merge_kernel(ExchangeArgs a) {
     if (row >= a.rows) return;
     // merge (same arithmetic as lse_merge_kernel); the local part is read in place
     auto part = [&](int r) -> const float* {
-        return r == a.rank ? a.local_part : a.inbox + ((size_t)par * a.world + r) * n;
+        return r == x.rank ? a.local_part : x.inbox + ((size_t)par * x.world + r) * n;
     };
     float mt = -1e30f;
-    for (int r = 0; r < a.world; ++r) mt = fmaxf(mt, __ldcv(part(r) + (size_t)a.rows * a.D + row));
+    for (int r = 0; r < x.world; ++r) mt = fmaxf(mt, __ldcv(part(r) + (size_t)a.rows * a.D + row));
     float w[kMaxPeers], lt = 0.f;
-    for (int r = 0; r < a.world; ++r) {
+    for (int r = 0; r < x.world; ++r) {
         const float* p = part(r) + (size_t)a.rows * a.D;
         w[r] = __expf(__ldcv(p + row) - mt);
         lt = fmaf(w[r], __ldcv(p + a.rows + row), lt);
     }
     for (int d = tid; d < a.D; d += 128) {
         float o = 0.f;
-        for (int r = 0; r < a.world; ++r) o = fmaf(w[r], __ldcv(part(r) + (size_t)row * a.D + d), o);
+        for (int r = 0; r < x.world; ++r) o = fmaf(w[r], __ldcv(part(r) + (size_t)row * a.D + d), o);
         a.out[(size_t)row * a.D + d] = lt > 0.f ? o / lt : 0.f;
     }
 }
@@ -130,22 +139,16 @@ int grl_ipc_release(grl_device* dev, void* ptr) {
 
 int grl_exchange_merge(grl_device* dev, const grl_exchange_params* p) {
     GRL_REQUIRE(dev && p, "NULL argument");
-    GRL_REQUIRE(p->world >= 1 && p->world <= kMaxPeers && p->rank >= 0 && p->rank < p->world, "bad rank / world");
     GRL_REQUIRE(p->rows > 0 && p->head_dim > 0, "bad shape");
-    GRL_REQUIRE(p->local_partial && p->inbox && p->flags && p->seq && p->out, "NULL buffer");
-    GRL_REQUIRE(p->peer_inbox && p->peer_flags, "NULL peer tables");
-    GRL_REQUIRE(((uintptr_t)p->local_partial % 16 == 0) && ((uintptr_t)p->inbox % 16 == 0) &&
-                    (((size_t)p->rows * (p->head_dim + 2) * 4) % 16 == 0),
+    GRL_REQUIRE(p->local_partial && p->out, "NULL buffer");
+    GRL_REQUIRE(((uintptr_t)p->local_partial % 16 == 0) && (((size_t)p->rows * (p->head_dim + 2) * 4) % 16 == 0),
                 "partials must be 16-byte aligned and a multiple of 16 bytes");
-    DeviceGuard g(dev->ordinal);
     ExchangeArgs a{};
-    a.local_part = p->local_partial; a.inbox = p->inbox; a.flags = p->flags; a.seq = p->seq; a.out = p->out;
-    a.status = dev->d_status; a.rank = p->rank; a.world = p->world; a.rows = p->rows; a.D = p->head_dim;
-    for (int r = 0; r < p->world; ++r) {
-        GRL_REQUIRE(r == p->rank || (p->peer_inbox[r] && p->peer_flags[r]), "peer %d has no inbox", r);
-        a.peer_inbox[r] = p->peer_inbox[r];
-        a.peer_flags[r] = p->peer_flags[r];
-    }
+    int rc = fill_peer_exchange(p, &a.x);
+    if (rc) return rc;
+    DeviceGuard g(dev->ordinal);
+    a.local_part = p->local_partial; a.out = p->out;
+    a.status = dev->d_status; a.rows = p->rows; a.D = p->head_dim;
     dev->status_dirty = true;
     bump_seq_kernel<<<1, 1, 0, dev->stream>>>(p->seq);
     GRL_LAUNCHED("bump_seq_kernel");

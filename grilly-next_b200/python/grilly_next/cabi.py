@@ -58,18 +58,19 @@ class AppendParams(C.Structure):
                 ("pos_base", C.c_int32), ("update_lens", C.c_int32)]
 
 
-class DecodeParams(C.Structure):
-    _fields_ = [("kv", KVLayout), ("q", C.c_void_p), ("out", C.c_void_p), ("num_q_heads", C.c_int32),
-                ("scale", C.c_float), ("n_splits", C.c_int32), ("max_seq_len", C.c_int32),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("partial_out", C.c_void_p),
-                ("force_simt", C.c_int32)]
-
-
 class ExchangeParams(C.Structure):
     _fields_ = [("local_partial", C.c_void_p), ("inbox", C.c_void_p), ("flags", C.c_void_p),
                 ("peer_inbox", C.POINTER(C.c_void_p)), ("peer_flags", C.POINTER(C.c_void_p)),
                 ("seq", C.c_void_p), ("out", C.c_void_p),
-                ("rank", C.c_int32), ("world", C.c_int32), ("rows", C.c_int32), ("head_dim", C.c_int32)]
+                ("rank", C.c_int32), ("world", C.c_int32), ("rows", C.c_int32), ("head_dim", C.c_int32),
+                ("flag_slots", C.c_int32)]
+
+
+class DecodeParams(C.Structure):
+    _fields_ = [("kv", KVLayout), ("q", C.c_void_p), ("out", C.c_void_p), ("num_q_heads", C.c_int32),
+                ("scale", C.c_float), ("n_splits", C.c_int32), ("max_seq_len", C.c_int32),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("partial_out", C.c_void_p),
+                ("force_simt", C.c_int32), ("exchange", C.POINTER(ExchangeParams))]
 
 
 class GrlError(RuntimeError):

@@ -57,6 +57,8 @@ class ShardedDecoder:
     def step(self, q):
         if self.world == 1 and hasattr(self.ops, "full"):
             return self.ops.full(q)          # one GPU holds everything: normalised output directly
+        if self.world > 1 and getattr(self.ops, "p2p_ready", False) and getattr(self.ops, "one_launch", False):
+            return self.ops.decode_exchange(q)   # decode, NVLink exchange and merge in ONE kernel launch
         part = self.ops.partial(q)
         if self.world == 1:
             return self.ops.merge(part.reshape(1, -1), 1)
@@ -92,7 +94,7 @@ class CudaShardOps:
         self.part = torch.empty(partial_floats(self.rows, self.D), dtype=torch.float32, device="cuda")
         self.out = torch.empty((self.B, 1, self.Hq, self.D), dtype=torch.float32, device="cuda")
 
-    def setup_p2p(self, dist):
+    def setup_p2p(self, dist, one_launch=True):
         """Map every peer's inbox into this process (CUDA IPC) for the fused exchange + merge kernel.
         Collective: every rank calls it once.  Falls back silently (p2p_ready stays False) if the
         handles cannot be opened, e.g. without peer access between the GPUs."""
@@ -100,9 +102,10 @@ class CudaShardOps:
         world, rank = dist.get_world_size(), dist.get_rank()
         n = partial_floats(self.rows, self.D)
         self._inbox = dev.malloc(2 * world * n * 4)
-        self._flags = dev.malloc(2 * world * 4 + 64)
+        slots = self.B * self.p.kv.num_kv_heads          # one flag per (sequence, kv head): heads cross as they finish
+        self._flags = dev.malloc(2 * world * slots * 4 + 64)
         self._seq = dev.malloc(64)
-        for p_, nb in ((self._inbox, 2 * world * n * 4), (self._flags, 2 * world * 4 + 64), (self._seq, 64)):
+        for p_, nb in ((self._inbox, 2 * world * n * 4), (self._flags, 2 * world * slots * 4 + 64), (self._seq, 64)):
             cabi.check(L.grl_memset(dev.h, p_, 0, nb))
         dev.sync()
         hi, hf = (C.c_char * 64)(), (C.c_char * 64)()
@@ -122,7 +125,6 @@ class CudaShardOps:
                 if L.grl_ipc_import(dev.h, C.create_string_buffer(raw, 64), C.byref(ptr)) != 0:
                     ok = False
                 table[r] = ptr.value
-        flags = [ok]
         all_ok = [None] * world
         dist.all_gather_object(all_ok, ok)
         dist.barrier()            # nobody stores into an inbox before everybody has zeroed and exported it
@@ -132,9 +134,21 @@ class CudaShardOps:
         e.peer_inbox = C.cast(self._peer_inbox, C.POINTER(C.c_void_p))
         e.peer_flags = C.cast(self._peer_flags, C.POINTER(C.c_void_p))
         e.seq, e.out = self._seq, self.out.data_ptr()
-        e.rank, e.world, e.rows, e.head_dim = rank, world, self.rows, self.D
+        e.rank, e.world, e.rows, e.head_dim, e.flag_slots = rank, world, self.rows, self.D, slots
         self._exchange = e
+        # the decode kernel itself can do the exchange for the tensor-core geometry with few enough heads
+        self.one_launch = bool(one_launch and self.p.kv.cache_dtype == cabi.BF16 and self.D == 128
+                               and self.p.kv.page_tokens == 64 and slots <= 128)
         return self.p2p_ready
+
+    def decode_exchange(self, q):
+        self.p.q, self.p.out, self.p.partial_out = q.data_ptr(), self.out.data_ptr(), None
+        self.p.exchange = C.pointer(self._exchange)
+        try:
+            self.cabi.check(self.dev.L.grl_gqa_decode(self.dev.h, C.byref(self.p)))
+        finally:
+            self.p.exchange = None
+        return self.out
 
     def exchange_merge(self):
         self.cabi.check(self.dev.L.grl_exchange_merge(self.dev.h, C.byref(self._exchange)))

@@ -192,6 +192,9 @@ typedef struct {
     size_t workspace_bytes;
     float* partial_out;
     int32_t force_simt;     /* != 0: use the generic SIMT kernel even where the tensor-core path applies */
+    const struct grl_exchange_params_s* exchange;   /* optional, see grl_exchange_params below: the KV shards of
+                             * other GPUs are merged in over NVLink inside the decode kernel; `out` then holds
+                             * the attention over ALL ranks' shards.  NULL: single-GPU decode. */
 } grl_decode_params;
 int grl_decode_pick_splits(grl_device* dev, const grl_decode_params* p, int* n_splits);
 int grl_decode_workspace_bytes(const grl_decode_params* p, int n_splits, size_t* bytes);
@@ -228,8 +231,14 @@ int grl_lse_merge(grl_device* dev, const float* parts, int n_parts, size_t part_
  * seq: local uint32 step counter, zero before the first step (the call increments it on the
  * device, so a captured CUDA graph can be replayed); peer_inbox / peer_flags: HOST arrays of
  * `world` device pointers (imported; the entry of this rank is ignored).  Every rank must make the
- * same sequence of calls. */
-typedef struct {
+ * same sequence of calls.
+ * With flag_slots = S the flags are uint32[2][world][S]; grl_exchange_merge uses slot 0.
+ * grl_decode_params.exchange (tensor-core geometry only: bf16 cache, head_dim 128, 64-token pages,
+ * B*Hkv <= the SM count, S >= B*Hkv) goes one step further: the CTA that finishes a (sequence, kv
+ * head) last merges its splits, stores the head's rows into the peers' inboxes, waits for theirs and
+ * writes the final rows -- decode, exchange and merge are ONE launch per step; local_partial, out,
+ * rows and head_dim of the exchange struct are then ignored. */
+typedef struct grl_exchange_params_s {
     const float* local_partial;
     float* inbox;
     uint32_t* flags;
@@ -238,6 +247,7 @@ typedef struct {
     uint32_t* seq;
     float* out;
     int32_t rank, world, rows, head_dim;
+    int32_t flag_slots;     /* flags per (parity, peer); 0 is read as 1 */
 } grl_exchange_params;
 int grl_ipc_export(grl_device* dev, void* ptr, void* handle_out_64_bytes);
 int grl_ipc_import(grl_device* dev, const void* handle_64_bytes, void** ptr_out);

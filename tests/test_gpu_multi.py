@@ -51,7 +51,11 @@ def _worker(rank, world, port, result_dir):
         want = orc.gqa_decode_attention(q, orc.round_bf16(k), orc.round_bf16(v), Hq, Hkv, D)
         errs.append(float(np.abs(out - want).max()))
     fused = ops.setup_p2p(dist)
-    for step in range(5):                       # fused NVLink exchange (several steps: both inbox parities)
+    assert ops.one_launch
+    for step in range(10):
+        # several steps each (both inbox parities): first the exchange fused with the merge kernel, then
+        # decode + exchange + merge as one launch; both share the inboxes and the step counter
+        ops.one_launch = step >= 5
         q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
         out = dec.step(torch.from_numpy(q).cuda()).cpu().numpy()
         want = orc.gqa_decode_attention(q, orc.round_bf16(k), orc.round_bf16(v), Hq, Hkv, D)
