@@ -32,10 +32,17 @@ public:
     int smCount() const { return info_.sm_count; }
     int ordinal() const { return info_.ordinal; }
     const grl_device_info& info() const { return info_; }
+    /// Two more queues on the same GPU (opened on first use) for host->device and device->host copies
+    /// that overlap the kernels of the main queue -- the transfer queues a Vulkan device offers next
+    /// to its compute queue.  Order between queues is set with grl_event_record / grl_event_wait.
+    grl_device* uploadQueue();
+    grl_device* downloadQueue();
 
 private:
     void open(int ordinal);
     grl_device* dev_ = nullptr;
+    grl_device* up_ = nullptr;
+    grl_device* down_ = nullptr;
     grl_device_info info_{};
     std::string name_;
 };

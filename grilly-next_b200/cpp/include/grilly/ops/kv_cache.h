@@ -89,6 +89,15 @@ void decodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVC
                 const float* kNew, const float* vNew, float* out, uint32_t numQHeads, RopeMode mode, float theta,
                 float scaling, float scale = 0.0f);
 
+/// Device-resident forms: q / kNew / vNew / out are HBM float32 buffers; asynchronous on the context
+/// stream (no copy, no wait).  `ws` receives the pooled split-KV workspace, to be released by the
+/// caller once the stream has passed the launch.
+void gqaAttentionDevice(BufferPool& pool, PipelineCache& cache, const KVCache& kvCache, const GrillyBuffer& q,
+                        GrillyBuffer& out, uint32_t numQHeads, float scale, int nSplits, GrillyBuffer& ws);
+void decodeStepDevice(BufferPool& pool, PipelineCache& cache, KVCache& kvCache, const GrillyBuffer& q,
+                      const GrillyBuffer& kNew, const GrillyBuffer& vNew, GrillyBuffer& qRotated, GrillyBuffer& out,
+                      uint32_t numQHeads, RopeMode mode, float theta, float scaling, float scale, GrillyBuffer& ws);
+
 // Eviction family of the reference (kv_cache.h:186-229): not built on the paged cache; each
 // throws std::runtime_error naming itself.
 void kvCacheEvictH2O(CommandBatch&, BufferPool&, PipelineCache&, KVCache&, const float* attentionScores,

@@ -5,8 +5,11 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <memory>
 #include <optional>
 #include <string>
+#include <thread>
+#include <vector>
 
 #include "grilly/buffer_pool.h"
 #include "grilly/command_batch.h"
@@ -29,10 +32,42 @@ struct GrillyCoreContext {
     CommandBatch batch;
     bool shadersLoaded = false;
     GrillyCoreContext() : device(), pool(device), cache(device), batch(device) {}
+    explicit GrillyCoreContext(int ordinal) : device(ordinal), pool(device), cache(device), batch(device) {}
     /// Kernels are compiled into the library; the call is kept so that callers written for the
     /// Vulkan backend keep working.
     void loadShaders(const std::string&) { shadersLoaded = true; }
 };
+
+using ContextPtr = std::shared_ptr<GrillyCoreContext>;
+
+/// HBM-resident tensor (float32 or bf16) owned by a Device's buffer pool.  Ops that take DeviceTensors
+/// run asynchronously on the device's stream: no host copy, no wait (Device.synchronize() waits).
+struct DeviceTensor {
+    ContextPtr ctx;
+    GrillyBuffer buf;
+    std::vector<py::ssize_t> shape;
+    int dtype = GRL_F32;
+    DeviceTensor(ContextPtr c, std::vector<py::ssize_t> s, int dt) : ctx(std::move(c)), shape(std::move(s)), dtype(dt) {
+        buf = ctx->pool.acquire(std::max<size_t>(nbytes(), 16));
+    }
+    DeviceTensor(const DeviceTensor&) = delete;
+    ~DeviceTensor() {
+        if (buf.valid()) ctx->pool.release(buf);
+    }
+    size_t numel() const {
+        size_t n = 1;
+        for (auto d : shape) n *= size_t(d);
+        return n;
+    }
+    size_t nbytes() const { return numel() * (dtype == GRL_BF16 ? 2 : 4); }
+};
+using TensorPtr = std::shared_ptr<DeviceTensor>;
+
+static int parseDtype(const std::string& s) {
+    if (s == "fp32" || s == "float32") return GRL_F32;
+    if (s == "bf16" || s == "bfloat16") return GRL_BF16;
+    throw std::runtime_error("dtype must be 'fp32' or 'bf16'");
+}
 
 static ops::RopeMode parseRopeMode(const std::string& m, bool allowNone) {
     if (m == "interleaved") return ops::RopeMode::Interleaved;
@@ -101,8 +136,16 @@ PYBIND11_MODULE(grilly_core, m) {
     m.doc() = "grilly C++ backend, CUDA (sm_100a) build of the attention / KV-cache ops";
     m.attr("BACKEND") = "cuda-sm100a";
 
-    py::class_<GrillyCoreContext>(m, "Device")
+    py::class_<GrillyCoreContext, ContextPtr>(m, "Device")
         .def(py::init<>(), "Initialize the CUDA device, buffer pool and kernel-plan cache")
+        .def(py::init<int>(), py::arg("gpu_index"), "Open the GPU with this ordinal")
+        .def("synchronize",
+             [](GrillyCoreContext& c) {
+                 py::gil_scoped_release nogil;
+                 check(grl_sync(c.device.handle(), 0), "Device.synchronize");
+             },
+             "Wait for the work queued on this device (DeviceTensor ops are asynchronous)")
+        .def_property_readonly("gpu_index", [](const GrillyCoreContext& c) { return c.device.ordinal(); })
         .def("load_shaders", &GrillyCoreContext::loadShaders, py::arg("shader_dir"),
              "Accepted for compatibility; kernels are linked into the library")
         .def_property_readonly("device_name", [](const GrillyCoreContext& c) { return c.device.deviceName(); })
@@ -124,6 +167,122 @@ PYBIND11_MODULE(grilly_core, m) {
             d["hits"] = s.hits; d["misses"] = s.misses; d["evictions"] = s.evictions; d["cached_sets"] = s.cachedSets;
             return d;
         });
+
+    // ---- device-resident tensors
+    py::class_<DeviceTensor, TensorPtr>(m, "DeviceTensor")
+        .def_static(
+            "from_numpy",
+            [](ContextPtr ctx, FArr a, const std::string& dtype) {
+                const int dt = parseDtype(dtype);
+                std::vector<py::ssize_t> shape(a.shape(), a.shape() + a.ndim());
+                auto t = std::make_shared<DeviceTensor>(ctx, shape, dt);
+                const size_t n = t->numel();
+                grl_device* dev = ctx->device.handle();
+                if (dt == GRL_F32) {
+                    check(grl_memcpy_h2d(dev, t->buf.dptr, a.data(), n * 4), "DeviceTensor.from_numpy");
+                    check(grl_sync(dev, 0), "DeviceTensor.from_numpy");     // the source array may go away
+                } else {
+                    GrillyBuffer tmp = ctx->pool.acquire(std::max<size_t>(n * 4, 16));
+                    check(grl_memcpy_h2d(dev, tmp.dptr, a.data(), n * 4), "DeviceTensor.from_numpy");
+                    check(grl_cast(dev, tmp.dptr, GRL_F32, t->buf.dptr, GRL_BF16, n), "DeviceTensor.from_numpy");
+                    check(grl_sync(dev, 0), "DeviceTensor.from_numpy");
+                    ctx->pool.release(tmp);
+                }
+                return t;
+            },
+            py::arg("device"), py::arg("array"), py::arg("dtype") = "fp32",
+            "Upload a float32 array (rounded to bf16 on the device when dtype='bf16')")
+        .def_static(
+            "empty",
+            [](ContextPtr ctx, std::vector<py::ssize_t> shape, const std::string& dtype) {
+                return std::make_shared<DeviceTensor>(ctx, shape, parseDtype(dtype));
+            },
+            py::arg("device"), py::arg("shape"), py::arg("dtype") = "fp32")
+        .def(
+            "to_numpy",
+            [](DeviceTensor& t, std::optional<py::array_t<float>> outArr) {
+                py::array_t<float> out;
+                if (outArr.has_value()) {
+                    out = *outArr;
+                    if (size_t(out.size()) != t.numel() || !(out.flags() & py::array::c_style) || !out.writeable())
+                        throw std::runtime_error("out must be a writable C-contiguous float32 array of the tensor's size");
+                } else {
+                    out = py::array_t<float>(t.shape);
+                }
+                grl_device* dev = t.ctx->device.handle();
+                const size_t n = t.numel();
+                float* dst = out.mutable_data();
+                py::gil_scoped_release nogil;
+                if (t.dtype == GRL_F32) {
+                    check(grl_memcpy_d2h(dev, dst, t.buf.dptr, n * 4), "DeviceTensor.to_numpy");
+                    check(grl_sync(dev, 0), "DeviceTensor.to_numpy");
+                } else {
+                    GrillyBuffer tmp = t.ctx->pool.acquire(std::max<size_t>(n * 4, 16));
+                    check(grl_cast(dev, t.buf.dptr, GRL_BF16, tmp.dptr, GRL_F32, n), "DeviceTensor.to_numpy");
+                    check(grl_memcpy_d2h(dev, dst, tmp.dptr, n * 4), "DeviceTensor.to_numpy");
+                    check(grl_sync(dev, 0), "DeviceTensor.to_numpy");
+                    t.ctx->pool.release(tmp);
+                }
+                return out;
+            },
+            py::arg("out") = py::none(), "Download as float32 (waits for the device)")
+        .def(
+            "copy_from_numpy",
+            [](DeviceTensor& t, FArr a) {
+                if (size_t(a.size()) != t.numel()) throw std::runtime_error("array size differs from the tensor's");
+                if (t.dtype != GRL_F32) throw std::runtime_error("copy_from_numpy needs a float32 tensor");
+                check(grl_memcpy_h2d(t.ctx->device.handle(), t.buf.dptr, a.data(), t.numel() * 4), "copy_from_numpy");
+                check(grl_sync(t.ctx->device.handle(), 0), "copy_from_numpy");
+            },
+            py::arg("array"))
+        .def_property_readonly("shape", [](const DeviceTensor& t) { return py::tuple(py::cast(t.shape)); })
+        .def_property_readonly("dtype", [](const DeviceTensor& t) { return t.dtype == GRL_BF16 ? "bf16" : "fp32"; })
+        .def_property_readonly("nbytes", [](const DeviceTensor& t) { return t.nbytes(); })
+        .def_property_readonly("data_ptr", [](const DeviceTensor& t) { return reinterpret_cast<uintptr_t>(t.buf.dptr); })
+        .def_property_readonly("device", [](const DeviceTensor& t) { return t.ctx; });
+
+    // flash_attention2 on DeviceTensors: same keywords; Q/K/V (B,H,S,D) of one dtype (bf16 selects the
+    // tcgen05 kernel), result a float32 DeviceTensor unless out= names one.  Asynchronous.
+    m.def(
+        "flash_attention2",
+        [](ContextPtr ctx, TensorPtr Q, TensorPtr K, TensorPtr V, py::object mask, float scale, uint32_t, uint32_t,
+           bool causal, std::optional<IArr> seqLens, float ropeTheta, float ropeScaling, const std::string& ropeMode,
+           const std::string& /*dtype: taken from the tensors*/, std::optional<TensorPtr> out) {
+            if (!mask.is_none()) throw std::runtime_error("DeviceTensor inputs take causal / seq_lens masks only");
+            if (Q->shape.size() != 4) throw std::runtime_error("Q must be 4D (batch, heads, seq_len, head_dim)");
+            if (K->shape != Q->shape || V->shape != Q->shape) throw std::runtime_error("Q, K and V must have the same shape");
+            if (K->dtype != Q->dtype || V->dtype != Q->dtype) throw std::runtime_error("Q, K and V must have the same dtype");
+            for (auto& t : {Q, K, V})
+                if (t->ctx.get() != ctx.get()) throw std::runtime_error("tensor lives on another Device");
+            const uint32_t B = uint32_t(Q->shape[0]), H = uint32_t(Q->shape[1]), S = uint32_t(Q->shape[2]),
+                           D = uint32_t(Q->shape[3]);
+            TensorPtr o = out.has_value() ? *out : std::make_shared<DeviceTensor>(ctx, Q->shape, GRL_F32);
+            if (o->shape != Q->shape || o->ctx.get() != ctx.get()) throw std::runtime_error("out must have Q's shape and Device");
+            GrillyBuffer lens;
+            if (seqLens.has_value()) {
+                if (seqLens->ndim() != 1 || seqLens->shape(0) != B) throw std::runtime_error("seq_lens must be (batch,)");
+                lens = ctx->pool.acquire(size_t(B) * 4);
+                ctx->pool.upload(lens, seqLens->data(), size_t(B) * 4);
+                check(grl_sync(ctx->device.handle(), 0), "flash_attention2: seq_lens upload");
+            }
+            const ops::RopeMode mode = ropeTheta != 0.0f ? parseRopeMode(ropeMode, false) : ops::RopeMode::None;
+            try {
+                ops::flashAttention2Device(ctx->batch, ctx->cache, Q->buf, K->buf, V->buf, o->buf, Q->dtype, o->dtype, B, S,
+                                           H, D, scale, causal, lens.valid() ? &lens : nullptr, mode,
+                                           ropeTheta != 0.0f ? ropeTheta : 10000.0f, ropeScaling);
+            } catch (...) {
+                ctx->pool.release(lens);
+                throw;
+            }
+            // stream order protects a pooled buffer that is handed out again; the pool waits before it frees one
+            ctx->pool.release(lens);
+            return o;
+        },
+        py::arg("device"), py::arg("Q"), py::arg("K"), py::arg("V"), py::arg("mask") = py::none(),
+        py::arg("scale") = 0.0f, py::arg("tile_size_q") = 64, py::arg("tile_size_k") = 64, py::arg("causal") = false,
+        py::arg("seq_lens") = py::none(), py::arg("rope_theta") = 0.0f, py::arg("rope_scaling") = 1.0f,
+        py::arg("rope_mode") = "interleaved", py::arg("dtype") = "", py::arg("out") = py::none(),
+        "Flash Attention 2 on DeviceTensors (asynchronous, result stays in HBM)");
 
     // ---- flash attention 2 (reference: bindings.cpp:416-462)
     m.def(
@@ -293,6 +452,58 @@ PYBIND11_MODULE(grilly_core, m) {
           [](GrillyCoreContext& ctx, ops::KVCache& kv) { ops::kvCacheCompact(ctx.batch, ctx.pool, ctx.cache, kv); },
           py::arg("device"), py::arg("kv_cache"));
 
+    // ---- GQA decode on DeviceTensors (asynchronous; q already rotated)
+    m.def(
+        "gqa_attention",
+        [](ContextPtr ctx, TensorPtr q, ops::KVCache& kv, py::object vCache, py::object cacheLen, float scale,
+           int nSplits, const std::string&) {
+            if (!vCache.is_none() || !cacheLen.is_none())
+                throw std::runtime_error("a DeviceTensor q attends over a KVCache; v_cache / cache_len do not apply");
+            if (q->dtype != GRL_F32 || q->shape.size() != 4 || q->shape[1] != 1)
+                throw std::runtime_error("q must be a float32 DeviceTensor (batch, 1, num_q_heads, head_dim)");
+            if (q->shape[0] != kv.config.batchSize || q->shape[3] != kv.config.headDim)
+                throw std::runtime_error("q does not match the cache");
+            auto out = std::make_shared<DeviceTensor>(ctx, q->shape, GRL_F32);
+            GrillyBuffer ws;
+            ops::gqaAttentionDevice(ctx->pool, ctx->cache, kv, q->buf, out->buf, uint32_t(q->shape[2]), scale, nSplits, ws);
+            ctx->pool.release(ws);
+            return out;
+        },
+        py::arg("device"), py::arg("q"), py::arg("k_cache"), py::arg("v_cache") = py::none(),
+        py::arg("cache_len") = py::none(), py::arg("scale") = 0.0f, py::arg("n_splits") = 0, py::arg("dtype") = "fp32",
+        "GQA decode attention of a DeviceTensor q over a KVCache (asynchronous)");
+
+    m.def(
+        "decode_step",
+        [](ContextPtr ctx, ops::KVCache& kv, TensorPtr q, TensorPtr kNew, TensorPtr vNew, float ropeTheta,
+           float ropeScaling, const std::string& ropeMode, float scale) {
+            const auto& c = kv.config;
+            for (auto& t : {q, kNew, vNew})
+                if (t->dtype != GRL_F32 || t->shape.size() != 4 || t->shape[0] != c.batchSize || t->shape[1] != 1 ||
+                    t->shape[3] != c.headDim)
+                    throw std::runtime_error("q / k_new / v_new must be float32 DeviceTensors (batch, 1, heads, head_dim)");
+            if (kNew->shape[2] != c.numHeads || vNew->shape[2] != c.numHeads)
+                throw std::runtime_error("k_new / v_new must be (batch, 1, num_kv_heads, head_dim)");
+            auto out = std::make_shared<DeviceTensor>(ctx, q->shape, GRL_F32);
+            GrillyBuffer qRot = ctx->pool.acquire(q->nbytes()), ws;
+            try {
+                ops::decodeStepDevice(ctx->pool, ctx->cache, kv, q->buf, kNew->buf, vNew->buf, qRot, out->buf,
+                                      uint32_t(q->shape[2]),
+                                      ropeTheta != 0.0f ? parseRopeMode(ropeMode, false) : ops::RopeMode::None,
+                                      ropeTheta != 0.0f ? ropeTheta : 10000.0f, ropeScaling, scale, ws);
+            } catch (...) {
+                ctx->pool.release(qRot);
+                ctx->pool.release(ws);
+                throw;
+            }
+            ctx->pool.release(qRot);
+            ctx->pool.release(ws);
+            return out;
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("q"), py::arg("k_new"), py::arg("v_new"),
+        py::arg("rope_theta") = 10000.0f, py::arg("rope_scaling") = 1.0f, py::arg("rope_mode") = "interleaved",
+        py::arg("scale") = 0.0f, "One decode step on DeviceTensors (asynchronous)");
+
     // ---- GQA decode (shaders/gqa-attention.glsl)
     m.def(
         "gqa_attention",
@@ -367,4 +578,99 @@ PYBIND11_MODULE(grilly_core, m) {
         py::arg("device"), py::arg("kv_cache"), py::arg("q"), py::arg("k_new"), py::arg("v_new"),
         py::arg("rope_theta") = 10000.0f, py::arg("rope_scaling") = 1.0f, py::arg("rope_mode") = "interleaved",
         py::arg("scale") = 0.0f, "RoPE(q,k) at the current position, append k/v, attend over the cache");
+
+    // ---- DeviceGroup: the GPUs of one node behind one object, one Device (own stream, own pool) each.
+    // flash_attention2 splits the heads in contiguous runs over the devices, one host thread per device
+    // (heads are independent: no collective); the KV-sharded decode across processes lives in
+    // grilly_next.parallel.
+    struct DeviceGroup {
+        std::vector<ContextPtr> devices;
+    };
+    py::class_<DeviceGroup>(m, "DeviceGroup")
+        .def(py::init([](int n) {
+                 int have = 0;
+                 check(grl_device_count(&have), "DeviceGroup");
+                 if (n <= 0) n = have;
+                 if (n > have) throw std::runtime_error("DeviceGroup: " + std::to_string(n) + " devices asked for, " +
+                                                        std::to_string(have) + " present");
+                 auto g = std::make_unique<DeviceGroup>();
+                 for (int i = 0; i < n; ++i) g->devices.push_back(std::make_shared<GrillyCoreContext>(i));
+                 return g;
+             }),
+             py::arg("n") = 0, "Open the first n GPUs (0 = all)")
+        .def("__len__", [](const DeviceGroup& g) { return g.devices.size(); })
+        .def("__getitem__",
+             [](const DeviceGroup& g, size_t i) {
+                 if (i >= g.devices.size()) throw py::index_error();
+                 return g.devices[i];
+             })
+        .def_property_readonly("devices", [](const DeviceGroup& g) { return g.devices; })
+        .def(
+            "flash_attention2",
+            [](DeviceGroup& g, FArr Q, FArr K, FArr V, float scale, bool causal, std::optional<IArr> seqLens,
+               float ropeTheta, float ropeScaling, const std::string& ropeMode, const std::string& dtype) {
+                if (Q.ndim() != 4) throw std::runtime_error("Q must be 4D (batch, heads, seq_len, head_dim)");
+                for (int i = 0; i < 4; ++i)
+                    if (K.ndim() != 4 || V.ndim() != 4 || K.shape(i) != Q.shape(i) || V.shape(i) != Q.shape(i))
+                        throw std::runtime_error("Q, K and V must have the same shape");
+                const uint32_t B = uint32_t(Q.shape(0)), H = uint32_t(Q.shape(1)), S = uint32_t(Q.shape(2)),
+                               D = uint32_t(Q.shape(3));
+                if (seqLens.has_value() && (seqLens->ndim() != 1 || seqLens->shape(0) != B))
+                    throw std::runtime_error("seq_lens must be (batch,)");
+                ops::FlashAttention2Options opt;
+                opt.causal = causal;
+                if (seqLens.has_value()) opt.seqLens = seqLens->data();
+                if (ropeTheta != 0.0f) {
+                    opt.ropeMode = parseRopeMode(ropeMode, false);
+                    opt.ropeTheta = ropeTheta;
+                    opt.ropeScaling = ropeScaling;
+                }
+                opt.precision = parseDtype(dtype) == GRL_BF16 ? ops::Precision::BF16 : ops::Precision::FP32;
+                py::array_t<float> result({py::ssize_t(B), py::ssize_t(H), py::ssize_t(S), py::ssize_t(D)});
+                float* out = result.mutable_data();
+                const float *q = Q.data(), *k = K.data(), *v = V.data();
+                const size_t G = g.devices.size(), slice = size_t(S) * D;
+                std::vector<std::string> errors(G);
+                {
+                    py::gil_scoped_release nogil;
+                    std::vector<std::thread> workers;
+                    for (size_t r = 0; r < G; ++r) {
+                        const uint32_t h0 = uint32_t(size_t(H) * r / G), h1 = uint32_t(size_t(H) * (r + 1) / G);
+                        if (h1 == h0) continue;
+                        workers.emplace_back([&, r, h0, h1] {
+                            try {
+                                auto& c = *g.devices[r];
+                                // every (batch) row of this device's head run is one call: (1, h1-h0, S, D) is contiguous
+                                for (uint32_t b = 0; b < B; ++b) {
+                                    const size_t off = (size_t(b) * H + h0) * slice;
+                                    ops::FlashAttention2Options o = opt;
+                                    if (opt.seqLens) o.seqLens = opt.seqLens + b;
+                                    ops::flashAttention2Ex(c.batch, c.pool, c.cache, q + off, k + off, v + off, nullptr,
+                                                           out + off, 1, S, h1 - h0, D, scale, o);
+                                }
+                            } catch (const std::exception& e) {
+                                errors[r] = e.what();
+                            }
+                        });
+                    }
+                    for (auto& w : workers) w.join();
+                }
+                for (auto& e : errors)
+                    if (!e.empty()) throw std::runtime_error(e);
+                return result;
+            },
+            py::arg("Q"), py::arg("K"), py::arg("V"), py::arg("scale") = 0.0f, py::arg("causal") = false,
+            py::arg("seq_lens") = py::none(), py::arg("rope_theta") = 0.0f, py::arg("rope_scaling") = 1.0f,
+            py::arg("rope_mode") = "interleaved", py::arg("dtype") = "fp32",
+            "Flash Attention 2 with the heads split over the group's GPUs");
+
+    // ---- names of the reference's module that this build does not implement: present, and say so
+    auto notBuilt = [&m](const char* name, const char* what) {
+        const std::string msg = std::string(name) + ": " + what;
+        m.def(name, [msg](py::args, py::kwargs) -> py::object { throw std::runtime_error(msg); });
+    };
+    notBuilt("kv_cache_init_eviction_head", "the trainable eviction head is not built on the paged cache");
+    notBuilt("kv_cache_train_eviction_head", "the trainable eviction head is not built on the paged cache");
+    notBuilt("kv_cache_evict_speculative", "speculative eviction is not built on the paged cache");
+    notBuilt("fused_attention_cpu", "the MLA latent path (CPU reference of the fused subgroup attention) is not built");
 }

@@ -1,6 +1,9 @@
 // Host side of the prefill ops: upload -> (cast) -> one kernel launch -> download.
+#include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <string>
+#include <vector>
 
 #include "grilly/ops/attention.h"
 #include "grilly/ops/rope.h"
@@ -9,6 +12,9 @@ namespace grilly {
 namespace ops {
 
 namespace {
+constexpr size_t kPipelineMinBytes = 8u << 20;     // per tensor: below this one upload / launch / download
+constexpr size_t kPipelineChunkBytes = 32u << 20;      // per tensor: the large chunks
+constexpr size_t kPipelineLastChunkBytes = 4u << 20;   // per tensor: the last chunk (nothing hides its kernel and download)
 struct Scoped {   // releases pooled buffers on every exit path
     BufferPool& pool;
     std::vector<GrillyBuffer*> bufs;
@@ -57,6 +63,109 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
     scope.add(q32); scope.add(k32); scope.add(v32); scope.add(out);
     GrillyBuffer maskBuf, lensBuf, q16, k16, v16;
     scope.add(maskBuf); scope.add(lensBuf); scope.add(q16); scope.add(k16); scope.add(v16);
+
+    // Large calls are bound by the host link (4 tensors of n floats cross it), not by the kernel: cut the
+    // (batch, head) slices into chunks and let the upload of chunk c+1, the kernel of chunk c and the
+    // download of chunk c-1 run on three queues at once.  Heads are independent, so a chunk is a smaller
+    // problem of the same kind.  Dense masks keep the one-shot path below.
+    const size_t slice = size_t(S) * D;                       // elements of one (b, h) slice
+    if (n * 4 >= kPipelineMinBytes && (!mask || opt.maskRank == 2) && size_t(B) * H > 1) {
+        // Chunk plan, in (b, h) slices.  Every chunk boundary costs the upload queue a bubble (the event
+        // between two copies), and the last chunk's kernel and download are not hidden by anything: so
+        // few, large chunks first and a short geometric tail (… 32, 32, 16, 8, 4 MiB per tensor).
+        size_t bigBytes = kPipelineChunkBytes, lastBytes = kPipelineLastChunkBytes;
+        if (const char* e = std::getenv("GRILLY_PIPELINE_CHUNK_MB")) bigBytes = size_t(std::max(1, std::atoi(e))) << 20;
+        if (const char* e = std::getenv("GRILLY_PIPELINE_LAST_MB")) lastBytes = size_t(std::max(1, std::atoi(e))) << 20;
+        const size_t total = size_t(B) * H;
+        const size_t big = std::max<size_t>(1, bigBytes / (slice * 4)), last = std::max<size_t>(1, lastBytes / (slice * 4));
+        std::vector<size_t> plan;                      // built back to front
+        for (size_t left = total, c = std::min(last, big); left > 0;) {
+            const size_t take = std::min(c, left);
+            plan.push_back(take);
+            left -= take;
+            c = std::min(big, c * 2);
+        }
+        std::reverse(plan.begin(), plan.end());
+        const bool perBatch = mask || opt.seqLens;     // a chunk then stays inside one batch row
+        grl_device* up = pool.device().uploadQueue();
+        grl_device* down = pool.device().downloadQueue();
+        struct Events {   // destroyed on every exit path
+            std::vector<grl_event*> v;
+            ~Events() { for (auto* e : v) grl_event_destroy(e); }
+            grl_event* make() {
+                grl_event* e = nullptr;
+                check(grl_event_create_untimed(&e), "flashAttention2: event");
+                v.push_back(e);
+                return e;
+            }
+        } events;
+        Recording rec(batch);
+        if (mask) {
+            maskBuf = pool.acquire(size_t(B) * S * 4);
+            pool.upload(maskBuf, mask, size_t(B) * S * 4);
+        }
+        if (opt.seqLens) {
+            lensBuf = pool.acquire(size_t(B) * 4);
+            pool.upload(lensBuf, opt.seqLens, size_t(B) * 4);
+        }
+        if (bf16) { q16 = pool.acquire(n * 2); k16 = pool.acquire(n * 2); v16 = pool.acquire(n * 2); }
+        // the buffers may have been used by earlier work on the main queue
+        grl_event* start = events.make();
+        check(grl_event_record(dev, start), "flashAttention2: event");
+        check(grl_event_wait(up, start), "flashAttention2: event");
+        check(grl_event_wait(down, start), "flashAttention2: event");
+        auto at = [](const GrillyBuffer& b, size_t byteOff) { return static_cast<char*>(b.dptr) + byteOff; };
+        size_t s0 = 0;
+        for (size_t chunk : plan) {
+            const size_t s1 = s0 + chunk;
+            // upload the whole chunk, then launch it piece by piece (one piece unless it crosses a batch row)
+            const size_t e0 = s0 * slice, ne = chunk * slice;
+            check(grl_memcpy_h2d(up, at(q32, e0 * 4), Q + e0, ne * 4), "flashAttention2: upload");
+            check(grl_memcpy_h2d(up, at(k32, e0 * 4), K + e0, ne * 4), "flashAttention2: upload");
+            check(grl_memcpy_h2d(up, at(v32, e0 * 4), V + e0, ne * 4), "flashAttention2: upload");
+            grl_event* uploaded = events.make();
+            check(grl_event_record(up, uploaded), "flashAttention2: event");
+            check(grl_event_wait(dev, uploaded), "flashAttention2: event");
+            if (bf16) {
+                check(grl_cast(dev, at(q32, e0 * 4), GRL_F32, at(q16, e0 * 2), GRL_BF16, ne), "flashAttention2: cast");
+                check(grl_cast(dev, at(k32, e0 * 4), GRL_F32, at(k16, e0 * 2), GRL_BF16, ne), "flashAttention2: cast");
+                check(grl_cast(dev, at(v32, e0 * 4), GRL_F32, at(v16, e0 * 2), GRL_BF16, ne), "flashAttention2: cast");
+            }
+            for (size_t p0 = s0; p0 < s1;) {
+                const size_t b = p0 / H;
+                const size_t p1 = perBatch ? std::min(s1, (b + 1) * size_t(H)) : s1;
+                const size_t pe = p0 * slice;
+                grl_flash_params p{};
+                p.o = at(out, pe * 4);
+                if (bf16) {
+                    p.q = at(q16, pe * 2); p.k = at(k16, pe * 2); p.v = at(v16, pe * 2);
+                    p.in_dtype = GRL_BF16; p.kernel = GRL_KERNEL_TCGEN05;
+                } else {
+                    p.q = at(q32, pe * 4); p.k = at(k32, pe * 4); p.v = at(v32, pe * 4);
+                    p.in_dtype = GRL_F32; p.kernel = GRL_KERNEL_AUTO;
+                }
+                p.out_dtype = GRL_F32;
+                p.batch = 1; p.heads = int(p1 - p0); p.seq_len = int(S); p.head_dim = int(D);
+                p.scale = scale; p.causal = opt.causal ? 1 : 0;
+                p.rope_mode = int(opt.ropeMode); p.rope_theta = opt.ropeTheta; p.rope_scaling = opt.ropeScaling;
+                if (mask) { p.mask_kind = GRL_MASK_KEY; p.mask = static_cast<const float*>(maskBuf.dptr) + b * S; }
+                if (opt.seqLens) p.seq_lens = static_cast<const int32_t*>(lensBuf.dptr) + b;
+                check(grl_flash_fwd(dev, &p), "flashAttention2");
+                p0 = p1;
+            }
+            grl_event* computed = events.make();
+            check(grl_event_record(dev, computed), "flashAttention2: event");
+            check(grl_event_wait(down, computed), "flashAttention2: event");
+            check(grl_memcpy_d2h(down, output + e0, at(out, e0 * 4), ne * 4), "flashAttention2: download");
+            s0 = s1;
+        }
+        // the main queue outlives the call: make it wait for the copies before its buffers are reused
+        grl_event* done = events.make();
+        check(grl_event_record(down, done), "flashAttention2: event");
+        check(grl_event_wait(dev, done), "flashAttention2: event");
+        batch.submit();      // waits for the main queue (and so for `done`), reports kernel failures
+        return;
+    }
 
     Recording rec(batch);
     pool.upload(q32, Q, n * 4);

@@ -280,6 +280,48 @@ void decodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVC
     releaseAll();
 }
 
+void gqaAttentionDevice(BufferPool& pool, PipelineCache& cache, const KVCache& kv, const GrillyBuffer& q,
+                        GrillyBuffer& out, uint32_t numQHeads, float scale, int nSplits, GrillyBuffer& ws) {
+    if (!kv.kPages.valid()) throw std::runtime_error("gqaAttention: cache was destroyed");
+    const auto& c = kv.config;
+    if (numQHeads == 0 || numQHeads % c.numHeads != 0)
+        throw std::runtime_error("gqaAttention: num_q_heads must be a positive multiple of num_kv_heads");
+    const size_t bytes = size_t(c.batchSize) * numQHeads * c.headDim * 4;
+    if (q.size < bytes || out.size < bytes) throw std::runtime_error("gqaAttention: q / out buffer too small");
+    cache.getOrCreate("gqa-attention-device/" + std::to_string(c.headDim));
+    launchDecode(pool.device().handle(), pool, kv, static_cast<const float*>(q.dptr), static_cast<float*>(out.dptr),
+                 numQHeads, scale, nSplits, ws);
+}
+
+void decodeStepDevice(BufferPool& pool, PipelineCache& cache, KVCache& kv, const GrillyBuffer& q,
+                      const GrillyBuffer& kNew, const GrillyBuffer& vNew, GrillyBuffer& qRotated, GrillyBuffer& out,
+                      uint32_t numQHeads, RopeMode mode, float theta, float scaling, float scale, GrillyBuffer& ws) {
+    if (!kv.kPages.valid()) throw std::runtime_error("decodeStep: cache was destroyed");
+    const auto& c = kv.config;
+    if (numQHeads == 0 || numQHeads % c.numHeads != 0)
+        throw std::runtime_error("decodeStep: num_q_heads must be a positive multiple of num_kv_heads");
+    const size_t qb = size_t(c.batchSize) * numQHeads * c.headDim * 4, kb = size_t(c.batchSize) * c.numHeads * c.headDim * 4;
+    if (q.size < qb || qRotated.size < qb || out.size < qb || kNew.size < kb || vNew.size < kb)
+        throw std::runtime_error("decodeStep: buffer too small");
+    grl_device* dev = pool.device().handle();
+    cache.getOrCreate("decode-step-device/" + std::to_string(c.headDim));
+    reservePages(pool, kv, 1);
+    grl_append_params ap{};
+    ap.kv = kv.layout();
+    ap.k_new = static_cast<const float*>(kNew.dptr);
+    ap.v_new = static_cast<const float*>(vNew.dptr);
+    ap.q_in = static_cast<const float*>(q.dptr);
+    ap.q_out = static_cast<float*>(qRotated.dptr);
+    ap.n_new = 1; ap.num_q_heads = int(numQHeads);
+    ap.rope_mode = int(mode); ap.rope_theta = theta; ap.rope_scaling = scaling;
+    ap.pos_base = 0; ap.update_lens = 1;
+    check(grl_kv_append(dev, &ap), "decodeStep: append");
+    for (auto& l : kv.hostSeqLens) l += 1;
+    kv.currentLen = uint32_t(kv.hostSeqLens[0]);
+    kv.totalAppended += c.batchSize;
+    launchDecode(dev, pool, kv, static_cast<const float*>(qRotated.dptr), static_cast<float*>(out.dptr), numQHeads, scale, 0, ws);
+}
+
 void kvCacheEvictH2O(CommandBatch&, BufferPool&, PipelineCache&, KVCache&, const float*, uint32_t) {
     throw std::runtime_error("kvCacheEvictH2O: the eviction family is not built on the paged cache");
 }

@@ -24,7 +24,19 @@ void GrillyDevice::open(int ordinal) {
 }
 
 GrillyDevice::~GrillyDevice() {
+    if (up_) grl_device_close(up_);
+    if (down_) grl_device_close(down_);
     if (dev_) grl_device_close(dev_);
+}
+
+grl_device* GrillyDevice::uploadQueue() {
+    if (!up_) check(grl_device_open(info_.ordinal, &up_), "GrillyDevice: cannot open the upload queue");
+    return up_;
+}
+
+grl_device* GrillyDevice::downloadQueue() {
+    if (!down_) check(grl_device_open(info_.ordinal, &down_), "GrillyDevice: cannot open the download queue");
+    return down_;
 }
 
 // ---------------------------------------------------------------- BufferPool

@@ -24,6 +24,7 @@ struct grl_device {
     // Status word written by kernels with bounded waits; read back by grl_sync when dirty.
     int32_t* d_status = nullptr;   // device int32[4], followed by the arrival counters below
     bool status_dirty = false;
+    int32_t* h_status = nullptr;   // pinned host int32[4]: the status word is copied here ahead of a wait
     // Arrival counters of the split-KV decode (one per (sequence, kv head), zero between launches: the
     // CTA that brings a counter to its final value resets it) and, last, the count of finished heads.
     static constexpr int kCounterSlots = 4096;

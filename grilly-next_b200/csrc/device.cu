@@ -124,7 +124,9 @@ int grl_device_open(int ordinal, grl_device** out) {
     d->stream = d->own_stream;
     const size_t status_bytes = (4 + grl_device::kCounterSlots + 1) * sizeof(int32_t);
     if (cudaMalloc(&d->d_status, status_bytes) != cudaSuccess ||
-        cudaMemset(d->d_status, 0, status_bytes) != cudaSuccess) {
+        cudaMemset(d->d_status, 0, status_bytes) != cudaSuccess ||
+        cudaHostAlloc(&d->h_status, 4 * sizeof(int32_t), cudaHostAllocDefault) != cudaSuccess) {
+        cudaFree(d->d_status);
         cudaStreamDestroy(d->own_stream);
         delete d;
         return set_error(GRL_ERR_OOM, "could not allocate the device status word");
@@ -132,6 +134,7 @@ int grl_device_open(int ordinal, grl_device** out) {
     if (d->prop.major != 10) {
         int maj = d->prop.major, min = d->prop.minor;
         cudaFree(d->d_status);
+        cudaFreeHost(d->h_status);
         cudaStreamDestroy(d->own_stream);
         delete d;
         return set_error(GRL_ERR_UNSUPPORTED,
@@ -148,6 +151,7 @@ int grl_device_close(grl_device* dev) {
     cudaStreamSynchronize(dev->stream);
     for (auto& kv : dev->rope_tables) cudaFree(kv.second);
     cudaFree(dev->d_status);
+    cudaFreeHost(dev->h_status);
     cudaStreamDestroy(dev->own_stream);
     delete dev;
     return GRL_OK;
@@ -229,13 +233,18 @@ int grl_memset(grl_device* dev, void* dst, int value, size_t bytes) {
     return GRL_OK;
 }
 
-// After the stream drained: report (and clear) a failure that a kernel left in the status word.
-static int check_kernel_status(grl_device* dev) {
-    if (!dev->status_dirty) return GRL_OK;
+// A kernel with bounded waits leaves its failure in the device status word.  The word is copied to
+// pinned host memory by the same stream AHEAD of the wait, so that one wait serves both.
+static bool queue_status_copy(grl_device* dev) {
+    if (!dev->status_dirty) return false;
     dev->status_dirty = false;
-    int32_t st[4] = {0, 0, 0, 0};
-    GRL_CUDA(cudaMemcpyAsync(st, dev->d_status, sizeof(st), cudaMemcpyDeviceToHost, dev->stream));
-    GRL_CUDA(cudaStreamSynchronize(dev->stream));
+    return cudaMemcpyAsync(dev->h_status, dev->d_status, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, dev->stream) ==
+           cudaSuccess;
+}
+
+static int report_kernel_status(grl_device* dev, bool copied) {
+    if (!copied) return GRL_OK;
+    const int32_t* st = dev->h_status;
     if (st[0] == 0) return GRL_OK;
     // a kernel that gave up may have left arrival counters half-way: clear them with the status
     GRL_CUDA(cudaMemsetAsync(dev->d_status, 0, (4 + grl_device::kCounterSlots + 1) * sizeof(int32_t), dev->stream));
@@ -246,21 +255,24 @@ static int check_kernel_status(grl_device* dev) {
 int grl_sync(grl_device* dev, uint64_t timeout_ns) {
     GRL_REQUIRE(dev, "dev is NULL");
     DeviceGuard g(dev->ordinal);
+    const bool copied = queue_status_copy(dev);
     if (timeout_ns == 0) {
         GRL_CUDA(cudaStreamSynchronize(dev->stream));
-        return check_kernel_status(dev);
+        return report_kernel_status(dev, copied);
     }
     auto t0 = std::chrono::steady_clock::now();
     for (;;) {
         cudaError_t e = cudaStreamQuery(dev->stream);
-        if (e == cudaSuccess) return check_kernel_status(dev);
+        if (e == cudaSuccess) return report_kernel_status(dev, copied);
         if (e != cudaErrorNotReady)
             return set_error(GRL_ERR_CUDA, "stream failed: %s", cudaGetErrorString(e));
         auto dt = std::chrono::steady_clock::now() - t0;
-        if ((uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(dt).count() > timeout_ns)
+        const uint64_t ns = (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(dt).count();
+        if (ns > timeout_ns)
             return set_error(GRL_ERR_TIMEOUT, "stream did not finish within %llu ns",
                              (unsigned long long)timeout_ns);
-        std::this_thread::sleep_for(std::chrono::microseconds(20));
+        // a decode step is over in ~100 us and a sleep costs 50+ us of timer slack: poll first, sleep later
+        if (ns > 500000) std::this_thread::sleep_for(std::chrono::microseconds(20));
     }
 }
 
@@ -268,6 +280,18 @@ int grl_event_create(grl_event** out) {
     GRL_REQUIRE(out, "out is NULL");
     grl_event* e = new grl_event();
     cudaError_t err = cudaEventCreate(&e->ev);
+    if (err != cudaSuccess) {
+        delete e;
+        return set_error(GRL_ERR_CUDA, "cudaEventCreate failed: %s", cudaGetErrorString(err));
+    }
+    *out = e;
+    return GRL_OK;
+}
+
+int grl_event_create_untimed(grl_event** out) {
+    GRL_REQUIRE(out, "out is NULL");
+    grl_event* e = new grl_event();
+    cudaError_t err = cudaEventCreateWithFlags(&e->ev, cudaEventDisableTiming);
     if (err != cudaSuccess) {
         delete e;
         return set_error(GRL_ERR_CUDA, "cudaEventCreate failed: %s", cudaGetErrorString(err));
@@ -288,6 +312,13 @@ int grl_event_record(grl_device* dev, grl_event* ev) {
     GRL_REQUIRE(dev && ev, "NULL argument");
     DeviceGuard g(dev->ordinal);
     GRL_CUDA(cudaEventRecord(ev->ev, dev->stream));
+    return GRL_OK;
+}
+
+int grl_event_wait(grl_device* dev, grl_event* ev) {
+    GRL_REQUIRE(dev && ev, "NULL argument");
+    DeviceGuard g(dev->ordinal);
+    GRL_CUDA(cudaStreamWaitEvent(dev->stream, ev->ev, 0));
     return GRL_OK;
 }
 

@@ -19,8 +19,8 @@ ERR_TIMEOUT = -4
 SYMBOLS = [
     "grl_last_error", "grl_device_count", "grl_device_open", "grl_device_close", "grl_device_get_info",
     "grl_device_use_stream", "grl_malloc", "grl_free", "grl_host_alloc", "grl_host_free", "grl_memcpy_h2d",
-    "grl_memcpy_d2h", "grl_memcpy_d2d", "grl_memset", "grl_sync", "grl_event_create", "grl_event_destroy",
-    "grl_event_record", "grl_event_elapsed_ms", "grl_graph_begin", "grl_graph_end", "grl_graph_launch",
+    "grl_memcpy_d2h", "grl_memcpy_d2d", "grl_memset", "grl_sync", "grl_event_create", "grl_event_create_untimed", "grl_event_destroy",
+    "grl_event_record", "grl_event_wait", "grl_event_elapsed_ms", "grl_graph_begin", "grl_graph_end", "grl_graph_launch",
     "grl_graph_destroy", "grl_launch_count", "grl_cast", "grl_flash_fwd", "grl_rope", "grl_attention_mask",
     "grl_kv_append", "grl_kv_gather", "grl_decode_pick_splits", "grl_decode_workspace_bytes", "grl_gqa_decode",
     "grl_gqa_decode_static", "grl_lse_merge", "grl_ipc_export", "grl_ipc_import", "grl_ipc_release",
@@ -103,6 +103,7 @@ def lib():
         _lib.grl_cast.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_size_t]
         _lib.grl_device_use_stream.argtypes = [C.c_void_p, C.c_void_p]
         _lib.grl_event_record.argtypes = [C.c_void_p, C.c_void_p]
+        _lib.grl_event_wait.argtypes = [C.c_void_p, C.c_void_p]
         _lib.grl_event_elapsed_ms.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]
         _lib.grl_event_destroy.argtypes = [C.c_void_p]
         _lib.grl_graph_begin.argtypes = [C.c_void_p]

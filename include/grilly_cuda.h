@@ -82,8 +82,13 @@ int grl_memset(grl_device* dev, void* dst, int value, size_t bytes);
 int grl_sync(grl_device* dev, uint64_t timeout_ns);
 
 int grl_event_create(grl_event** out);
+int grl_event_create_untimed(grl_event** out); /* ordering only (grl_event_wait): cheaper to record */
 int grl_event_destroy(grl_event* ev);
 int grl_event_record(grl_device* dev, grl_event* ev);
+/* Work submitted to dev after this call starts only when ev (recorded on any handle's stream, of any
+ * GPU) has completed; the host does not wait.  Several handles opened on one GPU are several streams:
+ * this is how an upload, a kernel and a download of different chunks overlap. */
+int grl_event_wait(grl_device* dev, grl_event* ev);
 int grl_event_elapsed_ms(grl_event* start, grl_event* stop, float* ms); /* syncs on stop */
 
 /* Stream capture of a launch sequence (the 256-step decode loop); replaces the record-once /

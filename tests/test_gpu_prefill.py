@@ -255,3 +255,26 @@ def test_python_op_bf16_path(gpu):
     assert np.array_equal(buf, out)
     with pytest.raises(RuntimeError, match="out must be"):
         gpu.flash_attention2(Q, K, V, out=np.empty((1, 2, 3, 4), np.float32))
+
+
+def test_python_op_chunked_pipeline_is_bit_identical(dev, gpu):
+    # Above 8 MiB per tensor the host op uploads, computes and downloads (batch, head) chunks on three
+    # queues at once; the chunks must give exactly what one launch over device-resident tensors gives.
+    from grilly_next import cabi
+    from gpu_helpers import flash_cabi
+    rng = np.random.default_rng(77)
+    # bf16 tensor-core kernel, causal + RoPE + ragged lengths: 2 chunks of 8 heads
+    B, H, S, D = 2, 8, 1024, 128
+    Q, K, V = (rng.standard_normal((B, H, S, D), dtype=np.float32) for _ in range(3))
+    lens = np.array([1024, 700], np.int32)
+    got = gpu.flash_attention2(Q, K, V, causal=True, seq_lens=lens, rope_theta=10000.0, dtype="bf16")
+    want = flash_cabi(dev, Q, K, V, causal=True, seq_lens=lens, rope_mode=cabi.ROPE_INTERLEAVED, bf16=True,
+                      kernel=cabi.KERNEL_TCGEN05)
+    assert np.array_equal(got, want)
+    # fp32 kernel with the reference's (batch, seq) key mask: 6 chunks, the last one short
+    B, H, S, D = 2, 40, 512, 128
+    Q, K, V = (rng.standard_normal((B, H, S, D), dtype=np.float32) for _ in range(3))
+    mask = (rng.random((B, S)) > 0.3).astype(np.float32)
+    got = gpu.flash_attention2(Q, K, V, mask=mask)
+    want = flash_cabi(dev, Q, K, V, mask=mask, mask_kind=cabi.MASK_KEY)
+    assert np.array_equal(got, want)
