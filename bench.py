@@ -360,18 +360,27 @@ def bench_decode_e2e(dist, steps=32):
     for _ in range(T0 // blk):
         k0 = rng.standard_normal((B, blk, Hkv, D), dtype=np.float32)
         grilly_core.kv_cache_append(ctx, kv, k0, k0)
-    q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
-    k1 = rng.standard_normal((B, 1, Hkv, D), dtype=np.float32)
+    from grilly_next import cabi
+    L = cabi.lib()
+    q, qp = pinned_array(L, (B, 1, Hq, D), np.float32)
+    k1, kp = pinned_array(L, (B, 1, Hkv, D), np.float32)
+    o, op = pinned_array(L, (B, 1, Hq, D), np.float32)
+    q[...] = rng.standard_normal(q.shape, dtype=np.float32)
+    k1[...] = rng.standard_normal(k1.shape, dtype=np.float32)
     for _ in range(4):
-        grilly_core.decode_step(ctx, kv, q, k1, k1, rope_theta=c["theta"])
+        grilly_core.decode_step(ctx, kv, q, k1, k1, rope_theta=c["theta"], out=o)
     dist["barrier"]()
     t0 = time.perf_counter()
     for _ in range(steps):
-        o = grilly_core.decode_step(ctx, kv, q, k1, k1, rope_theta=c["theta"])
+        grilly_core.decode_step(ctx, kv, q, k1, k1, rope_theta=c["theta"], out=o)
     dt = dist["max"]((time.perf_counter() - t0) / steps)
     assert np.isfinite(o).all()
     grilly_core.destroy_kv_cache(ctx, kv)
-    return dt, (q.nbytes + 2 * k1.nbytes), o.nbytes
+    nb = (q.nbytes + 2 * k1.nbytes, o.nbytes)
+    del q, k1, o
+    for pp in (qp, kp, op):
+        L.grl_host_free(pp)
+    return dt, nb[0], nb[1]
 
 
 def bench_long_decode(dev, cabi, dist, steps=50, repeats=3, n_splits=0):
@@ -611,7 +620,7 @@ def main():
         if not args.skip_decode:
             ddt, dh2d, dd2h = bench_decode_e2e(dist)
             line["decode"]["e2e"] = {"value": CFG3["B"] / ddt * world, "unit": "tokens/s", "h2d_bytes_per_step": dh2d,
-                                     "d2h_bytes_per_step": dd2h, "ms_per_step": ddt * 1e3, "api": "grilly_core.decode_step"}
+                                     "d2h_bytes_per_step": dd2h, "ms_per_step": ddt * 1e3, "api": "grilly_core.decode_step(out=pinned), pinned fp32 host arrays in and out"}
     if rank == 0 and world == 1 and not args.skip_cpu:
         line["cpu_baseline"] = cpu_baseline()
 

@@ -560,7 +560,7 @@ PYBIND11_MODULE(grilly_core, m) {
     m.def(
         "decode_step",
         [](GrillyCoreContext& ctx, ops::KVCache& kv, FArr q, FArr kNew, FArr vNew, float ropeTheta, float ropeScaling,
-           const std::string& ropeMode, float scale) {
+           const std::string& ropeMode, float scale, std::optional<py::array_t<float>> outArr) {
             const auto& c = kv.config;
             if (q.ndim() != 4 || q.shape(0) != c.batchSize || q.shape(1) != 1 || q.shape(3) != c.headDim)
                 throw std::runtime_error("q must be (batch, 1, num_q_heads, head_dim)");
@@ -569,7 +569,14 @@ PYBIND11_MODULE(grilly_core, m) {
                     a->shape(3) != c.headDim)
                     throw std::runtime_error("k_new / v_new must be (batch, 1, num_kv_heads, head_dim)");
             const uint32_t Hq = uint32_t(q.shape(2));
-            py::array_t<float> out({py::ssize_t(c.batchSize), py::ssize_t(1), py::ssize_t(Hq), py::ssize_t(c.headDim)});
+            py::array_t<float> out;
+            if (outArr.has_value()) {   // numpy style: a caller-owned (pinned) array saves the allocation and its page faults
+                out = *outArr;
+                if (out.size() != q.size() || !(out.flags() & py::array::c_style) || !out.writeable())
+                    throw std::runtime_error("out must be a writable C-contiguous float32 array of q's size");
+            } else {
+                out = py::array_t<float>({py::ssize_t(c.batchSize), py::ssize_t(1), py::ssize_t(Hq), py::ssize_t(c.headDim)});
+            }
             ops::decodeStep(ctx.batch, ctx.pool, ctx.cache, kv, q.data(), kNew.data(), vNew.data(), out.mutable_data(),
                             Hq, ropeTheta != 0.0f ? parseRopeMode(ropeMode, false) : ops::RopeMode::None,
                             ropeTheta != 0.0f ? ropeTheta : 10000.0f, ropeScaling, scale);
@@ -577,7 +584,8 @@ PYBIND11_MODULE(grilly_core, m) {
         },
         py::arg("device"), py::arg("kv_cache"), py::arg("q"), py::arg("k_new"), py::arg("v_new"),
         py::arg("rope_theta") = 10000.0f, py::arg("rope_scaling") = 1.0f, py::arg("rope_mode") = "interleaved",
-        py::arg("scale") = 0.0f, "RoPE(q,k) at the current position, append k/v, attend over the cache");
+        py::arg("scale") = 0.0f, py::arg("out") = py::none(),
+        "RoPE(q,k) at the current position, append k/v, attend over the cache");
 
     // ---- DeviceGroup: the GPUs of one node behind one object, one Device (own stream, own pool) each.
     // flash_attention2 splits the heads in contiguous runs over the devices, one host thread per device

@@ -26,7 +26,7 @@ struct AppendArgs {
 // update_lens the grid has ONE chunk per sequence, so that the length read at entry cannot race
 // with the write at exit.
 template <typename T>
-__global__ void __launch_bounds__(256) kv_append_kernel(AppendArgs a) {
+__global__ void __launch_bounds__(1024) kv_append_kernel(AppendArgs a) {
     const int b = blockIdx.y;
     const int half = a.D / 2;
     const int len0 = a.seq_lens[b];
@@ -34,15 +34,22 @@ __global__ void __launch_bounds__(256) kv_append_kernel(AppendArgs a) {
     T* vp = reinterpret_cast<T*>(a.v_pages);
     const int slots = a.Hkv + (a.q_in ? a.Hq : 0);
     const int items = a.n_new * slots * half;
+    // The angle depends on (position, pair) only: a thread whose stride keeps its pair (block size a
+    // multiple of D/2, the decode step's case) evaluates the double-precision range reduction once.
+    int cached_pos = -1, cached_j = -1;
+    float c = 1.f, s = 0.f;
+#pragma unroll 2
     for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < items; idx += gridDim.x * blockDim.x) {
         const int j = idx % half;
         const int hs = (idx / half) % slots;
         const int i = idx / (half * slots);
         const int slot_pos = len0 + i;
-        float c = 1.f, s = 0.f;
         int d0 = 2 * j, d1 = 2 * j + 1;
         if (a.rope_mode == GRL_ROPE_HALF) { d0 = j; d1 = j + half; }
-        if (a.rope_mode != GRL_ROPE_NONE) rope_sincos(a.pos_base + slot_pos, a.freq.inv_freq[j], &c, &s);
+        if (a.rope_mode != GRL_ROPE_NONE && (slot_pos != cached_pos || j != cached_j)) {
+            rope_sincos(a.pos_base + slot_pos, a.freq.inv_freq[j], &c, &s);
+            cached_pos = slot_pos; cached_j = j;
+        }
         if (hs < a.Hkv) {
             const int page = a.block_table[(size_t)b * a.max_pages + slot_pos / a.P];
             const int slot = slot_pos % a.P;
@@ -127,8 +134,10 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p) {
     const bool fused_update = p->update_lens && chunks == 1;
     a.update_lens = fused_update ? 1 : 0;
     dim3 grid(chunks, kv.batch);
-    if (kv.cache_dtype == GRL_BF16) kv_append_kernel<__nv_bfloat16><<<grid, 256, 0, dev->stream>>>(a);
-    else kv_append_kernel<float><<<grid, 256, 0, dev->stream>>>(a);
+    // one chunk (the decode step): a wide CTA, so that every thread has only a few dependent load chains
+    const int threads = chunks == 1 ? (items > 512 ? 1024 : 512) : 256;
+    if (kv.cache_dtype == GRL_BF16) kv_append_kernel<__nv_bfloat16><<<grid, threads, 0, dev->stream>>>(a);
+    else kv_append_kernel<float><<<grid, threads, 0, dev->stream>>>(a);
     GRL_LAUNCHED("kv_append_kernel");
     if (p->update_lens && !fused_update) {
         advance_lens_kernel<<<(kv.batch + 127) / 128, 128, 0, dev->stream>>>(kv.seq_lens, kv.batch, p->n_new);
