@@ -385,7 +385,8 @@ def bench_decode_e2e(dist, steps=32):
 
 def bench_long_decode(dev, cabi, dist, steps=50, repeats=3, n_splits=0):
     """cfg4: B=1, Hq32/Hkv8, D128, KV length 131072 split in contiguous shards over the ranks; per step
-    every rank decodes its shard to one partial, NCCL all-gathers the partials, every rank merges."""
+    every rank decodes its shard to one partial, the partials cross NVLink (peer stores, or NCCL all-gather
+    with GRILLY_EXCHANGE=nccl) and every rank merges."""
     import torch
     import torch.distributed as td
     from grilly_next.parallel import CudaShardOps, ShardedDecoder, shard_range, torch_stream_handle
@@ -445,8 +446,8 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3, n_splits=0):
             ops.set_layout(layouts[i % nbuf]); o = dec.step(q)
         return o
 
-    # The step is three small launches (decode, NCCL all-gather, merge): replay `steps` of them from one CUDA
-    # graph so that launch latency does not hide the kernels.  The library's launches are captured like any
+    # The step is one to three small launches: replay `steps` of them from one CUDA graph so that launch
+    # latency does not hide the kernels.  The library's launches are captured like any
     # other work on the capturing stream (grl_device_use_stream).
     graph = None
     try:
@@ -475,7 +476,9 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3, n_splits=0):
         torch.cuda.synchronize()
         ms = dist["max"](dev.elapsed_ms(e0, e1))
         best = ms if best is None else min(best, ms)
-    launches = 2 if world == 1 else 3          # decode (+ merge of splits inside it), all-gather is NCCL's, final merge
+    # this library's launches per step: the decode kernel merges its own splits; NCCL mode adds the final merge
+    # (the all-gather is NCCL's kernel), "merge" mode the step-counter bump and the exchange+merge kernel
+    launches = {"": 1 if world == 1 else 2, "merge": 3, "decode": 1}[fused]
     assert bool(torch.isfinite(out).all())
     cabi.check(L.grl_device_use_stream(dev.h, None))
     return best / steps, launches, ops.p.n_splits, nbuf, graph is not None, fused
