@@ -25,7 +25,7 @@ struct KVCacheConfig {
     bool useAsymmetricQuant = false;  // not built
     uint32_t valueBits = 4;
     bool crossLayerSharing = false;
-    bool useH2O = false;              // eviction family: not built on the paged cache
+    bool useH2O = false;              // append beyond maxCacheTokens evicts the lowest-scoring tokens first
     bool useSpeculativeEviction = false;
     float evictionThreshold = 0.1f;
     // paged-cache additions
@@ -45,6 +45,15 @@ struct KVCache {
     uint32_t nextFreePage = 0;        // bump allocator over the pool (no eviction => no free list churn)
     uint32_t currentLen = 0;          // tokens of sequence 0 (the reference's single-sequence view)
     uint64_t totalAppended = 0;
+    uint64_t totalEvicted = 0;        // tokens removed by compaction, all sequences
+    // Per-token metadata of the eviction family (the reference's TokenMeta array, kv_cache.h:68-73), in HBM:
+    GrillyBuffer cumScore;            // float  [B][capacity]
+    GrillyBuffer tombstone;           // uint8  [B][capacity]
+    GrillyBuffer relevance;           // float  [B][capacity]
+    GrillyBuffer evicted;             // int32  [B]: tokens compaction removed (RoPE position offset of appends)
+    grl_device* device = nullptr;     // the device the buffers live on (stats read the metadata back)
+    uint32_t capacity() const { return maxPages * config.pageTokens; }
+    grl_kv_meta meta() const;
     KVCacheConfig config;
     grl_kv_layout layout() const;
 };
@@ -98,11 +107,22 @@ void decodeStepDevice(BufferPool& pool, PipelineCache& cache, KVCache& kvCache, 
                       const GrillyBuffer& kNew, const GrillyBuffer& vNew, GrillyBuffer& qRotated, GrillyBuffer& out,
                       uint32_t numQHeads, RopeMode mode, float theta, float scaling, float scale, GrillyBuffer& ws);
 
-// Eviction family of the reference (kv_cache.h:186-229): not built on the paged cache; each
-// throws std::runtime_error naming itself.
+// Eviction family of the reference (kv_cache.h:186-229) on the paged cache.
+/// attentionScores: nullptr, or host (T, T) probabilities of sequence 0 -- (B, T, T) for a batched cache
+/// with every sequence at length T -- whose column sums are added to the cumulative scores first
+/// (kv_cache.cpp:603-616).  Then the numEvict lowest-scoring tokens of every sequence are tombstoned
+/// (0 => a quarter; nothing where numEvict >= the length).  Ties go to the lowest index.
 void kvCacheEvictH2O(CommandBatch&, BufferPool&, PipelineCache&, KVCache&, const float* attentionScores,
                      uint32_t numEvict = 0);
+/// The reference's behaviour without a trained eviction head (kv_cache.cpp:905-929; the head itself is
+/// not built): relevance = 0.7 cum/max + 0.3 t/len, tombstone below config.evictionThreshold.
+void kvCacheEvictSpeculative(CommandBatch&, BufferPool&, PipelineCache&, KVCache&, const float* hiddenStates,
+                             uint32_t hiddenDim);
+/// Move live tokens to the front of every sequence and shrink the lengths (kv_cache.cpp:941-992).
 void kvCacheCompact(CommandBatch&, BufferPool&, PipelineCache&, KVCache&);
+/// Metadata of sequence `seq` back on the host: cumulative scores, tombstones, predicted relevance.
+void kvCacheTokenMeta(BufferPool& pool, const KVCache&, uint32_t seq, std::vector<float>& cumScore,
+                      std::vector<uint8_t>& tombstone, std::vector<float>& relevance);
 
 }  // namespace ops
 }  // namespace grilly

@@ -445,12 +445,42 @@ PYBIND11_MODULE(grilly_core, m) {
     m.def(
         "kv_cache_evict_h2o",
         [](GrillyCoreContext& ctx, ops::KVCache& kv, std::optional<FArr> scores, uint32_t numEvict) {
+            if (scores.has_value()) {
+                const py::ssize_t T = kv.hostSeqLens.empty() ? 0 : kv.hostSeqLens[0];
+                const bool ok2 = scores->ndim() == 2 && kv.config.batchSize == 1 && scores->shape(0) == T && scores->shape(1) == T;
+                const bool ok3 = scores->ndim() == 3 && scores->shape(0) == kv.config.batchSize && scores->shape(1) == T &&
+                                 scores->shape(2) == T;
+                if (!ok2 && !ok3)
+                    throw std::runtime_error("attention_scores must be (cache_len, cache_len), or (batch, cache_len, cache_len)");
+            }
             ops::kvCacheEvictH2O(ctx.batch, ctx.pool, ctx.cache, kv, scores ? scores->data() : nullptr, numEvict);
         },
-        py::arg("device"), py::arg("kv_cache"), py::arg("attention_scores") = py::none(), py::arg("num_evict") = 0);
+        py::arg("device"), py::arg("kv_cache"), py::arg("attention_scores") = py::none(), py::arg("num_evict") = 0,
+        "Add the column sums of attention_scores to the cumulative scores, tombstone the num_evict lowest");
     m.def("kv_cache_compact",
           [](GrillyCoreContext& ctx, ops::KVCache& kv) { ops::kvCacheCompact(ctx.batch, ctx.pool, ctx.cache, kv); },
-          py::arg("device"), py::arg("kv_cache"));
+          py::arg("device"), py::arg("kv_cache"), "Move the live tokens to the front and shrink the cache length");
+    m.def(
+        "kv_cache_evict_speculative",
+        [](GrillyCoreContext& ctx, ops::KVCache& kv, py::object, uint32_t) {
+            // no eviction head is built, so this is the reference's behaviour for an untrained head
+            ops::kvCacheEvictSpeculative(ctx.batch, ctx.pool, ctx.cache, kv, nullptr, 0);
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("hidden_states") = py::none(), py::arg("hidden_dim") = 0,
+        "Tombstone tokens whose heuristic relevance (0.7 score/max + 0.3 recency) is below eviction_threshold");
+    m.def(
+        "kv_cache_token_meta",
+        [](GrillyCoreContext& ctx, const ops::KVCache& kv, uint32_t seq) {
+            std::vector<float> cum, rel;
+            std::vector<uint8_t> tomb;
+            ops::kvCacheTokenMeta(ctx.pool, kv, seq, cum, tomb, rel);
+            py::dict d;
+            d["cumulative_score"] = py::array_t<float>(py::ssize_t(cum.size()), cum.data());
+            d["tombstone"] = py::array_t<uint8_t>(py::ssize_t(tomb.size()), tomb.data());
+            d["predicted_relevance"] = py::array_t<float>(py::ssize_t(rel.size()), rel.data());
+            return d;
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("seq") = 0, "Per-token eviction metadata of one sequence");
 
     // ---- GQA decode on DeviceTensors (asynchronous; q already rotated)
     m.def(
@@ -679,6 +709,5 @@ PYBIND11_MODULE(grilly_core, m) {
     };
     notBuilt("kv_cache_init_eviction_head", "the trainable eviction head is not built on the paged cache");
     notBuilt("kv_cache_train_eviction_head", "the trainable eviction head is not built on the paged cache");
-    notBuilt("kv_cache_evict_speculative", "speculative eviction is not built on the paged cache");
     notBuilt("fused_attention_cpu", "the MLA latent path (CPU reference of the fused subgroup attention) is not built");
 }

@@ -65,6 +65,16 @@ grl_kv_layout KVCache::layout() const {
     return l;
 }
 
+grl_kv_meta KVCache::meta() const {
+    grl_kv_meta m{};
+    m.cum_score = static_cast<float*>(cumScore.dptr);
+    m.tombstone = static_cast<uint8_t*>(tombstone.dptr);
+    m.relevance = static_cast<float*>(relevance.dptr);
+    m.evicted = static_cast<int32_t*>(evicted.dptr);
+    m.capacity = int32_t(capacity());
+    return m;
+}
+
 KVCache createKVCache(BufferPool& pool, const KVCacheConfig& cfg) {
     if (cfg.compressionRatio != 1 || cfg.useAsymmetricQuant)
         throw std::runtime_error(
@@ -87,6 +97,16 @@ KVCache createKVCache(BufferPool& pool, const KVCacheConfig& cfg) {
     kv.hostBlockTable.assign(size_t(kv.maxPages) * cfg.batchSize, -1);
     kv.hostSeqLens.assign(cfg.batchSize, 0);
     grl_device* dev = pool.device().handle();
+    kv.device = dev;
+    const size_t slots = size_t(kv.capacity()) * cfg.batchSize;
+    kv.cumScore = pool.acquire(slots * 4);
+    kv.tombstone = pool.acquire(slots);
+    kv.relevance = pool.acquire(slots * 4);
+    kv.evicted = pool.acquire(size_t(cfg.batchSize) * 4);
+    check(grl_memset(dev, kv.cumScore.dptr, 0, slots * 4), "createKVCache");
+    check(grl_memset(dev, kv.tombstone.dptr, 0, slots), "createKVCache");
+    check(grl_memset(dev, kv.relevance.dptr, 0, slots * 4), "createKVCache");
+    check(grl_memset(dev, kv.evicted.dptr, 0, size_t(cfg.batchSize) * 4), "createKVCache");
     check(grl_memset(dev, kv.blockTable.dptr, 0, size_t(kv.maxPages) * cfg.batchSize * 4), "createKVCache");
     check(grl_memset(dev, kv.seqLens.dptr, 0, size_t(cfg.batchSize) * 4), "createKVCache");
     check(grl_sync(dev, 0), "createKVCache");
@@ -98,6 +118,10 @@ void destroyKVCache(BufferPool& pool, KVCache& kv) {
     pool.release(kv.vPages);
     pool.release(kv.blockTable);
     pool.release(kv.seqLens);
+    pool.release(kv.cumScore);
+    pool.release(kv.tombstone);
+    pool.release(kv.relevance);
+    pool.release(kv.evicted);
     kv.hostBlockTable.clear();
     kv.hostSeqLens.clear();
     kv.currentLen = 0;
@@ -113,6 +137,13 @@ void kvCacheAppendRope(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
     const auto& c = kv.config;
     grl_device* dev = pool.device().handle();
     cache.getOrCreate("kv-append/" + std::to_string(c.headDim));
+    // Overflow: evict what does not fit (lowest cumulative scores, if H2O is on), then compact
+    // (kv_cache.cpp:161-172).
+    const uint32_t longest = uint32_t(*std::max_element(kv.hostSeqLens.begin(), kv.hostSeqLens.end()));
+    if (longest + n > c.maxCacheTokens && longest > 0) {
+        if (c.useH2O) kvCacheEvictH2O(batch, pool, cache, kv, nullptr, longest + n - c.maxCacheTokens);
+        kvCacheCompact(batch, pool, cache, kv);
+    }
     reservePages(pool, kv, n);
     const size_t kvElems = size_t(c.batchSize) * n * c.numHeads * c.headDim;
     const size_t qElems = qIn ? size_t(c.batchSize) * n * numQHeads * c.headDim : 0;
@@ -132,6 +163,7 @@ void kvCacheAppendRope(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
         p.n_new = int(n); p.num_q_heads = int(numQHeads);
         p.rope_mode = int(mode); p.rope_theta = theta; p.rope_scaling = scaling;
         p.pos_base = posBase; p.update_lens = 1;
+        p.pos_offsets = static_cast<const int32_t*>(kv.evicted.dptr);
         check(grl_kv_append(dev, &p), "kvCacheAppend");
         if (qIn && qOut) check(grl_memcpy_d2h(dev, qOut, qo.dptr, qElems * 4), "kvCacheAppend: q download");
         batch.submit();
@@ -182,10 +214,23 @@ KVCacheStats kvCacheGetStats(const KVCache& kv) {
     KVCacheStats s{};
     s.currentTokens = kv.currentLen;
     s.maxTokens = kv.config.maxCacheTokens;
-    s.totalEvicted = 0;
+    s.totalEvicted = uint32_t(kv.totalEvicted);
     s.totalAppended = uint32_t(kv.totalAppended);
     s.compressionRatio = kv.config.dtype == GRL_BF16 ? 2.0f : 1.0f;  // bytes saved against float32 storage
+    // mean cumulative score of the active tokens of sequence 0, summed in index order (kv_cache.cpp:1004-1015)
     s.avgAttentionScore = 0.0f;
+    if (kv.device && kv.cumScore.valid() && kv.currentLen > 0) {
+        std::vector<float> cum(kv.currentLen);
+        std::vector<uint8_t> tomb(kv.currentLen);
+        check(grl_memcpy_d2h(kv.device, cum.data(), kv.cumScore.dptr, cum.size() * 4), "kvCacheGetStats");
+        check(grl_memcpy_d2h(kv.device, tomb.data(), kv.tombstone.dptr, tomb.size()), "kvCacheGetStats");
+        check(grl_sync(kv.device, 0), "kvCacheGetStats");
+        float total = 0.0f;
+        uint32_t active = 0;
+        for (uint32_t t = 0; t < kv.currentLen; ++t)
+            if (!tomb[t]) { total += cum[t]; ++active; }
+        if (active) s.avgAttentionScore = total / float(active);
+    }
     s.pagesTotal = kv.numPages;
     s.pagesUsed = kv.nextFreePage;
     s.bytes = uint64_t(kv.kPages.bucketSize) + kv.vPages.bucketSize;
@@ -265,6 +310,7 @@ void decodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVC
         ap.n_new = 1; ap.num_q_heads = int(numQHeads);
         ap.rope_mode = int(mode); ap.rope_theta = theta; ap.rope_scaling = scaling;
         ap.pos_base = 0; ap.update_lens = 1;
+        ap.pos_offsets = static_cast<const int32_t*>(kv.evicted.dptr);
         check(grl_kv_append(dev, &ap), "decodeStep: append");
         for (auto& l : kv.hostSeqLens) l += 1;
         kv.currentLen = uint32_t(kv.hostSeqLens[0]);
@@ -315,6 +361,7 @@ void decodeStepDevice(BufferPool& pool, PipelineCache& cache, KVCache& kv, const
     ap.n_new = 1; ap.num_q_heads = int(numQHeads);
     ap.rope_mode = int(mode); ap.rope_theta = theta; ap.rope_scaling = scaling;
     ap.pos_base = 0; ap.update_lens = 1;
+    ap.pos_offsets = static_cast<const int32_t*>(kv.evicted.dptr);
     check(grl_kv_append(dev, &ap), "decodeStep: append");
     for (auto& l : kv.hostSeqLens) l += 1;
     kv.currentLen = uint32_t(kv.hostSeqLens[0]);
@@ -322,11 +369,96 @@ void decodeStepDevice(BufferPool& pool, PipelineCache& cache, KVCache& kv, const
     launchDecode(dev, pool, kv, static_cast<const float*>(qRotated.dptr), static_cast<float*>(out.dptr), numQHeads, scale, 0, ws);
 }
 
-void kvCacheEvictH2O(CommandBatch&, BufferPool&, PipelineCache&, KVCache&, const float*, uint32_t) {
-    throw std::runtime_error("kvCacheEvictH2O: the eviction family is not built on the paged cache");
+void kvCacheEvictH2O(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kv,
+                     const float* attentionScores, uint32_t numEvict) {
+    if (!kv.kPages.valid()) throw std::runtime_error("kvCacheEvictH2O: cache was destroyed");
+    const auto& c = kv.config;
+    // nothing to do where the count reaches the length -- decided before the scores are touched, as the
+    // reference does (kv_cache.cpp:598-601); with ragged sequences the kernels apply it per sequence
+    bool any = false;
+    for (int32_t len : kv.hostSeqLens) {
+        const uint32_t k = numEvict ? numEvict : uint32_t(len) / 4;
+        if (k < uint32_t(len)) any = true;
+    }
+    if (!any) return;
+    grl_device* dev = pool.device().handle();
+    cache.getOrCreate("kv-evict-h2o");
+    grl_kv_layout l = kv.layout();
+    grl_kv_meta m = kv.meta();
+    GrillyBuffer scores;
+    try {
+        Recording rec(batch);
+        if (attentionScores) {
+            const uint32_t T = uint32_t(kv.hostSeqLens[0]);
+            for (int32_t len : kv.hostSeqLens)
+                if (uint32_t(len) != T)
+                    throw std::runtime_error("kvCacheEvictH2O: attention scores need sequences of equal length");
+            const size_t n = size_t(c.batchSize) * T * T;
+            scores = pool.acquire(n * 4);
+            pool.upload(scores, attentionScores, n * 4);
+            check(grl_kv_score_accumulate(dev, &l, &m, static_cast<const float*>(scores.dptr), int(T), int(T)),
+                  "kvCacheEvictH2O: accumulate");
+        }
+        check(grl_kv_evict_lowest(dev, &l, &m, int(numEvict)), "kvCacheEvictH2O");
+        batch.submit();
+    } catch (...) {
+        pool.release(scores);
+        throw;
+    }
+    pool.release(scores);
 }
-void kvCacheCompact(CommandBatch&, BufferPool&, PipelineCache&, KVCache&) {
-    throw std::runtime_error("kvCacheCompact: the eviction family is not built on the paged cache");
+
+void kvCacheEvictSpeculative(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kv,
+                             const float* /*hiddenStates*/, uint32_t /*hiddenDim*/) {
+    if (!kv.kPages.valid()) throw std::runtime_error("kvCacheEvictSpeculative: cache was destroyed");
+    cache.getOrCreate("kv-evict-heuristic");
+    grl_kv_layout l = kv.layout();
+    grl_kv_meta m = kv.meta();
+    Recording rec(batch);
+    check(grl_kv_evict_heuristic(pool.device().handle(), &l, &m, kv.config.evictionThreshold),
+          "kvCacheEvictSpeculative");
+    batch.submit();
+}
+
+void kvCacheCompact(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kv) {
+    if (!kv.kPages.valid()) throw std::runtime_error("kvCacheCompact: cache was destroyed");
+    grl_device* dev = pool.device().handle();
+    cache.getOrCreate("kv-compact/" + std::to_string(kv.config.headDim));
+    grl_kv_layout l = kv.layout();
+    grl_kv_meta m = kv.meta();
+    size_t bytes = 0;
+    check(grl_kv_compact_scratch_bytes(&l, &m, &bytes), "kvCacheCompact");
+    GrillyBuffer scratch = pool.acquire(bytes);
+    std::vector<int32_t> lens(kv.config.batchSize);
+    try {
+        Recording rec(batch);
+        check(grl_kv_compact(dev, &l, &m, scratch.dptr, scratch.bucketSize), "kvCacheCompact");
+        check(grl_memcpy_d2h(dev, lens.data(), kv.seqLens.dptr, lens.size() * 4), "kvCacheCompact: lengths");
+        batch.submit();
+    } catch (...) {
+        pool.release(scratch);
+        throw;
+    }
+    pool.release(scratch);
+    for (size_t b = 0; b < lens.size(); ++b) {
+        kv.totalEvicted += uint64_t(kv.hostSeqLens[b] - lens[b]);
+        kv.hostSeqLens[b] = lens[b];
+    }
+    kv.currentLen = uint32_t(kv.hostSeqLens[0]);
+}
+
+void kvCacheTokenMeta(BufferPool& pool, const KVCache& kv, uint32_t seq, std::vector<float>& cumScore,
+                      std::vector<uint8_t>& tombstone, std::vector<float>& relevance) {
+    if (!kv.kPages.valid()) throw std::runtime_error("kvCacheTokenMeta: cache was destroyed");
+    if (seq >= kv.config.batchSize) throw std::runtime_error("kvCacheTokenMeta: sequence index out of range");
+    const size_t T = size_t(kv.hostSeqLens[seq]), off = size_t(seq) * kv.capacity();
+    cumScore.resize(T); tombstone.resize(T); relevance.resize(T);
+    if (T == 0) return;
+    grl_device* dev = pool.device().handle();
+    check(grl_memcpy_d2h(dev, cumScore.data(), static_cast<const float*>(kv.cumScore.dptr) + off, T * 4), "kvCacheTokenMeta");
+    check(grl_memcpy_d2h(dev, tombstone.data(), static_cast<const uint8_t*>(kv.tombstone.dptr) + off, T), "kvCacheTokenMeta");
+    check(grl_memcpy_d2h(dev, relevance.data(), static_cast<const float*>(kv.relevance.dptr) + off, T * 4), "kvCacheTokenMeta");
+    check(grl_sync(dev, 0), "kvCacheTokenMeta");
 }
 
 }  // namespace ops

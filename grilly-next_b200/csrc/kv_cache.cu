@@ -17,6 +17,7 @@ struct AppendArgs {
     float* q_out;
     int B, Hkv, Hq, D, P, max_pages, n_new;
     int rope_mode, pos_base, update_lens;
+    const int32_t* pos_offsets;
     RopeFreq freq;
 };
 
@@ -30,6 +31,7 @@ __global__ void __launch_bounds__(1024) kv_append_kernel(AppendArgs a) {
     const int b = blockIdx.y;
     const int half = a.D / 2;
     const int len0 = a.seq_lens[b];
+    const int pos_off = a.pos_offsets ? a.pos_offsets[b] : 0;
     T* kp = reinterpret_cast<T*>(a.k_pages);
     T* vp = reinterpret_cast<T*>(a.v_pages);
     const int slots = a.Hkv + (a.q_in ? a.Hq : 0);
@@ -44,10 +46,11 @@ __global__ void __launch_bounds__(1024) kv_append_kernel(AppendArgs a) {
         const int hs = (idx / half) % slots;
         const int i = idx / (half * slots);
         const int slot_pos = len0 + i;
+        const int rope_pos = a.pos_base + pos_off + slot_pos;
         int d0 = 2 * j, d1 = 2 * j + 1;
         if (a.rope_mode == GRL_ROPE_HALF) { d0 = j; d1 = j + half; }
         if (a.rope_mode != GRL_ROPE_NONE && (slot_pos != cached_pos || j != cached_j)) {
-            rope_sincos(a.pos_base + slot_pos, a.freq.inv_freq[j], &c, &s);
+            rope_sincos(rope_pos, a.freq.inv_freq[j], &c, &s);
             cached_pos = slot_pos; cached_j = j;
         }
         if (hs < a.Hkv) {
@@ -125,7 +128,7 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p) {
     a.k_new = p->k_new; a.v_new = p->v_new; a.q_in = p->q_in; a.q_out = p->q_out;
     a.B = kv.batch; a.Hkv = kv.num_kv_heads; a.Hq = p->num_q_heads; a.D = kv.head_dim; a.P = kv.page_tokens;
     a.max_pages = kv.max_pages; a.n_new = p->n_new;
-    a.rope_mode = p->rope_mode; a.pos_base = p->pos_base;
+    a.rope_mode = p->rope_mode; a.pos_base = p->pos_base; a.pos_offsets = p->pos_offsets;
     if (p->rope_mode != GRL_ROPE_NONE) a.freq = make_rope_freq(kv.head_dim, p->rope_theta, p->rope_scaling);
     const long long items = (long long)p->n_new * (kv.num_kv_heads + (p->q_in ? p->num_q_heads : 0)) * (kv.head_dim / 2);
     // one CTA per sequence while a CTA has at most 16 items per thread (a decode step), more for bulk appends

@@ -1,0 +1,341 @@
+// Eviction on the paged KV cache: H2O selection, the heuristic branch of speculative eviction, and
+// compaction.  Replaces the host loops of kvCacheEvictH2O (cpp/src/ops/kv_cache.cpp:595-634),
+// kvCacheEvictSpeculative's fallback (:905-929) and kvCacheCompact (:941-992), which in the reference
+// walk persistently mapped metadata on the CPU; here the metadata (cumulative score, tombstone) and the
+// K/V rows live in HBM and every step is a kernel.  Everything is exact: the column sums add in the
+// reference's order (one thread per cached token walks the query rows), selection is a radix select on
+// the float bit patterns with ties going to the lowest index, and rows move as raw bytes.
+#include "common.cuh"
+
+namespace grl {
+namespace evict {
+
+constexpr int kThreads = 1024;
+
+// float -> uint32 whose unsigned order is the float order
+__device__ __forceinline__ uint32_t order_key(float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// cum[b][t] += sum_q attn[b][q][t], the sum over q taken in ascending q with plain float adds
+// (kv_cache.cpp:606-615).
+__global__ void score_accumulate_kernel(const float* __restrict__ attn, int q_rows, int ld, const int32_t* seq_lens,
+                                        float* cum, int capacity) {
+    const int b = blockIdx.y;
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const int len = seq_lens[b];
+    if (t >= len || t >= ld) return;
+    const float* col = attn + (size_t)b * q_rows * ld + t;
+    float acc = 0.f;
+    for (int q = 0; q < q_rows; ++q) acc = __fadd_rn(acc, col[(size_t)q * ld]);
+    float* c = cum + (size_t)b * capacity + t;
+    *c = __fadd_rn(*c, acc);
+}
+
+// block-wide exclusive scan of one int per thread; returns the exclusive prefix, *total = block sum
+__device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* s_warp /* [33] */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += n;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = lane < (int)(blockDim.x >> 5) ? s_warp[lane] : 0;
+        int winc = w;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, winc, d);
+            if (lane >= d) winc += n;
+        }
+        s_warp[lane] = winc - w;                 // exclusive prefix of the warp sums
+        if (lane == 31) s_warp[32] = winc;       // block total
+    }
+    __syncthreads();
+    const int ex = s_warp[warp] + inc - v;
+    *total = s_warp[32];
+    __syncthreads();                             // s_warp is reused by the next call
+    return ex;
+}
+
+// One CTA per sequence: tombstone the num_evict tokens of [0, len) with the lowest cumulative score,
+// ties to the lowest index (kv_cache.cpp:618-633; std::partial_sort leaves the order of ties open).
+__global__ void __launch_bounds__(kThreads) evict_lowest_kernel(const float* __restrict__ cum, uint8_t* tomb,
+                                                               const int32_t* seq_lens, int capacity, int num_evict) {
+    __shared__ int s_hist[256];
+    __shared__ int s_warp[33];
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_k;
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const int len = seq_lens[b];
+    int k = num_evict > 0 ? num_evict : len / 4;          // default: a quarter (kv_cache.cpp:598-600)
+    if (k <= 0 || k >= len) return;                       // kv_cache.cpp:601
+    const float* c = cum + (size_t)b * capacity;
+    uint8_t* tb = tomb + (size_t)b * capacity;
+    // radix select, most significant byte first: after the four passes `prefix` is the key of the k-th
+    // smallest element and k has become its rank among the elements equal to it
+    if (tid == 0) { s_prefix = 0; s_k = k; }
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        for (int i = tid; i < 256; i += kThreads) s_hist[i] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix;
+        const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        for (int t = tid; t < len; t += kThreads) {
+            const uint32_t key = order_key(c[t]);
+            if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int kk = s_k, bin = 0;
+            for (; bin < 256; ++bin) {
+                if (kk <= s_hist[bin]) break;
+                kk -= s_hist[bin];
+            }
+            s_prefix = prefix | ((uint32_t)bin << shift);
+            s_k = kk;
+        }
+        __syncthreads();
+    }
+    const uint32_t kth = s_prefix;
+    const int need_equal = s_k;        // how many of the elements equal to kth go, in index order
+    int taken = 0;                     // equal elements tombstoned so far (same in every thread)
+    for (int base = 0; base < len; base += kThreads) {
+        const int t = base + tid;
+        const uint32_t key = t < len ? order_key(c[t]) : 0xffffffffu;
+        const int eq = (t < len && key == kth) ? 1 : 0;
+        int total;
+        const int rank = block_exclusive_scan(eq, &total, s_warp);
+        if (t < len && (key < kth || (eq && taken + rank < need_equal))) tb[t] = 1;
+        taken += total;
+    }
+}
+
+// Heuristic of kvCacheEvictSpeculative without a trained head (kv_cache.cpp:905-929): relevance =
+// 0.7 * cum / max(cum) + 0.3 * t / len; tombstone below the threshold.  The maximum runs over every
+// token of [0, len), tombstoned or not, and starts from 0 as the reference's does.
+__global__ void __launch_bounds__(kThreads) evict_heuristic_kernel(const float* __restrict__ cum, uint8_t* tomb,
+                                                                  float* relevance, const int32_t* seq_lens,
+                                                                  int capacity, float threshold) {
+    __shared__ float s_max[32];
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int len = seq_lens[b];
+    const float* c = cum + (size_t)b * capacity;
+    float m = 0.f;
+    for (int t = tid; t < len; t += kThreads) m = fmaxf(m, c[t]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    if (lane == 0) s_max[warp] = m;
+    __syncthreads();
+    m = s_max[0];
+    for (int w = 1; w < kThreads / 32; ++w) m = fmaxf(m, s_max[w]);
+    const float inv = m > 0.f ? __fdiv_rn(1.f, m) : 1.f;
+    for (int t = tid; t < len; t += kThreads) {
+        if (tomb[(size_t)b * capacity + t]) continue;
+        const float norm = __fmul_rn(c[t], inv);
+        const float rec = __fdiv_rn((float)t, (float)len);
+        const float rel = __fadd_rn(__fmul_rn(0.7f, norm), __fmul_rn(0.3f, rec));
+        if (relevance) relevance[(size_t)b * capacity + t] = rel;
+        if (rel < threshold) tomb[(size_t)b * capacity + t] = 1;
+    }
+}
+
+// One CTA per sequence: new_pos[t] = number of live tokens before t (or -1 for a tombstone), live count
+// to new_len[b].
+__global__ void __launch_bounds__(kThreads) compact_scan_kernel(const uint8_t* __restrict__ tomb,
+                                                               const int32_t* seq_lens, int capacity,
+                                                               int32_t* new_pos, int32_t* new_len) {
+    __shared__ int s_warp[33];
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const int len = seq_lens[b];
+    int carried = 0;
+    for (int base = 0; base < len; base += kThreads) {
+        const int t = base + tid;
+        const int live = (t < len && !tomb[(size_t)b * capacity + t]) ? 1 : 0;
+        int total;
+        const int ex = block_exclusive_scan(live, &total, s_warp);
+        if (t < len) new_pos[(size_t)b * capacity + t] = live ? carried + ex : -1;
+        carried += total;
+    }
+    if (tid == 0) new_len[b] = carried;
+}
+
+struct MoveArgs {
+    uint8_t* k_pages;
+    uint8_t* v_pages;
+    const int32_t* block_table;
+    const int32_t* seq_lens;     // lengths BEFORE compaction
+    const int32_t* new_pos;
+    int Hkv, P, max_pages, capacity, row_bytes;
+};
+
+// One CTA per (kv head, sequence, K|V) walks the sequence in tiles of 64 tokens: load the live rows of
+// the tile, barrier, store them at their new positions, barrier.  new_pos[t] <= t and order is kept, so
+// a tile never overwrites a row that a later tile still has to read -- the in-order loop of
+// kv_cache.cpp:957-989, one head at a time.
+constexpr int kTile = 64;
+__global__ void __launch_bounds__(256) compact_move_kernel(MoveArgs a) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    uint8_t* pool = blockIdx.z == 0 ? a.k_pages : a.v_pages;
+    const int len = a.seq_lens[b];
+    const int32_t* bt = a.block_table + (size_t)b * a.max_pages;
+    const int32_t* np = a.new_pos + (size_t)b * a.capacity;
+    const int vec_per_row = a.row_bytes / 16;
+    auto row_ptr = [&](int t) -> uint4* {
+        const size_t page = (size_t)bt[t / a.P];
+        return reinterpret_cast<uint4*>(pool + ((page * a.Hkv + h) * a.P + (t % a.P)) * (size_t)a.row_bytes);
+    };
+    constexpr int kMaxPerThread = 8;     // 64 rows x 512 B (float32, D=128) / 16 B / 256 threads
+    uint4 regs[kMaxPerThread];
+    for (int base = 0; base < len; base += kTile) {
+        const int items = kTile * vec_per_row;
+#pragma unroll
+        for (int i = 0; i < kMaxPerThread; ++i) {
+            const int idx = threadIdx.x + i * 256;
+            if (idx < items) {
+                const int t = base + idx / vec_per_row;
+                if (t < len && np[t] >= 0 && np[t] != t) regs[i] = row_ptr(t)[idx % vec_per_row];
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < kMaxPerThread; ++i) {
+            const int idx = threadIdx.x + i * 256;
+            if (idx < items) {
+                const int t = base + idx / vec_per_row;
+                if (t < len && np[t] >= 0 && np[t] != t) row_ptr(np[t])[idx % vec_per_row] = regs[i];
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// One CTA per sequence, after the rows have moved: compact the scores the same way, clear the
+// tombstones, zero the scores of the freed tail, publish the new length and the evicted count.
+__global__ void __launch_bounds__(kThreads) compact_meta_kernel(float* cum, uint8_t* tomb, float* relevance,
+                                                               int32_t* seq_lens, int32_t* evicted,
+                                                               const int32_t* new_pos, const int32_t* new_len,
+                                                               int capacity) {
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const int len = seq_lens[b], nl = new_len[b];
+    float* c = cum + (size_t)b * capacity;
+    float* r = relevance ? relevance + (size_t)b * capacity : nullptr;
+    const int32_t* np = new_pos + (size_t)b * capacity;
+    for (int base = 0; base < len; base += kThreads) {
+        const int t = base + tid;
+        const bool mv = t < len && np[t] >= 0;
+        const float v = mv ? c[t] : 0.f;
+        const float rv = (mv && r) ? r[t] : 0.f;
+        __syncthreads();
+        if (mv) { c[np[t]] = v; if (r) r[np[t]] = rv; }
+        __syncthreads();
+    }
+    for (int t = tid; t < len; t += kThreads) {
+        tomb[(size_t)b * capacity + t] = 0;
+        if (t >= nl) { c[t] = 0.f; if (r) r[t] = 0.f; }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        seq_lens[b] = nl;
+        if (evicted) evicted[b] += len - nl;
+    }
+}
+
+static int check_meta(const grl_kv_layout* kv, const grl_kv_meta* m) {
+    GRL_REQUIRE(kv && m, "NULL argument");
+    GRL_REQUIRE(kv->block_table && kv->seq_lens && kv->batch > 0 && kv->page_tokens > 0 && kv->max_pages > 0,
+                "bad cache layout");
+    GRL_REQUIRE(m->cum_score && m->tombstone, "NULL metadata buffer");
+    GRL_REQUIRE(m->capacity >= kv->max_pages * kv->page_tokens, "metadata capacity %d below the cache's %d tokens",
+                m->capacity, kv->max_pages * kv->page_tokens);
+    return GRL_OK;
+}
+
+}  // namespace evict
+}  // namespace grl
+
+using namespace grl;
+using namespace grl::evict;
+
+extern "C" {
+
+int grl_kv_score_accumulate(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, const float* attn,
+                            int q_rows, int ld) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    int rc = check_meta(kv, meta);
+    if (rc) return rc;
+    GRL_REQUIRE(attn && q_rows > 0 && ld > 0 && ld <= meta->capacity, "bad attention-score shape");
+    DeviceGuard g(dev->ordinal);
+    dim3 grid((ld + 255) / 256, kv->batch);
+    score_accumulate_kernel<<<grid, 256, 0, dev->stream>>>(attn, q_rows, ld, kv->seq_lens, meta->cum_score, meta->capacity);
+    GRL_LAUNCHED("score_accumulate_kernel");
+    return GRL_OK;
+}
+
+int grl_kv_evict_lowest(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, int num_evict) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    int rc = check_meta(kv, meta);
+    if (rc) return rc;
+    GRL_REQUIRE(num_evict >= 0, "num_evict must not be negative");
+    DeviceGuard g(dev->ordinal);
+    evict_lowest_kernel<<<kv->batch, kThreads, 0, dev->stream>>>(meta->cum_score, meta->tombstone, kv->seq_lens,
+                                                                meta->capacity, num_evict);
+    GRL_LAUNCHED("evict_lowest_kernel");
+    return GRL_OK;
+}
+
+int grl_kv_evict_heuristic(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, float threshold) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    int rc = check_meta(kv, meta);
+    if (rc) return rc;
+    DeviceGuard g(dev->ordinal);
+    evict_heuristic_kernel<<<kv->batch, kThreads, 0, dev->stream>>>(meta->cum_score, meta->tombstone, meta->relevance,
+                                                                   kv->seq_lens, meta->capacity, threshold);
+    GRL_LAUNCHED("evict_heuristic_kernel");
+    return GRL_OK;
+}
+
+int grl_kv_compact_scratch_bytes(const grl_kv_layout* kv, const grl_kv_meta* meta, size_t* bytes) {
+    GRL_REQUIRE(kv && meta && bytes, "NULL argument");
+    *bytes = ((size_t)kv->batch * meta->capacity + (size_t)kv->batch) * sizeof(int32_t);
+    return GRL_OK;
+}
+
+int grl_kv_compact(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, void* scratch,
+                   size_t scratch_bytes) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    int rc = check_meta(kv, meta);
+    if (rc) return rc;
+    GRL_REQUIRE(kv->k_pages && kv->v_pages && kv->num_kv_heads > 0 && kv->head_dim > 0, "bad cache layout");
+    size_t need = 0;
+    grl_kv_compact_scratch_bytes(kv, meta, &need);
+    GRL_REQUIRE(scratch && scratch_bytes >= need, "compaction scratch too small: %zu < %zu", scratch_bytes, need);
+    const int row_bytes = kv->head_dim * (kv->cache_dtype == GRL_BF16 ? 2 : 4);
+    GRL_REQUIRE(row_bytes % 16 == 0 && kTile * (row_bytes / 16) <= 8 * 256, "unsupported row size %d bytes", row_bytes);
+    GRL_REQUIRE(((uintptr_t)kv->k_pages % 16 == 0) && ((uintptr_t)kv->v_pages % 16 == 0), "page pools must be 16-byte aligned");
+    DeviceGuard g(dev->ordinal);
+    int32_t* new_pos = static_cast<int32_t*>(scratch);
+    int32_t* new_len = new_pos + (size_t)kv->batch * meta->capacity;
+    compact_scan_kernel<<<kv->batch, kThreads, 0, dev->stream>>>(meta->tombstone, kv->seq_lens, meta->capacity, new_pos,
+                                                                new_len);
+    GRL_LAUNCHED("compact_scan_kernel");
+    MoveArgs a{};
+    a.k_pages = static_cast<uint8_t*>(kv->k_pages); a.v_pages = static_cast<uint8_t*>(kv->v_pages);
+    a.block_table = kv->block_table; a.seq_lens = kv->seq_lens; a.new_pos = new_pos;
+    a.Hkv = kv->num_kv_heads; a.P = kv->page_tokens; a.max_pages = kv->max_pages; a.capacity = meta->capacity;
+    a.row_bytes = row_bytes;
+    dim3 grid(kv->num_kv_heads, kv->batch, 2);
+    compact_move_kernel<<<grid, 256, 0, dev->stream>>>(a);
+    GRL_LAUNCHED("compact_move_kernel");
+    compact_meta_kernel<<<kv->batch, kThreads, 0, dev->stream>>>(meta->cum_score, meta->tombstone, meta->relevance,
+                                                                kv->seq_lens, meta->evicted, new_pos, new_len,
+                                                                meta->capacity);
+    GRL_LAUNCHED("compact_meta_kernel");
+    return GRL_OK;
+}
+
+}  // extern "C"

@@ -22,7 +22,8 @@ SYMBOLS = [
     "grl_memcpy_d2h", "grl_memcpy_d2d", "grl_memset", "grl_sync", "grl_event_create", "grl_event_create_untimed", "grl_event_destroy",
     "grl_event_record", "grl_event_wait", "grl_event_elapsed_ms", "grl_graph_begin", "grl_graph_end", "grl_graph_launch",
     "grl_graph_destroy", "grl_launch_count", "grl_cast", "grl_flash_fwd", "grl_rope", "grl_attention_mask",
-    "grl_kv_append", "grl_kv_gather", "grl_decode_pick_splits", "grl_decode_workspace_bytes", "grl_gqa_decode",
+    "grl_kv_append", "grl_kv_gather", "grl_kv_score_accumulate", "grl_kv_evict_lowest", "grl_kv_evict_heuristic",
+    "grl_kv_compact_scratch_bytes", "grl_kv_compact", "grl_decode_pick_splits", "grl_decode_workspace_bytes", "grl_gqa_decode",
     "grl_gqa_decode_static", "grl_lse_merge", "grl_ipc_export", "grl_ipc_import", "grl_ipc_release",
     "grl_exchange_merge",
 ]
@@ -55,7 +56,12 @@ class AppendParams(C.Structure):
     _fields_ = [("kv", KVLayout), ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("q_in", C.c_void_p),
                 ("q_out", C.c_void_p), ("n_new", C.c_int32), ("num_q_heads", C.c_int32),
                 ("rope_mode", C.c_int32), ("rope_theta", C.c_float), ("rope_scaling", C.c_float),
-                ("pos_base", C.c_int32), ("update_lens", C.c_int32)]
+                ("pos_base", C.c_int32), ("update_lens", C.c_int32), ("pos_offsets", C.c_void_p)]
+
+
+class KVMeta(C.Structure):
+    _fields_ = [("cum_score", C.c_void_p), ("tombstone", C.c_void_p), ("relevance", C.c_void_p),
+                ("evicted", C.c_void_p), ("capacity", C.c_int32)]
 
 
 class ExchangeParams(C.Structure):

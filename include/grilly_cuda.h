@@ -171,6 +171,8 @@ typedef struct {
     float rope_theta, rope_scaling;
     int32_t pos_base;
     int32_t update_lens;
+    const int32_t* pos_offsets; /* optional device int32[B]: added to the position of sequence b (the tokens
+                                 * compaction has removed from it, grl_kv_meta.evicted) */
 } grl_append_params;
 int grl_kv_append(grl_device* dev, const grl_append_params* p);
 
@@ -178,6 +180,34 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p);
  * (cpp/src/ops/kv_cache.cpp:435-578; kv_cache.h:175-177). */
 int grl_kv_gather(grl_device* dev, const grl_kv_layout* kv, int b, int n_tokens, float* out_k,
                   float* out_v);
+
+/* ---- eviction on the paged cache: replaces the host loops of kvCacheEvictH2O
+ * (cpp/src/ops/kv_cache.cpp:595-634), the untrained-head branch of kvCacheEvictSpeculative (:905-929)
+ * and kvCacheCompact (:941-992; signatures kv_cache.h:186-229).  The reference's TokenMeta array
+ * (kv_cache.h:68-73) becomes device arrays, one entry per token slot of every sequence; all-zero is
+ * the state of a fresh cache, and appended tokens need no initialisation. */
+typedef struct {
+    float* cum_score;     /* [B][capacity] attention mass received so far (TokenMeta.cumulativeScore) */
+    uint8_t* tombstone;   /* [B][capacity] 1 = evicted, awaiting compaction (nextActive == UINT32_MAX-1) */
+    float* relevance;     /* [B][capacity] TokenMeta.predictedRelevance; may be NULL */
+    int32_t* evicted;     /* [B] tokens compaction has removed from the sequence; may be NULL */
+    int32_t capacity;     /* token slots per sequence, >= max_pages * page_tokens */
+} grl_kv_meta;
+/* cum_score[b][t] += sum over q of attn[b][q][t], t < seq_lens[b]; attn is (B, q_rows, ld) float32
+ * probabilities.  The sum runs in ascending q with float adds, as kv_cache.cpp:606-615 does. */
+int grl_kv_score_accumulate(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta,
+                            const float* attn, int q_rows, int ld);
+/* Tombstone the num_evict tokens with the lowest cum_score in every sequence (0 => a quarter of the
+ * sequence; nothing happens where num_evict >= its length).  Ties go to the lowest index. */
+int grl_kv_evict_lowest(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, int num_evict);
+/* relevance = 0.7 * cum_score / max(cum_score) + 0.3 * t / len; tombstone where it is below threshold. */
+int grl_kv_evict_heuristic(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, float threshold);
+/* Move the live tokens of every sequence to the front (order kept, K and V rows and scores), clear the
+ * tombstones, shrink seq_lens, add the removed count to meta->evicted.  scratch: device memory of
+ * grl_kv_compact_scratch_bytes(). */
+int grl_kv_compact_scratch_bytes(const grl_kv_layout* kv, const grl_kv_meta* meta, size_t* bytes);
+int grl_kv_compact(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, void* scratch,
+                   size_t scratch_bytes);
 
 /* ---- decode attention: replaces shaders/gqa-attention.glsl:34-130 (no host dispatcher exists
  * in the reference).  q, out: (B,1,Hq,D) float32.  kv_head = q_head / (Hq/Hkv).

@@ -39,7 +39,9 @@ def load_ref_function(path, name):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of Grillcheese-AI/grilly-next>")
+    ref_root = sys.argv[1]
     ref_attn = load_ref_function(os.path.join(ref_root, "tests/test_attention.py"), "_ref_attention_4d")
     ref_gqa = load_ref_function(os.path.join(ref_root, "tests/test_inference_ops.py"),
                                 "_ref_gqa_decode_attention")

@@ -67,7 +67,8 @@ class PagedCache:
         l.num_pages = self.max_pages * self.B
         return l
 
-    def append(self, k_new, v_new, q=None, rope_mode=cabi.ROPE_NONE, theta=10000.0, scaling=1.0, pos_base=0):
+    def append(self, k_new, v_new, q=None, rope_mode=cabi.ROPE_NONE, theta=10000.0, scaling=1.0, pos_base=0,
+               pos_offsets=None):
         """k_new/v_new (B,n,Hkv,D) float32; q (B,n,Hq,D) or None. Returns rotated q (or None)."""
         dev = self.dev
         n = k_new.shape[1]
@@ -81,6 +82,8 @@ class PagedCache:
             qd = dev.upload(q.astype(np.float32)); qo = dev.malloc(q.nbytes)
             p.q_in, p.q_out, p.num_q_heads = qd, qo, q.shape[2]
         p.rope_mode, p.rope_theta, p.rope_scaling, p.pos_base, p.update_lens = rope_mode, theta, scaling, pos_base, 1
+        if pos_offsets is not None:
+            p.pos_offsets = pos_offsets
         cabi.check(dev.L.grl_kv_append(dev.h, C.byref(p)))
         dev.sync()
         self.lens += n

@@ -34,11 +34,12 @@ def test_struct_sizes_match_header_layout(tmp_path):
     src = tmp_path / "sz.c"
     src.write_text(
         '#include <stdio.h>\n#include <stddef.h>\n#include "grilly_cuda.h"\n'
-        'int main(void){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(grl_kv_layout), sizeof(grl_flash_params),'
+        'int main(void){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(grl_kv_layout), sizeof(grl_flash_params),'
         ' sizeof(grl_append_params), sizeof(grl_decode_params), sizeof(grl_device_info),'
         ' offsetof(grl_flash_params, status), offsetof(grl_append_params, update_lens),'
         ' offsetof(grl_decode_params, partial_out), offsetof(grl_decode_params, exchange),'
-        ' sizeof(grl_exchange_params), offsetof(grl_exchange_params, flag_slots)); return 0;}\n')
+        ' sizeof(grl_exchange_params), offsetof(grl_exchange_params, flag_slots),'
+        ' sizeof(grl_kv_meta), offsetof(grl_append_params, pos_offsets)); return 0;}\n')
     exe = tmp_path / "sz"
     cc = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else "gcc"
     subprocess.check_call([cc, "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
@@ -46,7 +47,8 @@ def test_struct_sizes_match_header_layout(tmp_path):
     got = [C.sizeof(cabi.KVLayout), C.sizeof(cabi.FlashParams), C.sizeof(cabi.AppendParams),
            C.sizeof(cabi.DecodeParams), C.sizeof(cabi.DeviceInfo), cabi.FlashParams.status.offset,
            cabi.AppendParams.update_lens.offset, cabi.DecodeParams.partial_out.offset,
-           cabi.DecodeParams.exchange.offset, C.sizeof(cabi.ExchangeParams), cabi.ExchangeParams.flag_slots.offset]
+           cabi.DecodeParams.exchange.offset, C.sizeof(cabi.ExchangeParams), cabi.ExchangeParams.flag_slots.offset,
+           C.sizeof(cabi.KVMeta), cabi.AppendParams.pos_offsets.offset]
     assert got == want
 
 

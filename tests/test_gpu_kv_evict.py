@@ -1,0 +1,190 @@
+"""GPU parity of the eviction family on the paged cache (C ABI and Python module) against the oracle.
+Everything here is exact: scores add in the reference's order, selection and row moves are index work."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from oracle import attention_oracle as orc
+from oracle import kv_evict_oracle as ev
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    from grilly_next import cabi
+    d = cabi.Device(0)
+    yield d
+    d.close()
+
+
+class Meta:
+    def __init__(self, dev, pc):
+        from grilly_next import cabi
+        self.dev, self.B = dev, pc.B
+        self.cap = pc.max_pages * pc.P
+        n = self.B * self.cap
+        self.cum, self.tomb, self.rel, self.evicted = dev.malloc(n * 4), dev.malloc(n), dev.malloc(n * 4), dev.malloc(self.B * 4)
+        for p, nb in ((self.cum, n * 4), (self.tomb, n), (self.rel, n * 4), (self.evicted, self.B * 4)):
+            cabi.check(dev.L.grl_memset(dev.h, p, 0, nb))
+        dev.sync()
+        m = cabi.KVMeta()
+        m.cum_score, m.tombstone, m.relevance, m.evicted, m.capacity = self.cum, self.tomb, self.rel, self.evicted, self.cap
+        self.m = m
+
+    def host(self):
+        d = self.dev
+        return (d.download(self.cum, (self.B, self.cap), np.float32), d.download(self.tomb, (self.B, self.cap), np.uint8),
+                d.download(self.rel, (self.B, self.cap), np.float32), d.download(self.evicted, (self.B,), np.int32))
+
+
+def _set_lens(dev, pc, lens):
+    from grilly_next import cabi
+    arr = np.asarray(lens, np.int32)
+    cabi.check(dev.L.grl_memcpy_h2d(dev.h, pc.seq_lens, arr.ctypes.data_as(C.c_void_p), arr.nbytes))
+    dev.sync()
+    pc.lens[:] = arr
+
+
+@pytest.mark.parametrize("dtype_name,D", [("bf16", 128), ("fp32", 64), ("bf16", 32)])
+def test_evict_and_compact_through_the_c_abi(dev, dtype_name, D):
+    from grilly_next import cabi
+    from gpu_helpers import PagedCache
+    dtype = cabi.BF16 if dtype_name == "bf16" else cabi.F32
+    rng = np.random.default_rng(11)
+    B, Hkv, T = 3, 2, 300
+    lens = [300, 131, 64]
+    pc = PagedCache(dev, B, Hkv, D, 320, dtype=dtype, shuffle_pages=True, seed=3)
+    k = rng.standard_normal((B, T, Hkv, D), dtype=np.float32)
+    v = rng.standard_normal((B, T, Hkv, D), dtype=np.float32)
+    pc.append(k, v)
+    _set_lens(dev, pc, lens)
+    stored = (lambda x: orc.round_bf16(x)) if dtype == cabi.BF16 else (lambda x: x)
+    meta = Meta(dev, pc)
+    l = pc.layout()
+    # ---- scores: two rounds of column sums, 7 and 300 query rows
+    want_cum = [np.zeros(n, np.float32) for n in lens]
+    for q_rows in (7, 300):
+        attn = rng.random((B, q_rows, T), dtype=np.float32)
+        ad = dev.upload(attn)
+        cabi.check(dev.L.grl_kv_score_accumulate(dev.h, C.byref(l), C.byref(meta.m), ad, q_rows, T))
+        dev.sync(); dev.free(ad)
+        for b, n in enumerate(lens):
+            want_cum[b] = ev.accumulate_scores(want_cum[b], attn[b][:, :n])
+    cum, tomb, _, _ = meta.host()
+    for b, n in enumerate(lens):
+        assert np.array_equal(cum[b, :n], want_cum[b]) and not cum[b, n:].any()
+    # make some ties so that the tie rule is exercised
+    cum[0, [5, 17, 200]] = cum[0, 3]
+    cabi.check(dev.L.grl_memcpy_h2d(dev.h, meta.cum, cum.ctypes.data_as(C.c_void_p), cum.nbytes)); dev.sync()
+    want_cum = [cum[b, :n].copy() for b, n in enumerate(lens)]
+    # ---- H2O selection: explicit count (larger than the shortest sequence: that one is left alone), then default
+    want_tomb = [np.zeros(n, np.uint8) for n in lens]
+    for num in (70, 0):
+        cabi.check(dev.L.grl_kv_evict_lowest(dev.h, C.byref(l), C.byref(meta.m), num)); dev.sync()
+        for b in range(B):
+            _, want_tomb[b] = ev.evict_h2o(want_cum[b], want_tomb[b], None, num)
+    _, tomb, _, _ = meta.host()
+    for b, n in enumerate(lens):
+        assert np.array_equal(tomb[b, :n], want_tomb[b]), f"sequence {b}"
+    assert want_tomb[2].sum() == 16                       # 70 >= 64: only the default quarter applied
+    # ---- heuristic on top
+    cabi.check(dev.L.grl_kv_evict_heuristic(dev.h, C.byref(l), C.byref(meta.m), C.c_float(0.35))); dev.sync()
+    want_rel = []
+    for b in range(B):
+        want_tomb[b], r = ev.evict_heuristic(want_cum[b], want_tomb[b], 0.35)
+        want_rel.append(r)
+    _, tomb, rel, _ = meta.host()
+    for b, n in enumerate(lens):
+        assert np.array_equal(tomb[b, :n], want_tomb[b]) and np.array_equal(rel[b, :n], want_rel[b])
+    # ---- compaction
+    nb = C.c_size_t()
+    cabi.check(dev.L.grl_kv_compact_scratch_bytes(C.byref(l), C.byref(meta.m), C.byref(nb)))
+    scratch = dev.malloc(nb.value)
+    cabi.check(dev.L.grl_kv_compact(dev.h, C.byref(l), C.byref(meta.m), scratch, nb.value)); dev.sync()
+    new_lens = dev.download(pc.seq_lens, (B,), np.int32)
+    cum, tomb, _, evicted = meta.host()
+    pc.lens[:] = new_lens
+    for b, n in enumerate(lens):
+        wk, wv, wc = ev.compact(stored(k[b, :n]), stored(v[b, :n]), want_cum[b], want_tomb[b])
+        assert new_lens[b] == len(wc) and evicted[b] == n - len(wc)
+        gk, gv = pc.gather(b)
+        assert np.array_equal(gk, wk) and np.array_equal(gv, wv)
+        assert np.array_equal(cum[b, :len(wc)], wc) and not cum[b, len(wc):].any() and not tomb[b].any()
+    # compaction with nothing to remove leaves everything in place
+    cabi.check(dev.L.grl_kv_compact(dev.h, C.byref(l), C.byref(meta.m), scratch, nb.value)); dev.sync()
+    assert np.array_equal(dev.download(pc.seq_lens, (B,), np.int32), new_lens)
+    # ---- the next append rotates its keys at the true position: evicted + length
+    k1 = rng.standard_normal((B, 1, Hkv, D), dtype=np.float32)
+    pc.append(k1, k1, rope_mode=cabi.ROPE_INTERLEAVED, pos_offsets=meta.evicted)
+    for b in range(B):
+        gk, _ = pc.gather(b)
+        pos = np.array([int(evicted[b]) + int(new_lens[b])])
+        want = stored(orc.rope_interleaved(k1[b:b + 1].transpose(0, 2, 1, 3), pos)[0].transpose(1, 0, 2)[0])
+        assert np.abs(gk[-1] - want).max() <= (1e-2 if dtype == cabi.BF16 else 1e-5)
+    dev.free(scratch)
+
+
+def test_reference_api_flow():
+    import grilly_core as core
+    ctx = core.Device()
+    rng = np.random.default_rng(5)
+    H, D, T = 4, 64, 96
+    kv = core.create_kv_cache(ctx, max_seq_len=128, num_heads=H, head_dim=D, compression_ratio=1, max_cache_tokens=128,
+                              use_h2o=True, eviction_threshold=0.2, dtype="fp32")
+    k = rng.standard_normal((T, H, D), dtype=np.float32)
+    v = rng.standard_normal((T, H, D), dtype=np.float32)
+    core.kv_cache_append(ctx, kv, k, v)
+    attn = rng.random((T, T), dtype=np.float32)
+    core.kv_cache_evict_h2o(ctx, kv, attn, 10)
+    want_cum, want_tomb = ev.evict_h2o(np.zeros(T, np.float32), np.zeros(T, np.uint8), attn, 10)
+    meta = core.kv_cache_token_meta(ctx, kv)
+    assert np.array_equal(meta["cumulative_score"], want_cum) and np.array_equal(meta["tombstone"], want_tomb)
+    assert abs(kv.stats()["avg_attention_score"] - ev.average_score(want_cum, want_tomb)) < 1e-6
+    core.kv_cache_evict_speculative(ctx, kv)
+    want_tomb, want_rel = ev.evict_heuristic(want_cum, want_tomb, 0.2)
+    meta = core.kv_cache_token_meta(ctx, kv)
+    assert np.array_equal(meta["tombstone"], want_tomb) and np.array_equal(meta["predicted_relevance"], want_rel)
+    core.kv_cache_compact(ctx, kv)
+    wk, wv, wc = ev.compact(k, v, want_cum, want_tomb)
+    assert kv.current_len == len(wc) and kv.stats()["total_evicted"] == T - len(wc)
+    d = core.kv_cache_decode(ctx, kv)
+    assert np.array_equal(d["keys"], wk) and np.array_equal(d["values"], wv)
+    # appending past max_cache_tokens evicts the lowest-scoring tokens first (kv_cache.cpp:161-172)
+    n_now = kv.current_len
+    extra = 128 - n_now + 5
+    k2 = rng.standard_normal((extra, H, D), dtype=np.float32)
+    core.kv_cache_append(ctx, kv, k2, k2)
+    assert kv.current_len == 128
+    _, t2 = ev.evict_h2o(wc, np.zeros(len(wc), np.uint8), None, 5)
+    wk2, _, _ = ev.compact(wk, wv, wc, t2)
+    d = core.kv_cache_decode(ctx, kv)
+    assert np.array_equal(d["keys"], np.concatenate([wk2, k2]))
+    with pytest.raises(RuntimeError, match="attention_scores must be"):
+        core.kv_cache_evict_h2o(ctx, kv, np.zeros((3, 3), np.float32))
+    core.destroy_kv_cache(ctx, kv)
+
+
+def test_decode_after_compaction_matches_oracle():
+    import grilly_core as core
+    ctx = core.Device()
+    rng = np.random.default_rng(6)
+    B, Hq, Hkv, D, T = 2, 8, 2, 128, 200
+    kv = core.create_kv_cache(ctx, max_seq_len=256, num_heads=Hkv, head_dim=D, compression_ratio=1, max_cache_tokens=256,
+                              batch_size=B)
+    k = rng.standard_normal((B, T, Hkv, D), dtype=np.float32)
+    v = rng.standard_normal((B, T, Hkv, D), dtype=np.float32)
+    core.kv_cache_append(ctx, kv, k, v)
+    attn = rng.random((B, T, T), dtype=np.float32)
+    core.kv_cache_evict_h2o(ctx, kv, attn, 50)
+    core.kv_cache_compact(ctx, kv)
+    assert kv.seq_lens == [150, 150]
+    q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
+    out = core.gqa_attention(ctx, q, kv)
+    for b in range(B):
+        cum, tomb = ev.evict_h2o(np.zeros(T, np.float32), np.zeros(T, np.uint8), attn[b], 50)
+        wk, wv, _ = ev.compact(orc.round_bf16(k[b]), orc.round_bf16(v[b]), cum, tomb)
+        want = orc.gqa_decode_attention(q[b:b + 1], wk[None], wv[None], Hq, Hkv, D)
+        assert np.abs(out[b:b + 1] - want).max() <= 5e-3
+    core.destroy_kv_cache(ctx, kv)
