@@ -88,15 +88,18 @@ void kvCacheDecode(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, 
 KVCacheStats kvCacheGetStats(const KVCache& kvCache);
 
 /// GQA decode attention over the cache (shaders/gqa-attention.glsl:34-130): q, out (B,1,Hq,D)
-/// host float32, already rotated.
+/// host float32, already rotated.  accumulateScores: also add the attention mass every cached token
+/// received in this step (summed over the query heads) to its cumulative score, the quantity
+/// kvCacheEvictH2O ranks by -- without the caller having to build an attention matrix.
 void gqaAttention(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const KVCache& kvCache,
-                  const float* q, float* out, uint32_t numQHeads, float scale = 0.0f, int nSplits = 0);
+                  const float* q, float* out, uint32_t numQHeads, float scale = 0.0f, int nSplits = 0,
+                  bool accumulateScores = false);
 
 /// One decode step: RoPE(q, k) at the current position, append k/v, attend over the cache.
 /// q (B,1,Hq,D), kNew/vNew (B,1,Hkv,D), out (B,1,Hq,D): host float32.
 void decodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kvCache, const float* q,
                 const float* kNew, const float* vNew, float* out, uint32_t numQHeads, RopeMode mode, float theta,
-                float scaling, float scale = 0.0f);
+                float scaling, float scale = 0.0f, bool accumulateScores = false);
 
 /// Device-resident forms: q / kNew / vNew / out are HBM float32 buffers; asynchronous on the context
 /// stream (no copy, no wait).  `ws` receives the pooled split-KV workspace, to be released by the

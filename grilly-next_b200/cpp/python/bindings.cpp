@@ -538,16 +538,18 @@ PYBIND11_MODULE(grilly_core, m) {
     m.def(
         "gqa_attention",
         [](GrillyCoreContext& ctx, FArr q, py::object kvOrK, std::optional<FArr> vCache, std::optional<uint32_t> cacheLen,
-           float scale, int nSplits, const std::string& dtype) {
+           float scale, int nSplits, const std::string& dtype, bool accumulateScores) {
             if (q.ndim() != 4 || q.shape(1) != 1) throw std::runtime_error("q must be (batch, 1, num_q_heads, head_dim)");
             const uint32_t B = uint32_t(q.shape(0)), Hq = uint32_t(q.shape(2)), D = uint32_t(q.shape(3));
             py::array_t<float> out({py::ssize_t(B), py::ssize_t(1), py::ssize_t(Hq), py::ssize_t(D)});
             if (py::isinstance<ops::KVCache>(kvOrK)) {
                 auto& kv = kvOrK.cast<ops::KVCache&>();
                 if (kv.config.batchSize != B || kv.config.headDim != D) throw std::runtime_error("q does not match the cache");
-                ops::gqaAttention(ctx.batch, ctx.pool, ctx.cache, kv, q.data(), out.mutable_data(), Hq, scale, nSplits);
+                ops::gqaAttention(ctx.batch, ctx.pool, ctx.cache, kv, q.data(), out.mutable_data(), Hq, scale, nSplits,
+                                  accumulateScores);
                 return out;
             }
+            if (accumulateScores) throw std::runtime_error("accumulate_scores needs a KVCache (explicit arrays have no metadata)");
             // explicit (B,T,Hkv,D) arrays in the reference shader's layout: stage them in a temporary cache
             FArr kC = kvOrK.cast<FArr>();
             if (!vCache.has_value()) throw std::runtime_error("v_cache is required with an explicit k_cache");
@@ -585,12 +587,14 @@ PYBIND11_MODULE(grilly_core, m) {
         },
         py::arg("device"), py::arg("q"), py::arg("k_cache"), py::arg("v_cache") = py::none(),
         py::arg("cache_len") = py::none(), py::arg("scale") = 0.0f, py::arg("n_splits") = 0, py::arg("dtype") = "fp32",
-        "GQA decode attention: q (B,1,Hq,D) over a KVCache, or over explicit (B,T,Hkv,D) arrays");
+        py::arg("accumulate_scores") = false,
+        "GQA decode attention: q (B,1,Hq,D) over a KVCache, or over explicit (B,T,Hkv,D) arrays; "
+        "accumulate_scores adds the attention mass each cached token received to its H2O score");
 
     m.def(
         "decode_step",
         [](GrillyCoreContext& ctx, ops::KVCache& kv, FArr q, FArr kNew, FArr vNew, float ropeTheta, float ropeScaling,
-           const std::string& ropeMode, float scale, std::optional<py::array_t<float>> outArr) {
+           const std::string& ropeMode, float scale, std::optional<py::array_t<float>> outArr, bool accumulateScores) {
             const auto& c = kv.config;
             if (q.ndim() != 4 || q.shape(0) != c.batchSize || q.shape(1) != 1 || q.shape(3) != c.headDim)
                 throw std::runtime_error("q must be (batch, 1, num_q_heads, head_dim)");
@@ -609,12 +613,12 @@ PYBIND11_MODULE(grilly_core, m) {
             }
             ops::decodeStep(ctx.batch, ctx.pool, ctx.cache, kv, q.data(), kNew.data(), vNew.data(), out.mutable_data(),
                             Hq, ropeTheta != 0.0f ? parseRopeMode(ropeMode, false) : ops::RopeMode::None,
-                            ropeTheta != 0.0f ? ropeTheta : 10000.0f, ropeScaling, scale);
+                            ropeTheta != 0.0f ? ropeTheta : 10000.0f, ropeScaling, scale, accumulateScores);
             return out;
         },
         py::arg("device"), py::arg("kv_cache"), py::arg("q"), py::arg("k_new"), py::arg("v_new"),
         py::arg("rope_theta") = 10000.0f, py::arg("rope_scaling") = 1.0f, py::arg("rope_mode") = "interleaved",
-        py::arg("scale") = 0.0f, py::arg("out") = py::none(),
+        py::arg("scale") = 0.0f, py::arg("out") = py::none(), py::arg("accumulate_scores") = false,
         "RoPE(q,k) at the current position, append k/v, attend over the cache");
 
     // ---- DeviceGroup: the GPUs of one node behind one object, one Device (own stream, own pool) each.

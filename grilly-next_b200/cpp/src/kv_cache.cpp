@@ -237,8 +237,12 @@ KVCacheStats kvCacheGetStats(const KVCache& kv) {
     return s;
 }
 
+// Queues the decode of q over the cache.  With `track`, the step also adds the attention mass every cached
+// token received (summed over the query heads) to the cache's cumulative scores -- what H2O eviction
+// ranks by: the kernel leaves its scaled scores and an un-normalised result, a merge of one part
+// normalises it, and grl_kv_mass_accumulate turns scores into probabilities.
 static void launchDecode(grl_device* dev, BufferPool& pool, const KVCache& kv, const float* qDev, float* outDev,
-                         uint32_t numQHeads, float scale, int nSplits, GrillyBuffer& ws) {
+                         uint32_t numQHeads, float scale, int nSplits, GrillyBuffer& ws, bool track = false) {
     grl_decode_params p{};
     p.kv = kv.layout();
     p.q = qDev; p.out = outDev;
@@ -249,13 +253,28 @@ static void launchDecode(grl_device* dev, BufferPool& pool, const KVCache& kv, c
     check(grl_decode_pick_splits(dev, &p, &splits), "gqaAttention");
     size_t bytes = 0;
     check(grl_decode_workspace_bytes(&p, splits, &bytes), "gqaAttention");
-    ws = pool.acquire(bytes);
-    p.n_splits = splits; p.workspace = ws.dptr; p.workspace_bytes = ws.bucketSize;
+    const size_t rows = size_t(kv.config.batchSize) * numQHeads, D = kv.config.headDim;
+    const size_t ld = (size_t(p.max_seq_len) + 3) / 4 * 4;
+    const size_t partBytes = rows * (D + 2) * 4, scoreBytes = rows * ld * 4;
+    const size_t wsBytes = (bytes + 255) / 256 * 256;
+    ws = pool.acquire(wsBytes + (track ? partBytes + 256 + scoreBytes : 0));
+    p.n_splits = splits; p.workspace = ws.dptr; p.workspace_bytes = wsBytes;
+    if (!track) {
+        check(grl_gqa_decode(dev, &p), "gqaAttention");
+        return;
+    }
+    float* part = reinterpret_cast<float*>(static_cast<char*>(ws.dptr) + wsBytes);
+    float* scores = reinterpret_cast<float*>(static_cast<char*>(ws.dptr) + wsBytes + (partBytes + 255) / 256 * 256);
+    p.out = nullptr; p.partial_out = part;
+    p.scores_out = scores; p.scores_ld = int(ld);
     check(grl_gqa_decode(dev, &p), "gqaAttention");
+    check(grl_lse_merge(dev, part, 1, rows * (D + 2), int(rows), int(D), 1, outDev), "gqaAttention: normalise");
+    grl_kv_meta m = kv.meta();
+    check(grl_kv_mass_accumulate(dev, &p.kv, &m, scores, int(ld), part, int(numQHeads)), "gqaAttention: scores");
 }
 
 void gqaAttention(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const KVCache& kv, const float* q,
-                  float* out, uint32_t numQHeads, float scale, int nSplits) {
+                  float* out, uint32_t numQHeads, float scale, int nSplits, bool accumulateScores) {
     if (!kv.kPages.valid()) throw std::runtime_error("gqaAttention: cache was destroyed");
     if (!q || !out) throw std::runtime_error("gqaAttention: null tensor pointer");
     const auto& c = kv.config;
@@ -269,7 +288,7 @@ void gqaAttention(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, c
         Recording rec(batch);
         pool.upload(qb, q, n * 4);
         launchDecode(dev, pool, kv, static_cast<const float*>(qb.dptr), static_cast<float*>(ob.dptr), numQHeads, scale,
-                     nSplits, ws);
+                     nSplits, ws, accumulateScores);
         check(grl_memcpy_d2h(dev, out, ob.dptr, n * 4), "gqaAttention: download");
         batch.submit();
     } catch (...) {
@@ -281,7 +300,7 @@ void gqaAttention(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, c
 
 void decodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kv, const float* q,
                 const float* kNew, const float* vNew, float* out, uint32_t numQHeads, RopeMode mode, float theta,
-                float scaling, float scale) {
+                float scaling, float scale, bool accumulateScores) {
     if (!kv.kPages.valid()) throw std::runtime_error("decodeStep: cache was destroyed");
     if (!q || !kNew || !vNew || !out) throw std::runtime_error("decodeStep: null tensor pointer");
     const auto& c = kv.config;
@@ -316,7 +335,7 @@ void decodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVC
         kv.currentLen = uint32_t(kv.hostSeqLens[0]);
         kv.totalAppended += c.batchSize;
         launchDecode(dev, pool, kv, static_cast<const float*>(qr.dptr), static_cast<float*>(ob.dptr), numQHeads, scale,
-                     0, ws);
+                     0, ws, accumulateScores);
         check(grl_memcpy_d2h(dev, out, ob.dptr, qn * 4), "decodeStep: download");
         batch.submit();
     } catch (...) {

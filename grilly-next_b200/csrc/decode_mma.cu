@@ -42,6 +42,8 @@ struct Args {
     int fuse;               // 0: leave the splits to lse_merge_kernel
     int32_t* counters;      // arrival counters, zero between launches; [kDoneSlot] counts finished heads
     float* partial_out;     // != NULL: merged rows leave un-normalised as [O | m | l]
+    float* scores_out;      // != NULL: (B*Hq, scores_ld) scaled scores, natural-log domain
+    int scores_ld;
     PeerExchange x;         // x.world > 1: the merged rows are exchanged with the peers and merged again
 };
 constexpr int kDoneSlot = grl_device::kCounterSlots;
@@ -247,6 +249,14 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                         valid[nt][e] = tok0 + nt * 8 + 2 * t4 + e < len;
                         if (valid[nt][e]) mx = fmaxf(mx, sacc[nt][e]);
                     }
+                if (a.scores_out && g < a.group) {      // what H2O eviction accumulates; off on the plain path
+                    float* srow = a.scores_out + ((size_t)b * a.Hq + qh0 + g) * a.scores_ld + tok0 + 2 * t4;
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e)
+                            if (valid[nt][e]) srow[nt * 8 + e] = sacc[nt][e] * 0.6931471805599453f;
+                }
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                 const float m_new = fmaxf(m_run, mx);
@@ -523,6 +533,7 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
     a.n_splits = n_splits; a.group = p->num_q_heads / kv.num_kv_heads;
     a.scale = scale; a.direct = direct ? 1 : 0;
     a.fuse = fuse ? 1 : 0; a.counters = dev->d_counters; a.partial_out = p->partial_out;
+    a.scores_out = p->scores_out; a.scores_ld = p->scores_ld;
     a.x.world = 1;
     if (p->exchange) {
         GRL_REQUIRE(fuse && !direct, "the fused cross-GPU merge needs the split-KV path");

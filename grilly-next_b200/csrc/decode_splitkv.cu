@@ -20,6 +20,8 @@ struct DecodeArgs {
     const float* q;
     float* part;       // [n_splits][rows*(D+2)]
     float* out;        // direct output when n_splits == 1 and no partial is wanted
+    float* scores_out; // optional (B*Hq, scores_ld): scaled scores, natural-log domain
+    int scores_ld;
     int B, Hq, Hkv, P, max_pages, n_splits, group, chunks;
     float scale;
     int direct;
@@ -118,6 +120,11 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(DecodeArgs
         for (int off2 = 1; off2 < LPT; off2 <<= 1)
 #pragma unroll
             for (int g = 0; g < GC; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off2);
+        if (live && a.scores_out && li == 0) {
+#pragma unroll
+            for (int g = 0; g < GC; ++g)
+                if (g < n_heads) a.scores_out[((size_t)b * a.Hq + qh0 + g) * a.scores_ld + t] = s[g];
+        }
         if (live) {
 #pragma unroll
             for (int g = 0; g < GC; ++g) {
@@ -270,6 +277,9 @@ static int check_decode(const grl_decode_params* p, bool need_tensors = true) {
     if (need_tensors) {
         GRL_REQUIRE(p->q, "q is NULL");
         GRL_REQUIRE(p->out || p->partial_out, "out and partial_out are both NULL");
+        const int bound = p->max_seq_len > 0 ? p->max_seq_len : kv.max_pages * kv.page_tokens;
+        GRL_REQUIRE(!p->scores_out || p->scores_ld >= bound, "scores_ld %d is below the sequence bound %d",
+                    p->scores_ld, bound);
     }
     return GRL_OK;
 }
@@ -343,6 +353,7 @@ int grl_gqa_decode(grl_device* dev, const grl_decode_params* p) {
     DecodeArgs a{};
     a.k_pages = kv.k_pages; a.v_pages = kv.v_pages; a.block_table = kv.block_table; a.seq_lens = kv.seq_lens;
     a.q = p->q; a.part = (float*)p->workspace; a.out = p->out;
+    a.scores_out = p->scores_out; a.scores_ld = p->scores_ld;
     a.B = kv.batch; a.Hq = p->num_q_heads; a.Hkv = kv.num_kv_heads; a.P = kv.page_tokens;
     a.max_pages = kv.max_pages; a.n_splits = n_splits; a.group = p->num_q_heads / kv.num_kv_heads;
     a.scale = p->scale == 0.f ? 1.f / sqrtf((float)D) : p->scale;

@@ -33,6 +33,28 @@ __global__ void score_accumulate_kernel(const float* __restrict__ attn, int q_ro
     *c = __fadd_rn(*c, acc);
 }
 
+// cum[b][t] += sum_h exp(scores[b][h][t] - m[b][h]) / l[b][h]: the attention mass token t received from
+// the Hq query heads of one decode step.  (m, l) come from the step's un-normalised partial [O | m | l].
+__global__ void mass_accumulate_kernel(const float* __restrict__ scores, int ld, const float* __restrict__ partial,
+                                       int Hq, int D, int rows, const int32_t* seq_lens, float* cum, int capacity) {
+    extern __shared__ float s_ml[];          // [Hq] m, [Hq] 1/l
+    const int b = blockIdx.y;
+    const int len = seq_lens[b];
+    for (int h = threadIdx.x; h < Hq; h += blockDim.x) {
+        const int row = b * Hq + h;
+        const float l = partial[(size_t)rows * D + rows + row];
+        s_ml[h] = partial[(size_t)rows * D + row];
+        s_ml[Hq + h] = l > 0.f ? 1.f / l : 0.f;
+    }
+    __syncthreads();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= len) return;
+    float acc = 0.f;
+    for (int h = 0; h < Hq; ++h)
+        acc += __expf(scores[((size_t)b * Hq + h) * ld + t] - s_ml[h]) * s_ml[Hq + h];
+    cum[(size_t)b * capacity + t] += acc;
+}
+
 // block-wide exclusive scan of one int per thread; returns the exclusive prefix, *total = block sum
 __device__ __forceinline__ int block_exclusive_scan(int v, int* total, int* s_warp /* [33] */) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -273,6 +295,23 @@ int grl_kv_score_accumulate(grl_device* dev, const grl_kv_layout* kv, const grl_
     dim3 grid((ld + 255) / 256, kv->batch);
     score_accumulate_kernel<<<grid, 256, 0, dev->stream>>>(attn, q_rows, ld, kv->seq_lens, meta->cum_score, meta->capacity);
     GRL_LAUNCHED("score_accumulate_kernel");
+    return GRL_OK;
+}
+
+int grl_kv_mass_accumulate(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, const float* scores,
+                           int scores_ld, const float* partial, int num_q_heads) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    int rc = check_meta(kv, meta);
+    if (rc) return rc;
+    GRL_REQUIRE(scores && partial && scores_ld > 0 && num_q_heads > 0 && num_q_heads <= 4096, "bad argument");
+    GRL_REQUIRE(kv->head_dim > 0, "bad cache layout");
+    DeviceGuard g(dev->ordinal);
+    const int tokens = scores_ld < meta->capacity ? scores_ld : meta->capacity;
+    dim3 grid((tokens + 255) / 256, kv->batch);
+    mass_accumulate_kernel<<<grid, 256, 2 * num_q_heads * sizeof(float), dev->stream>>>(
+        scores, scores_ld, partial, num_q_heads, kv->head_dim, kv->batch * num_q_heads, kv->seq_lens, meta->cum_score,
+        meta->capacity);
+    GRL_LAUNCHED("mass_accumulate_kernel");
     return GRL_OK;
 }
 

@@ -64,6 +64,14 @@ def kv_cache_compact(device, kv_cache):
     return _core.kv_cache_compact(device, kv_cache)
 
 
+def kv_cache_evict_speculative(device, kv_cache, hidden_states=None, hidden_dim=0):
+    return _core.kv_cache_evict_speculative(device, kv_cache, hidden_states, hidden_dim)
+
+
+def kv_cache_token_meta(device, kv_cache, seq=0):
+    return _core.kv_cache_token_meta(device, kv_cache, seq)
+
+
 def destroy_kv_cache(device, kv_cache):
     return _core.destroy_kv_cache(device, kv_cache)
 

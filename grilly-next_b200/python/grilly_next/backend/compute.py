@@ -45,6 +45,15 @@ class VulkanCompute:
     def kv_cache_evict_h2o(self, kv_cache, attention_scores=None, num_evict=0):
         return _bridge.kv_cache_evict_h2o(self._device, kv_cache, attention_scores, num_evict)
 
+    def kv_cache_evict_speculative(self, kv_cache, hidden_states=None, hidden_dim=0):
+        return _bridge.kv_cache_evict_speculative(self._device, kv_cache, hidden_states, hidden_dim)
+
+    def kv_cache_compact(self, kv_cache):
+        return _bridge.kv_cache_compact(self._device, kv_cache)
+
+    def kv_cache_token_meta(self, kv_cache, seq=0):
+        return _bridge.kv_cache_token_meta(self._device, kv_cache, seq)
+
     def destroy_kv_cache(self, kv_cache):
         return _bridge.destroy_kv_cache(self._device, kv_cache)
 

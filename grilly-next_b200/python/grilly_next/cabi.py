@@ -22,7 +22,7 @@ SYMBOLS = [
     "grl_memcpy_d2h", "grl_memcpy_d2d", "grl_memset", "grl_sync", "grl_event_create", "grl_event_create_untimed", "grl_event_destroy",
     "grl_event_record", "grl_event_wait", "grl_event_elapsed_ms", "grl_graph_begin", "grl_graph_end", "grl_graph_launch",
     "grl_graph_destroy", "grl_launch_count", "grl_cast", "grl_flash_fwd", "grl_rope", "grl_attention_mask",
-    "grl_kv_append", "grl_kv_gather", "grl_kv_score_accumulate", "grl_kv_evict_lowest", "grl_kv_evict_heuristic",
+    "grl_kv_append", "grl_kv_gather", "grl_kv_score_accumulate", "grl_kv_mass_accumulate", "grl_kv_evict_lowest", "grl_kv_evict_heuristic",
     "grl_kv_compact_scratch_bytes", "grl_kv_compact", "grl_decode_pick_splits", "grl_decode_workspace_bytes", "grl_gqa_decode",
     "grl_gqa_decode_static", "grl_lse_merge", "grl_ipc_export", "grl_ipc_import", "grl_ipc_release",
     "grl_exchange_merge",
@@ -76,7 +76,8 @@ class DecodeParams(C.Structure):
     _fields_ = [("kv", KVLayout), ("q", C.c_void_p), ("out", C.c_void_p), ("num_q_heads", C.c_int32),
                 ("scale", C.c_float), ("n_splits", C.c_int32), ("max_seq_len", C.c_int32),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("partial_out", C.c_void_p),
-                ("force_simt", C.c_int32), ("exchange", C.POINTER(ExchangeParams))]
+                ("force_simt", C.c_int32), ("scores_out", C.c_void_p), ("scores_ld", C.c_int32),
+                ("exchange", C.POINTER(ExchangeParams))]
 
 
 class GrlError(RuntimeError):

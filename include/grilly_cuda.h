@@ -197,6 +197,12 @@ typedef struct {
  * probabilities.  The sum runs in ascending q with float adds, as kv_cache.cpp:606-615 does. */
 int grl_kv_score_accumulate(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta,
                             const float* attn, int q_rows, int ld);
+/* One decode step's contribution without an attention matrix from the caller: cum_score[b][t] +=
+ * sum over the Hq query heads of softmax probability p[b][h][t] = exp(scores[b][h][t] - m[b][h]) / l[b][h],
+ * with `scores` the scores_out of grl_gqa_decode and `partial` its partial_out ([O | m | l]) of the same
+ * call.  Heads add in ascending order. */
+int grl_kv_mass_accumulate(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, const float* scores,
+                           int scores_ld, const float* partial, int num_q_heads);
 /* Tombstone the num_evict tokens with the lowest cum_score in every sequence (0 => a quarter of the
  * sequence; nothing happens where num_evict >= its length).  Ties go to the lowest index. */
 int grl_kv_evict_lowest(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, int num_evict);
@@ -227,6 +233,10 @@ typedef struct {
     size_t workspace_bytes;
     float* partial_out;
     int32_t force_simt;     /* != 0: use the generic SIMT kernel even where the tensor-core path applies */
+    float* scores_out;      /* optional (B*Hq, scores_ld) float32: the scaled scores q.k of every cached token,
+                             * natural-log domain, written for t < seq_lens[b] (what H2O eviction accumulates:
+                             * grl_kv_mass_accumulate) */
+    int32_t scores_ld;
     const struct grl_exchange_params_s* exchange;   /* optional, see grl_exchange_params below: the KV shards of
                              * other GPUs are merged in over NVLink inside the decode kernel; `out` then holds
                              * the attention over ALL ranks' shards.  NULL: single-GPU decode. */

@@ -214,8 +214,13 @@ def test_kv_cache_reference_single_sequence_form(gpu):
         gpu.kv_cache_append(kv, np.zeros((200, 4, 64), np.float32), np.zeros((200, 4, 64), np.float32))
     with pytest.raises(RuntimeError, match="compression_ratio"):
         gpu.create_kv_cache()                     # the reference default (MLA, ratio 4) is not built
-    with pytest.raises(RuntimeError):
-        gpu.kv_cache_evict_h2o(kv)
+    # the eviction calls of the reference API: a quarter of the 13 tokens goes (all scores are zero, so the
+    # tie rule picks the first three), compaction closes the gaps
+    gpu.kv_cache_evict_h2o(kv)
+    assert gpu.kv_cache_token_meta(kv)["tombstone"].tolist() == [1, 1, 1] + [0] * 10
+    gpu.kv_cache_compact(kv)
+    assert kv.current_len == 10
+    assert np.array_equal(gpu.kv_cache_decode(kv)["keys"], np.concatenate([k, k[:3]])[3:])
 
 
 def test_lse_merge_matches_oracle(dev):

@@ -188,3 +188,41 @@ def test_decode_after_compaction_matches_oracle():
         want = orc.gqa_decode_attention(q[b:b + 1], wk[None], wv[None], Hq, Hkv, D)
         assert np.abs(out[b:b + 1] - want).max() <= 5e-3
     core.destroy_kv_cache(ctx, kv)
+
+
+@pytest.mark.parametrize("dtype,D,tol", [("bf16", 128, 2e-3), ("fp32", 64, 1e-5), ("bf16", 64, 2e-3)])
+def test_decode_accumulates_attention_mass(dtype, D, tol):
+    # tensor-core kernel (bf16, D=128) and the generic kernel: the scores the step computed become the
+    # cumulative H2O scores, summed over the query heads, without an attention matrix from the caller
+    import grilly_core as core
+    ctx = core.Device()
+    rng = np.random.default_rng(8)
+    B, Hq, Hkv, T = 2, 8, 2, 333
+    kv = core.create_kv_cache(ctx, max_seq_len=512, num_heads=Hkv, head_dim=D, compression_ratio=1, max_cache_tokens=512,
+                              batch_size=B, dtype=dtype)
+    k = rng.standard_normal((B, T, Hkv, D), dtype=np.float32)
+    v = rng.standard_normal((B, T, Hkv, D), dtype=np.float32)
+    core.kv_cache_append(ctx, kv, k, v)
+    ks = orc.round_bf16(k) if dtype == "bf16" else k
+    want_cum = np.zeros((B, T), np.float64)
+    for step in range(2):
+        q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
+        plain = core.gqa_attention(ctx, q, kv)
+        out = core.gqa_attention(ctx, q, kv, accumulate_scores=True)
+        assert np.abs(out - plain).max() <= 1e-5
+        for b in range(B):
+            for h in range(Hq):
+                s = ks[b, :, h // (Hq // Hkv), :].astype(np.float64) @ q[b, 0, h].astype(np.float64) / np.sqrt(D)
+                p = np.exp(s - s.max())
+                want_cum[b] += p / p.sum()
+        for b in range(B):
+            got = core.kv_cache_token_meta(ctx, kv, b)["cumulative_score"]
+            assert np.abs(got - want_cum[b]).max() <= tol * (step + 1)
+            assert abs(got.sum() - Hq * (step + 1)) <= 1e-2        # every head hands out one unit of mass per step
+    # the decode-step form appends first, so the new token receives mass too
+    q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
+    kn = rng.standard_normal((B, 1, Hkv, D), dtype=np.float32)
+    core.decode_step(ctx, kv, q, kn, kn, rope_theta=0.0, accumulate_scores=True)
+    got = core.kv_cache_token_meta(ctx, kv, 0)["cumulative_score"]
+    assert got.shape == (T + 1,) and got[-1] > 0 and abs(got.sum() - 3 * Hq) <= 2e-2
+    core.destroy_kv_cache(ctx, kv)
