@@ -34,6 +34,17 @@ struct KVCacheConfig {
     int dtype = GRL_BF16;             // storage type of the pages
 };
 
+/// Trainable auxiliary head for speculative eviction (the reference's EvictionHead, kv_cache.h:100-121;
+/// its gradient buffers are not needed: the update kernel reduces and applies a gradient in one pass).
+struct EvictionHead {
+    GrillyBuffer w1, b1, w2, b2;      // (inputDim, hiddenDim), (hiddenDim), (hiddenDim), (1): float32 in HBM
+    uint32_t inputDim = 0, hiddenDim = 0;
+    float learningRate = 1e-3f;
+    uint32_t totalUpdates = 0;
+    bool initialized = false;
+    grl_evict_head view() const;
+};
+
 struct KVCache {
     GrillyBuffer kPages, vPages;      // [numPages][Hkv][pageTokens][D]
     GrillyBuffer blockTable;          // int32 [B][maxPages]
@@ -52,6 +63,7 @@ struct KVCache {
     GrillyBuffer relevance;           // float  [B][capacity]
     GrillyBuffer evicted;             // int32  [B]: tokens compaction removed (RoPE position offset of appends)
     grl_device* device = nullptr;     // the device the buffers live on (stats read the metadata back)
+    EvictionHead evictionHead;
     uint32_t capacity() const { return maxPages * config.pageTokens; }
     grl_kv_meta meta() const;
     KVCacheConfig config;
@@ -117,8 +129,17 @@ void decodeStepDevice(BufferPool& pool, PipelineCache& cache, KVCache& kvCache, 
 /// (0 => a quarter; nothing where numEvict >= the length).  Ties go to the lowest index.
 void kvCacheEvictH2O(CommandBatch&, BufferPool&, PipelineCache&, KVCache&, const float* attentionScores,
                      uint32_t numEvict = 0);
-/// The reference's behaviour without a trained eviction head (kv_cache.cpp:905-929; the head itself is
-/// not built): relevance = 0.7 cum/max + 0.3 t/len, tombstone below config.evictionThreshold.
+/// Eviction head: Xavier-uniform weights drawn with rand() as the reference draws them (kv_cache.cpp:653-701),
+/// one SGD step on binarised attention (:734-845).  Single-sequence caches only.
+void kvCacheInitEvictionHead(BufferPool& pool, KVCache& kvCache, uint32_t inputDim, uint32_t hiddenDim = 32,
+                             float lr = 1e-3f);
+void kvCacheDestroyEvictionHead(BufferPool& pool, KVCache& kvCache);
+/// tokenFeatures (currentLen, inputDim), attentionScores (seqLen, currentLen): host float32.
+void kvCacheTrainEvictionHead(CommandBatch&, BufferPool&, PipelineCache&, KVCache&, const float* tokenFeatures,
+                              const float* attentionScores, uint32_t seqLen);
+/// With a trained head and hiddenStates (currentLen, head.inputDim): predicted relevance below
+/// config.evictionThreshold tombstones the token (kv_cache.cpp:863-903).  Otherwise the heuristic
+/// (:905-929): relevance = 0.7 cum/max + 0.3 t/len.
 void kvCacheEvictSpeculative(CommandBatch&, BufferPool&, PipelineCache&, KVCache&, const float* hiddenStates,
                              uint32_t hiddenDim);
 /// Move live tokens to the front of every sequence and shrink the lengths (kv_cache.cpp:941-992).

@@ -461,13 +461,69 @@ PYBIND11_MODULE(grilly_core, m) {
           [](GrillyCoreContext& ctx, ops::KVCache& kv) { ops::kvCacheCompact(ctx.batch, ctx.pool, ctx.cache, kv); },
           py::arg("device"), py::arg("kv_cache"), "Move the live tokens to the front and shrink the cache length");
     m.def(
-        "kv_cache_evict_speculative",
-        [](GrillyCoreContext& ctx, ops::KVCache& kv, py::object, uint32_t) {
-            // no eviction head is built, so this is the reference's behaviour for an untrained head
-            ops::kvCacheEvictSpeculative(ctx.batch, ctx.pool, ctx.cache, kv, nullptr, 0);
+        "kv_cache_init_eviction_head",
+        [](GrillyCoreContext& ctx, ops::KVCache& kv, uint32_t inputDim, uint32_t hiddenDim, float lr) {
+            ops::kvCacheInitEvictionHead(ctx.pool, kv, inputDim, hiddenDim, lr);
         },
-        py::arg("device"), py::arg("kv_cache"), py::arg("hidden_states") = py::none(), py::arg("hidden_dim") = 0,
-        "Tombstone tokens whose heuristic relevance (0.7 score/max + 0.3 recency) is below eviction_threshold");
+        py::arg("device"), py::arg("kv_cache"), py::arg("input_dim"), py::arg("hidden_dim") = 32, py::arg("lr") = 1e-3f,
+        "Initialize trainable eviction head for speculative eviction");
+    m.def(
+        "kv_cache_train_eviction_head",
+        [](GrillyCoreContext& ctx, ops::KVCache& kv, FArr tokenFeatures, FArr attentionScores, uint32_t seqLen) {
+            const auto& head = kv.evictionHead;
+            if (head.initialized) {
+                if (size_t(tokenFeatures.size()) != size_t(kv.currentLen) * head.inputDim)
+                    throw std::runtime_error("token_features must be (cache_len, input_dim)");
+                if (size_t(attentionScores.size()) != size_t(seqLen) * kv.currentLen)
+                    throw std::runtime_error("attention_scores must be (seq_len, cache_len)");
+            }
+            ops::kvCacheTrainEvictionHead(ctx.batch, ctx.pool, ctx.cache, kv, tokenFeatures.data(), attentionScores.data(),
+                                          seqLen);
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("token_features"), py::arg("attention_scores"), py::arg("seq_len"),
+        "Train the eviction head on attention patterns from latest forward pass");
+    m.def(
+        "kv_cache_eviction_head_weights",
+        [](GrillyCoreContext& ctx, ops::KVCache& kv, std::optional<py::dict> set) {
+            auto& head = kv.evictionHead;
+            if (!head.initialized) throw std::runtime_error("the eviction head is not initialized");
+            grl_device* dev = ctx.device.handle();
+            const size_t n1 = size_t(head.inputDim) * head.hiddenDim, nh = head.hiddenDim;
+            if (set.has_value()) {
+                auto put = [&](const char* key, GrillyBuffer& buf, size_t n) {
+                    if (!set->contains(key)) return;
+                    FArr a = (*set)[key].cast<FArr>();
+                    if (size_t(a.size()) != n) throw std::runtime_error(std::string(key) + " has the wrong size");
+                    check(grl_memcpy_h2d(dev, buf.dptr, a.data(), n * 4), "eviction head weights");
+                    check(grl_sync(dev, 0), "eviction head weights");
+                };
+                put("w1", head.w1, n1); put("b1", head.b1, nh); put("w2", head.w2, nh); put("b2", head.b2, 1);
+            }
+            py::array_t<float> w1({py::ssize_t(head.inputDim), py::ssize_t(head.hiddenDim)});
+            py::array_t<float> b1{py::ssize_t(nh)}, w2{py::ssize_t(nh)}, b2{py::ssize_t(1)};
+            check(grl_memcpy_d2h(dev, w1.mutable_data(), head.w1.dptr, n1 * 4), "eviction head weights");
+            check(grl_memcpy_d2h(dev, b1.mutable_data(), head.b1.dptr, nh * 4), "eviction head weights");
+            check(grl_memcpy_d2h(dev, w2.mutable_data(), head.w2.dptr, nh * 4), "eviction head weights");
+            check(grl_memcpy_d2h(dev, b2.mutable_data(), head.b2.dptr, 4), "eviction head weights");
+            check(grl_sync(dev, 0), "eviction head weights");
+            py::dict d;
+            d["w1"] = w1; d["b1"] = b1; d["w2"] = w2; d["b2"] = b2; d["total_updates"] = head.totalUpdates;
+            return d;
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("set") = py::none(),
+        "Read (and optionally overwrite) the eviction head's parameters");
+    m.def(
+        "kv_cache_evict_speculative",
+        [](GrillyCoreContext& ctx, ops::KVCache& kv, std::optional<FArr> hiddenStates, uint32_t hiddenDim) {
+            const auto& head = kv.evictionHead;
+            if (hiddenStates.has_value() && head.initialized && head.totalUpdates > 0 &&
+                size_t(hiddenStates->size()) != size_t(kv.currentLen) * head.inputDim)
+                throw std::runtime_error("hidden_states must be (cache_len, input_dim of the eviction head)");
+            ops::kvCacheEvictSpeculative(ctx.batch, ctx.pool, ctx.cache, kv,
+                                         hiddenStates ? hiddenStates->data() : nullptr, hiddenDim);
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("hidden_states") = py::none(), py::arg("hidden_dim") = 64,
+        "Run speculative eviction using trained auxiliary head (heuristic relevance until it has been trained)");
     m.def(
         "kv_cache_token_meta",
         [](GrillyCoreContext& ctx, const ops::KVCache& kv, uint32_t seq) {
@@ -711,7 +767,5 @@ PYBIND11_MODULE(grilly_core, m) {
         const std::string msg = std::string(name) + ": " + what;
         m.def(name, [msg](py::args, py::kwargs) -> py::object { throw std::runtime_error(msg); });
     };
-    notBuilt("kv_cache_init_eviction_head", "the trainable eviction head is not built on the paged cache");
-    notBuilt("kv_cache_train_eviction_head", "the trainable eviction head is not built on the paged cache");
     notBuilt("fused_attention_cpu", "the MLA latent path (CPU reference of the fused subgroup attention) is not built");
 }

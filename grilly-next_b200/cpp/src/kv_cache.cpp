@@ -1,5 +1,7 @@
 // Host side of the paged KV cache and the GQA decode ops.
 #include <algorithm>
+#include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -113,7 +115,16 @@ KVCache createKVCache(BufferPool& pool, const KVCacheConfig& cfg) {
     return kv;
 }
 
+grl_evict_head EvictionHead::view() const {
+    grl_evict_head v{};
+    v.w1 = static_cast<float*>(w1.dptr); v.b1 = static_cast<float*>(b1.dptr);
+    v.w2 = static_cast<float*>(w2.dptr); v.b2 = static_cast<float*>(b2.dptr);
+    v.input_dim = int32_t(inputDim); v.hidden_dim = int32_t(hiddenDim);
+    return v;
+}
+
 void destroyKVCache(BufferPool& pool, KVCache& kv) {
+    kvCacheDestroyEvictionHead(pool, kv);
     pool.release(kv.kPages);
     pool.release(kv.vPages);
     pool.release(kv.blockTable);
@@ -427,15 +438,103 @@ void kvCacheEvictH2O(CommandBatch& batch, BufferPool& pool, PipelineCache& cache
     pool.release(scores);
 }
 
-void kvCacheEvictSpeculative(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kv,
-                             const float* /*hiddenStates*/, uint32_t /*hiddenDim*/) {
-    if (!kv.kPages.valid()) throw std::runtime_error("kvCacheEvictSpeculative: cache was destroyed");
-    cache.getOrCreate("kv-evict-heuristic");
+void kvCacheInitEvictionHead(BufferPool& pool, KVCache& kv, uint32_t inputDim, uint32_t hiddenDim, float lr) {
+    if (!kv.kPages.valid()) throw std::runtime_error("kvCacheInitEvictionHead: cache was destroyed");
+    if (kv.config.batchSize != 1) throw std::runtime_error("kvCacheInitEvictionHead: single-sequence caches only");
+    if (inputDim == 0 || hiddenDim == 0) throw std::runtime_error("kvCacheInitEvictionHead: empty shape");
+    kvCacheDestroyEvictionHead(pool, kv);
+    auto& head = kv.evictionHead;
+    head.inputDim = inputDim; head.hiddenDim = hiddenDim; head.learningRate = lr; head.totalUpdates = 0;
+    head.w1 = pool.acquire(size_t(inputDim) * hiddenDim * 4);
+    head.b1 = pool.acquire(size_t(hiddenDim) * 4);
+    head.w2 = pool.acquire(size_t(hiddenDim) * 4);
+    head.b2 = pool.acquire(4);
+    // Xavier-uniform from rand(), W1 first then W2, biases zero -- the draw order of kv_cache.cpp:676-701
+    const float x1 = std::sqrt(6.0f / float(inputDim + hiddenDim));
+    std::vector<float> w1(size_t(inputDim) * hiddenDim);
+    for (auto& v : w1) v = (static_cast<float>(rand()) / RAND_MAX * 2.0f - 1.0f) * x1;
+    const float x2 = std::sqrt(6.0f / float(hiddenDim + 1));
+    std::vector<float> w2(hiddenDim);
+    for (auto& v : w2) v = (static_cast<float>(rand()) / RAND_MAX * 2.0f - 1.0f) * x2;
+    grl_device* dev = pool.device().handle();
+    check(grl_memcpy_h2d(dev, head.w1.dptr, w1.data(), w1.size() * 4), "kvCacheInitEvictionHead");
+    check(grl_memcpy_h2d(dev, head.w2.dptr, w2.data(), w2.size() * 4), "kvCacheInitEvictionHead");
+    check(grl_memset(dev, head.b1.dptr, 0, size_t(hiddenDim) * 4), "kvCacheInitEvictionHead");
+    check(grl_memset(dev, head.b2.dptr, 0, 4), "kvCacheInitEvictionHead");
+    check(grl_sync(dev, 0), "kvCacheInitEvictionHead");
+    head.initialized = true;
+}
+
+void kvCacheDestroyEvictionHead(BufferPool& pool, KVCache& kv) {
+    auto& head = kv.evictionHead;
+    if (!head.initialized) return;
+    pool.release(head.w1); pool.release(head.b1); pool.release(head.w2); pool.release(head.b2);
+    head.initialized = false;
+}
+
+void kvCacheTrainEvictionHead(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kv,
+                              const float* tokenFeatures, const float* attentionScores, uint32_t seqLen) {
+    auto& head = kv.evictionHead;
+    if (!head.initialized) return;                    // kv_cache.cpp:741
+    const uint32_t T = kv.currentLen;
+    if (T == 0) return;
+    if (!tokenFeatures || !attentionScores || seqLen == 0)
+        throw std::runtime_error("kvCacheTrainEvictionHead: null features / scores");
+    grl_device* dev = pool.device().handle();
+    cache.getOrCreate("kv-eviction-head-train");
     grl_kv_layout l = kv.layout();
     grl_kv_meta m = kv.meta();
+    grl_evict_head hv = head.view();
+    size_t bytes = 0;
+    check(grl_evict_head_scratch_bytes(&hv, int(T), &bytes), "kvCacheTrainEvictionHead");
+    GrillyBuffer feat = pool.acquire(size_t(T) * head.inputDim * 4), attn = pool.acquire(size_t(seqLen) * T * 4),
+                 scratch = pool.acquire(bytes);
+    try {
+        Recording rec(batch);
+        pool.upload(feat, tokenFeatures, size_t(T) * head.inputDim * 4);
+        pool.upload(attn, attentionScores, size_t(seqLen) * T * 4);
+        check(grl_evict_head_train(dev, &l, &m, &hv, static_cast<const float*>(feat.dptr),
+                                   static_cast<const float*>(attn.dptr), int(seqLen), int(T), head.learningRate,
+                                   scratch.dptr, scratch.bucketSize),
+              "kvCacheTrainEvictionHead");
+        batch.submit();
+    } catch (...) {
+        pool.release(feat); pool.release(attn); pool.release(scratch);
+        throw;
+    }
+    pool.release(feat); pool.release(attn); pool.release(scratch);
+    head.totalUpdates++;
+}
+
+void kvCacheEvictSpeculative(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kv,
+                             const float* hiddenStates, uint32_t /*hiddenDim: the reference strides by head.inputDim*/) {
+    if (!kv.kPages.valid()) throw std::runtime_error("kvCacheEvictSpeculative: cache was destroyed");
+    grl_device* dev = pool.device().handle();
+    grl_kv_layout l = kv.layout();
+    grl_kv_meta m = kv.meta();
+    const auto& head = kv.evictionHead;
+    if (head.initialized && head.totalUpdates > 0 && hiddenStates && kv.currentLen > 0) {   // kv_cache.cpp:863-866
+        cache.getOrCreate("kv-eviction-head-predict");
+        grl_evict_head hv = head.view();
+        const size_t n = size_t(kv.currentLen) * head.inputDim;
+        GrillyBuffer feat = pool.acquire(n * 4);
+        try {
+            Recording rec(batch);
+            pool.upload(feat, hiddenStates, n * 4);
+            check(grl_evict_head_predict(dev, &l, &m, &hv, static_cast<const float*>(feat.dptr), int(kv.currentLen),
+                                         kv.config.evictionThreshold),
+                  "kvCacheEvictSpeculative");
+            batch.submit();
+        } catch (...) {
+            pool.release(feat);
+            throw;
+        }
+        pool.release(feat);
+        return;
+    }
+    cache.getOrCreate("kv-evict-heuristic");
     Recording rec(batch);
-    check(grl_kv_evict_heuristic(pool.device().handle(), &l, &m, kv.config.evictionThreshold),
-          "kvCacheEvictSpeculative");
+    check(grl_kv_evict_heuristic(dev, &l, &m, kv.config.evictionThreshold), "kvCacheEvictSpeculative");
     batch.submit();
 }
 

@@ -267,6 +267,119 @@ __global__ void __launch_bounds__(kThreads) compact_meta_kernel(float* cum, uint
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Trainable eviction head (kv_cache.cpp:636-845,856-903): relevance = sigmoid(W2 . relu(W1^T x + b1) + b2)
+// for one sequence.  The reference runs it token by token on the CPU; here a token is a thread in the
+// forward pass and a parameter is a thread in the gradient pass, each walking its sum in the
+// reference's order with unfused multiplies and adds, so only exp() separates the two.
+
+// received[t] = sum_q attn[q][t] (ascending q), one thread per token
+__global__ void head_received_kernel(const float* __restrict__ attn, int seq_len, int T, float* received) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    float acc = 0.f;
+    for (int q = 0; q < seq_len; ++q) acc = __fadd_rn(acc, attn[(size_t)q * T + t]);
+    received[t] = acc;
+}
+
+// One CTA: median[0] = the element std::nth_element would leave at index T/2 (the (T/2+1)-th smallest)
+__global__ void __launch_bounds__(kThreads) head_median_kernel(const float* __restrict__ received, int T, float* median) {
+    __shared__ int s_hist[256];
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_k;
+    const int tid = threadIdx.x;
+    if (tid == 0) { s_prefix = 0; s_k = T / 2 + 1; }
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        for (int i = tid; i < 256; i += kThreads) s_hist[i] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix;
+        const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        for (int t = tid; t < T; t += kThreads) {
+            const uint32_t key = order_key(received[t]);
+            if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int kk = s_k, bin = 0;
+            for (; bin < 256; ++bin) {
+                if (kk <= s_hist[bin]) break;
+                kk -= s_hist[bin];
+            }
+            s_prefix = prefix | ((uint32_t)bin << shift);
+            s_k = kk;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        const uint32_t key = s_prefix;
+        const uint32_t u = (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
+        median[0] = __uint_as_float(u);
+    }
+}
+
+struct HeadArgs {
+    const float* w1; const float* b1; const float* w2; const float* b2;
+    int in_dim, h_dim;
+};
+
+// Forward pass, one thread per live token: hidden (kept for the gradient pass), score -> relevance,
+// dlogit = score - label (train) or tombstone below the threshold (predict).
+__global__ void head_forward_kernel(HeadArgs hd, const float* __restrict__ feat, int T, const uint8_t* tomb_in,
+                                    float* relevance, float* hidden, float* dlogit, const float* received,
+                                    const float* median, uint8_t* tomb_out, float threshold) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    if (tomb_in[t]) {                       // skipped by the reference: contributes nothing
+        if (dlogit) dlogit[t] = 0.f;
+        if (hidden) for (int h = 0; h < hd.h_dim; ++h) hidden[(size_t)t * hd.h_dim + h] = 0.f;
+        return;
+    }
+    const float* x = feat + (size_t)t * hd.in_dim;
+    float logit = hd.b2[0];
+    for (int h = 0; h < hd.h_dim; ++h) {
+        float sum = hd.b1[h];
+        for (int i = 0; i < hd.in_dim; ++i) sum = __fadd_rn(sum, __fmul_rn(hd.w1[(size_t)i * hd.h_dim + h], x[i]));
+        const float hv = fmaxf(0.f, sum);
+        if (hidden) hidden[(size_t)t * hd.h_dim + h] = hv;
+        logit = __fadd_rn(logit, __fmul_rn(hd.w2[h], hv));
+    }
+    const float score = __fdiv_rn(1.f, __fadd_rn(1.f, expf(-logit)));
+    relevance[t] = score;
+    if (dlogit) dlogit[t] = __fadd_rn(score, received[t] > median[0] ? -1.f : -0.f);
+    if (tomb_out && score < threshold) tomb_out[t] = 1;
+}
+
+// Gradient pass + SGD step, one thread per parameter, tokens in ascending order:
+// index < in*h: W1[i][h]; then b1[h]; then W2[h]; then b2.
+__global__ void head_update_kernel(float* w1, float* b1, float* w2, float* b2, int in_dim, int h_dim,
+                                   const float* __restrict__ feat, const float* __restrict__ hidden,
+                                   const float* __restrict__ dlogit, const float* __restrict__ w2_old, int T, float step) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n_w1 = in_dim * h_dim;
+    if (idx >= n_w1 + 2 * h_dim + 1) return;
+    float g = 0.f;
+    if (idx < n_w1 + h_dim) {               // W1[i][h] or b1[h]: through the ReLU
+        const bool bias = idx >= n_w1;
+        const int h = bias ? idx - n_w1 : idx % h_dim, i = bias ? 0 : idx / h_dim;
+        const float w2h = w2_old[h];
+        for (int t = 0; t < T; ++t) {
+            const float hv = hidden[(size_t)t * h_dim + h];
+            const float dh = __fmul_rn(__fmul_rn(dlogit[t], w2h), hv > 0.f ? 1.f : 0.f);
+            g = __fadd_rn(g, bias ? dh : __fmul_rn(dh, feat[(size_t)t * in_dim + i]));
+        }
+        float* p = bias ? b1 + h : w1 + idx;
+        *p = __fadd_rn(*p, -__fmul_rn(step, g));
+    } else if (idx < n_w1 + 2 * h_dim) {    // W2[h]
+        const int h = idx - n_w1 - h_dim;
+        for (int t = 0; t < T; ++t) g = __fadd_rn(g, __fmul_rn(dlogit[t], hidden[(size_t)t * h_dim + h]));
+        w2[h] = __fadd_rn(w2[h], -__fmul_rn(step, g));
+    } else {                                // b2
+        for (int t = 0; t < T; ++t) g = __fadd_rn(g, dlogit[t]);
+        b2[0] = __fadd_rn(b2[0], -__fmul_rn(step, g));
+    }
+}
+
 static int check_meta(const grl_kv_layout* kv, const grl_kv_meta* m) {
     GRL_REQUIRE(kv && m, "NULL argument");
     GRL_REQUIRE(kv->block_table && kv->seq_lens && kv->batch > 0 && kv->page_tokens > 0 && kv->max_pages > 0,
@@ -374,6 +487,75 @@ int grl_kv_compact(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* 
                                                                 kv->seq_lens, meta->evicted, new_pos, new_len,
                                                                 meta->capacity);
     GRL_LAUNCHED("compact_meta_kernel");
+    return GRL_OK;
+}
+
+static int check_head(const grl_evict_head* h) {
+    GRL_REQUIRE(h && h->w1 && h->b1 && h->w2 && h->b2, "NULL eviction-head buffer");
+    GRL_REQUIRE(h->input_dim > 0 && h->hidden_dim > 0 && h->hidden_dim <= 4096, "bad eviction-head shape");
+    return GRL_OK;
+}
+
+int grl_evict_head_scratch_bytes(const grl_evict_head* head, int tokens, size_t* bytes) {
+    GRL_REQUIRE(head && bytes && tokens >= 0, "bad argument");
+    // received[T], dlogit[T], median[1] (+pad), hidden[T][h], w2 copy[h]
+    *bytes = sizeof(float) * ((size_t)tokens * (2 + head->hidden_dim) + 4 + head->hidden_dim);
+    return GRL_OK;
+}
+
+int grl_evict_head_train(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, const grl_evict_head* head,
+                         const float* features, const float* attn, int seq_len, int tokens, float lr, void* scratch,
+                         size_t scratch_bytes) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    int rc = check_meta(kv, meta);
+    if (!rc) rc = check_head(head);
+    if (rc) return rc;
+    GRL_REQUIRE(kv->batch == 1, "the eviction head works on a single-sequence cache");
+    GRL_REQUIRE(meta->relevance, "metadata has no relevance array");
+    GRL_REQUIRE(features && attn && seq_len > 0 && tokens > 0 && tokens <= meta->capacity, "bad argument");
+    size_t need = 0;
+    grl_evict_head_scratch_bytes(head, tokens, &need);
+    GRL_REQUIRE(scratch && scratch_bytes >= need, "eviction-head scratch too small: %zu < %zu", scratch_bytes, need);
+    DeviceGuard g(dev->ordinal);
+    float* received = static_cast<float*>(scratch);
+    float* dlogit = received + tokens;
+    float* median = dlogit + tokens;
+    float* hidden = median + 4;
+    float* w2_old = hidden + (size_t)tokens * head->hidden_dim;
+    const int blocks = (tokens + 127) / 128;
+    head_received_kernel<<<blocks, 128, 0, dev->stream>>>(attn, seq_len, tokens, received);
+    GRL_LAUNCHED("head_received_kernel");
+    head_median_kernel<<<1, kThreads, 0, dev->stream>>>(received, tokens, median);
+    GRL_LAUNCHED("head_median_kernel");
+    HeadArgs hd{head->w1, head->b1, head->w2, head->b2, head->input_dim, head->hidden_dim};
+    head_forward_kernel<<<blocks, 128, 0, dev->stream>>>(hd, features, tokens, meta->tombstone, meta->relevance, hidden,
+                                                        dlogit, received, median, nullptr, 0.f);
+    GRL_LAUNCHED("head_forward_kernel");
+    // the W1 gradient uses W2 as it was in the forward pass, while another thread updates W2
+    GRL_CUDA(cudaMemcpyAsync(w2_old, head->w2, sizeof(float) * head->hidden_dim, cudaMemcpyDeviceToDevice, dev->stream));
+    const int params = head->input_dim * head->hidden_dim + 2 * head->hidden_dim + 1;
+    head_update_kernel<<<(params + 127) / 128, 128, 0, dev->stream>>>(head->w1, head->b1, head->w2, head->b2,
+                                                                     head->input_dim, head->hidden_dim, features, hidden,
+                                                                     dlogit, w2_old, tokens, lr / (float)tokens);
+    GRL_LAUNCHED("head_update_kernel");
+    return GRL_OK;
+}
+
+int grl_evict_head_predict(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, const grl_evict_head* head,
+                           const float* features, int tokens, float threshold) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    int rc = check_meta(kv, meta);
+    if (!rc) rc = check_head(head);
+    if (rc) return rc;
+    GRL_REQUIRE(kv->batch == 1, "the eviction head works on a single-sequence cache");
+    GRL_REQUIRE(meta->relevance, "metadata has no relevance array");
+    GRL_REQUIRE(features && tokens > 0 && tokens <= meta->capacity, "bad argument");
+    DeviceGuard g(dev->ordinal);
+    HeadArgs hd{head->w1, head->b1, head->w2, head->b2, head->input_dim, head->hidden_dim};
+    head_forward_kernel<<<(tokens + 127) / 128, 128, 0, dev->stream>>>(hd, features, tokens, meta->tombstone, meta->relevance,
+                                                                      nullptr, nullptr, nullptr, nullptr, meta->tombstone,
+                                                                      threshold);
+    GRL_LAUNCHED("head_forward_kernel");
     return GRL_OK;
 }
 

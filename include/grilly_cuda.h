@@ -215,6 +215,28 @@ int grl_kv_compact_scratch_bytes(const grl_kv_layout* kv, const grl_kv_meta* met
 int grl_kv_compact(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, void* scratch,
                    size_t scratch_bytes);
 
+/* Trainable eviction head (kvCacheTrainEvictionHead, cpp/src/ops/kv_cache.cpp:734-845, and the
+ * trained-head branch of kvCacheEvictSpeculative, :856-903): relevance = sigmoid(W2 . relu(W1^T x + b1) + b2)
+ * per token of a single-sequence cache.  w1 (input_dim, hidden_dim) row-major, b1 (hidden_dim),
+ * w2 (hidden_dim), b2 (1): device float32, owned and initialised by the caller. */
+typedef struct {
+    float* w1;
+    float* b1;
+    float* w2;
+    float* b2;
+    int32_t input_dim, hidden_dim;
+} grl_evict_head;
+int grl_evict_head_scratch_bytes(const grl_evict_head* head, int tokens, size_t* bytes);
+/* One SGD step: labels = (attention received > its median), attention received = column sums of attn
+ * (seq_len, tokens); binary cross-entropy; mean gradient over `tokens`; tombstoned tokens are skipped.
+ * features (tokens, input_dim), attn: device float32.  Writes the predictions to meta->relevance. */
+int grl_evict_head_train(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, const grl_evict_head* head,
+                         const float* features, const float* attn, int seq_len, int tokens, float lr, void* scratch,
+                         size_t scratch_bytes);
+/* Predict relevance of every live token and tombstone those below threshold. */
+int grl_evict_head_predict(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* meta, const grl_evict_head* head,
+                           const float* features, int tokens, float threshold);
+
 /* ---- decode attention: replaces shaders/gqa-attention.glsl:34-130 (no host dispatcher exists
  * in the reference).  q, out: (B,1,Hq,D) float32.  kv_head = q_head / (Hq/Hkv).
  * The KV range of every sequence is cut into n_splits parts that run on different SMs; each

@@ -79,3 +79,62 @@ def average_score(cum, tomb):
             total = np.float32(total + np.float32(cum[t]))
             active += 1
     return float(total / np.float32(active)) if active else 0.0
+
+
+# ---- trainable eviction head (kv_cache.cpp:734-845 and :863-903) -----------------------------------
+
+def _head_forward(w1, b1, w2, b2, x):
+    """hidden = relu(W1^T x + b1) with the sum over inputs in ascending order starting from the bias,
+    logit = b2 + sum_h w2[h] hidden[h] in ascending h, score = sigmoid(logit): float32 throughout."""
+    hidden = b1.astype(np.float32).copy()
+    for i in range(w1.shape[0]):
+        hidden = hidden + np.float32(x[i]) * w1[i]          # one multiply, one add per term (no fusing)
+    hidden = np.maximum(np.float32(0.0), hidden)
+    logit = np.float32(b2[0])
+    for h in range(len(hidden)):
+        logit = np.float32(logit + np.float32(w2[h] * hidden[h]))
+    score = np.float32(1.0) / (np.float32(1.0) + np.exp(-logit, dtype=np.float32))
+    return hidden, np.float32(score)
+
+
+def head_train_step(w1, b1, w2, b2, features, attn, tomb, lr):
+    """One call of kvCacheTrainEvictionHead.  features (T, in), attn (seq_len, T), tomb (T,).
+    Returns (w1, b1, w2, b2, relevance) with relevance[t] = prediction made before the update
+    (0 where the token is tombstoned and skipped)."""
+    w1, b1, w2, b2 = (np.asarray(a, np.float32).copy() for a in (w1, b1, w2, b2))
+    T = features.shape[0]
+    received = np.zeros(T, np.float32)
+    for q in range(attn.shape[0]):
+        received = received + attn[q].astype(np.float32)
+    median = np.sort(received)[T // 2]                      # what nth_element leaves at T/2
+    labels = (received > median).astype(np.float32)
+    g_w1, g_b1 = np.zeros_like(w1), np.zeros_like(b1)
+    g_w2, g_b2 = np.zeros_like(w2), np.float32(0.0)
+    rel = np.zeros(T, np.float32)
+    for t in range(T):
+        if tomb[t]:
+            continue
+        x = features[t].astype(np.float32)
+        hidden, score = _head_forward(w1, b1, w2, b2, x)
+        rel[t] = score
+        d_logit = np.float32(score - labels[t])
+        g_w2 = g_w2 + d_logit * hidden
+        g_b2 = np.float32(g_b2 + d_logit)
+        d_hidden = np.float32(d_logit) * w2 * (hidden > 0).astype(np.float32)
+        g_b1 = g_b1 + d_hidden
+        g_w1 = g_w1 + x[:, None] * d_hidden[None, :]
+    step = np.float32(lr) / np.float32(T)
+    return w1 - step * g_w1, b1 - step * g_b1, w2 - step * g_w2, np.float32(b2 - step * g_b2).reshape(1), rel
+
+
+def head_predict(w1, b1, w2, b2, features, tomb, threshold):
+    """Trained-head branch of kvCacheEvictSpeculative: returns (tomb, relevance)."""
+    tomb = np.asarray(tomb, np.uint8).copy()
+    rel = np.zeros(features.shape[0], np.float32)
+    for t in range(features.shape[0]):
+        if tomb[t]:
+            continue
+        _, rel[t] = _head_forward(w1, b1, w2, b2, features[t].astype(np.float32))
+        if rel[t] < np.float32(threshold):
+            tomb[t] = 1
+    return tomb, rel

@@ -226,3 +226,47 @@ def test_decode_accumulates_attention_mass(dtype, D, tol):
     got = core.kv_cache_token_meta(ctx, kv, 0)["cumulative_score"]
     assert got.shape == (T + 1,) and got[-1] > 0 and abs(got.sum() - 3 * Hq) <= 2e-2
     core.destroy_kv_cache(ctx, kv)
+
+
+def test_eviction_head_training_and_prediction():
+    # kv_cache_init_eviction_head / kv_cache_train_eviction_head / kv_cache_evict_speculative with a trained head
+    import grilly_core as core
+    ctx = core.Device()
+    rng = np.random.default_rng(9)
+    H, D, T, inp, hid = 2, 64, 150, 24, 16
+    kv = core.create_kv_cache(ctx, max_seq_len=256, num_heads=H, head_dim=D, compression_ratio=1, max_cache_tokens=256,
+                              eviction_threshold=0.45, dtype="fp32")
+    k = rng.standard_normal((T, H, D), dtype=np.float32)
+    core.kv_cache_append(ctx, kv, k, k)
+    feats = rng.standard_normal((T, inp), dtype=np.float32)
+    # before a head exists (or before its first update) the call is the heuristic, as in the reference
+    core.kv_cache_train_eviction_head(ctx, kv, feats, np.ones((3, T), np.float32), 3)      # no head: a no-op
+    core.kv_cache_init_eviction_head(ctx, kv, inp, hid, 0.5)
+    w = core.kv_cache_eviction_head_weights(ctx, kv)
+    lim1, lim2 = np.sqrt(6.0 / (inp + hid)), np.sqrt(6.0 / (hid + 1))
+    assert w["w1"].shape == (inp, hid) and np.abs(w["w1"]).max() <= lim1 and np.abs(w["w2"]).max() <= lim2
+    assert not w["b1"].any() and not w["b2"].any() and w["total_updates"] == 0 and w["w1"].std() > 0.1 * lim1
+    # some tombstones first (they are skipped by training and prediction)
+    core.kv_cache_evict_h2o(ctx, kv, rng.random((T, T), dtype=np.float32), 20)
+    tomb = core.kv_cache_token_meta(ctx, kv)["tombstone"]
+    params = (w["w1"], w["b1"], w["w2"], w["b2"])
+    for step in range(3):
+        attn = rng.random((11, T), dtype=np.float32)
+        core.kv_cache_train_eviction_head(ctx, kv, feats, attn, 11)
+        *params, rel = ev.head_train_step(*params, feats, attn, tomb, 0.5)
+        got = core.kv_cache_eviction_head_weights(ctx, kv)
+        for name, want in zip(("w1", "b1", "w2", "b2"), params):
+            assert np.abs(got[name] - want).max() <= 2e-6, (step, name)
+        assert got["total_updates"] == step + 1
+        assert np.abs(core.kv_cache_token_meta(ctx, kv)["predicted_relevance"] - rel).max() <= 2e-6
+    # prediction with the trained head tombstones what falls below the threshold
+    core.kv_cache_evict_speculative(ctx, kv, feats)
+    want_tomb, want_rel = ev.head_predict(*params, feats, tomb, 0.45)
+    meta = core.kv_cache_token_meta(ctx, kv)
+    near = np.abs(want_rel - 0.45) < 1e-5                         # predictions on the threshold may fall either way
+    assert np.array_equal(meta["tombstone"][~near], want_tomb[~near])
+    assert np.abs(meta["predicted_relevance"] - want_rel).max() <= 2e-6
+    assert want_tomb.sum() > tomb.sum()
+    with pytest.raises(RuntimeError, match="hidden_states must be"):
+        core.kv_cache_evict_speculative(ctx, kv, feats[:, :5])
+    core.destroy_kv_cache(ctx, kv)

@@ -62,3 +62,34 @@ def test_heuristic_threshold():
     # all-zero scores: the inverse maximum is 1 (kv_cache.cpp:913)
     t3, rel3 = ev.evict_heuristic(np.zeros(4, np.float32), np.zeros(4, np.uint8), 0.1)
     assert t3.tolist() == [1, 1, 0, 0] and np.allclose(rel3, [0, 0.075, 0.15, 0.225], atol=1e-6)
+
+
+def test_head_training_lowers_the_loss():
+    # the restated SGD step is a gradient step of the binary cross-entropy it claims to minimise
+    rng = np.random.default_rng(2)
+    T, inp, hid = 40, 6, 5
+    w1 = rng.standard_normal((inp, hid)).astype(np.float32) * 0.5
+    b1, w2, b2 = np.zeros(hid, np.float32), rng.standard_normal(hid).astype(np.float32) * 0.5, np.zeros(1, np.float32)
+    feats = rng.standard_normal((T, inp)).astype(np.float32)
+    attn = rng.random((7, T), dtype=np.float32)
+    tomb = np.zeros(T, np.uint8); tomb[3] = 1
+    received = attn.sum(0)
+    labels = (received > np.sort(received)[T // 2]).astype(np.float64)
+
+    def loss(params):
+        total = 0.0
+        for t in range(T):
+            if tomb[t]:
+                continue
+            _, s = ev._head_forward(*params, feats[t])
+            s = min(max(float(s), 1e-7), 1 - 1e-7)
+            total += -(labels[t] * np.log(s) + (1 - labels[t]) * np.log(1 - s))
+        return total
+
+    params = (w1, b1, w2, b2)
+    before = loss(params)
+    for _ in range(20):
+        *params, rel = ev.head_train_step(*params, feats, attn, tomb, lr=0.5)
+    assert loss(params) < before and rel[3] == 0.0 and np.all((rel >= 0) & (rel <= 1))
+    t2, r2 = ev.head_predict(*params, feats, tomb, 0.5)
+    assert t2[3] == 1 and np.array_equal(t2[r2 < 0.5] == 1, np.ones((r2 < 0.5).sum(), bool))
