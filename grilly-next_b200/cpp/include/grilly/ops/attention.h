@@ -52,5 +52,13 @@ void flashAttention2Device(CommandBatch& batch, PipelineCache& cache, const Gril
                            uint32_t seqLen, uint32_t numHeads, uint32_t headDim, float scale, bool causal,
                            const GrillyBuffer* seqLensDev, RopeMode ropeMode, float ropeTheta, float ropeScaling);
 
+/// Bytes of the swizzled form of a (B,H,S,D) float32 tensor (cpp/src/ops/swizzle.cpp swizzledBufferSize).
+size_t swizzledBufferSize(uint32_t batchSize, uint32_t numHeads, uint32_t seqLen, uint32_t headDim, uint32_t waveSize = 32);
+/// (B,H,S,D) -> (B,H,S_pad/W,D_pad/W,W,W) with zero padding, or back with reverse: host pointers, synchronous
+/// (the reference's ops::swizzle, cpp/src/ops/swizzle.cpp:164-229).
+void swizzle(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* input, float* output,
+             uint32_t batchSize, uint32_t numHeads, uint32_t seqLen, uint32_t headDim, uint32_t waveSize = 32,
+             bool reverse = false);
+
 }  // namespace ops
 }  // namespace grilly

@@ -350,6 +350,29 @@ PYBIND11_MODULE(grilly_core, m) {
         py::arg("device"), py::arg("scores"), py::arg("mask") = py::none(), py::arg("causal") = false,
         py::arg("mask_value") = -1e9f, "Causal or key-padding fill on attention scores; returns the masked copy");
 
+    // ---- swizzle_kv (reference: bindings.cpp:784-832)
+    m.def(
+        "swizzle_kv",
+        [](GrillyCoreContext& ctx, FArr input, uint32_t waveSize, bool reverse) -> py::array_t<float> {
+            if (input.ndim() != 4) throw std::runtime_error("input must be 4D (batch, heads, seq_len, head_dim)");
+            if (waveSize == 0) throw std::runtime_error("wave_size must be positive");
+            const uint32_t B = uint32_t(input.shape(0)), H = uint32_t(input.shape(1)), S = uint32_t(input.shape(2)),
+                           D = uint32_t(input.shape(3));
+            py::array_t<float> result;
+            if (reverse) {
+                // the 4-D array holds swizzled data, which only has that many elements when nothing was padded
+                if (S % waveSize || D % waveSize)
+                    throw std::runtime_error("reverse needs seq_len and head_dim to be multiples of wave_size");
+                result = py::array_t<float>({py::ssize_t(B), py::ssize_t(H), py::ssize_t(S), py::ssize_t(D)});
+            } else {
+                result = py::array_t<float>(py::ssize_t(ops::swizzledBufferSize(B, H, S, D, waveSize) / sizeof(float)));
+            }
+            ops::swizzle(ctx.batch, ctx.pool, ctx.cache, input.data(), result.mutable_data(), B, H, S, D, waveSize, reverse);
+            return result;
+        },
+        py::arg("device"), py::arg("input"), py::arg("wave_size") = 32, py::arg("reverse") = false,
+        "Swizzle/unswizzle KV tensor: [B,H,S,D] -> [B,H,S/W,D/W,W,W] (flat, zero padded) and back");
+
     // ---- KV cache (reference: bindings.cpp:592-694)
     py::class_<ops::KVCache>(m, "KVCache")
         .def_readonly("current_len", &ops::KVCache::currentLen)

@@ -273,5 +273,30 @@ void attentionMask(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, 
     batch.submit();
 }
 
+size_t swizzledBufferSize(uint32_t B, uint32_t H, uint32_t S, uint32_t D, uint32_t W) {
+    const size_t sp = (size_t(S) + W - 1) / W * W, dp = (size_t(D) + W - 1) / W * W;
+    return size_t(B) * H * sp * dp * sizeof(float);
+}
+
+void swizzle(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* input, float* output, uint32_t B,
+             uint32_t H, uint32_t S, uint32_t D, uint32_t W, bool reverse) {
+    if (!input || !output) throw std::runtime_error("swizzle: null tensor pointer");
+    if (B == 0 || H == 0 || S == 0 || D == 0 || W == 0) throw std::runtime_error("swizzle: empty shape");
+    cache.getOrCreate("kv-swizzle");
+    const size_t plain = size_t(B) * H * S * D * 4, swz = swizzledBufferSize(B, H, S, D, W);
+    const size_t inBytes = reverse ? swz : plain, outBytes = reverse ? plain : swz;
+    Scoped scope(pool);
+    GrillyBuffer in = pool.acquire(inBytes), out = pool.acquire(outBytes);
+    scope.add(in); scope.add(out);
+    grl_device* dev = pool.device().handle();
+    Recording rec(batch);
+    pool.upload(in, input, inBytes);
+    check(grl_swizzle_kv(dev, static_cast<const float*>(in.dptr), static_cast<float*>(out.dptr), int(B), int(H), int(S),
+                         int(D), int(W), reverse ? 1 : 0),
+          "swizzle");
+    check(grl_memcpy_d2h(dev, output, out.dptr, outBytes), "swizzle: download");
+    batch.submit();
+}
+
 }  // namespace ops
 }  // namespace grilly

@@ -99,6 +99,30 @@ __global__ void kv_gather_kernel(const T* __restrict__ kp, const T* __restrict__
     }
 }
 
+// Block swizzle of cpp/src/ops/swizzle.cpp:49-123: (B,H,S,D) <-> (B,H,S_pad/W,D_pad/W,W,W), padding zero.
+// One thread per element of the swizzled tensor; W consecutive threads touch W consecutive floats on
+// both sides.
+__global__ void swizzle_kv_kernel(const float* __restrict__ in, float* __restrict__ out, int S, int D, int W,
+                                  int s_pad, int d_pad, size_t total, int reverse) {
+    const int d_blocks = d_pad / W;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int dw = (int)(idx % W);
+        const int sw = (int)((idx / W) % W);
+        const int db = (int)((idx / ((size_t)W * W)) % d_blocks);
+        const size_t rest = idx / ((size_t)W * W * d_blocks);
+        const int sb = (int)(rest % (s_pad / W));
+        const size_t bh = rest / (s_pad / W);
+        const int s = sb * W + sw, d = db * W + dw;
+        const bool inside = s < S && d < D;
+        const size_t plain = (bh * S + s) * D + d;
+        if (reverse) {
+            if (inside) out[plain] = in[idx];
+        } else {
+            out[idx] = inside ? in[plain] : 0.f;
+        }
+    }
+}
+
 static int check_layout(const grl_kv_layout& kv) {
     GRL_REQUIRE(kv.k_pages && kv.v_pages && kv.block_table && kv.seq_lens, "NULL cache pointer");
     GRL_REQUIRE(kv.batch > 0 && kv.num_kv_heads > 0 && kv.page_tokens > 0 && kv.max_pages > 0, "bad cache shape");
@@ -146,6 +170,20 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p) {
         advance_lens_kernel<<<(kv.batch + 127) / 128, 128, 0, dev->stream>>>(kv.seq_lens, kv.batch, p->n_new);
         GRL_LAUNCHED("advance_lens_kernel");
     }
+    return GRL_OK;
+}
+
+int grl_swizzle_kv(grl_device* dev, const float* in, float* out, int batch, int heads, int seq_len, int head_dim,
+                   int wave, int reverse) {
+    GRL_REQUIRE(dev && in && out, "NULL argument");
+    GRL_REQUIRE(batch > 0 && heads > 0 && seq_len > 0 && head_dim > 0 && wave > 0, "bad shape");
+    DeviceGuard g(dev->ordinal);
+    const int s_pad = (seq_len + wave - 1) / wave * wave, d_pad = (head_dim + wave - 1) / wave * wave;
+    const size_t total = (size_t)batch * heads * s_pad * d_pad;
+    const size_t blocks = (total + 255) / 256;
+    swizzle_kv_kernel<<<(unsigned)(blocks < 65535 * 16 ? blocks : 65535 * 16), 256, 0, dev->stream>>>(
+        in, out, seq_len, head_dim, wave, s_pad, d_pad, total, reverse ? 1 : 0);
+    GRL_LAUNCHED("swizzle_kv_kernel");
     return GRL_OK;
 }
 

@@ -86,3 +86,7 @@ def decode_step(device, kv_cache, q, k_new, v_new, **kwargs):
 
 KVCache = getattr(_core, "KVCache", None)
 Device = getattr(_core, "Device", None)
+
+
+def swizzle_kv(device, input, wave_size=32, reverse=False):
+    return _core.swizzle_kv(device, input, wave_size, reverse)

@@ -58,7 +58,7 @@ class VulkanCompute:
         return _bridge.destroy_kv_cache(self._device, kv_cache)
 
     def swizzle_kv(self, input, wave_size=32, reverse=False):
-        raise RuntimeError("swizzle_kv is not built in the CUDA backend (Wave32 layout op)")
+        return _bridge.swizzle_kv(self._device, input, wave_size, reverse)
 
     # ---- decode
     def gqa_attention(self, q, k_cache, v_cache=None, **kwargs):

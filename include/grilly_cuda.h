@@ -181,6 +181,12 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p);
 int grl_kv_gather(grl_device* dev, const grl_kv_layout* kv, int b, int n_tokens, float* out_k,
                   float* out_v);
 
+/* Block swizzle of a (B,H,S,D) float32 tensor into (B,H,ceil(S/W),ceil(D/W),W,W) with zero padding, or
+ * back (reverse != 0): replaces ops::swizzle / swizzleCPU / unswizzleCPU (cpp/src/ops/swizzle.cpp:49-229).
+ * The swizzled side holds B*H*S_pad*D_pad floats. */
+int grl_swizzle_kv(grl_device* dev, const float* in, float* out, int batch, int heads, int seq_len, int head_dim,
+                   int wave, int reverse);
+
 /* ---- eviction on the paged cache: replaces the host loops of kvCacheEvictH2O
  * (cpp/src/ops/kv_cache.cpp:595-634), the untrained-head branch of kvCacheEvictSpeculative (:905-929)
  * and kvCacheCompact (:941-992; signatures kv_cache.h:186-229).  The reference's TokenMeta array

@@ -138,3 +138,21 @@ def head_predict(w1, b1, w2, b2, features, tomb, threshold):
         if rel[t] < np.float32(threshold):
             tomb[t] = 1
     return tomb, rel
+
+
+# ---- block swizzle (cpp/src/ops/swizzle.cpp:49-123) ------------------------------------------------
+
+def swizzle(x, wave=32):
+    """(B,H,S,D) -> flat (B*H*S_pad*D_pad) with layout [b][h][s/W][d/W][s%W][d%W], padding zero."""
+    B, H, S, D = x.shape
+    sp, dp = -(-S // wave) * wave, -(-D // wave) * wave
+    pad = np.zeros((B, H, sp, dp), np.float32)
+    pad[:, :, :S, :D] = x
+    return pad.reshape(B, H, sp // wave, wave, dp // wave, wave).transpose(0, 1, 2, 4, 3, 5).reshape(-1)
+
+
+def unswizzle(flat, shape, wave=32):
+    B, H, S, D = shape
+    sp, dp = -(-S // wave) * wave, -(-D // wave) * wave
+    pad = np.asarray(flat, np.float32).reshape(B, H, sp // wave, dp // wave, wave, wave).transpose(0, 1, 2, 4, 3, 5)
+    return pad.reshape(B, H, sp, dp)[:, :, :S, :D].copy()

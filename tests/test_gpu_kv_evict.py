@@ -270,3 +270,20 @@ def test_eviction_head_training_and_prediction():
     with pytest.raises(RuntimeError, match="hidden_states must be"):
         core.kv_cache_evict_speculative(ctx, kv, feats[:, :5])
     core.destroy_kv_cache(ctx, kv)
+
+
+def test_swizzle_kv():
+    import grilly_core as core
+    ctx = core.Device()
+    rng = np.random.default_rng(10)
+    for shape, wave in (((2, 3, 100, 64), 32), ((1, 2, 64, 128), 32), ((1, 1, 7, 5), 4)):
+        x = rng.standard_normal(shape, dtype=np.float32)
+        got = core.swizzle_kv(ctx, x, wave_size=wave)
+        assert got.ndim == 1 and np.array_equal(got, ev.swizzle(x, wave))
+    x = rng.standard_normal((2, 2, 64, 64), dtype=np.float32)
+    back = core.swizzle_kv(ctx, core.swizzle_kv(ctx, x).reshape(x.shape), reverse=True)
+    assert np.array_equal(back, x)
+    with pytest.raises(RuntimeError, match="multiples of wave_size"):
+        core.swizzle_kv(ctx, np.zeros((1, 1, 10, 64), np.float32), reverse=True)
+    with pytest.raises(RuntimeError, match="input must be 4D"):
+        core.swizzle_kv(ctx, np.zeros((4, 4), np.float32))

@@ -93,3 +93,21 @@ def test_head_training_lowers_the_loss():
     assert loss(params) < before and rel[3] == 0.0 and np.all((rel >= 0) & (rel <= 1))
     t2, r2 = ev.head_predict(*params, feats, tomb, 0.5)
     assert t2[3] == 1 and np.array_equal(t2[r2 < 0.5] == 1, np.ones((r2 < 0.5).sum(), bool))
+
+
+def test_swizzle_matches_the_index_formula():
+    # destination index of cpp/src/ops/swizzle.cpp:77-84, element by element
+    rng = np.random.default_rng(3)
+    B, H, S, D, W = 2, 3, 10, 6, 4
+    x = rng.standard_normal((B, H, S, D), dtype=np.float32)
+    sp, dp = 12, 8
+    want = np.zeros(B * H * sp * dp, np.float32)
+    for b in range(B):
+        for h in range(H):
+            for s in range(S):
+                for d in range(D):
+                    dst = (b * H + h) * sp * dp + (s // W) * ((dp // W) * W * W) + (d // W) * W * W + (s % W) * W + d % W
+                    want[dst] = x[b, h, s, d]
+    got = ev.swizzle(x, W)
+    assert np.array_equal(got, want)
+    assert np.array_equal(ev.unswizzle(got, x.shape, W), x)
