@@ -78,7 +78,7 @@ def build_pybind(force=False, verbose=False):
     lib = os.path.join(LIBDIR, "libgrilly_cuda.so")
     if not (force or _newer(out, srcs + hdrs + [lib, os.path.join(ROOT, "include", "grilly_cuda.h")])):
         return out
-    cmd = [HOST_CXX, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+    cmd = [HOST_CXX, "-O3", "-mavx2", "-pthread", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
            "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
            "-I", os.path.join(CPPDIR, "include"), "-I", os.path.join(ROOT, "include")] + srcs + [
            "-L", LIBDIR, "-lgrilly_cuda", "-Wl,-rpath,$ORIGIN/../lib", "-o", out]

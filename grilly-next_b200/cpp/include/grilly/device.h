@@ -2,6 +2,7 @@
 // CUDA device context of the op layer.  Same role and accessors as the reference's Vulkan
 // GrillyDevice (cpp/include/grilly/device.h:16-53): picks a GPU, owns the queue (here: a CUDA
 // stream inside the C-ABI handle) and reports capabilities.
+#include <cstddef>
 #include <stdexcept>
 #include <string>
 
@@ -37,12 +38,17 @@ public:
     /// to its compute queue.  Order between queues is set with grl_event_record / grl_event_wait.
     grl_device* uploadQueue();
     grl_device* downloadQueue();
+    /// Pinned host scratch kept for the life of the device (slot 0..5): staging for converted uploads.
+    static constexpr int kStagingSlots = 6;
+    void* pinnedStaging(int slot, size_t bytes);
 
 private:
     void open(int ordinal);
     grl_device* dev_ = nullptr;
     grl_device* up_ = nullptr;
     grl_device* down_ = nullptr;
+    void* staging_[kStagingSlots] = {};
+    size_t stagingBytes_[kStagingSlots] = {};
     grl_device_info info_{};
     std::string name_;
 };

@@ -14,6 +14,7 @@
 #include "grilly/buffer_pool.h"
 #include "grilly/command_batch.h"
 #include "grilly/device.h"
+#include "grilly/host_workers.h"
 #include "grilly/ops/attention.h"
 #include "grilly/ops/kv_cache.h"
 #include "grilly/ops/rope.h"
@@ -167,6 +168,16 @@ PYBIND11_MODULE(grilly_core, m) {
             d["hits"] = s.hits; d["misses"] = s.misses; d["evictions"] = s.evictions; d["cached_sets"] = s.cachedSets;
             return d;
         });
+
+    // host-side rounding used by the chunked upload path (needs no GPU; exposed for the tests)
+    m.def(
+        "_host_round_bf16",
+        [](FArr a) {
+            py::array_t<uint16_t> out{py::ssize_t(a.size())};
+            convertF32ToBF16(a.data(), out.mutable_data(), size_t(a.size()));
+            return out;
+        },
+        py::arg("array"), "float32 -> bf16 bit patterns (round to nearest even) on the host worker threads");
 
     // ---- device-resident tensors
     py::class_<DeviceTensor, TensorPtr>(m, "DeviceTensor")

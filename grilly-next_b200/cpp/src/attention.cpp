@@ -5,6 +5,7 @@
 #include <string>
 #include <vector>
 
+#include "grilly/host_workers.h"
 #include "grilly/ops/attention.h"
 #include "grilly/ops/rope.h"
 
@@ -14,6 +15,8 @@ namespace ops {
 namespace {
 constexpr size_t kPipelineMinBytes = 8u << 20;     // per tensor: below this one upload / launch / download
 constexpr size_t kPipelineChunkBytes = 32u << 20;      // per tensor: the large chunks
+constexpr size_t kPipelineHostCastPct = 100;   // all of it: with pinned sources 75 % was 5 % faster (16 host threads, 55 GB/s
+                                              // link), but a pageable float32 source uploads synchronously and three times slower
 constexpr size_t kPipelineLastChunkBytes = 4u << 20;   // per tensor: the last chunk (nothing hides its kernel and download)
 struct Scoped {   // releases pooled buffers on every exit path
     BufferPool& pool;
@@ -58,8 +61,15 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
     cache.getOrCreate(std::string(bf16 ? "flash-attention2-tcgen05/" : "flash-attention2/") + std::to_string(D));
 
     Scoped scope(pool);
-    GrillyBuffer q32 = pool.acquire(n * 4), k32 = pool.acquire(n * 4), v32 = pool.acquire(n * 4),
-                 out = pool.acquire(n * 4);
+    const size_t slice = size_t(S) * D;                       // elements of one (b, h) slice
+    const bool pipelined = n * 4 >= kPipelineMinBytes && (!mask || opt.maskRank == 2) && size_t(B) * H > 1;
+    GrillyBuffer q32, k32, v32, out = pool.acquire(n * 4);
+    // share of a chunk that the host threads round to bf16 themselves (the rest is cast on the device)
+    size_t hostPct = kPipelineHostCastPct;
+    if (const char* e = std::getenv("GRILLY_PIPELINE_HOST_CAST_PCT")) hostPct = size_t(std::min(100, std::max(0, std::atoi(e))));
+    if (!(pipelined && bf16 && hostPct == 100)) {
+        q32 = pool.acquire(n * 4); k32 = pool.acquire(n * 4); v32 = pool.acquire(n * 4);
+    }
     scope.add(q32); scope.add(k32); scope.add(v32); scope.add(out);
     GrillyBuffer maskBuf, lensBuf, q16, k16, v16;
     scope.add(maskBuf); scope.add(lensBuf); scope.add(q16); scope.add(k16); scope.add(v16);
@@ -68,8 +78,7 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
     // (batch, head) slices into chunks and let the upload of chunk c+1, the kernel of chunk c and the
     // download of chunk c-1 run on three queues at once.  Heads are independent, so a chunk is a smaller
     // problem of the same kind.  Dense masks keep the one-shot path below.
-    const size_t slice = size_t(S) * D;                       // elements of one (b, h) slice
-    if (n * 4 >= kPipelineMinBytes && (!mask || opt.maskRank == 2) && size_t(B) * H > 1) {
+    if (pipelined) {
         // Chunk plan, in (b, h) slices.  Every chunk boundary costs the upload queue a bubble (the event
         // between two copies), and the last chunk's kernel and download are not hidden by anything: so
         // few, large chunks first and a short geometric tail (… 32, 32, 16, 8, 4 MiB per tensor).
@@ -115,22 +124,51 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
         check(grl_event_wait(up, start), "flashAttention2: event");
         check(grl_event_wait(down, start), "flashAttention2: event");
         auto at = [](const GrillyBuffer& b, size_t byteOff) { return static_cast<char*>(b.dptr) + byteOff; };
-        size_t s0 = 0;
+        size_t s0 = 0, chunkIndex = 0;
+        grl_event* stagingBusy[2] = {nullptr, nullptr};
         for (size_t chunk : plan) {
             const size_t s1 = s0 + chunk;
             // upload the whole chunk, then launch it piece by piece (one piece unless it crosses a batch row)
             const size_t e0 = s0 * slice, ne = chunk * slice;
-            check(grl_memcpy_h2d(up, at(q32, e0 * 4), Q + e0, ne * 4), "flashAttention2: upload");
-            check(grl_memcpy_h2d(up, at(k32, e0 * 4), K + e0, ne * 4), "flashAttention2: upload");
-            check(grl_memcpy_h2d(up, at(v32, e0 * 4), V + e0, ne * 4), "flashAttention2: upload");
-            grl_event* uploaded = events.make();
-            check(grl_event_record(up, uploaded), "flashAttention2: event");
-            check(grl_event_wait(dev, uploaded), "flashAttention2: event");
             if (bf16) {
-                check(grl_cast(dev, at(q32, e0 * 4), GRL_F32, at(q16, e0 * 2), GRL_BF16, ne), "flashAttention2: cast");
-                check(grl_cast(dev, at(k32, e0 * 4), GRL_F32, at(k16, e0 * 2), GRL_BF16, ne), "flashAttention2: cast");
-                check(grl_cast(dev, at(v32, e0 * 4), GRL_F32, at(v16, e0 * 2), GRL_BF16, ne), "flashAttention2: cast");
+                // Two routes share the chunk so that the host threads and the link finish together: the tail
+                // of the chunk is uploaded as float32 (and cast on the device), the head is rounded to bf16 by
+                // the host threads meanwhile -- half the bytes to upload -- into one of two pinned staging sets
+                // (a set is reused only after the upload that read it has completed).
+                const size_t nHost = chunk * hostPct / 100, eh = nHost * slice;     // slices / elements via the host
+                const float* src[3] = {Q + e0, K + e0, V + e0};
+                const GrillyBuffer* dst32[3] = {&q32, &k32, &v32};
+                const GrillyBuffer* dst16[3] = {&q16, &k16, &v16};
+                if (eh < ne)
+                    for (int x = 0; x < 3; ++x)
+                        check(grl_memcpy_h2d(up, at(*dst32[x], (e0 + eh) * 4), src[x] + eh, (ne - eh) * 4),
+                              "flashAttention2: upload");
+                const int set = int(chunkIndex & 1);
+                if (eh > 0) {
+                    if (stagingBusy[set]) check(grl_event_sync(stagingBusy[set]), "flashAttention2: staging");
+                    for (int x = 0; x < 3; ++x) {
+                        auto* st = static_cast<uint16_t*>(pool.device().pinnedStaging(set * 3 + x, big * slice * 2));
+                        convertF32ToBF16(src[x], st, eh);
+                        check(grl_memcpy_h2d(up, at(*dst16[x], e0 * 2), st, eh * 2), "flashAttention2: upload");
+                    }
+                }
+                stagingBusy[set] = events.make();
+                check(grl_event_record(up, stagingBusy[set]), "flashAttention2: event");
+                check(grl_event_wait(dev, stagingBusy[set]), "flashAttention2: event");
+                if (eh < ne)
+                    for (int x = 0; x < 3; ++x)
+                        check(grl_cast(dev, at(*dst32[x], (e0 + eh) * 4), GRL_F32, at(*dst16[x], (e0 + eh) * 2), GRL_BF16,
+                                       ne - eh),
+                              "flashAttention2: cast");
+            } else {
+                check(grl_memcpy_h2d(up, at(q32, e0 * 4), Q + e0, ne * 4), "flashAttention2: upload");
+                check(grl_memcpy_h2d(up, at(k32, e0 * 4), K + e0, ne * 4), "flashAttention2: upload");
+                check(grl_memcpy_h2d(up, at(v32, e0 * 4), V + e0, ne * 4), "flashAttention2: upload");
+                grl_event* uploaded = events.make();
+                check(grl_event_record(up, uploaded), "flashAttention2: event");
+                check(grl_event_wait(dev, uploaded), "flashAttention2: event");
             }
+            ++chunkIndex;
             for (size_t p0 = s0; p0 < s1;) {
                 const size_t b = p0 / H;
                 const size_t p1 = perBatch ? std::min(s1, (b + 1) * size_t(H)) : s1;

@@ -1,10 +1,17 @@
 // GrillyDevice, BufferPool, PipelineCache, CommandBatch over the CUDA C ABI.
+#include <algorithm>
+#include <cstdint>
 #include <cstdlib>
 #include <cstring>
+
+#if defined(__AVX2__)
+#include <immintrin.h>
+#endif
 
 #include "grilly/buffer_pool.h"
 #include "grilly/command_batch.h"
 #include "grilly/device.h"
+#include "grilly/host_workers.h"
 #include "grilly/pipeline_cache.h"
 
 namespace grilly {
@@ -24,6 +31,8 @@ void GrillyDevice::open(int ordinal) {
 }
 
 GrillyDevice::~GrillyDevice() {
+    for (void* p : staging_)
+        if (p) grl_host_free(p);
     if (up_) grl_device_close(up_);
     if (down_) grl_device_close(down_);
     if (dev_) grl_device_close(dev_);
@@ -37,6 +46,125 @@ grl_device* GrillyDevice::uploadQueue() {
 grl_device* GrillyDevice::downloadQueue() {
     if (!down_) check(grl_device_open(info_.ordinal, &down_), "GrillyDevice: cannot open the download queue");
     return down_;
+}
+
+void* GrillyDevice::pinnedStaging(int slot, size_t bytes) {
+    if (slot < 0 || slot >= kStagingSlots) throw std::runtime_error("GrillyDevice::pinnedStaging: bad slot");
+    if (stagingBytes_[slot] < bytes) {
+        if (staging_[slot]) grl_host_free(staging_[slot]);
+        staging_[slot] = nullptr;
+        stagingBytes_[slot] = 0;
+        check(grl_host_alloc(bytes, &staging_[slot]), "GrillyDevice: pinned staging");
+        stagingBytes_[slot] = bytes;
+    }
+    return staging_[slot];
+}
+
+// ---------------------------------------------------------------- HostWorkers
+HostWorkers& HostWorkers::instance() {
+    static HostWorkers pool;
+    return pool;
+}
+
+HostWorkers::HostWorkers() {
+    int n = int(std::thread::hardware_concurrency());
+    if (n <= 0) n = 4;
+    if (n > 32) n = 32;
+    if (const char* e = std::getenv("GRILLY_HOST_THREADS")) n = std::max(1, std::atoi(e));
+    for (int i = 1; i < n; ++i) workers_.emplace_back([this, i] { loop(i); });
+}
+
+HostWorkers::~HostWorkers() {
+    {
+        std::lock_guard<std::mutex> lock(mu_);
+        stop_ = true;
+    }
+    start_.notify_all();
+    for (auto& t : workers_) t.join();
+}
+
+void HostWorkers::loop(int id) {
+    uint64_t seen = 0;
+    for (;;) {
+        const std::function<void(int, int)>* job;
+        {
+            std::unique_lock<std::mutex> lock(mu_);
+            start_.wait(lock, [&] { return stop_ || generation_ != seen; });
+            if (stop_) return;
+            seen = generation_;
+            job = job_;
+        }
+        (*job)(id, threads());
+        {
+            std::lock_guard<std::mutex> lock(mu_);
+            if (--pending_ == 0) done_.notify_one();
+        }
+    }
+}
+
+void HostWorkers::parallel(const std::function<void(int, int)>& fn) {
+    {
+        std::lock_guard<std::mutex> lock(mu_);
+        job_ = &fn;
+        pending_ = int(workers_.size());
+        ++generation_;
+    }
+    start_.notify_all();
+    fn(0, threads());
+    std::unique_lock<std::mutex> lock(mu_);
+    done_.wait(lock, [&] { return pending_ == 0; });
+}
+
+void convertF32ToBF16(const float* src, uint16_t* dst, size_t n) {
+    auto scalar = [src, dst](size_t i0, size_t i1) {
+        const uint32_t* s = reinterpret_cast<const uint32_t*>(src);
+        for (size_t i = i0; i < i1; ++i) {
+            const uint32_t u = s[i];
+            const uint32_t rounded = (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+            dst[i] = uint16_t((u & 0x7fffffffu) > 0x7f800000u ? 0x7fffu : rounded);
+        }
+    };
+    auto range = [&](size_t i0, size_t i1) {
+#if defined(__AVX2__)
+        // 16 values per step; results leave with streaming stores (the destination is staging memory that
+        // only the copy engine reads next, so it should not displace the source in the caches).
+        size_t i = i0;
+        while (i < i1 && (reinterpret_cast<uintptr_t>(dst + i) & 31u)) ++i;
+        scalar(i0, i);
+        const __m256i bias = _mm256_set1_epi32(0x7fff), one = _mm256_set1_epi32(1);
+        const __m256i absmask = _mm256_set1_epi32(0x7fffffff), inf = _mm256_set1_epi32(0x7f800000);
+        const __m256i qnan = _mm256_set1_epi32(0x7fff);
+        for (; i + 16 <= i1; i += 16) {
+            __m256i a = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(src + i));
+            __m256i b = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(src + i + 8));
+            auto round = [&](__m256i u) {
+                const __m256i lsb = _mm256_and_si256(_mm256_srli_epi32(u, 16), one);
+                const __m256i r = _mm256_srli_epi32(_mm256_add_epi32(_mm256_add_epi32(u, bias), lsb), 16);
+                const __m256i isnan = _mm256_cmpgt_epi32(_mm256_and_si256(u, absmask), inf);
+                return _mm256_blendv_epi8(r, qnan, isnan);
+            };
+            a = round(a);
+            b = round(b);
+            __m256i p = _mm256_packus_epi32(a, b);                  // lanes: a0-3 b0-3 | a4-7 b4-7
+            p = _mm256_permute4x64_epi64(p, 0xD8);                  // a0-3 a4-7 b0-3 b4-7
+            _mm256_stream_si256(reinterpret_cast<__m256i*>(dst + i), p);
+        }
+        _mm_sfence();
+        scalar(i, i1);
+#else
+        scalar(i0, i1);
+#endif
+    };
+    if (n < (1u << 16)) {
+        range(0, n);
+        return;
+    }
+    HostWorkers::instance().parallel([&](int part, int parts) {
+        size_t per = (n + size_t(parts) - 1) / size_t(parts);
+        per = (per + 63) / 64 * 64;
+        const size_t i0 = std::min(n, per * size_t(part)), i1 = std::min(n, i0 + per);
+        range(i0, i1);
+    });
 }
 
 // ---------------------------------------------------------------- BufferPool

@@ -322,6 +322,12 @@ int grl_event_wait(grl_device* dev, grl_event* ev) {
     return GRL_OK;
 }
 
+int grl_event_sync(grl_event* ev) {
+    GRL_REQUIRE(ev, "ev is NULL");
+    GRL_CUDA(cudaEventSynchronize(ev->ev));
+    return GRL_OK;
+}
+
 int grl_event_elapsed_ms(grl_event* start, grl_event* stop, float* ms) {
     GRL_REQUIRE(start && stop && ms, "NULL argument");
     GRL_CUDA(cudaEventSynchronize(stop->ev));

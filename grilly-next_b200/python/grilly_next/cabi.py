@@ -20,7 +20,7 @@ SYMBOLS = [
     "grl_last_error", "grl_device_count", "grl_device_open", "grl_device_close", "grl_device_get_info",
     "grl_device_use_stream", "grl_malloc", "grl_free", "grl_host_alloc", "grl_host_free", "grl_memcpy_h2d",
     "grl_memcpy_d2h", "grl_memcpy_d2d", "grl_memset", "grl_sync", "grl_event_create", "grl_event_create_untimed", "grl_event_destroy",
-    "grl_event_record", "grl_event_wait", "grl_event_elapsed_ms", "grl_graph_begin", "grl_graph_end", "grl_graph_launch",
+    "grl_event_record", "grl_event_wait", "grl_event_sync", "grl_event_elapsed_ms", "grl_graph_begin", "grl_graph_end", "grl_graph_launch",
     "grl_graph_destroy", "grl_launch_count", "grl_cast", "grl_flash_fwd", "grl_rope", "grl_attention_mask",
     "grl_kv_append", "grl_kv_gather", "grl_swizzle_kv", "grl_kv_score_accumulate", "grl_kv_mass_accumulate", "grl_kv_evict_lowest", "grl_kv_evict_heuristic",
     "grl_kv_compact_scratch_bytes", "grl_kv_compact", "grl_evict_head_scratch_bytes", "grl_evict_head_train",

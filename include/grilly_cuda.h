@@ -89,6 +89,7 @@ int grl_event_record(grl_device* dev, grl_event* ev);
  * GPU) has completed; the host does not wait.  Several handles opened on one GPU are several streams:
  * this is how an upload, a kernel and a download of different chunks overlap. */
 int grl_event_wait(grl_device* dev, grl_event* ev);
+int grl_event_sync(grl_event* ev); /* the host waits until the event has completed */
 int grl_event_elapsed_ms(grl_event* start, grl_event* stop, float* ms); /* syncs on stop */
 
 /* Stream capture of a launch sequence (the 256-step decode loop); replaces the record-once /

@@ -86,3 +86,18 @@ def test_no_device_means_a_loud_error_not_a_fallback():
     h = C.c_void_p()
     assert L.grl_device_open(0, C.byref(h)) != 0
     assert len(L.grl_last_error()) > 0
+
+
+def test_host_bf16_rounding_matches_oracle():
+    # the chunked upload path rounds on the host threads; it must give the bits the device cast gives
+    import grilly_core
+    from oracle import attention_oracle as orc
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal(300_001, dtype=np.float32) * np.float32(10.0) ** rng.integers(-30, 30, 300_001).astype(np.float32)
+    special = np.array([0.0, -0.0, np.inf, -np.inf, 1.0, 1.00390625, 1.01171875, 3.3895314e38, 1e-40, -1e-45],
+                       np.float32)                      # ties to even both ways, overflow to inf, denormals
+    x[: len(special)] = special
+    got = grilly_core._host_round_bf16(x)
+    assert got.dtype == np.uint16 and np.array_equal(got, orc.to_bf16_bits(x))
+    assert grilly_core._host_round_bf16(np.array([np.nan], np.float32))[0] == 0x7FFF
+    assert np.array_equal(grilly_core._host_round_bf16(x[:100]), orc.to_bf16_bits(x[:100]))   # single-thread path
