@@ -70,6 +70,8 @@ HostWorkers::HostWorkers() {
     int n = int(std::thread::hardware_concurrency());
     if (n <= 0) n = 4;
     if (n > 32) n = 32;
+    // one process per GPU: the processes of a node share the host's cores
+    if (const char* e = std::getenv("LOCAL_WORLD_SIZE")) n = std::max(1, n / std::max(1, std::atoi(e)));
     if (const char* e = std::getenv("GRILLY_HOST_THREADS")) n = std::max(1, std::atoi(e));
     for (int i = 1; i < n; ++i) workers_.emplace_back([this, i] { loop(i); });
 }
