@@ -432,8 +432,8 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3, n_splits=0):
     mode = os.environ.get("GRILLY_EXCHANGE", "decode")     # profiling aid: "nccl" | "merge" | "decode"
     if world > 1 and mode != "nccl":
         # peers' inboxes over CUDA IPC; NCCL all-gather is the fallback
-        if ops.setup_p2p(td, one_launch=(mode == "decode")):
-            fused = "decode" if ops.one_launch else "merge"
+        if ops.setup_p2p(td, one_launch=(mode == "decode"), low_latency=(mode != "merge")):
+            fused = "decode" if ops.one_launch else ("ll" if mode == "ll" else "merge")
     dec = ShardedDecoder(td if world > 1 else _NoDist(), ops, lambda n, m: torch.empty((n, m), dtype=torch.float32, device="cuda"))
     layouts = [layout(i) for i in range(nbuf)]
     for i in range(5):
@@ -478,7 +478,7 @@ def bench_long_decode(dev, cabi, dist, steps=50, repeats=3, n_splits=0):
         best = ms if best is None else min(best, ms)
     # this library's launches per step: the decode kernel merges its own splits; NCCL mode adds the final merge
     # (the all-gather is NCCL's kernel), "merge" mode the step-counter bump and the exchange+merge kernel
-    launches = {"": 1 if world == 1 else 2, "merge": 3, "decode": 1}[fused]
+    launches = {"": 1 if world == 1 else 2, "merge": 3, "ll": 3, "decode": 1}[fused]
     assert bool(torch.isfinite(out).all())
     cabi.check(L.grl_device_use_stream(dev.h, None))
     return best / steps, launches, ops.p.n_splits, nbuf, graph is not None, fused
@@ -609,6 +609,7 @@ def main():
                                            f"per-GPU partial (16,640 B/rank) + "
                                            + {"decode": "exchange over NVLink peer stores and LSE merge inside the decode kernel (one launch per step)",
                                               "merge": "exchange over NVLink peer stores fused with the LSE merge",
+                                              "ll": "exchange over NVLink peer stores ({value, step} pairs, no flag) fused with the LSE merge",
                                               "": "NCCL all-gather + LSE merge" if world > 1 else "LSE merge"}[fused]
                                            + f"; {nbuf} rotating KV buffers (L2); "
                                            + ("CUDA-graph replay" if graphed else "plain launches"),

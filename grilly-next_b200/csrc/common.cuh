@@ -56,6 +56,28 @@ struct PeerExchange {
     int rank, world, flag_slots;
 };
 int fill_peer_exchange(const grl_exchange_params* p, PeerExchange* x);
+
+#ifdef __CUDACC__
+// Low-latency inbox element: {value bits, step number} in one 8-byte word.  take3 reads three elements
+// of one peer with the loads in flight together and repeats until all three carry step `e` (or the cycle
+// limit passes: returns false).
+__device__ __forceinline__ uint2 ld_pair_volatile(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ bool take3(const uint2* a, const uint2* b, const uint2* c, unsigned int e, long long t0,
+                                      float* va, float* vb, float* vc) {
+    for (;;) {
+        const uint2 x = ld_pair_volatile(a), y = ld_pair_volatile(b), z = ld_pair_volatile(c);
+        if (x.y == e && y.y == e && z.y == e) {
+            *va = __uint_as_float(x.x); *vb = __uint_as_float(y.x); *vc = __uint_as_float(z.x);
+            return true;
+        }
+        if (clock64() - t0 > kPeerWaitLimitCycles) return false;
+    }
+}
+#endif
 extern std::atomic<long long> g_launches;
 
 #define GRL_CUDA(call)                                                                       \

@@ -397,9 +397,13 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         for (; s < a.n_splits; ++s) ov = fmaf(sm_w[h * kMaxFusedSplits + s], __ldcg(col + (size_t)s * pstride), ov);
         const float lt = sm_mt[8 + h];
         if (exchange) {
+            // every 8-byte inbox element carries the step number next to the value: a reader that sees the
+            // number sees the value, so there is neither a fence nor a flag between the peers
             sm_res[idx] = ov;
             for (int r = 0; r < x.world; ++r)
-                if (r != x.rank) x.peer_inbox[r][((size_t)par * x.world + x.rank) * pstride + (size_t)(row0 + h) * D + d] = ov;
+                if (r != x.rank)
+                    reinterpret_cast<uint2*>(x.peer_inbox[r])[((size_t)par * x.world + x.rank) * pstride +
+                                                              (size_t)(row0 + h) * D + d] = make_uint2(__float_as_uint(ov), e);
         } else if (a.partial_out) {
             a.partial_out[(size_t)(row0 + h) * D + d] = ov;
         } else {
@@ -414,67 +418,51 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         return;
     }
 
-    // ---- cross-GPU exchange of this head's rows: plain stores into the peers' inboxes, then a flag
+    // ---- cross-GPU exchange of this head's rows: the O rows have gone out above, now m and l
     if (tid < a.group) {
         for (int r = 0; r < x.world; ++r) {
             if (r == x.rank) continue;
-            float* dst = x.peer_inbox[r] + ((size_t)par * x.world + x.rank) * pstride + (size_t)rows * D;
-            dst[row0 + tid] = sm_mt[tid];
-            dst[rows + row0 + tid] = sm_mt[8 + tid];
+            uint2* dst = reinterpret_cast<uint2*>(x.peer_inbox[r]) + ((size_t)par * x.world + x.rank) * pstride + (size_t)rows * D;
+            dst[row0 + tid] = make_uint2(__float_as_uint(sm_mt[tid]), e);
+            dst[rows + row0 + tid] = make_uint2(__float_as_uint(sm_mt[8 + tid]), e);
         }
     }
-    __threadfence_system();
-    __syncthreads();
-    if (tid < x.world && tid != x.rank) {
-        __threadfence_system();
-        volatile unsigned int* f = x.peer_flags[tid] + (size_t)(par * x.world + x.rank) * x.flag_slots + slot;
-        *f = e;
-    }
-    if (tid == 0) {
-        int ok = 1;
-        const long long t0 = clock64();
-        for (int r = 0; r < x.world && ok; ++r) {
-            if (r == x.rank) continue;
-            volatile unsigned int* f = x.flags + (size_t)(par * x.world + r) * x.flag_slots + slot;
-            while (*f != e) {
-                if (clock64() - t0 > kPeerWaitLimitCycles) {
-                    ok = 0;
-                    if (a.status && atomicCAS(a.status, 0, GRL_ERR_TIMEOUT) == 0) {
-                        a.status[1] = 0x200 | r;
-                        a.status[2] = (int)e;
-                        a.status[3] = x.rank;
-                    }
-                    break;
+    __syncthreads();                    // sm_res complete
+    const long long t0 = clock64();
+    bool ok = true;
+    for (int idx = tid; idx < a.group * D; idx += kThreads) {
+        const int h = idx / D, d = idx % D;
+        float mr[kMaxPeers], lr[kMaxPeers], orow[kMaxPeers];
+        float mt = sm_mt[h];
+#pragma unroll 1
+        for (int r = 0; r < x.world; ++r) {
+            if (r == x.rank) { mr[r] = sm_mt[h]; lr[r] = sm_mt[8 + h]; orow[r] = sm_res[idx]; continue; }
+            const uint2* in = reinterpret_cast<const uint2*>(x.inbox) + ((size_t)par * x.world + r) * pstride;
+            if (!take3(in + (size_t)rows * D + row0 + h, in + (size_t)rows * D + rows + row0 + h,
+                       in + (size_t)(row0 + h) * D + d, e, t0, &mr[r], &lr[r], &orow[r])) {
+                ok = false;
+                mr[r] = kEmpty; lr[r] = 0.f; orow[r] = 0.f;
+                if (a.status && atomicCAS(a.status, 0, GRL_ERR_TIMEOUT) == 0) {
+                    a.status[1] = 0x200 | r;
+                    a.status[2] = (int)e;
+                    a.status[3] = x.rank;
                 }
             }
+            mt = fmaxf(mt, mr[r]);
         }
-        __threadfence_system();
-        *s_flag = ok;
+        float ov = 0.f, lt = 0.f;
+#pragma unroll 1
+        for (int r = 0; r < x.world; ++r) {
+            const float w = __expf(mr[r] - mt);
+            ov = fmaf(w, orow[r], ov);
+            lt = fmaf(w, lr[r], lt);
+        }
+        if (ok) a.out[(size_t)(row0 + h) * D + d] = lt > 0.f ? ov / lt : 0.f;
     }
+    // the head that finishes last advances the step counter for the next launch (every head has read it by
+    // then); after a timeout the counter stays and grl_sync reports the failure
     __syncthreads();
-    if (*s_flag) {
-        for (int idx = tid; idx < a.group * D; idx += kThreads) {
-            const int h = idx / D, d = idx % D;
-            auto m_of = [&](int r) {
-                return r == x.rank ? sm_mt[h]
-                                   : __ldcv(x.inbox + ((size_t)par * x.world + r) * pstride + (size_t)rows * D + row0 + h);
-            };
-            float mt = sm_mt[h];
-            for (int r = 0; r < x.world; ++r) mt = fmaxf(mt, m_of(r));
-            float ov = 0.f, lt = 0.f;
-            for (int r = 0; r < x.world; ++r) {
-                const float w = __expf(m_of(r) - mt);
-                const float* in = x.inbox + ((size_t)par * x.world + r) * pstride;
-                const float orow = r == x.rank ? sm_res[idx] : __ldcv(in + (size_t)(row0 + h) * D + d);
-                const float lrow = r == x.rank ? sm_mt[8 + h] : __ldcv(in + (size_t)rows * D + rows + row0 + h);
-                ov = fmaf(w, orow, ov);
-                lt = fmaf(w, lrow, lt);
-            }
-            a.out[(size_t)(row0 + h) * D + d] = lt > 0.f ? ov / lt : 0.f;
-        }
-    }
-    // the head that finishes last advances the step counter for the next launch (every head has read it by then)
-    if (tid == 0 && *s_flag) {
+    if (tid == 0 && ok) {
         const int heads = a.B * a.Hkv;
         if (atomicAdd(&a.counters[kDoneSlot], 1) == heads - 1) {
             a.counters[kDoneSlot] = 0;
@@ -543,7 +531,8 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
         GRL_REQUIRE(heads <= dev->prop.multiProcessorCount,
                     "fused cross-GPU merge: B*Hkv = %d exceeds the %d SMs (waiting CTAs must leave room for the rest)",
                     heads, dev->prop.multiProcessorCount);
-        GRL_REQUIRE(a.x.flag_slots >= heads, "fused cross-GPU merge: flag_slots %d < B*Hkv %d", a.x.flag_slots, heads);
+        GRL_REQUIRE(p->exchange->low_latency, "the exchange inside the decode kernel uses the low-latency inbox "
+                                              "format ({value, step} pairs): set low_latency");
         GRL_REQUIRE(p->out, "out is NULL");
     }
     dev->status_dirty = true;

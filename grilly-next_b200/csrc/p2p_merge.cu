@@ -106,6 +106,60 @@ __global__ void __launch_bounds__(128) exchange_merge_kernel(ExchangeArgs a) {
     }
 }
 
+// Low-latency form: every 8-byte inbox element carries its own step number, {value bits, step}.  An
+// 8-byte store is one transaction, so a reader that sees the step also sees the value: no fence, no
+// separate flag, one NVLink crossing instead of store + acknowledge + flag.  grid = rows CTAs; the CTA of
+// a row stores that row (D values, m, l) to every peer, then polls the peers' copies of the same row.
+// inbox: uint2 [2][world][n]; zero before the first step (step numbers start at 1).
+__global__ void __launch_bounds__(128) exchange_merge_ll_kernel(ExchangeArgs a) {
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const PeerExchange& x = a.x;
+    const unsigned int e = *x.seq;
+    const int par = e & 1;
+    const size_t n = (size_t)a.rows * (a.D + 2);
+    const size_t off_m = (size_t)a.rows * a.D + row, off_l = off_m + a.rows;
+    const float my_m = a.local_part[off_m], my_l = a.local_part[off_l];
+    for (int r = 0; r < x.world; ++r) {
+        if (r == x.rank) continue;
+        uint2* dst = reinterpret_cast<uint2*>(x.peer_inbox[r]) + ((size_t)par * x.world + x.rank) * n;
+        for (int d = tid; d < a.D; d += 128)
+            dst[(size_t)row * a.D + d] = make_uint2(__float_as_uint(a.local_part[(size_t)row * a.D + d]), e);
+        if (tid == 0) {
+            dst[off_m] = make_uint2(__float_as_uint(my_m), e);
+            dst[off_l] = make_uint2(__float_as_uint(my_l), e);
+        }
+    }
+    const long long t0 = clock64();
+    for (int d = tid; d < a.D; d += 128) {
+        float mr[kMaxPeers], lr[kMaxPeers], orow[kMaxPeers];
+        float mt = my_m;
+        bool ok = true;
+#pragma unroll 1
+        for (int r = 0; r < x.world; ++r) {
+            if (r == x.rank) { mr[r] = my_m; lr[r] = my_l; orow[r] = a.local_part[(size_t)row * a.D + d]; continue; }
+            const uint2* in = reinterpret_cast<const uint2*>(x.inbox) + ((size_t)par * x.world + r) * n;
+            if (!take3(in + off_m, in + off_l, in + (size_t)row * a.D + d, e, t0, &mr[r], &lr[r], &orow[r])) {
+                ok = false;
+                mr[r] = -1e30f; lr[r] = 0.f; orow[r] = 0.f;
+                if (a.status && atomicCAS(a.status, 0, GRL_ERR_TIMEOUT) == 0) {
+                    a.status[1] = 0x300 | r;
+                    a.status[2] = (int)e;
+                    a.status[3] = x.rank;
+                }
+            }
+            mt = fmaxf(mt, mr[r]);
+        }
+        float o = 0.f, lt = 0.f;
+#pragma unroll 1
+        for (int r = 0; r < x.world; ++r) {
+            const float w = __expf(mr[r] - mt);
+            o = fmaf(w, orow[r], o);
+            lt = fmaf(w, lr[r], lt);
+        }
+        if (ok) a.out[(size_t)row * a.D + d] = lt > 0.f ? o / lt : 0.f;
+    }
+}
+
 }  // namespace grl
 
 using namespace grl;
@@ -152,6 +206,11 @@ int grl_exchange_merge(grl_device* dev, const grl_exchange_params* p) {
     dev->status_dirty = true;
     bump_seq_kernel<<<1, 1, 0, dev->stream>>>(p->seq);
     GRL_LAUNCHED("bump_seq_kernel");
+    if (p->low_latency) {
+        exchange_merge_ll_kernel<<<p->rows, 128, 0, dev->stream>>>(a);
+        GRL_LAUNCHED("exchange_merge_ll_kernel");
+        return GRL_OK;
+    }
     const int ctas = p->rows > p->world ? p->rows : p->world;
     exchange_merge_kernel<<<ctas, 128, 0, dev->stream>>>(a);
     GRL_LAUNCHED("exchange_merge_kernel");

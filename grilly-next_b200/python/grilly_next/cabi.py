@@ -70,7 +70,7 @@ class ExchangeParams(C.Structure):
                 ("peer_inbox", C.POINTER(C.c_void_p)), ("peer_flags", C.POINTER(C.c_void_p)),
                 ("seq", C.c_void_p), ("out", C.c_void_p),
                 ("rank", C.c_int32), ("world", C.c_int32), ("rows", C.c_int32), ("head_dim", C.c_int32),
-                ("flag_slots", C.c_int32)]
+                ("flag_slots", C.c_int32), ("low_latency", C.c_int32)]
 
 
 class DecodeParams(C.Structure):

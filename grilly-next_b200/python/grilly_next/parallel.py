@@ -94,18 +94,19 @@ class CudaShardOps:
         self.part = torch.empty(partial_floats(self.rows, self.D), dtype=torch.float32, device="cuda")
         self.out = torch.empty((self.B, 1, self.Hq, self.D), dtype=torch.float32, device="cuda")
 
-    def setup_p2p(self, dist, one_launch=True):
+    def setup_p2p(self, dist, one_launch=True, low_latency=True):
         """Map every peer's inbox into this process (CUDA IPC) for the fused exchange + merge kernel.
         Collective: every rank calls it once.  Falls back silently (p2p_ready stays False) if the
         handles cannot be opened, e.g. without peer access between the GPUs."""
         cabi, dev, L = self.cabi, self.dev, self.dev.L
         world, rank = dist.get_world_size(), dist.get_rank()
         n = partial_floats(self.rows, self.D)
-        self._inbox = dev.malloc(2 * world * n * 4)
+        inbox_bytes = 2 * world * n * (8 if low_latency else 4)   # low latency: {value, step} pairs
+        self._inbox = dev.malloc(inbox_bytes)
         slots = self.B * self.p.kv.num_kv_heads          # one flag per (sequence, kv head): heads cross as they finish
         self._flags = dev.malloc(2 * world * slots * 4 + 64)
         self._seq = dev.malloc(64)
-        for p_, nb in ((self._inbox, 2 * world * n * 4), (self._flags, 2 * world * slots * 4 + 64), (self._seq, 64)):
+        for p_, nb in ((self._inbox, inbox_bytes), (self._flags, 2 * world * slots * 4 + 64), (self._seq, 64)):
             cabi.check(L.grl_memset(dev.h, p_, 0, nb))
         dev.sync()
         hi, hf = (C.c_char * 64)(), (C.c_char * 64)()
@@ -135,9 +136,10 @@ class CudaShardOps:
         e.peer_flags = C.cast(self._peer_flags, C.POINTER(C.c_void_p))
         e.seq, e.out = self._seq, self.out.data_ptr()
         e.rank, e.world, e.rows, e.head_dim, e.flag_slots = rank, world, self.rows, self.D, slots
+        e.low_latency = int(low_latency)
         self._exchange = e
         # the decode kernel itself can do the exchange for the tensor-core geometry with few enough heads
-        self.one_launch = bool(one_launch and self.p.kv.cache_dtype == cabi.BF16 and self.D == 128
+        self.one_launch = bool(one_launch and low_latency and self.p.kv.cache_dtype == cabi.BF16 and self.D == 128
                                and self.p.kv.page_tokens == 64 and slots <= 128)
         return self.p2p_ready
 

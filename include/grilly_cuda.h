@@ -308,7 +308,7 @@ int grl_lse_merge(grl_device* dev, const float* parts, int n_parts, size_t part_
  * same sequence of calls.
  * With flag_slots = S the flags are uint32[2][world][S]; grl_exchange_merge uses slot 0.
  * grl_decode_params.exchange (tensor-core geometry only: bf16 cache, head_dim 128, 64-token pages,
- * B*Hkv <= the SM count, S >= B*Hkv) goes one step further: the CTA that finishes a (sequence, kv
+ * B*Hkv <= the SM count, low_latency inbox format) goes one step further: the CTA that finishes a (sequence, kv
  * head) last merges its splits, stores the head's rows into the peers' inboxes, waits for theirs and
  * writes the final rows -- decode, exchange and merge are ONE launch per step; local_partial, out,
  * rows and head_dim of the exchange struct are then ignored. */
@@ -322,6 +322,9 @@ typedef struct grl_exchange_params_s {
     float* out;
     int32_t rank, world, rows, head_dim;
     int32_t flag_slots;     /* flags per (parity, peer); 0 is read as 1 */
+    int32_t low_latency;    /* != 0 => every inbox element is 8 bytes {value, step number}
+                             * (inbox: uint2[2][world][n], twice the bytes, zero before the first step); the flags
+                             * are not used and no fence separates data from flag: one NVLink crossing per step */
 } grl_exchange_params;
 int grl_ipc_export(grl_device* dev, void* ptr, void* handle_out_64_bytes);
 int grl_ipc_import(grl_device* dev, const void* handle_64_bytes, void** ptr_out);

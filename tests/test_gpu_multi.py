@@ -60,6 +60,15 @@ def _worker(rank, world, port, result_dir):
         out = dec.step(torch.from_numpy(q).cuda()).cpu().numpy()
         want = orc.gqa_decode_attention(q, orc.round_bf16(k), orc.round_bf16(v), Hq, Hkv, D)
         errs.append(float(np.abs(out - want).max()))
+    # the flag-and-fence form of the exchange kernel (the default above is the {value, step} pair form)
+    ops2 = CudaShardOps(cabi, dev, pc.layout(), Hq, hi - lo, torch)
+    assert ops2.setup_p2p(dist, one_launch=False, low_latency=False) == fused
+    dec2 = ShardedDecoder(dist, ops2, lambda n, m: torch.empty((n, m), dtype=torch.float32, device="cuda"))
+    for step in range(5):
+        q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
+        out = dec2.step(torch.from_numpy(q).cuda()).cpu().numpy()
+        want = orc.gqa_decode_attention(q, orc.round_bf16(k), orc.round_bf16(v), Hq, Hkv, D)
+        errs.append(float(np.abs(out - want).max()))
     dev.sync()
     np.save(os.path.join(result_dir, f"res{rank}.npy"), np.array(errs + [1.0 if fused else 0.0]))
     dist.barrier()
