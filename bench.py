@@ -242,7 +242,12 @@ def bench_prefill_e2e(args, L, steps, dist):
     for pp in ptrs:
         L.grl_host_free(pp)
     nbytes = int(np.prod(shape)) * 4
-    return dt, 3 * nbytes, nbytes
+    # what crosses the link: the op's host threads round a share of every chunk to bf16 before the upload
+    # (all of it with one process per node, 50 %/N with N), the rest goes up as float32
+    lws = int(os.environ.get("LOCAL_WORLD_SIZE", "1"))
+    pct = int(os.environ.get("GRILLY_PIPELINE_HOST_CAST_PCT", 100 if lws <= 1 else 50 // lws))
+    h2d = 3 * (nbytes // 2 * pct + nbytes * (100 - pct)) // 100
+    return dt, h2d, nbytes
 
 
 def bench_decode(dev, cabi, dist, repeats=3, use_graph=True, force_splits=0):
@@ -606,11 +611,11 @@ def main():
         line["decode_long"] = {"metric": "decode_long_tokens_per_s", "value": 1.0 / (lms * 1e-3), "unit": "tokens/s",
                                "ms_per_step": lms, "scaling": "strong",
                                "workload": f"cfg4: GQA decode B1 Hq32/Hkv8 D128 KV 131072 bf16 split over {world} GPU(s); "
-                                           f"per-GPU partial (16,640 B/rank) + "
+                                           + ("18 splits merged inside the decode kernel" if world == 1 else "per-GPU partial (16,640 B/rank) + ")
                                            + {"decode": "exchange over NVLink peer stores and LSE merge inside the decode kernel (one launch per step)",
                                               "merge": "exchange over NVLink peer stores fused with the LSE merge",
                                               "ll": "exchange over NVLink peer stores ({value, step} pairs, no flag) fused with the LSE merge",
-                                              "": "NCCL all-gather + LSE merge" if world > 1 else "LSE merge"}[fused]
+                                              "": "NCCL all-gather + LSE merge" if world > 1 else ""}[fused]
                                            + f"; {nbuf} rotating KV buffers (L2); "
                                            + ("CUDA-graph replay" if graphed else "plain launches"),
                                "gpu_launches_per_step": int(ll), "n_splits": lsplit,
@@ -620,7 +625,8 @@ def main():
         os.environ["GRILLY_GPU_INDEX"] = str(local_rank)     # the op layer's device selector
         dt, h2d, d2h = bench_prefill_e2e(args, L, min(args.steps, 5), dist)
         line["e2e"] = {"value": fl / dt / 1e12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                       "ms_per_step": dt * 1e3, "api": "grilly_core.flash_attention2(dtype='bf16', out=pinned), pinned fp32 host arrays in and out"}
+                       "ms_per_step": dt * 1e3, "api": "grilly_core.flash_attention2(dtype='bf16', out=pinned), pinned fp32 host arrays in and out; "
+                              "h2d bytes are what crosses the link (the op rounds inputs to bf16 on host threads; 402,653,184 B of fp32 are read)"}
         if not args.skip_decode:
             ddt, dh2d, dd2h = bench_decode_e2e(dist)
             line["decode"]["e2e"] = {"value": CFG3["B"] / ddt * world, "unit": "tokens/s", "h2d_bytes_per_step": dh2d,
