@@ -352,6 +352,59 @@ def bench_decode(dev, cabi, dist, repeats=3, use_graph=True, force_splits=0):
     return best, launches_per_run, ns.value
 
 
+def bench_evict(dev, cabi, repeats=3):
+    """Eviction on a cfg3-sized cache (B32, Hkv8, D128, 4096 tokens, bf16): H2O selection of a quarter of every
+    sequence, then compaction.  Returns (select_us, compact_us, bytes moved by one compaction)."""
+    from oracle import attention_oracle as orc
+    c = CFG3
+    B, Hkv, D, T, P = c["B"], c["Hkv"], c["D"], c["T0"], c["page"]
+    L = dev.L
+    rng = np.random.default_rng(7)
+    max_pages = T // P
+    n_pages, page_elems = max_pages * B, Hkv * P * D
+    kp, vp = dev.malloc(n_pages * page_elems * 2), dev.malloc(n_pages * page_elems * 2)
+    for p_ in (kp, vp):
+        cabi.check(L.grl_memset(dev.h, p_, 0x3c, n_pages * page_elems * 2))
+    table = dev.upload(np.arange(n_pages, dtype=np.int32).reshape(B, max_pages))
+    lens_host = np.full(B, T, np.int32)
+    seq_lens = dev.upload(lens_host)
+    lay = cabi.KVLayout()
+    lay.k_pages, lay.v_pages, lay.cache_dtype = kp, vp, cabi.BF16
+    lay.block_table, lay.seq_lens = table, seq_lens
+    lay.batch, lay.num_kv_heads, lay.head_dim, lay.page_tokens, lay.max_pages, lay.num_pages = B, Hkv, D, P, max_pages, n_pages
+    cap = max_pages * P
+    scores = rng.random((B, cap), dtype=np.float32)
+    cum, tomb, evicted = dev.malloc(B * cap * 4), dev.malloc(B * cap), dev.malloc(B * 4)
+    m = cabi.KVMeta()
+    m.cum_score, m.tombstone, m.relevance, m.evicted, m.capacity = cum, tomb, None, evicted, cap
+    nb = C.c_size_t()
+    cabi.check(L.grl_kv_compact_scratch_bytes(C.byref(lay), C.byref(m), C.byref(nb)))
+    scratch = dev.malloc(nb.value)
+    e0, e1, e2 = dev.event(), dev.event(), dev.event()
+    best_sel = best_cmp = None
+    for _ in range(repeats + 1):
+        cabi.check(L.grl_memcpy_h2d(dev.h, seq_lens, lens_host.ctypes.data_as(C.c_void_p), lens_host.nbytes))
+        cabi.check(L.grl_memcpy_h2d(dev.h, cum, scores.ctypes.data_as(C.c_void_p), scores.nbytes))
+        cabi.check(L.grl_memset(dev.h, tomb, 0, B * cap))
+        cabi.check(L.grl_memset(dev.h, evicted, 0, B * 4))
+        dev.sync()
+        dev.record(e0)
+        cabi.check(L.grl_kv_evict_lowest(dev.h, C.byref(lay), C.byref(m), T // 4))
+        dev.record(e1)
+        cabi.check(L.grl_kv_compact(dev.h, C.byref(lay), C.byref(m), scratch, nb.value))
+        dev.record(e2)
+        dev.sync()
+        sel, cmp_ = dev.elapsed_ms(e0, e1) * 1e3, dev.elapsed_ms(e1, e2) * 1e3
+        best_sel = sel if best_sel is None else min(best_sel, sel)
+        best_cmp = cmp_ if best_cmp is None else min(best_cmp, cmp_)
+    left = dev.download(seq_lens, (B,), np.int32)
+    assert (left == T - T // 4).all(), left
+    moved = 2 * 2 * B * (T - T // 4) * Hkv * D * 2          # K and V, survivors read and written, bf16
+    for x in (kp, vp, table, seq_lens, cum, tomb, evicted, scratch):
+        dev.free(x)
+    return best_sel, best_cmp, moved
+
+
 def bench_decode_e2e(dist, steps=32):
     """grilly_core.decode_step with host arrays per step (upload q/k/v, append, attend, download)."""
     import grilly_core
@@ -604,6 +657,13 @@ def main():
                                        "note": "achieved = algorithmic bytes of the 256-step run / its time (append + decode + merge per step)",
                                        "kernel": "decode_mma_kernel"}}
 
+    if not args.skip_decode and world == 1:
+        sel_us, cmp_us, moved = bench_evict(dev, cabi)
+        gbs = moved / (cmp_us * 1e-6) / 1e9
+        line["evict"] = {"workload": "cfg3-sized cache (B32 Hkv8 D128 4096 tokens bf16): H2O selection of a quarter of every sequence, "
+                                     "then compaction", "select_us": sel_us, "compact_us": cmp_us,
+                         "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
+                                      "peak_source": pk["src"], "note": "surviving K/V rows read once and written once; rows that stay in place are skipped, so this is an upper bound on the traffic"}}
     if not args.skip_decode and not args.skip_long:
         lms, ll, lsplit, nbuf, graphed, fused = bench_long_decode(dev, cabi, dist)
         kv_bytes = 2 * CFG4["Hkv"] * CFG4["D"] * 2 * CFG4["T"]

@@ -195,44 +195,60 @@ struct MoveArgs {
     int Hkv, P, max_pages, capacity, row_bytes;
 };
 
-// One CTA per (kv head, sequence, K|V) walks the sequence in tiles of 64 tokens: load the live rows of
-// the tile, barrier, store them at their new positions, barrier.  new_pos[t] <= t and order is kept, so
-// a tile never overwrites a row that a later tile still has to read -- the in-order loop of
-// kv_cache.cpp:957-989, one head at a time.
-constexpr int kTile = 64;
-__global__ void __launch_bounds__(256) compact_move_kernel(MoveArgs a) {
+// One CTA per (kv head, sequence, K|V, column part) walks the sequence in tiles of 2048 16-byte vectors:
+// load the live rows of the tile, ONE barrier, store them at their new positions.  new_pos[t] <= t and order
+// is kept, so the rows a tile writes lie at or before the rows it read and strictly before anything a later
+// tile reads -- the in-order loop of kv_cache.cpp:957-989, one head at a time; the barrier only has to
+// separate a tile's loads from its own stores.  Column ranges of a row are independent of one another, so
+// wide rows are cut in two for twice the CTAs (the walk itself is sequential).  The block table sits in
+// shared memory and the next tile's new positions are fetched before the barrier, so that a tile costs one
+// dependent global load (the row itself), not three.
+constexpr int kMoveThreads = 256, kMovePerThread = 8, kMoveBtSmem = 2048;
+__global__ void __launch_bounds__(kMoveThreads, 3) compact_move_kernel(MoveArgs a) {
+    __shared__ int32_t s_bt[kMoveBtSmem];
     const int h = blockIdx.x, b = blockIdx.y;
-    uint8_t* pool = blockIdx.z == 0 ? a.k_pages : a.v_pages;
+    const int parts = gridDim.z / 2, part = blockIdx.z >> 1;
+    uint8_t* pool = (blockIdx.z & 1) == 0 ? a.k_pages : a.v_pages;
     const int len = a.seq_lens[b];
-    const int32_t* bt = a.block_table + (size_t)b * a.max_pages;
+    const int32_t* bt_g = a.block_table + (size_t)b * a.max_pages;
     const int32_t* np = a.new_pos + (size_t)b * a.capacity;
-    const int vec_per_row = a.row_bytes / 16;
-    auto row_ptr = [&](int t) -> uint4* {
+    const int n_pages = (len + a.P - 1) / a.P;
+    const bool bt_in_smem = n_pages <= kMoveBtSmem;
+    if (bt_in_smem)
+        for (int i = threadIdx.x; i < n_pages; i += kMoveThreads) s_bt[i] = bt_g[i];
+    __syncthreads();
+    const int32_t* bt = bt_in_smem ? s_bt : bt_g;
+    const int vpr = a.row_bytes / 16 / parts;                  // 16-byte vectors of a row that this CTA moves
+    const int v0 = part * vpr;
+    const int tile_rows = kMoveThreads * kMovePerThread / vpr;
+    auto vec_ptr = [&](int t, int v) -> uint4* {
         const size_t page = (size_t)bt[t / a.P];
-        return reinterpret_cast<uint4*>(pool + ((page * a.Hkv + h) * a.P + (t % a.P)) * (size_t)a.row_bytes);
+        return reinterpret_cast<uint4*>(pool + ((page * a.Hkv + h) * a.P + (t % a.P)) * (size_t)a.row_bytes) + v0 + v;
     };
-    constexpr int kMaxPerThread = 8;     // 64 rows x 512 B (float32, D=128) / 16 B / 256 threads
-    uint4 regs[kMaxPerThread];
-    for (int base = 0; base < len; base += kTile) {
-        const int items = kTile * vec_per_row;
+    uint4 regs[kMovePerThread];
+    int dst[kMovePerThread], nxt[kMovePerThread];
 #pragma unroll
-        for (int i = 0; i < kMaxPerThread; ++i) {
-            const int idx = threadIdx.x + i * 256;
-            if (idx < items) {
-                const int t = base + idx / vec_per_row;
-                if (t < len && np[t] >= 0 && np[t] != t) regs[i] = row_ptr(t)[idx % vec_per_row];
-            }
+    for (int i = 0; i < kMovePerThread; ++i) {                 // new positions of the first tile
+        const int t = (threadIdx.x + i * kMoveThreads) / vpr;
+        nxt[i] = t < len ? np[t] : -1;
+    }
+    for (int base = 0; base < len; base += tile_rows) {
+#pragma unroll
+        for (int i = 0; i < kMovePerThread; ++i) {
+            const int idx = threadIdx.x + i * kMoveThreads;
+            const int t = base + idx / vpr;
+            dst[i] = (t < len && nxt[i] != t) ? nxt[i] : -1;   // -1: tombstone, past the end, or already in place
+            if (dst[i] >= 0) regs[i] = *vec_ptr(t, idx % vpr);
+        }
+#pragma unroll
+        for (int i = 0; i < kMovePerThread; ++i) {             // the next tile's positions travel with this tile's rows
+            const int t = base + tile_rows + (threadIdx.x + i * kMoveThreads) / vpr;
+            nxt[i] = t < len ? np[t] : -1;
         }
         __syncthreads();
 #pragma unroll
-        for (int i = 0; i < kMaxPerThread; ++i) {
-            const int idx = threadIdx.x + i * 256;
-            if (idx < items) {
-                const int t = base + idx / vec_per_row;
-                if (t < len && np[t] >= 0 && np[t] != t) row_ptr(np[t])[idx % vec_per_row] = regs[i];
-            }
-        }
-        __syncthreads();
+        for (int i = 0; i < kMovePerThread; ++i)
+            if (dst[i] >= 0) *vec_ptr(dst[i], (threadIdx.x + i * kMoveThreads) % vpr) = regs[i];
     }
 }
 
@@ -467,7 +483,8 @@ int grl_kv_compact(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* 
     grl_kv_compact_scratch_bytes(kv, meta, &need);
     GRL_REQUIRE(scratch && scratch_bytes >= need, "compaction scratch too small: %zu < %zu", scratch_bytes, need);
     const int row_bytes = kv->head_dim * (kv->cache_dtype == GRL_BF16 ? 2 : 4);
-    GRL_REQUIRE(row_bytes % 16 == 0 && kTile * (row_bytes / 16) <= 8 * 256, "unsupported row size %d bytes", row_bytes);
+    GRL_REQUIRE(row_bytes % 16 == 0 && (kMoveThreads * kMovePerThread) % (row_bytes / 16) == 0,
+                "unsupported row size %d bytes", row_bytes);
     GRL_REQUIRE(((uintptr_t)kv->k_pages % 16 == 0) && ((uintptr_t)kv->v_pages % 16 == 0), "page pools must be 16-byte aligned");
     DeviceGuard g(dev->ordinal);
     int32_t* new_pos = static_cast<int32_t*>(scratch);
@@ -480,8 +497,9 @@ int grl_kv_compact(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* 
     a.block_table = kv->block_table; a.seq_lens = kv->seq_lens; a.new_pos = new_pos;
     a.Hkv = kv->num_kv_heads; a.P = kv->page_tokens; a.max_pages = kv->max_pages; a.capacity = meta->capacity;
     a.row_bytes = row_bytes;
-    dim3 grid(kv->num_kv_heads, kv->batch, 2);
-    compact_move_kernel<<<grid, 256, 0, dev->stream>>>(a);
+    const int parts = row_bytes >= 256 ? 2 : 1;          // half rows of >= 128 bytes
+    dim3 grid(kv->num_kv_heads, kv->batch, 2 * parts);
+    compact_move_kernel<<<grid, kMoveThreads, 0, dev->stream>>>(a);
     GRL_LAUNCHED("compact_move_kernel");
     compact_meta_kernel<<<kv->batch, kThreads, 0, dev->stream>>>(meta->cum_score, meta->tombstone, meta->relevance,
                                                                 kv->seq_lens, meta->evicted, new_pos, new_len,
