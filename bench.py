@@ -1,18 +1,27 @@
 #!/usr/bin/env python
 """Benchmark of the attention hot path on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--legs a,b,...]
 
 One JSON line on stdout (rank 0).  Headline metric: prefill attention TFLOP/s on configuration 2
 (FlashAttention-2 + RoPE, causal, batch 4, 32 heads, seq 2048, head_dim 128, bf16 tensor-core
-path); the decode configuration 3 (GQA decode, batch 32, 32/8 heads, KV 4096 -> 4352, 256 steps)
-is measured in the same run and reported under "decode".  Synthetic N(0,1) inputs from a seed.
+path).  The other configurations are measured in the same run and reported as objects of the same
+line: "cfg1" (fp32 exact path, absolute time), "cfg5" (padded batch of ragged lengths), "decode"
+(configuration 3: GQA decode, batch 32, 32/8 heads, KV 4096 -> 4352, 256 steps), "decode_long"
+(configuration 4: KV length 131072 sharded over the GPUs), "evict" (H2O selection + compaction).
+Synthetic N(0,1) inputs from a seed.
 
 A step is one pass of the hot path over one batch.  `value` times the kernel with inputs resident
 in HBM (CUDA events on the library's stream); `e2e` times the public Python op
 (grilly_core.flash_attention2 / decode_step) with pinned HOST buffers, copies inside the timed
 region.  With N > 1 (torchrun, one process per GPU) every rank runs the same per-GPU workload on
-its own GPU (weak scaling, no data-path collective); times are the max over ranks.
+its own GPU (weak scaling, no data-path collective) for the headline; "strong_scaling" times ONE
+problem whose (batch, head) slices are split over the ranks; configuration 4 is strong scaling by
+construction.  Times are the max over ranks.  Every leg checks one sampled result against the CPU
+oracle before it is timed ("parity"); a result outside its tolerance ends the run with a non-zero
+exit code.
+
+Legs (--legs, default all): prefill, cfg1, cfg5, decode, evict, long, e2e, cpu.
 """
 import argparse
 import ctypes as C
@@ -29,13 +38,22 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "grilly-next_b200", "python"))
 
+CFG1 = dict(B=1, H=4, S=256, D=64, seed=1001)
 CFG2 = dict(B=4, H=32, S=2048, D=128, theta=10000.0, seed=1002)
-CFG4 = dict(Hq=32, Hkv=8, D=128, T=131072, seed=1004)
 CFG3 = dict(B=32, Hq=32, Hkv=8, D=128, T0=4096, steps=256, theta=10000.0, seed=1003, page=64)
+CFG4 = dict(Hq=32, Hkv=8, D=128, T=131072, seed=1004)
+CFG5 = dict(B=8, H=32, S=4096, D=128, theta=10000.0, seed=1005)
+ALL_LEGS = ("prefill", "cfg1", "cfg5", "decode", "evict", "long", "e2e", "cpu")
+TOL_BF16_PREFILL, TOL_FP32_PREFILL, TOL_DECODE = 2e-2, 1e-4, 5e-3
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch (ncu, see profiles/)
+PREFILL_TRAFFIC_BYTES = 208.9e6 + 103.1e6   # flash_fwd_sm100_kernel on cfg2
+DECODE_TRAFFIC_BYTES = 546.1e6 + 11.0e6     # decode_mma_kernel at cache length ~4117
 
 
-def prefill_flops(c):
-    return 4 * c["D"] * c["B"] * c["H"] * (c["S"] * (c["S"] + 1) // 2)
+def causal_flops(D, heads, lens):
+    """4*D FLOP per visible (q, k) pair: QK^T and PV, multiply and add."""
+    return 4 * D * heads * sum(int(L) * (int(L) + 1) // 2 for L in lens)
 
 
 def decode_bytes(c):
@@ -46,21 +64,13 @@ def decode_bytes(c):
     return kv + other
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one flash_fwd_sm100_kernel launch on cfg2 (ncu, see profiles/)
-PREFILL_TRAFFIC_BYTES = 208.9e6 + 103.1e6
-DECODE_TRAFFIC_BYTES = 546.1e6 + 11.0e6     # one decode_mma_kernel launch at cache length ~4117 (ncu, see profiles/)
+def to_bf16_bits(x):
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
 
 
-def prefill_roofline(tflops_gpu, timed_ms, pk):
-    """The prefill kernel against the measured cuBLAS bf16 rate: the burst figure when the timed region is
-    short (clocks still at boost), the sustained one when it runs long enough to sit under the power cap."""
-    long_run = timed_ms > 100.0 and pk["tf_sustained"]
-    peak = pk["tf_sustained"] if long_run else pk["tf"]
-    return {"bound": "tensor", "achieved": tflops_gpu, "peak": peak, "unit": "TFLOP/s", "frac": tflops_gpu / peak,
-            "traffic": PREFILL_TRAFFIC_BYTES, "peak_source": pk["src"] + (" (sustained: timed region > 100 ms)" if long_run else " (burst)"),
-            "frac_of_burst": tflops_gpu / pk["tf"],
-            "frac_of_sustained": tflops_gpu / pk["tf_sustained"] if pk["tf_sustained"] else None,
-            "frac_of_nominal_2250": tflops_gpu / 2250.0, "kernel": "flash_fwd_sm100_kernel"}
+def round_bf16(x):
+    return (to_bf16_bits(x).astype(np.uint32) << np.uint32(16)).view(np.float32).reshape(np.shape(x))
 
 
 def peaks():
@@ -71,21 +81,38 @@ def peaks():
     return dict(hbm=6650.0, tf=1590.0, tf_sustained=1400.0, src="fallback")
 
 
+def prefill_roofline(tflops_gpu, timed_ms, pk, traffic=None):
+    """The prefill kernel against the measured cuBLAS bf16 rate: the burst figure when the timed region is
+    short (clocks still at boost), the sustained one when it runs long enough to sit under the power cap."""
+    long_run = timed_ms > 100.0 and pk["tf_sustained"]
+    peak = pk["tf_sustained"] if long_run else pk["tf"]
+    return {"bound": "tensor", "achieved": tflops_gpu, "peak": peak, "unit": "TFLOP/s", "frac": tflops_gpu / peak,
+            "traffic": traffic, "peak_source": pk["src"] + (" (sustained: timed region > 100 ms)" if long_run else " (burst)"),
+            "frac_of_burst": tflops_gpu / pk["tf"],
+            "frac_of_sustained": tflops_gpu / pk["tf_sustained"] if pk["tf_sustained"] else None,
+            "frac_of_nominal_2250": tflops_gpu / 2250.0, "kernel": "flash_fwd_sm100_kernel"}
+
+
+class ParityError(RuntimeError):
+    pass
+
+
+def parity(name, max_abs, tol, **extra):
+    d = {"max_abs": float(max_abs), "tol": tol, **extra}
+    if not (max_abs <= tol):
+        raise ParityError(f"{name}: max-abs {max_abs:.3e} exceeds {tol:.1e} ({extra})")
+    return d
+
+
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons from start() to stop(); regions are marked by time."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
-        self.t0 = self.t1 = None
-
-    def mark_start(self):
-        self.t0 = time.time()
-
-    def mark_end(self):
-        self.t1 = time.time()
 
     def start(self):
         try:
@@ -102,16 +129,18 @@ class ClockSampler:
             self.rows.append([time.time()] + [x.strip() for x in line.split(",")])
 
     def stop(self):
+        if self.proc:
+            self.proc.terminate()
+            self.t.join(timeout=2)
+
+    def region(self, t0, t1):
+        """Median SM clock and the throttle reasons seen between two time.time() stamps."""
         if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        self.t.join(timeout=2)
-        # samples taken while the timed region ran (20 ms of slack for the sampler's own latency)
-        rows = [r[1:] for r in self.rows if len(r) >= 7 and self.t0 is not None and self.t0 <= r[0] <= self.t1 + 0.02]
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        rows = [r[1:] for r in self.rows if len(r) >= 7 and t0 <= r[0] <= t1 + 0.02]
         sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[2].replace(".", "").isdigit() for r in [r[1:]]]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[2 + i] == "Active" for r in rows)]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 7 and r[2].replace(".", "").isdigit()]
+        reasons = [n for i, n in enumerate(self.NAMES) if any(r[2 + i] == "Active" for r in rows)]
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
 
@@ -120,7 +149,8 @@ class ClockSampler:
 def run_reference(args):
     """The reference's CPU implementation of the path: its Vulkan shaders cannot run here (no
     graphics stack) and its C++ library does not build without the Vulkan SDK, so this arm times
-    the C restatement of its CPU attention (oracle/attn_oracle.c, OpenMP, all host threads)."""
+    the C restatement of its CPU attention (oracle/attn_oracle.c, OpenMP, all host threads), the
+    rotation of Q and K included (also C/OpenMP)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -130,17 +160,20 @@ def run_reference(args):
     heads = 32                                   # bounded sample: 32 of the 128 (batch, head) pairs per step
     rng = np.random.default_rng(c["seed"])
     Q, K, V = (rng.standard_normal((1, heads, c["S"], c["D"]), dtype=np.float32) for _ in range(3))
-    from oracle import attention_oracle as orc
-    pos = np.arange(c["S"])
-    fl = 4 * c["D"] * heads * (c["S"] * (c["S"] + 1) // 2)
+    fl = causal_flops(c["D"], heads, [c["S"]])
+
+    def step():
+        c_oracle.attention(c_oracle.rope_interleaved(Q, c["theta"]), c_oracle.rope_interleaved(K, c["theta"]), V, causal=True)
+
     for _ in range(max(1, min(args.warmup, 2))):
-        c_oracle.attention(Q, K, V, causal=True)
+        step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        q = orc.rope_interleaved(Q, pos, c["theta"])   # RoPE is part of the path
-        k = orc.rope_interleaved(K, pos, c["theta"])
-        c_oracle.attention(q, k, V, causal=True)
+        step()
     dt = time.perf_counter() - t0
+    t1 = time.perf_counter()
+    c_oracle.rope_interleaved(Q, c["theta"]); c_oracle.rope_interleaved(K, c["theta"])
+    rope_share = (time.perf_counter() - t1) / (dt / args.steps)
     val = fl * args.steps / dt / 1e12
     line = {
         "impl": "reference", "metric": "prefill_attn_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
@@ -148,13 +181,55 @@ def run_reference(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "cfg2: FlashAttention-2+RoPE causal prefill, B4 H32 S2048 D128", "l2": "inputs larger than L2"},
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": c_oracle.num_threads(), "kind": "port",
-                         "sample": f"{heads} of 128 (batch, head) slices of cfg2 per step, RoPE + causal attention, C/OpenMP"},
+                         "sample": f"{heads} of 128 (batch, head) slices of cfg2 per step, RoPE (C/OpenMP, {rope_share:.1%} of the "
+                                   "step) + causal attention, C/OpenMP"},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-# ------------------------------------------------------------------------------------- our arm
+# ------------------------------------------------------------------------------------- plumbing
+class Dist:
+    """One process per GPU.  torch.distributed (NCCL) is plumbing only: barrier, max over ranks, and the
+    host channel that carries the NCCL id and the CUDA IPC handles of the library's own exchange."""
+
+    def __init__(self):
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.td = None
+        if self.world > 1:
+            import torch
+            import torch.distributed as td
+            torch.cuda.set_device(self.local_rank)
+            td.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+            self.td, self.torch = td, torch
+
+    def barrier(self):
+        if self.td:
+            self.td.barrier()
+            self.torch.cuda.synchronize()
+
+    def max(self, x):
+        if not self.td:
+            return x
+        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        self.td.all_reduce(t, op=self.td.ReduceOp.MAX)
+        return float(t.item())
+
+    def all_gather_bytes(self, payload):
+        if not self.td:
+            return [bytes(payload)]
+        out = [None] * self.world
+        self.td.all_gather_object(out, bytes(payload))
+        return out
+
+    def close(self):
+        if self.td:
+            self.td.barrier()
+            self.td.destroy_process_group()
+
+
 def pinned_array(L, shape, dtype):
     n = int(np.prod(shape)) * np.dtype(dtype).itemsize
     p = C.c_void_p()
@@ -165,53 +240,229 @@ def pinned_array(L, shape, dtype):
     return np.frombuffer(buf, dtype=dtype).reshape(shape), p
 
 
-def bench_prefill(dev, cabi, args, dist):
-    c = CFG2
-    B, H, S, D = c["B"], c["H"], c["S"], c["D"]
-    rng = np.random.default_rng(c["seed"] + dist["rank"])
-    n = B * H * S * D
-    q = dev.upload_bf16(rng.standard_normal((B, H, S, D), dtype=np.float32))
-    k = dev.upload_bf16(rng.standard_normal((B, H, S, D), dtype=np.float32))
-    v = dev.upload_bf16(rng.standard_normal((B, H, S, D), dtype=np.float32))
-    o = dev.malloc(n * 4)
+def fill_random_bf16(dev, cabi, dst, n_elems, rng, block_elems=1 << 21):
+    """iid N(0,1) bf16 over a large device buffer: one random block from the host, then doubling copies on
+    the device.  (The timed kernels read every element once; their time does not depend on the values.)"""
+    L = dev.L
+    m = min(block_elems, n_elems)
+    bits = to_bf16_bits(rng.standard_normal(m, dtype=np.float32))
+    cabi.check(L.grl_memcpy_h2d(dev.h, dst, bits.ctypes.data_as(C.c_void_p), m * 2))
+    dev.sync()
+    filled = m
+    while filled < n_elems:
+        k = min(filled, n_elems - filled)
+        cabi.check(L.grl_memcpy_d2d(dev.h, C.c_void_p(dst.value + filled * 2), dst, k * 2))
+        filled += k
+    dev.sync()
+
+
+def time_steps(dev, dist, step, steps):
+    """steps launches between two events on the library's stream; max over ranks, in ms."""
+    e0, e1 = dev.event(), dev.event()
+    dev.sync()
+    dist.barrier()
+    dev.record(e0)
+    for _ in range(steps):
+        step()
+    dev.record(e1)
+    dev.sync()
+    ms = dev.elapsed_ms(e0, e1)
+    for e in (e0, e1):
+        dev.L.grl_event_destroy(e)
+    return dist.max(ms)
+
+
+def flash_params(cabi, q, k, v, o, B, H, S, D, *, bf16, causal=True, theta=0.0, seq_lens=None, kernel=None, scale=0.0):
     p = cabi.FlashParams()
     p.q, p.k, p.v, p.o = q, k, v, o
-    p.in_dtype, p.out_dtype = cabi.BF16, cabi.F32
+    p.in_dtype, p.out_dtype = (cabi.BF16 if bf16 else cabi.F32), cabi.F32
     p.batch, p.heads, p.seq_len, p.head_dim = B, H, S, D
-    p.causal, p.rope_mode, p.rope_theta, p.rope_scaling = 1, cabi.ROPE_INTERLEAVED, c["theta"], 1.0
-    if args.variant == "norope":          # profiling aids: not the benchmark configuration
-        p.rope_mode = cabi.ROPE_NONE
-    elif args.variant == "noncausal":
-        p.causal = 0
-    p.kernel = cabi.KERNEL_TCGEN05
+    p.causal, p.scale = int(causal), scale
+    if theta:
+        p.rope_mode, p.rope_theta, p.rope_scaling = cabi.ROPE_INTERLEAVED, theta, 1.0
+    if seq_lens is not None:
+        p.seq_lens = seq_lens
+    p.kernel = kernel if kernel is not None else (cabi.KERNEL_TCGEN05 if bf16 else cabi.KERNEL_SIMT_F32)
+    return p
+
+
+def oracle_head(Qh, Kh, Vh, theta, causal=True, length=None):
+    """The checker on one (batch, head) slice: RoPE + causal attention in float32 on the unrounded inputs."""
+    from oracle import c_oracle
+    q, k = Qh[None, None], Kh[None, None]
+    if theta:
+        q, k = c_oracle.rope_interleaved(q, theta), c_oracle.rope_interleaved(k, theta)
+    sl = None if length is None else np.array([length], np.int32)
+    return c_oracle.attention(q, k, Vh[None, None], causal=causal, seq_lens=sl)[0, 0]
+
+
+# ------------------------------------------------------------------------------------- prefill legs
+def bench_prefill(dev, cabi, args, dist, pk, sampler):
+    """cfg2 on every GPU (the headline), the same block repeated for a sustained figure, and -- with several
+    GPUs -- the ONE problem split by heads over the ranks."""
+    c = CFG2
+    B, H, S, D = c["B"], c["H"], c["S"], c["D"]
+    rng = np.random.default_rng(c["seed"] + dist.rank)
+    n = B * H * S * D
+    sb, sh = B - 1, 5                                   # the sampled (batch, head) slice of the parity check
+    host, dptr = [], []
+    for _ in range(3):
+        a = rng.standard_normal((B, H, S, D), dtype=np.float32)
+        host.append(a[sb, sh].copy())
+        dptr.append(dev.upload_bf16(a))
+        del a
+    q, k, v = dptr
+    o = dev.malloc(n * 4)
     L = dev.L
+    p = flash_params(cabi, q, k, v, o, B, H, S, D, bf16=True, theta=c["theta"])
 
     def step():
         cabi.check(L.grl_flash_fwd(dev.h, C.byref(p)))
 
-    sampler = ClockSampler(dist["local_rank"])
-    sampler.start()
     for _ in range(args.warmup):
         step()
     dev.sync()
-    e0, e1 = dev.event(), dev.event()
-    dist["barrier"]()
+    got = dev.download(C.c_void_p(o.value + (sb * H + sh) * S * D * 4), (S, D), np.float32)
+    par = parity("prefill cfg2", np.abs(got - oracle_head(*host, c["theta"])).max(), TOL_BF16_PREFILL,
+                 sample=f"(batch, head) = ({sb}, {sh}) of rank {dist.rank}, all {S} rows, against the fp32 oracle on the unrounded inputs")
     launches0 = L.grl_launch_count()
-    sampler.mark_start()
-    dev.record(e0)
-    for _ in range(args.steps):
-        step()
-    dev.record(e1)
-    dev.sync()
-    sampler.mark_end()
-    ms = dev.elapsed_ms(e0, e1)
+    t0 = time.time()
+    ms = time_steps(dev, dist, step, args.steps)
+    t1 = time.time()
     launches = L.grl_launch_count() - launches0
-    ms = dist["max"](ms)
-    dist["barrier"]()
-    clocks = sampler.stop()
+    fl = causal_flops(D, B * H, [S])
+    tflops_gpu = fl * args.steps / (ms * 1e-3) / 1e12
+    # the same block back to back until the timed region is long enough for the clock sampler (and the power cap)
+    reps, t2 = max(1, int(np.ceil(0.5 / max(ms * 1e-3, 1e-6)))), time.time()
+    ms_long = time_steps(dev, dist, step, args.steps * reps) if reps > 1 else ms
+    t3 = time.time()
+    tf_long = fl * args.steps * reps / (ms_long * 1e-3) / 1e12
+    ck_short, ck_long = sampler.region(t0, t1), sampler.region(t2, t3)
+    clocks = dict(ck_short if ck_short["samples"] >= 3 else ck_long)
+    clocks["region"] = "headline timed region" if ck_short["samples"] >= 3 else "sustained repeat of the timed block (the headline region is shorter than the sampler's period)"
+    clocks["headline_samples"] = ck_short["samples"]
+    out = {"ms": ms, "launches": launches, "tflops_gpu": tflops_gpu, "flops": fl, "clocks": clocks, "parity": par,
+           "sustained": {"value": tf_long * dist.world, "unit": "TFLOP/s", "ms_per_step": ms_long / (args.steps * reps),
+                         "timed_region_ms": ms_long, "steps": args.steps * reps, "clocks": ck_long,
+                         "ms_x_mhz": (ms_long / (args.steps * reps)) * ck_long["sm_mhz"] if ck_long["sm_mhz"] else None,
+                         "frac_of_sustained_peak": tf_long / pk["tf_sustained"] if pk["tf_sustained"] else None}}
+    if dist.world > 1 and H % dist.world == 0:
+        # strong scaling: the 128 (batch, head) slices of ONE cfg2 problem, heads split over the ranks
+        Hl = H // dist.world
+        ps = flash_params(cabi, q, k, v, o, B, Hl, S, D, bf16=True, theta=c["theta"])
+        steps = args.steps
+        for _ in range(args.warmup):
+            cabi.check(L.grl_flash_fwd(dev.h, C.byref(ps)))
+        ms_s = time_steps(dev, dist, lambda: cabi.check(L.grl_flash_fwd(dev.h, C.byref(ps))), steps)
+        out["strong"] = {"value": fl * steps / (ms_s * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_s / steps,
+                         "scaling": "strong", "parallelism": f"one cfg2 problem, {Hl} of {H} heads per GPU (x{B} batch rows), no collective",
+                         "ctas_per_gpu": B * Hl * (S // 256)}
     for x in (q, k, v, o):
         dev.free(x)
-    return ms, launches, clocks
+    return out
+
+
+def bench_cfg1(dev, cabi, args, dist):
+    """cfg1: the exact fp32 path, B1 H4 S256 D64 causal -- 33.7 MFLOP, bounded by launch latency: absolute time."""
+    c = CFG1
+    B, H, S, D = c["B"], c["H"], c["S"], c["D"]
+    rng = np.random.default_rng(c["seed"])
+    Q, K, V = (rng.standard_normal((B, H, S, D), dtype=np.float32) for _ in range(3))
+    L = dev.L
+    q, k, v = dev.upload(Q), dev.upload(K), dev.upload(V)
+    o = dev.malloc(Q.nbytes)
+    p = flash_params(cabi, q, k, v, o, B, H, S, D, bf16=False, scale=0.125)
+    cabi.check(L.grl_flash_fwd(dev.h, C.byref(p)))
+    dev.sync()
+    from oracle import c_oracle
+    got = dev.download(o, Q.shape, np.float32)
+    par = parity("prefill cfg1", np.abs(got - c_oracle.attention(Q, K, V, causal=True, scale=0.125)).max(), TOL_FP32_PREFILL,
+                 sample="all heads and rows")
+    # cold: 1 MiB of tensors would sit in L2, so a 256 MiB write flushes it before every timed launch
+    flush = dev.malloc(256 << 20)
+    e0, e1 = dev.event(), dev.event()
+    cold = []
+    for _ in range(12):
+        cabi.check(L.grl_memset(dev.h, flush, 0, 256 << 20))
+        dev.record(e0)
+        cabi.check(L.grl_flash_fwd(dev.h, C.byref(p)))
+        dev.record(e1)
+        dev.sync()
+        cold.append(dev.elapsed_ms(e0, e1) * 1e3)
+    warm = time_steps(dev, dist, lambda: cabi.check(L.grl_flash_fwd(dev.h, C.byref(p))), 200) / 200 * 1e3
+    for x in (q, k, v, o, flush):
+        dev.free(x)
+    cold_us = float(np.median(cold[2:]))
+    fl = causal_flops(D, B * H, [S])
+    res = {"workload": "cfg1: flash-attention2 fp32 exact path, B1 H4 S256 D64 causal, scale 1/8 (flash_fwd_f32_kernel)",
+           "us_per_call": cold_us, "us_per_call_l2_warm": warm, "flops": fl, "gflops": fl / cold_us / 1e3,
+           "l2": "cold figure: L2 flushed by a 256 MiB write before every timed launch; warm: 200 launches back to back",
+           "bound": "launch latency and fp32 FMA (no tensor cores on the exact path)", "parity": par}
+    return res, (Q, K, V)
+
+
+def bench_cfg1_e2e(qkv, dist):
+    import grilly_core
+    ctx = grilly_core.Device()
+    Q, K, V = qkv
+    for _ in range(3):
+        grilly_core.flash_attention2(ctx, Q, K, V, causal=True, scale=0.125)
+    t0 = time.perf_counter()
+    for _ in range(50):
+        out = grilly_core.flash_attention2(ctx, Q, K, V, causal=True, scale=0.125)
+    dt = dist.max((time.perf_counter() - t0) / 50)
+    assert np.isfinite(out).all()
+    return {"us_per_call": dt * 1e6, "h2d_bytes_per_step": 3 * Q.nbytes, "d2h_bytes_per_step": Q.nbytes,
+            "api": "grilly_core.flash_attention2(causal=True, scale=0.125) on numpy arrays"}
+
+
+def bench_cfg5(dev, cabi, args, dist, pk):
+    """cfg5: batch of 8 ragged sequences (512..4096 tokens) padded to 4096, causal + length mask, RoPE."""
+    c = CFG5
+    B, H, S, D = c["B"], c["H"], c["S"], c["D"]
+    rng = np.random.default_rng(c["seed"])
+    lens = rng.integers(512, 4097, size=B).astype(np.int32)
+    n = B * H * S * D
+    sb, sh = int(np.argmin(lens)), 3                     # the shortest sequence: padding rows and a ragged last tile
+    host, dptr = [], []
+    for _ in range(3):
+        a = rng.standard_normal((B, H, S, D), dtype=np.float32)
+        host.append(a[sb, sh].copy())
+        dptr.append(dev.upload_bf16(a))
+        del a
+    q, k, v = dptr
+    o = dev.malloc(n * 4)
+    sl = dev.upload(lens)
+    L = dev.L
+    p = flash_params(cabi, q, k, v, o, B, H, S, D, bf16=True, theta=c["theta"], seq_lens=sl)
+    steps = max(3, min(args.steps, 20))
+    for _ in range(3):
+        cabi.check(L.grl_flash_fwd(dev.h, C.byref(p)))
+    dev.sync()
+    got = dev.download(C.c_void_p(o.value + (sb * H + sh) * S * D * 4), (S, D), np.float32)
+    Lb = int(lens[sb])
+    want = oracle_head(*host, c["theta"], length=Lb)
+    assert not got[Lb:].any(), "rows at or beyond the sequence length must be zero"
+    par = parity("prefill cfg5", np.abs(got[:Lb] - want[:Lb]).max(), TOL_BF16_PREFILL,
+                 sample=f"(batch, head) = ({sb}, {sh}), length {Lb}: valid rows against the fp32 oracle, padded rows exactly zero")
+    ms = time_steps(dev, dist, lambda: cabi.check(L.grl_flash_fwd(dev.h, C.byref(p))), steps)
+    fl = causal_flops(D, H, lens)
+    tf = fl * steps / (ms * 1e-3) / 1e12
+    res = {"metric": "prefill_attn_tflops", "value": tf * dist.world, "unit": "TFLOP/s", "ms_per_step": ms / steps, "steps": steps,
+           "workload": f"cfg5: FlashAttention-2+RoPE, B8 H32 D128, lengths {lens.tolist()} padded to {S}, causal and length mask, "
+                       "bf16 in / fp32 out, per GPU", "flops_per_step_per_gpu": fl, "scaling": "weak",
+           "roofline": prefill_roofline(tf, ms, pk), "parity": par}
+    if dist.world > 1 and H % dist.world == 0:
+        Hl = H // dist.world
+        ps = flash_params(cabi, q, k, v, o, B, Hl, S, D, bf16=True, theta=c["theta"], seq_lens=sl)
+        for _ in range(3):
+            cabi.check(L.grl_flash_fwd(dev.h, C.byref(ps)))
+        ms_s = time_steps(dev, dist, lambda: cabi.check(L.grl_flash_fwd(dev.h, C.byref(ps))), steps)
+        res["strong"] = {"value": fl * steps / (ms_s * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_s / steps, "scaling": "strong",
+                         "parallelism": f"one cfg5 problem, {Hl} of {H} heads per GPU, all 8 sequences on every GPU, no collective"}
+    for x in (q, k, v, o, sl):
+        dev.free(x)
+    return res
 
 
 def bench_prefill_e2e(args, L, steps, dist):
@@ -232,66 +483,59 @@ def bench_prefill_e2e(args, L, steps, dist):
     kw = dict(causal=True, rope_theta=c["theta"], dtype="bf16", out=out_arr)
     for _ in range(2):
         out = grilly_core.flash_attention2(ctx, *arrs, **kw)
-    dist["barrier"]()
+    sb, sh = 2, 11
+    par = parity("prefill e2e", np.abs(out[sb, sh] - oracle_head(arrs[0][sb, sh], arrs[1][sb, sh], arrs[2][sb, sh], c["theta"])).max(),
+                 TOL_BF16_PREFILL, sample=f"(batch, head) = ({sb}, {sh}) of the op's host result")
+    dist.barrier()
     t0 = time.perf_counter()
     for _ in range(steps):
         out = grilly_core.flash_attention2(ctx, *arrs, **kw)   # synchronous: returns with the result on the host
-    dt = dist["max"]((time.perf_counter() - t0) / steps)
-    assert np.isfinite(out[0, 0, -1]).all()
+    dt = dist.max((time.perf_counter() - t0) / steps)
+    info = grilly_core.last_pipeline_info() if hasattr(grilly_core, "last_pipeline_info") else None
     del ctx
     for pp in ptrs:
         L.grl_host_free(pp)
     nbytes = int(np.prod(shape)) * 4
-    # what crosses the link: the op's host threads round a share of every chunk to bf16 before the upload
-    # (all of it with one process per node, 50 %/N with N), the rest goes up as float32
-    lws = int(os.environ.get("LOCAL_WORLD_SIZE", "1"))
-    pct = int(os.environ.get("GRILLY_PIPELINE_HOST_CAST_PCT", 100 if lws <= 1 else 50 // lws))
+    pct = info["host_cast_pct"] if info else 100
     h2d = 3 * (nbytes // 2 * pct + nbytes * (100 - pct)) // 100
-    return dt, h2d, nbytes
+    return dt, h2d, nbytes, par, info
 
 
-def bench_decode(dev, cabi, dist, repeats=3, use_graph=True, force_splits=0):
+# ------------------------------------------------------------------------------------- decode legs
+def kv_layout(cabi, kp, vp, table, seq_lens, B, Hkv, D, P, max_pages, n_pages):
+    lay = cabi.KVLayout()
+    lay.k_pages, lay.v_pages, lay.cache_dtype = kp, vp, cabi.BF16
+    lay.block_table, lay.seq_lens = table, seq_lens
+    lay.batch, lay.num_kv_heads, lay.head_dim, lay.page_tokens, lay.max_pages, lay.num_pages = B, Hkv, D, P, max_pages, n_pages
+    return lay
+
+
+def bench_decode(dev, cabi, dist, repeats=3, use_graph=True):
     """cfg3: 256 decode steps (RoPE + append + split-KV attention + merge), graph-replayed."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from oracle import attention_oracle as orc
+    from oracle import c_oracle
     c = CFG3
     B, Hq, Hkv, D, T0, steps, P = c["B"], c["Hq"], c["Hkv"], c["D"], c["T0"], c["steps"], c["page"]
     L = dev.L
-    rng = np.random.default_rng(c["seed"] + dist["rank"])
+    rng = np.random.default_rng(c["seed"] + dist.rank)
     max_tokens = T0 + steps
     max_pages = (max_tokens + P - 1) // P
     n_pages = max_pages * B
     page_elems = Hkv * P * D
     kp, vp = dev.malloc(n_pages * page_elems * 2), dev.malloc(n_pages * page_elems * 2)
-    # iid N(0,1) bf16 in every page (the prefix is "already rotated" keys; layout does not matter for iid data)
-    chunk = rng.standard_normal(32 * page_elems, dtype=np.float32)
-    bits = orc.to_bf16_bits(chunk)
-    for dst in (kp, vp):
-        off = 0
-        total = n_pages * page_elems
-        while off < total:
-            m = min(bits.size, total - off)
-            rolled = np.roll(bits, int(rng.integers(0, bits.size)))[:m]
-            cabi.check(L.grl_memcpy_h2d(dev.h, C.c_void_p(dst.value + off * 2), rolled.ctypes.data_as(C.c_void_p), m * 2))
-            dev.sync()
-            off += m
+    for dst in (kp, vp):      # the prefix is "already rotated" keys: iid N(0,1) bf16
+        fill_random_bf16(dev, cabi, dst, n_pages * page_elems, rng)
     table = dev.upload(np.arange(n_pages, dtype=np.int32).reshape(B, max_pages))
     lens0 = np.full(B, T0, np.int32)
     seq_lens = dev.upload(lens0)
-    qs = dev.upload(rng.standard_normal((steps, B, 1, Hq, D), dtype=np.float32))
-    ks = dev.upload(rng.standard_normal((steps, B, 1, Hkv, D), dtype=np.float32))
+    q_host = rng.standard_normal((steps, B, 1, Hq, D), dtype=np.float32)
+    k_host = rng.standard_normal((steps, B, 1, Hkv, D), dtype=np.float32)
+    qs, ks = dev.upload(q_host), dev.upload(k_host)
     vs = dev.upload(rng.standard_normal((steps, B, 1, Hkv, D), dtype=np.float32))
     q_rot = dev.malloc(B * Hq * D * 4)
     out = dev.malloc(steps * B * Hq * D * 4)
-
-    lay = cabi.KVLayout()
-    lay.k_pages, lay.v_pages, lay.cache_dtype = kp, vp, cabi.BF16
-    lay.block_table, lay.seq_lens = table, seq_lens
-    lay.batch, lay.num_kv_heads, lay.head_dim, lay.page_tokens, lay.max_pages = B, Hkv, D, P, max_pages
-    lay.num_pages = n_pages
+    lay = kv_layout(cabi, kp, vp, table, seq_lens, B, Hkv, D, P, max_pages, n_pages)
     dp = cabi.DecodeParams()
     dp.kv, dp.num_q_heads, dp.max_seq_len = lay, Hq, max_tokens
-    dp.n_splits = force_splits
     ns = C.c_int()
     cabi.check(L.grl_decode_pick_splits(dev.h, C.byref(dp), C.byref(ns)))
     wb = C.c_size_t()
@@ -331,31 +575,52 @@ def bench_decode(dev, cabi, dist, repeats=3, use_graph=True, force_splits=0):
     reset()
     run()                                       # warm-up run
     dev.sync()
+    # parity of the last step of sequence 0: its cache read back through grl_kv_gather (bf16 values, exact in
+    # float32), the rotated q of that step, and the checker's decode over them; the appended key of that step
+    # against the rotation of the new key at its position
+    sb = 0
+    T = T0 + steps
+    gk, gv = dev.malloc(T * Hkv * D * 4), dev.malloc(T * Hkv * D * 4)
+    cabi.check(L.grl_kv_gather(dev.h, C.byref(lay), sb, T, gk, gv))
+    dev.sync()
+    Kc, Vc = dev.download(gk, (1, T, Hkv, D), np.float32), dev.download(gv, (1, T, Hkv, D), np.float32)
+    q_last = dev.download(q_rot, (B, 1, Hq, D), np.float32)[sb:sb + 1]
+    o_last = dev.download(C.c_void_p(out.value + (steps - 1) * B * Hq * D * 4), (B, 1, Hq, D), np.float32)[sb:sb + 1]
+    par = parity("decode cfg3", np.abs(o_last - c_oracle.gqa_decode(q_last, Kc, Vc)).max(), TOL_DECODE,
+                 sample=f"sequence {sb}, step {steps}: all 32 query heads over its {T} cached tokens")
+    k_rot = c_oracle.rope_interleaved(np.concatenate([np.zeros((Hkv, T - 1, D), np.float32),
+                                                      k_host[steps - 1, sb, 0][:, None, :]], axis=1), c["theta"])[:, -1]
+    par["appended_key_max_abs"] = float(np.abs(Kc[0, T - 1] - round_bf16(k_rot)).max())
+    if par["appended_key_max_abs"] > 2e-2:
+        raise ParityError(f"decode cfg3: appended key differs from RoPE(k) by {par['appended_key_max_abs']}")
+    q_want = c_oracle.rope_interleaved(np.concatenate([np.zeros((Hq, T - 1, D), np.float32),
+                                                       q_host[steps - 1, sb, 0][:, None, :]], axis=1), c["theta"])[:, -1]
+    par["rotated_q_max_abs"] = float(np.abs(q_last[0, 0] - q_want).max())
+    if par["rotated_q_max_abs"] > 1e-4:
+        raise ParityError(f"decode cfg3: rotated q differs from RoPE(q) by {par['rotated_q_max_abs']}")
+    dev.free(gk); dev.free(gv)
     best = None
     e0, e1 = dev.event(), dev.event()
     for _ in range(repeats):
         reset()
         dev.sync()
-        dist["barrier"]()
+        dist.barrier()
         dev.record(e0)
         run()
         dev.record(e1)
         dev.sync()
-        ms = dist["max"](dev.elapsed_ms(e0, e1))
+        ms = dist.max(dev.elapsed_ms(e0, e1))
         best = ms if best is None else min(best, ms)
-    o_last = dev.download(C.c_void_p(out.value + (steps - 1) * B * Hq * D * 4), (B, Hq, D), np.float32)
-    assert np.isfinite(o_last).all()
     if use_graph:
         L.grl_graph_destroy(g)
     for x in (kp, vp, table, seq_lens, qs, ks, vs, q_rot, out, ws):
         dev.free(x)
-    return best, launches_per_run, ns.value
+    return best, launches_per_run, ns.value, par
 
 
 def bench_evict(dev, cabi, repeats=3):
     """Eviction on a cfg3-sized cache (B32, Hkv8, D128, 4096 tokens, bf16): H2O selection of a quarter of every
     sequence, then compaction.  Returns (select_us, compact_us, bytes moved by one compaction)."""
-    from oracle import attention_oracle as orc
     c = CFG3
     B, Hkv, D, T, P = c["B"], c["Hkv"], c["D"], c["T0"], c["page"]
     L = dev.L
@@ -368,10 +633,7 @@ def bench_evict(dev, cabi, repeats=3):
     table = dev.upload(np.arange(n_pages, dtype=np.int32).reshape(B, max_pages))
     lens_host = np.full(B, T, np.int32)
     seq_lens = dev.upload(lens_host)
-    lay = cabi.KVLayout()
-    lay.k_pages, lay.v_pages, lay.cache_dtype = kp, vp, cabi.BF16
-    lay.block_table, lay.seq_lens = table, seq_lens
-    lay.batch, lay.num_kv_heads, lay.head_dim, lay.page_tokens, lay.max_pages, lay.num_pages = B, Hkv, D, P, max_pages, n_pages
+    lay = kv_layout(cabi, kp, vp, table, seq_lens, B, Hkv, D, P, max_pages, n_pages)
     cap = max_pages * P
     scores = rng.random((B, cap), dtype=np.float32)
     cum, tomb, evicted = dev.malloc(B * cap * 4), dev.malloc(B * cap), dev.malloc(B * 4)
@@ -427,11 +689,11 @@ def bench_decode_e2e(dist, steps=32):
     k1[...] = rng.standard_normal(k1.shape, dtype=np.float32)
     for _ in range(4):
         grilly_core.decode_step(ctx, kv, q, k1, k1, rope_theta=c["theta"], out=o)
-    dist["barrier"]()
+    dist.barrier()
     t0 = time.perf_counter()
     for _ in range(steps):
         grilly_core.decode_step(ctx, kv, q, k1, k1, rope_theta=c["theta"], out=o)
-    dt = dist["max"]((time.perf_counter() - t0) / steps)
+    dt = dist.max((time.perf_counter() - t0) / steps)
     assert np.isfinite(o).all()
     grilly_core.destroy_kv_cache(ctx, kv)
     nb = (q.nbytes + 2 * k1.nbytes, o.nbytes)
@@ -441,113 +703,152 @@ def bench_decode_e2e(dist, steps=32):
     return dt, nb[0], nb[1]
 
 
-def bench_long_decode(dev, cabi, dist, steps=50, repeats=3, n_splits=0):
-    """cfg4: B=1, Hq32/Hkv8, D128, KV length 131072 split in contiguous shards over the ranks; per step
-    every rank decodes its shard to one partial, the partials cross NVLink (peer stores, or NCCL all-gather
-    with GRILLY_EXCHANGE=nccl) and every rank merges."""
-    import torch
-    import torch.distributed as td
-    from grilly_next.parallel import CudaShardOps, ShardedDecoder, shard_range, torch_stream_handle
-    from oracle import attention_oracle as orc
+LONG_MODES = ("decode", "ll", "merge", "nccl")
+LONG_MODE_TEXT = {
+    "decode": "exchange over NVLink peer stores and LSE merge inside the decode kernel (one launch per step)",
+    "ll": "exchange over NVLink peer stores ({value, step} pairs, no flag) fused with the LSE merge",
+    "merge": "exchange over NVLink peer stores (fence + flag) fused with the LSE merge",
+    "nccl": "NCCL all-gather (grl_group_allgather_merge) + LSE merge",
+}
+
+
+def long_decode_parity(dev, cabi, dist, ops_factory):
+    """Every form of the exchange on a small seeded case (T = 1000 per rank) against the checker on the
+    bf16-rounded cache, before anything is timed.  Returns {mode: max-abs}."""
+    from grilly_next.parallel import ShardedDecoder, shard_range
+    from oracle import c_oracle
     c = CFG4
-    B, Hq, Hkv, D, T, P = 1, c["Hq"], c["Hkv"], c["D"], c["T"], 64
-    world, rank = dist["world"], dist["rank"]
+    B, Hq, Hkv, D, P = 1, c["Hq"], c["Hkv"], c["D"], 64
+    world, rank = dist.world, dist.rank
+    T = 1000 * world
+    rng = np.random.default_rng(c["seed"])                    # the same data on every rank
+    k = rng.standard_normal((B, T, Hkv, D), dtype=np.float32)
+    v = rng.standard_normal((B, T, Hkv, D), dtype=np.float32)
     lo, hi = shard_range(T, world, rank)
     Tg = hi - lo
+    n_pages = (Tg + P - 1) // P
     L = dev.L
-    cabi.check(L.grl_device_use_stream(dev.h, torch_stream_handle(torch)))
+    kp, vp = dev.malloc(n_pages * Hkv * P * D * 2), dev.malloc(n_pages * Hkv * P * D * 2)
+    table = dev.upload(np.arange(n_pages, dtype=np.int32).reshape(B, n_pages))
+    seq_lens = dev.upload(np.zeros(B, np.int32))
+    lay = kv_layout(cabi, kp, vp, table, seq_lens, B, Hkv, D, P, n_pages, n_pages)
+    kd, vd = dev.upload(k[:, lo:hi]), dev.upload(v[:, lo:hi])
+    ap = cabi.AppendParams()
+    ap.kv, ap.k_new, ap.v_new, ap.n_new, ap.update_lens = lay, kd, vd, Tg, 1
+    cabi.check(L.grl_kv_append(dev.h, C.byref(ap)))
+    dev.sync()
+    kb, vb = round_bf16(k), round_bf16(v)
+    res = {}
+    for mode in (LONG_MODES if world > 1 else ("decode",)):
+        ops = ops_factory(lay, Tg, mode)
+        dec = ShardedDecoder(dist, ops)
+        worst = 0.0
+        for _ in range(3):                                     # both inbox parities
+            q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
+            qd = dev.upload(q)
+            out_ptr = dec.step(qd)
+            dev.sync()
+            out = dev.download(out_ptr, (B, 1, Hq, D), np.float32)
+            dev.free(qd)
+            worst = max(worst, float(np.abs(out - c_oracle.gqa_decode(q, kb, vb)).max()))
+        ops.close()
+        res[mode if world > 1 else "single_gpu"] = worst
+    worst = max(res.values())
+    out = parity("decode_long cfg4", worst, TOL_DECODE,
+                 sample=f"T = {T} tokens over {world} GPU(s), 3 steps per exchange form, rank {rank}'s output against the checker on the bf16-rounded cache")
+    out.update(res)
+    for x in (kp, vp, table, seq_lens, kd, vd):
+        dev.free(x)
+    return out
+
+
+def bench_long_decode(dev, cabi, dist, steps=50, repeats=3):
+    """cfg4: B=1, Hq32/Hkv8, D128, KV length 131072 split in contiguous shards over the ranks; per step
+    every rank decodes its shard to one partial, the partials cross NVLink and every rank merges."""
+    from grilly_next.parallel import CudaShardOps, ShardedDecoder, shard_range
+    c = CFG4
+    B, Hq, Hkv, D, T, P = 1, c["Hq"], c["Hkv"], c["D"], c["T"], 64
+    world, rank = dist.world, dist.rank
+    L = dev.L
+
+    def make_ops(lay, Tg, mode):
+        ops = CudaShardOps(cabi, dev, lay, Hq, Tg)
+        if world > 1:
+            if mode == "nccl":
+                ops.setup_nccl(dist)
+            elif not ops.setup_p2p(dist, one_launch=(mode == "decode"), low_latency=(mode != "merge")):
+                raise RuntimeError("peer inboxes could not be mapped (no peer access between the GPUs?)")
+        return ops
+
+    par = long_decode_parity(dev, cabi, dist, make_ops)
+    lo, hi = shard_range(T, world, rank)
+    Tg = hi - lo
     n_pages = (Tg + P - 1) // P
     page_elems = Hkv * P * D
     shard_bytes = 2 * n_pages * page_elems * 2
     nbuf = max(1, -(-(512 << 20) // shard_bytes))        # rotate buffers so that a shard never sits in L2
     rng = np.random.default_rng(c["seed"] + rank)
-    bits = orc.to_bf16_bits(rng.standard_normal(32 * page_elems, dtype=np.float32))
     pools = []
     for _ in range(nbuf):
-        pair = []
-        for _kv in range(2):
-            t = torch.empty(n_pages * page_elems, dtype=torch.int16, device="cuda")
-            src = torch.from_numpy(np.roll(bits, int(rng.integers(0, bits.size))).view(np.int16)).cuda()
-            reps = -(-t.numel() // src.numel())
-            t.copy_(src.repeat(reps)[: t.numel()])
-            pair.append(t)
+        pair = [dev.malloc(n_pages * page_elems * 2) for _ in range(2)]
+        for dst in pair:
+            fill_random_bf16(dev, cabi, dst, n_pages * page_elems, rng)
         pools.append(pair)
-    table = torch.arange(n_pages, dtype=torch.int32, device="cuda").reshape(B, n_pages)
-    lens = torch.full((B,), Tg, dtype=torch.int32, device="cuda")
-    q = torch.from_numpy(rng.standard_normal((B, 1, Hq, D), dtype=np.float32)).cuda()
-    if world > 1:
-        td.broadcast(q, src=0)
+    table = dev.upload(np.arange(n_pages, dtype=np.int32).reshape(B, n_pages))
+    lens = dev.upload(np.full(B, Tg, np.int32))
+    q = dev.upload(np.random.default_rng(c["seed"]).standard_normal((B, 1, Hq, D), dtype=np.float32))   # same q on every rank
+    layouts = [kv_layout(cabi, pools[i][0], pools[i][1], table, lens, B, Hkv, D, P, n_pages, n_pages) for i in range(nbuf)]
+    timings, n_splits, graphed = {}, 0, True
+    for mode in (LONG_MODES if world > 1 else ("decode",)):
+        ops = make_ops(layouts[0], Tg, mode)
+        dec = ShardedDecoder(dist, ops)
+        n_splits = ops.p.n_splits
+        for i in range(5):
+            ops.set_layout(layouts[i % nbuf]); dec.step(q)
+        dev.sync()
 
-    def layout(i):
-        l = cabi.KVLayout()
-        l.k_pages, l.v_pages, l.cache_dtype = pools[i][0].data_ptr(), pools[i][1].data_ptr(), cabi.BF16
-        l.block_table, l.seq_lens = table.data_ptr(), lens.data_ptr()
-        l.batch, l.num_kv_heads, l.head_dim, l.page_tokens, l.max_pages, l.num_pages = B, Hkv, D, P, n_pages, n_pages
-        return l
+        def run_steps():
+            for i in range(steps):
+                ops.set_layout(layouts[i % nbuf]); dec.step(q)
 
-    ops = CudaShardOps(cabi, dev, layout(0), Hq, Tg, torch, n_splits=n_splits)
-    fused = ""
-    mode = os.environ.get("GRILLY_EXCHANGE", "decode")     # profiling aid: "nccl" | "merge" | "decode"
-    if world > 1 and mode != "nccl":
-        # peers' inboxes over CUDA IPC; NCCL all-gather is the fallback
-        if ops.setup_p2p(td, one_launch=(mode == "decode"), low_latency=(mode != "merge")):
-            fused = "decode" if ops.one_launch else ("ll" if mode == "ll" else "merge")
-    dec = ShardedDecoder(td if world > 1 else _NoDist(), ops, lambda n, m: torch.empty((n, m), dtype=torch.float32, device="cuda"))
-    layouts = [layout(i) for i in range(nbuf)]
-    for i in range(5):
-        ops.set_layout(layouts[i % nbuf]); out = dec.step(q)
-    torch.cuda.synchronize()
-
-    def run_steps():
-        o = None
-        for i in range(steps):
-            ops.set_layout(layouts[i % nbuf]); o = dec.step(q)
-        return o
-
-    # The step is one to three small launches: replay `steps` of them from one CUDA graph so that launch
-    # latency does not hide the kernels.  The library's launches are captured like any
-    # other work on the capturing stream (grl_device_use_stream).
-    graph = None
-    try:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            cabi.check(L.grl_device_use_stream(dev.h, torch_stream_handle(torch)))
-            out = run_steps()
-        cabi.check(L.grl_device_use_stream(dev.h, torch_stream_handle(torch)))
-        graph.replay()
-        torch.cuda.synchronize()
-    except Exception as e:          # fall back to plain launches, and say so
-        graph = None
-        cabi.check(L.grl_device_use_stream(dev.h, torch_stream_handle(torch)))
-        sys.stderr.write(f"long decode: graph capture unavailable ({e}); timing plain launches\n")
-    best = None
-    e0, e1 = dev.event(), dev.event()
-    launches0 = L.grl_launch_count()
-    for _ in range(repeats):
-        dist["barrier"]()
-        dev.record(e0)
-        if graph is not None:
-            graph.replay()
-        else:
-            out = run_steps()
-        dev.record(e1)
-        torch.cuda.synchronize()
-        ms = dist["max"](dev.elapsed_ms(e0, e1))
-        best = ms if best is None else min(best, ms)
-    # this library's launches per step: the decode kernel merges its own splits; NCCL mode adds the final merge
-    # (the all-gather is NCCL's kernel), "merge" mode the step-counter bump and the exchange+merge kernel
-    launches = {"": 1 if world == 1 else 2, "merge": 3, "ll": 3, "decode": 1}[fused]
-    assert bool(torch.isfinite(out).all())
-    cabi.check(L.grl_device_use_stream(dev.h, None))
-    return best / steps, launches, ops.p.n_splits, nbuf, graph is not None, fused
+        # a step is one to three small launches: replay `steps` of them from one CUDA graph so that launch
+        # latency does not hide the kernels
+        g = C.c_void_p()
+        dist.barrier()
+        cabi.check(L.grl_graph_begin(dev.h))
+        run_steps()
+        cabi.check(L.grl_graph_end(dev.h, C.byref(g)))
+        cabi.check(L.grl_graph_launch(dev.h, g))
+        dev.sync()
+        best = None
+        e0, e1 = dev.event(), dev.event()
+        for _ in range(repeats):
+            dev.sync()
+            dist.barrier()
+            dev.record(e0)
+            cabi.check(L.grl_graph_launch(dev.h, g))
+            dev.record(e1)
+            dev.sync()
+            ms = dist.max(dev.elapsed_ms(e0, e1))
+            best = ms if best is None else min(best, ms)
+        L.grl_graph_destroy(g)
+        out = dev.download(ops.out, (B, 1, Hq, D), np.float32)
+        assert np.isfinite(out).all()
+        timings[mode] = best / steps
+        dist.barrier()
+        ops.close()
+    for pair in pools:
+        for x in pair:
+            dev.free(x)
+    for x in (table, lens, q):
+        dev.free(x)
+    launches = {"decode": 1, "ll": 3, "merge": 3, "nccl": 2}
+    return timings, launches, n_splits, nbuf, graphed, par
 
 
-class _NoDist:
-    def is_initialized(self):
-        return False
-
-
+# ------------------------------------------------------------------------------------- CPU baselines
 def cpu_baseline():
+    """The checker's C/OpenMP restatement of the reference's CPU attention, RoPE included, on a bounded sample."""
     os.environ["OMP_NUM_THREADS"] = str(os.cpu_count())
     from oracle import attention_oracle as orc
     from oracle import c_oracle
@@ -555,150 +856,191 @@ def cpu_baseline():
     heads = 32
     rng = np.random.default_rng(c["seed"])
     Q, K, V = (rng.standard_normal((1, heads, c["S"], c["D"]), dtype=np.float32) for _ in range(3))
-    pos = np.arange(c["S"])
     c_oracle.attention(Q[:, :2], K[:, :2], V[:, :2], causal=True)
     t0 = time.perf_counter()
     reps = 0
     while time.perf_counter() - t0 < 10.0 and reps < 8:
-        c_oracle.attention(orc.rope_interleaved(Q, pos, c["theta"]), orc.rope_interleaved(K, pos, c["theta"]), V, causal=True)
+        c_oracle.attention(c_oracle.rope_interleaved(Q, c["theta"]), c_oracle.rope_interleaved(K, c["theta"]), V, causal=True)
         reps += 1
     dt = time.perf_counter() - t0
-    fl = 4 * c["D"] * heads * (c["S"] * (c["S"] + 1) // 2) * reps
-    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": c_oracle.num_threads(), "kind": "port",
-            "sample": f"{reps} passes over {heads} of 128 (batch, head) slices of cfg2 (RoPE + causal attention), C/OpenMP oracle"}
+    fl = causal_flops(c["D"], heads, [c["S"]]) * reps
+    res = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": c_oracle.num_threads(), "kind": "port",
+           "sample": f"{reps} passes over {heads} of 128 (batch, head) slices of cfg2 (RoPE + causal attention), C/OpenMP oracle"}
+    # the numpy form the reference's tests define (tests/test_attention.py:20-35), restated in oracle/attention_oracle.py
+    nh = 2
+    pos = np.arange(c["S"])
+    mask = orc.causal_length_mask(1, nh, c["S"], None, True)
+    t0 = time.perf_counter()
+    orc.attention_4d(orc.rope_interleaved(Q[:, :nh], pos, c["theta"]), orc.rope_interleaved(K[:, :nh], pos, c["theta"]), V[:, :nh], mask=mask)
+    dt = time.perf_counter() - t0
+    res["numpy"] = {"value": causal_flops(c["D"], nh, [c["S"]]) / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(),
+                    "sample": f"one pass over {nh} of 128 (batch, head) slices, numpy restatement of the reference's _ref_attention_4d "
+                              "(dense (S,S) scores with a tril mask, so it also computes the masked half)"}
+    return res
 
 
+def cpu_baseline_decode():
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count())
+    from oracle import c_oracle
+    c = CFG3
+    Bs, T = 4, c["T0"]
+    rng = np.random.default_rng(c["seed"])
+    k = rng.standard_normal((Bs, T, c["Hkv"], c["D"]), dtype=np.float32)
+    v = rng.standard_normal((Bs, T, c["Hkv"], c["D"]), dtype=np.float32)
+    q = rng.standard_normal((Bs, 1, c["Hq"], c["D"]), dtype=np.float32)
+    c_oracle.gqa_decode(q, k, v)
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < 4.0 and reps < 200:
+        c_oracle.gqa_decode(q, k, v)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": Bs / dt, "unit": "tokens/s", "cores": c_oracle.num_threads(), "kind": "port",
+            "sample": f"{reps} decode steps of {Bs} of the 32 sequences at cache length {T} (fp32 cache, attention only: no RoPE, no append), "
+                      "C/OpenMP oracle_gqa_decode_f32"}
+
+
+def cpu_baseline_long():
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count())
+    from oracle import c_oracle
+    c = CFG4
+    Ts = c["T"] // 4
+    rng = np.random.default_rng(c["seed"])
+    k = rng.standard_normal((1, Ts, c["Hkv"], c["D"]), dtype=np.float32)
+    v = rng.standard_normal((1, Ts, c["Hkv"], c["D"]), dtype=np.float32)
+    q = rng.standard_normal((1, 1, c["Hq"], c["D"]), dtype=np.float32)
+    c_oracle.gqa_decode(q, k, v)
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < 4.0 and reps < 200:
+        c_oracle.gqa_decode(q, k, v)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": 1.0 / (dt * 4), "unit": "tokens/s", "cores": c_oracle.num_threads(), "kind": "port",
+            "sample": f"{reps} decode steps over a quarter of the cache ({Ts} of {c['T']} tokens, fp32), time scaled by 4 (the step is linear "
+                      "in the cache length), C/OpenMP oracle_gqa_decode_f32"}
+
+
+# ------------------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--skip-decode", action="store_true")
-    ap.add_argument("--skip-prefill", action="store_true", help="profiling aid: run the decode workload only")
-    ap.add_argument("--no-graph", action="store_true", help="profiling aid: plain launches instead of graph replay")
+    ap.add_argument("--legs", default=",".join(ALL_LEGS), help="comma-separated subset of: " + ", ".join(ALL_LEGS))
+    ap.add_argument("--no-graph", action="store_true", help="cfg3 as plain launches instead of graph replay (for a profiler's launch list)")
     ap.add_argument("--decode-repeats", type=int, default=3)
-    ap.add_argument("--decode-splits", type=int, default=0, help="profiling aid: force the split-KV count (0 = library choice)")
-    ap.add_argument("--variant", default="cfg2", choices=["cfg2", "norope", "noncausal"],
-                    help="profiling aid: drop RoPE or the causal mask from the prefill workload")
-    ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--skip-long", action="store_true", help="skip the long-context (cfg4) decode leg")
-    ap.add_argument("--skip-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    legs = set(x for x in args.legs.split(",") if x)
+    unknown = legs - set(ALL_LEGS)
+    if unknown:
+        ap.error(f"unknown legs {sorted(unknown)}")
 
     if args.impl == "reference":
         return run_reference(args)
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    dist = {"rank": rank, "world": world, "local_rank": local_rank, "barrier": lambda: None, "max": lambda x: x}
-    if world > 1:
-        import torch
-        import torch.distributed as td
-        torch.cuda.set_device(local_rank)
-        td.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-
-        def _barrier():
-            td.barrier()
-            torch.cuda.synchronize()
-
-        def _max(x):
-            t = torch.tensor([x], dtype=torch.float64, device="cuda")
-            td.all_reduce(t, op=td.ReduceOp.MAX)
-            return float(t.item())
-
-        dist["barrier"], dist["max"] = _barrier, _max
-
-    if world == 1 and not (args.skip_decode or args.skip_long):
-        import torch
-        torch.cuda.set_device(local_rank)
+    dist = Dist()
+    rank, world, local_rank = dist.rank, dist.world, dist.local_rank
+    os.environ["GRILLY_GPU_INDEX"] = str(local_rank)     # the op layer's device selector
     from grilly_next import cabi
-    if os.environ.get("GRL_LIB_OVERRIDE"):      # profiling aid: try an experimental build of the library
-        cabi.LIB_PATH = os.environ["GRL_LIB_OVERRIDE"]
     dev = cabi.Device(local_rank)          # raises if the CUDA library or the GPU is missing: no fallback
     L = dev.L
     pk = peaks()
-
-    if args.skip_prefill:
-        dms, dl, nsplit = bench_decode(dev, cabi, dist, args.decode_repeats, not args.no_graph, args.decode_splits)
-        print(json.dumps({"decode_ms": dms, "launches": int(dl), "n_splits": nsplit}), flush=True)
-        dev.close()
-        return
-    ms, launches, clocks = bench_prefill(dev, cabi, args, dist)
-    fl = prefill_flops(CFG2)
-    if args.variant == "noncausal":
-        fl = 4 * CFG2["D"] * CFG2["B"] * CFG2["H"] * CFG2["S"] * CFG2["S"]
-    tflops_gpu = fl * args.steps / (ms * 1e-3) / 1e12
-    value = tflops_gpu * world
-    line = {
-        "metric": "prefill_attn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "cfg2: FlashAttention-2+RoPE causal prefill, B4 H32 S2048 D128, bf16 in / fp32 out, per GPU"
-                   + ("" if args.variant == "cfg2" else f" [variant {args.variant}: NOT the benchmark configuration]"),
-                   "flops_per_step_per_gpu": fl, "l2": "inputs larger than L2 (320 MiB per step)",
-                   "parallelism": f"replica per GPU x{world}, no collective"},
-        "clocks": clocks, "gpu_launches": int(launches),
-        "roofline": prefill_roofline(tflops_gpu, ms, pk),
-    }
-
-    if not args.skip_decode:
-        dms, dl, nsplit = bench_decode(dev, cabi, dist, args.decode_repeats, not args.no_graph, args.decode_splits)
-        c = CFG3
-        toks = c["B"] * c["steps"] / (dms * 1e-3)
-        gbs = decode_bytes(c) / (dms * 1e-3) / 1e9
-        line["decode"] = {"metric": "decode_tokens_per_s", "value": toks * world, "unit": "tokens/s",
-                          "ms_per_step": dms / c["steps"], "workload": "cfg3: GQA decode B32 Hq32/Hkv8 D128 KV 4096->4352, 256 steps, bf16 paged cache, CUDA-graph replay, per GPU",
-                          "gpu_launches": int(dl), "n_splits": nsplit,
-                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
-                                       "traffic": DECODE_TRAFFIC_BYTES, "peak_source": pk["src"], "frac_of_nominal_8000": gbs / 8000.0,
-                                       "note": "achieved = algorithmic bytes of the 256-step run / its time (append + decode + merge per step)",
-                                       "kernel": "decode_mma_kernel"}}
-
-    if not args.skip_decode and world == 1:
-        sel_us, cmp_us, moved = bench_evict(dev, cabi)
-        gbs = moved / (cmp_us * 1e-6) / 1e9
-        line["evict"] = {"workload": "cfg3-sized cache (B32 Hkv8 D128 4096 tokens bf16): H2O selection of a quarter of every sequence, "
-                                     "then compaction", "select_us": sel_us, "compact_us": cmp_us,
-                         "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
-                                      "peak_source": pk["src"], "note": "surviving K/V rows read once and written once; rows that stay in place are skipped, so this is an upper bound on the traffic"}}
-    if not args.skip_decode and not args.skip_long:
-        lms, ll, lsplit, nbuf, graphed, fused = bench_long_decode(dev, cabi, dist)
-        kv_bytes = 2 * CFG4["Hkv"] * CFG4["D"] * 2 * CFG4["T"]
-        gbs = kv_bytes / (lms * 1e-3) / 1e9
-        line["decode_long"] = {"metric": "decode_long_tokens_per_s", "value": 1.0 / (lms * 1e-3), "unit": "tokens/s",
-                               "ms_per_step": lms, "scaling": "strong",
-                               "workload": f"cfg4: GQA decode B1 Hq32/Hkv8 D128 KV 131072 bf16 split over {world} GPU(s); "
-                                           + ("18 splits merged inside the decode kernel" if world == 1 else "per-GPU partial (16,640 B/rank) + ")
-                                           + {"decode": "exchange over NVLink peer stores and LSE merge inside the decode kernel (one launch per step)",
-                                              "merge": "exchange over NVLink peer stores fused with the LSE merge",
-                                              "ll": "exchange over NVLink peer stores ({value, step} pairs, no flag) fused with the LSE merge",
-                                              "": "NCCL all-gather + LSE merge" if world > 1 else ""}[fused]
-                                           + f"; {nbuf} rotating KV buffers (L2); "
-                                           + ("CUDA-graph replay" if graphed else "plain launches"),
-                               "gpu_launches_per_step": int(ll), "n_splits": lsplit,
-                               "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"] * world, "unit": "GB/s",
-                                            "frac": gbs / (pk["hbm"] * world), "peak_source": pk["src"] + f" x{world}"}}
-    if not args.skip_e2e:
-        os.environ["GRILLY_GPU_INDEX"] = str(local_rank)     # the op layer's device selector
-        dt, h2d, d2h = bench_prefill_e2e(args, L, min(args.steps, 5), dist)
-        line["e2e"] = {"value": fl / dt / 1e12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                       "ms_per_step": dt * 1e3, "api": "grilly_core.flash_attention2(dtype='bf16', out=pinned), pinned fp32 host arrays in and out; "
-                              "h2d bytes are what crosses the link (the op rounds inputs to bf16 on host threads; 402,653,184 B of fp32 are read)"}
-        if not args.skip_decode:
+    line = {"metric": "prefill_attn_tflops", "value": None, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic"}
+    try:
+        if "prefill" in legs:
+            sampler = ClockSampler(local_rank)
+            sampler.start()
+            r = bench_prefill(dev, cabi, args, dist, pk, sampler)
+            sampler.stop()
+            line.update({
+                "value": r["tflops_gpu"] * world, "ms_per_step": r["ms"] / args.steps,
+                "config": {"workload": "cfg2: FlashAttention-2+RoPE causal prefill, B4 H32 S2048 D128, bf16 in / fp32 out, per GPU",
+                           "flops_per_step_per_gpu": r["flops"], "l2": "inputs larger than L2 (320 MiB per step)",
+                           "parallelism": f"replica per GPU x{world}, no collective",
+                           "rope": "rotation of Q and K inside the attention kernel (device-resident bf16 inputs, unrotated)"},
+                "clocks": r["clocks"], "gpu_launches": int(r["launches"]),
+                "roofline": prefill_roofline(r["tflops_gpu"], r["ms"], pk, PREFILL_TRAFFIC_BYTES),
+                "parity": r["parity"], "sustained": r["sustained"]})
+            if "strong" in r:
+                line["strong_scaling"] = {"cfg2": r["strong"]}
+        if "cfg1" in legs:
+            line["cfg1"], qkv1 = bench_cfg1(dev, cabi, args, dist)
+            if "e2e" in legs:
+                line["cfg1"]["e2e"] = bench_cfg1_e2e(qkv1, dist)
+        if "cfg5" in legs:
+            r5 = bench_cfg5(dev, cabi, args, dist, pk)
+            if "strong" in r5:
+                line.setdefault("strong_scaling", {})["cfg5"] = r5.pop("strong")
+            line["cfg5"] = r5
+        if "decode" in legs:
+            dms, dl, nsplit, dpar = bench_decode(dev, cabi, dist, args.decode_repeats, not args.no_graph)
+            c = CFG3
+            toks = c["B"] * c["steps"] / (dms * 1e-3)
+            gbs = decode_bytes(c) / (dms * 1e-3) / 1e9
+            line["decode"] = {"metric": "decode_tokens_per_s", "value": toks * world, "unit": "tokens/s",
+                              "ms_per_step": dms / c["steps"],
+                              "workload": "cfg3: GQA decode B32 Hq32/Hkv8 D128 KV 4096->4352, 256 steps, bf16 paged cache, "
+                                          + ("CUDA-graph replay" if not args.no_graph else "plain launches") + ", per GPU",
+                              "gpu_launches": int(dl), "n_splits": nsplit, "parity": dpar,
+                              "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
+                                           "traffic": DECODE_TRAFFIC_BYTES, "peak_source": pk["src"], "frac_of_nominal_8000": gbs / 8000.0,
+                                           "note": "achieved = algorithmic bytes of the 256-step run / its time (append + decode + merge per step)",
+                                           "kernel": "decode_mma_kernel"}}
+        if "evict" in legs and world == 1:
+            sel_us, cmp_us, moved = bench_evict(dev, cabi)
+            gbs = moved / (cmp_us * 1e-6) / 1e9
+            line["evict"] = {"workload": "cfg3-sized cache (B32 Hkv8 D128 4096 tokens bf16): H2O selection of a quarter of every sequence, "
+                                         "then compaction", "select_us": sel_us, "compact_us": cmp_us,
+                             "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
+                                          "peak_source": pk["src"], "note": "surviving K/V rows read once and written once; rows that stay in place are skipped, so this is an upper bound on the traffic"}}
+        if "long" in legs:
+            timings, launches, lsplit, nbuf, graphed, lpar = bench_long_decode(dev, cabi, dist)
+            kv_bytes = 2 * CFG4["Hkv"] * CFG4["D"] * 2 * CFG4["T"]
+            lms = timings["decode"]
+            gbs = kv_bytes / (lms * 1e-3) / 1e9
+            line["decode_long"] = {
+                "metric": "decode_long_tokens_per_s", "value": 1.0 / (lms * 1e-3), "unit": "tokens/s", "ms_per_step": lms, "scaling": "strong",
+                "workload": f"cfg4: GQA decode B1 Hq32/Hkv8 D128 KV 131072 bf16 split over {world} GPU(s); "
+                            + (f"{lsplit} splits merged inside the decode kernel" if world == 1 else "per-GPU partial (16,640 B/rank) + " + LONG_MODE_TEXT["decode"])
+                            + f"; {nbuf} rotating KV buffers (L2); CUDA-graph replay",
+                "gpu_launches_per_step": launches["decode"], "n_splits": lsplit, "parity": lpar,
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"] * world, "unit": "GB/s",
+                             "frac": gbs / (pk["hbm"] * world), "peak_source": pk["src"] + f" x{world}"}}
+            if world > 1:
+                line["decode_long"]["ms_per_step_by_exchange"] = {m: {"ms_per_step": t, "launches_per_step": launches[m], "how": LONG_MODE_TEXT[m]}
+                                                                  for m, t in timings.items()}
+        if "e2e" in legs and "prefill" in legs:
+            fl = causal_flops(CFG2["D"], CFG2["B"] * CFG2["H"], [CFG2["S"]])
+            dt, h2d, d2h, epar, info = bench_prefill_e2e(args, L, min(args.steps, 5), dist)
+            line["e2e"] = {"value": fl / dt / 1e12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                           "ms_per_step": dt * 1e3, "parity": epar,
+                           "api": "grilly_core.flash_attention2(dtype='bf16', out=pinned), pinned fp32 host arrays in and out; "
+                                  "h2d bytes are what crosses the link (the op rounds inputs to bf16 on host threads; 402,653,184 B of fp32 are read)"}
+            if info:
+                line["e2e"]["pipeline"] = info
+        if "e2e" in legs and "decode" in legs:
             ddt, dh2d, dd2h = bench_decode_e2e(dist)
             line["decode"]["e2e"] = {"value": CFG3["B"] / ddt * world, "unit": "tokens/s", "h2d_bytes_per_step": dh2d,
                                      "d2h_bytes_per_step": dd2h, "ms_per_step": ddt * 1e3, "api": "grilly_core.decode_step(out=pinned), pinned fp32 host arrays in and out"}
-    if rank == 0 and world == 1 and not args.skip_cpu:
-        line["cpu_baseline"] = cpu_baseline()
+        if "cpu" in legs and rank == 0 and world == 1:
+            if "prefill" in legs:
+                line["cpu_baseline"] = cpu_baseline()
+            if "decode" in legs:
+                line["decode"]["cpu_baseline"] = cpu_baseline_decode()
+            if "long" in legs:
+                line["decode_long"]["cpu_baseline"] = cpu_baseline_long()
+    except ParityError as e:
+        sys.stderr.write(f"PARITY FAILURE on rank {rank}: {e}\n")
+        sys.stderr.flush()
+        os._exit(3)
 
     dev.close()
-    if world > 1:
-        import torch.distributed as td
-        td.barrier()
-        td.destroy_process_group()
+    dist.close()
     if rank == 0:
         print(json.dumps(line), flush=True)
 

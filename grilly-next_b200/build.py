@@ -25,7 +25,7 @@ CUDA_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC", "-ccbin", HOST_CXX, "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
 CU_SOURCES = ["device.cu", "flash.cu", "prefill_fp32.cu", "prefill_sm100.cu", "decode_splitkv.cu", "decode_mma.cu", "p2p_merge.cu", "kv_evict.cu",
-              "kv_cache.cu", "rope_mask.cu"]
+              "kv_cache.cu", "rope_mask.cu", "nccl_group.cu"]
 HEADERS = ["common.cuh", "tmem_ops.cuh", os.path.join(ROOT, "include", "grilly_cuda.h")]
 
 
@@ -62,7 +62,7 @@ def build_cuda(force=False, verbose=False):
             raise RuntimeError(f"nvcc failed on {src}")
     lib = os.path.join(LIBDIR, "libgrilly_cuda.so")
     if force or procs or _newer(lib, objs):
-        _run([NVCC, "-shared", "-ccbin", HOST_CXX, "-o", lib] + objs + ["-lcudart"], verbose)
+        _run([NVCC, "-shared", "-ccbin", HOST_CXX, "-o", lib] + objs + ["-lcudart", "-ldl"], verbose)
     return lib
 
 

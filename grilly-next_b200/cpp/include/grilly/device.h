@@ -41,6 +41,10 @@ public:
     /// Pinned host scratch kept for the life of the device (slot 0..5): staging for converted uploads.
     static constexpr int kStagingSlots = 6;
     void* pinnedStaging(int slot, size_t bytes);
+    /// Waits (without limit, ignoring errors) for everything queued on the main, upload and download queues.
+    /// Error paths call it before they hand buffers back to the pool: a buffer that a kernel or a copy in
+    /// flight still touches must not be re-acquired, and a timed-out submit leaves work in flight.
+    void quiesce() noexcept;
 
 private:
     void open(int ordinal);

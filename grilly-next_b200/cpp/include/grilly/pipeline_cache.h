@@ -2,7 +2,9 @@
 // Kernel-plan registry.  In the reference, PipelineCache holds SPIR-V pipelines and an LRU of
 // descriptor sets (cpp/include/grilly/pipeline_cache.h:35-115).  CUDA kernels are linked into
 // the library, so what remains is the bookkeeping the bindings expose: named plans looked up
-// per dispatch, with the same hits / misses / evictions / cachedSets counters.
+// per dispatch, with the same hits / misses / evictions / cachedSets counters.  The descriptor
+// sets themselves have a counterpart inside the CUDA library: the tensor maps (TMA descriptors)
+// of a launch are cached per (pointer, shape, box) and reported here beside the plan counters.
 #include <cstdint>
 #include <list>
 #include <mutex>
@@ -15,6 +17,8 @@ namespace grilly {
 
 struct CacheStats {
     uint64_t hits = 0, misses = 0, evictions = 0, cachedSets = 0;
+    // encoded tensor maps kept by the CUDA library per (pointer, shape, box): grl_tensor_map_cache_stats
+    uint64_t tensorMapHits = 0, tensorMapMisses = 0, tensorMapsCached = 0;
 };
 
 class PipelineCache {

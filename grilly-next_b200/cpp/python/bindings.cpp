@@ -17,6 +17,7 @@
 #include "grilly/host_workers.h"
 #include "grilly/ops/attention.h"
 #include "grilly/ops/kv_cache.h"
+#include "grilly/ops/sharded_decode.h"
 #include "grilly/ops/rope.h"
 #include "grilly/pipeline_cache.h"
 
@@ -166,6 +167,13 @@ PYBIND11_MODULE(grilly_core, m) {
             auto s = c.cache.cacheStats();
             py::dict d;
             d["hits"] = s.hits; d["misses"] = s.misses; d["evictions"] = s.evictions; d["cached_sets"] = s.cachedSets;
+            return d;
+        })
+        // additive: the TMA descriptors the CUDA library keeps per (pointer, shape, box)
+        .def("tensor_map_stats", [](const GrillyCoreContext& c) {
+            auto s = c.cache.cacheStats();
+            py::dict d;
+            d["hits"] = s.tensorMapHits; d["misses"] = s.tensorMapMisses; d["cached"] = s.tensorMapsCached;
             return d;
         });
 
@@ -710,6 +718,63 @@ PYBIND11_MODULE(grilly_core, m) {
         py::arg("rope_theta") = 10000.0f, py::arg("rope_scaling") = 1.0f, py::arg("rope_mode") = "interleaved",
         py::arg("scale") = 0.0f, py::arg("out") = py::none(), py::arg("accumulate_scores") = false,
         "RoPE(q,k) at the current position, append k/v, attend over the cache");
+
+    // ---- KV-sharded decode across processes (one per GPU): NCCL behind the C ABI
+    struct PyShardGroup {
+        ContextPtr ctx;
+        ops::ShardGroup g;
+        ~PyShardGroup() { ops::destroyShardGroup(ctx->pool, g); }
+    };
+    m.def("shard_group_unique_id", []() {
+        auto id = ops::shardGroupUniqueId();
+        return py::bytes(reinterpret_cast<const char*>(id.data()), id.size());
+    }, "128-byte id that rank 0 creates and hands to the other ranks before ShardGroup(...)");
+    m.def("shard_range", [](uint64_t total, int world, int rank) { return ops::shardRange(total, world, rank); },
+          py::arg("total_tokens"), py::arg("world"), py::arg("rank"), "Contiguous [start, end) of a rank's tokens");
+    py::class_<PyShardGroup, std::shared_ptr<PyShardGroup>>(m, "ShardGroup")
+        .def(py::init([](ContextPtr ctx, py::bytes id, int rank, int world) {
+                 const std::string raw = id;
+                 if (raw.size() != 128) throw std::runtime_error("ShardGroup: the id must be the 128 bytes of shard_group_unique_id()");
+                 auto g = std::make_shared<PyShardGroup>();
+                 g->ctx = ctx;
+                 {
+                     py::gil_scoped_release nogil;
+                     g->g = ops::createShardGroup(ctx->device, reinterpret_cast<const uint8_t*>(raw.data()), rank, world);
+                 }
+                 return g;
+             }),
+             py::arg("device"), py::arg("unique_id"), py::arg("rank"), py::arg("world"),
+             "Collective: every rank constructs it with the same id")
+        .def_property_readonly("rank", [](const PyShardGroup& g) { return g.g.rank; })
+        .def_property_readonly("world", [](const PyShardGroup& g) { return g.g.world; });
+    m.def(
+        "sharded_decode_step",
+        [](ContextPtr ctx, ops::KVCache& kv, std::shared_ptr<PyShardGroup> group, FArr q, float scale,
+           std::optional<py::array_t<float>> outArr, double timeoutMs) {
+            const auto& c = kv.config;
+            if (q.ndim() != 4 || q.shape(0) != c.batchSize || q.shape(1) != 1 || q.shape(3) != c.headDim)
+                throw std::runtime_error("q must be (batch, 1, num_q_heads, head_dim)");
+            const uint32_t Hq = uint32_t(q.shape(2));
+            py::array_t<float> out;
+            if (outArr.has_value()) {
+                out = *outArr;
+                if (out.size() != q.size() || !(out.flags() & py::array::c_style) || !out.writeable())
+                    throw std::runtime_error("out must be a writable C-contiguous float32 array of q's size");
+            } else {
+                out = py::array_t<float>({py::ssize_t(c.batchSize), py::ssize_t(1), py::ssize_t(Hq), py::ssize_t(c.headDim)});
+            }
+            const float* qp = q.data();
+            float* op = out.mutable_data();
+            {
+                py::gil_scoped_release nogil;
+                ops::shardedDecodeStep(ctx->batch, ctx->pool, ctx->cache, kv, group->g, qp, op, Hq, scale,
+                                       uint64_t(timeoutMs * 1e6));
+            }
+            return out;
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("group"), py::arg("q"), py::arg("scale") = 0.0f,
+        py::arg("out") = py::none(), py::arg("timeout_ms") = 2000.0,
+        "Decode step over a KV cache sharded across the group's GPUs: local decode, NCCL all-gather of the partials, merge");
 
     // ---- DeviceGroup: the GPUs of one node behind one object, one Device (own stream, own pool) each.
     // flash_attention2 splits the heads in contiguous runs over the devices, one host thread per device

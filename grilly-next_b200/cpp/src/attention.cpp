@@ -2,6 +2,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
+#include <exception>
 #include <string>
 #include <vector>
 
@@ -23,6 +24,8 @@ struct Scoped {   // releases pooled buffers on every exit path
     std::vector<GrillyBuffer*> bufs;
     explicit Scoped(BufferPool& p) : pool(p) {}
     ~Scoped() {
+        // leaving through an exception: copies and kernels may still be in flight on the three queues
+        if (std::uncaught_exceptions() > 0) pool.device().quiesce();
         for (auto* b : bufs) pool.release(*b);
     }
     GrillyBuffer& add(GrillyBuffer& b) {

@@ -179,6 +179,7 @@ void kvCacheAppendRope(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
         if (qIn && qOut) check(grl_memcpy_d2h(dev, qOut, qo.dptr, qElems * 4), "kvCacheAppend: q download");
         batch.submit();
     } catch (...) {
+        pool.device().quiesce();   // nothing in flight may still touch the buffers released below
         pool.release(kb); pool.release(vb); pool.release(qb); pool.release(qo);
         throw;
     }
@@ -215,6 +216,7 @@ void kvCacheDecode(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, 
         check(grl_memcpy_d2h(dev, decodedValues, vb.dptr, n * 4), "kvCacheDecode: download");
         batch.submit();
     } catch (...) {
+        pool.device().quiesce();   // nothing in flight may still touch the buffers released below
         pool.release(kb); pool.release(vb);
         throw;
     }
@@ -303,6 +305,7 @@ void gqaAttention(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, c
         check(grl_memcpy_d2h(dev, out, ob.dptr, n * 4), "gqaAttention: download");
         batch.submit();
     } catch (...) {
+        pool.device().quiesce();   // nothing in flight may still touch the buffers released below
         pool.release(qb); pool.release(ob); pool.release(ws);
         throw;
     }
@@ -350,6 +353,7 @@ void decodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVC
         check(grl_memcpy_d2h(dev, out, ob.dptr, qn * 4), "decodeStep: download");
         batch.submit();
     } catch (...) {
+        pool.device().quiesce();   // nothing in flight may still touch the buffers released below
         releaseAll();
         throw;
     }
@@ -432,6 +436,7 @@ void kvCacheEvictH2O(CommandBatch& batch, BufferPool& pool, PipelineCache& cache
         check(grl_kv_evict_lowest(dev, &l, &m, int(numEvict)), "kvCacheEvictH2O");
         batch.submit();
     } catch (...) {
+        pool.device().quiesce();   // nothing in flight may still touch the buffers released below
         pool.release(scores);
         throw;
     }
@@ -499,6 +504,7 @@ void kvCacheTrainEvictionHead(CommandBatch& batch, BufferPool& pool, PipelineCac
               "kvCacheTrainEvictionHead");
         batch.submit();
     } catch (...) {
+        pool.device().quiesce();   // nothing in flight may still touch the buffers released below
         pool.release(feat); pool.release(attn); pool.release(scratch);
         throw;
     }
@@ -526,6 +532,7 @@ void kvCacheEvictSpeculative(CommandBatch& batch, BufferPool& pool, PipelineCach
                   "kvCacheEvictSpeculative");
             batch.submit();
         } catch (...) {
+            pool.device().quiesce();   // nothing in flight may still touch the buffers released below
             pool.release(feat);
             throw;
         }
@@ -554,6 +561,7 @@ void kvCacheCompact(CommandBatch& batch, BufferPool& pool, PipelineCache& cache,
         check(grl_memcpy_d2h(dev, lens.data(), kv.seqLens.dptr, lens.size() * 4), "kvCacheCompact: lengths");
         batch.submit();
     } catch (...) {
+        pool.device().quiesce();   // nothing in flight may still touch the buffers released below
         pool.release(scratch);
         throw;
     }

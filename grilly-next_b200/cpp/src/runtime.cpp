@@ -48,9 +48,16 @@ grl_device* GrillyDevice::downloadQueue() {
     return down_;
 }
 
+void GrillyDevice::quiesce() noexcept {
+    if (up_) grl_sync(up_, 0);
+    if (dev_) grl_sync(dev_, 0);
+    if (down_) grl_sync(down_, 0);
+}
+
 void* GrillyDevice::pinnedStaging(int slot, size_t bytes) {
     if (slot < 0 || slot >= kStagingSlots) throw std::runtime_error("GrillyDevice::pinnedStaging: bad slot");
     if (stagingBytes_[slot] < bytes) {
+        quiesce();      // an upload in flight may still read the old staging block
         if (staging_[slot]) grl_host_free(staging_[slot]);
         staging_[slot] = nullptr;
         stagingBytes_[slot] = 0;
@@ -267,8 +274,17 @@ bool PipelineCache::getOrCreate(const std::string& key) {
 }
 
 CacheStats PipelineCache::cacheStats() const {
-    std::lock_guard<std::mutex> lock(mu_);
-    return stats_;
+    CacheStats s;
+    {
+        std::lock_guard<std::mutex> lock(mu_);
+        s = stats_;
+    }
+    // the tensor maps the library keeps per (pointer, shape, box): the descriptor sets of this build
+    int64_t h = 0, m = 0, c = 0;
+    if (grl_tensor_map_cache_stats(device_.handle(), &h, &m, &c) == GRL_OK) {
+        s.tensorMapHits = uint64_t(h); s.tensorMapMisses = uint64_t(m); s.tensorMapsCached = uint64_t(c);
+    }
+    return s;
 }
 
 // ---------------------------------------------------------------- CommandBatch

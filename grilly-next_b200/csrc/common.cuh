@@ -1,16 +1,34 @@
 // Shared host/device helpers for the C-ABI kernels.
 #pragma once
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
 
 #include <atomic>
 #include <map>
 #include <mutex>
 #include <string>
 #include <tuple>
+#include <vector>
 
 #include "grilly_cuda.h"
+
+namespace grl {
+// Key of a cached tiled tensor map (bf16 elements): everything cuTensorMapEncodeTiled is given.
+struct TmapKey {
+    const void* ptr;
+    uint32_t rank;
+    uint32_t swizzle_128b;     // 1: 128-byte swizzle, 0: none
+    uint64_t dims[3];
+    uint64_t strides[2];       // bytes, dimensions 1..rank-1
+    uint32_t box[3];
+    uint32_t pad;
+};
+constexpr long long kDefaultWaitLimitCycles = 2000000000LL;       // ~1 s at 2 GHz: mbarrier waits inside a kernel
+constexpr long long kDefaultPeerWaitLimitCycles = 1000000000LL;   // ~0.5 s: a peer GPU that never posts
+}  // namespace grl
 
 struct grl_device {
     int ordinal = 0;
@@ -18,9 +36,19 @@ struct grl_device {
     cudaStream_t stream = nullptr;   // the stream launches go to (own_stream or an adopted one)
     cudaDeviceProp prop{};
     std::mutex mu;
-    // RoPE cos/sin tables, float2 (cos, sin) per (position, pair), keyed by
-    // (positions, head_dim, theta bits, scaling bits).
-    std::map<std::tuple<int, int, uint32_t, uint32_t>, float2*> rope_tables;
+    // RoPE cos/sin tables, float2 (cos, sin) per (position, pair), one per (head_dim, theta bits,
+    // scaling bits); a table covers `first` positions and is replaced by a longer one on demand.
+    std::map<std::tuple<int, uint32_t, uint32_t>, std::pair<int, float2*>> rope_tables;
+    std::vector<float2*> retired_tables;   // replaced tables: kernels in flight may still read them; freed at close
+    // Tensor maps already encoded for this device (the descriptor-set cache of the reference's
+    // PipelineCache, cpp/src/pipeline_cache.cpp:217-305): a launch looks its maps up by
+    // (pointer, shape, box) instead of encoding them again.
+    std::vector<std::pair<grl::TmapKey, CUtensorMap>> tmaps;
+    size_t tmap_next = 0;
+    long long tmap_hits = 0, tmap_misses = 0;
+    // Cycle budgets of the bounded device-side waits (grl_device_set_wait_limits).
+    long long wait_limit_cycles = grl::kDefaultWaitLimitCycles;
+    long long peer_wait_limit_cycles = grl::kDefaultPeerWaitLimitCycles;
     // Status word written by kernels with bounded waits; read back by grl_sync when dirty.
     int32_t* d_status = nullptr;   // device int32[4], followed by the arrival counters below
     bool status_dirty = false;
@@ -46,7 +74,6 @@ int set_error(int code, const char* fmt, ...);
 
 // Peer inboxes of the cross-GPU merge, by value in kernel parameters (filled from grl_exchange_params).
 constexpr int kMaxPeers = 16;
-constexpr long long kPeerWaitLimitCycles = 1000000000LL;   // ~0.5 s: a missing peer ends in an error code, not a hang
 struct PeerExchange {
     float* inbox;                        // local: [2][world][n]
     unsigned int* flags;                 // local: [2][world][flag_slots]
@@ -54,8 +81,12 @@ struct PeerExchange {
     unsigned int* peer_flags[kMaxPeers];
     unsigned int* seq;                   // local step counter
     int rank, world, flag_slots;
+    long long wait_cycles;               // a missing peer ends in an error code after this many cycles, not in a hang
 };
-int fill_peer_exchange(const grl_exchange_params* p, PeerExchange* x);
+int fill_peer_exchange(grl_device* dev, const grl_exchange_params* p, PeerExchange* x);
+
+// Cached cuTensorMapEncodeTiled for bf16 tensors (zero fill out of bounds, 256-byte L2 promotion).
+int get_tensor_map(grl_device* dev, const TmapKey& key, CUtensorMap* out);
 
 #ifdef __CUDACC__
 // Low-latency inbox element: {value bits, step number} in one 8-byte word.  take3 reads three elements
@@ -67,14 +98,14 @@ __device__ __forceinline__ uint2 ld_pair_volatile(const uint2* p) {
     return v;
 }
 __device__ __forceinline__ bool take3(const uint2* a, const uint2* b, const uint2* c, unsigned int e, long long t0,
-                                      float* va, float* vb, float* vc) {
+                                      long long limit, float* va, float* vb, float* vc) {
     for (;;) {
         const uint2 x = ld_pair_volatile(a), y = ld_pair_volatile(b), z = ld_pair_volatile(c);
         if (x.y == e && y.y == e && z.y == e) {
             *va = __uint_as_float(x.x); *vb = __uint_as_float(y.x); *vc = __uint_as_float(z.x);
             return true;
         }
-        if (clock64() - t0 > kPeerWaitLimitCycles) return false;
+        if (clock64() - t0 > limit) return false;
     }
 }
 #endif
@@ -121,7 +152,9 @@ struct RopeFreq {
 };
 RopeFreq make_rope_freq(int head_dim, float theta, float scaling);
 
-// Device table of (cos, sin) for positions [0, n_pos) x pairs [0, D/2); cached per device.
+// Device table of (cos, sin) for positions [0, >= n_pos) x pairs [0, D/2); cached per device.  Creating or
+// growing a table allocates and launches, which a capturing stream does not allow: the call then fails and
+// names the remedy (run the op once, or grl_rope_table_prepare, before the capture).
 int get_rope_table(grl_device* dev, int n_pos, int head_dim, float theta, float scaling,
                    const float2** out);
 

@@ -24,7 +24,6 @@ constexpr int STAGE = 2 * SLAB;     // K then V
 constexpr int kThreads = 160;       // 4 compute warps + 1 producer warp
 constexpr int SMEM_BAR = NST * STAGE;
 constexpr int SMEM_TOTAL = SMEM_BAR + 128 + 1024;
-constexpr long long kWaitLimitCycles = 2000000000LL;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kEmpty = -1e30f;
 
@@ -45,6 +44,7 @@ struct Args {
     float* scores_out;      // != NULL: (B*Hq, scores_ld) scaled scores, natural-log domain
     int scores_ld;
     PeerExchange x;         // x.world > 1: the merged rows are exchanged with the peers and merged again
+    long long wait_limit;   // cycle budget of every mbarrier wait
 };
 constexpr int kDoneSlot = grl_device::kCounterSlots;
 constexpr int kMaxFusedSplits = 256;
@@ -102,6 +102,7 @@ struct Ctx {
     uint32_t bars;
     volatile int* abort;
     int32_t* status;
+    long long limit;
 };
 __device__ __forceinline__ bool wait_bar(const Ctx& c, int bar, uint32_t parity) {
     const uint32_t addr = c.bars + bar * 8;
@@ -110,10 +111,10 @@ __device__ __forceinline__ bool wait_bar(const Ctx& c, int bar, uint32_t parity)
     for (;;) {
         if (mbar_try_wait(addr, parity)) return true;
         if (*c.abort) return false;
-        if (clock64() - t0 > kWaitLimitCycles) {
+        if (clock64() - t0 > c.limit) {
             *c.abort = 1;
             if (c.status && atomicCAS(c.status, 0, GRL_ERR_TIMEOUT) == 0) {
-                c.status[1] = 0x100 | bar;
+                c.status[1] = (2 << 28) | bar;
                 c.status[2] = blockIdx.x;
                 c.status[3] = blockIdx.y | (blockIdx.z << 16);
             }
@@ -136,14 +137,14 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int len = a.seq_lens[b];
+    const int len = max(0, min(a.seq_lens[b], a.max_pages * P));   // never past the block table
     const int n_pages = (len + P - 1) / P;
     const int pps = (n_pages + a.n_splits - 1) / a.n_splits;
     const int p_begin = min(n_pages, split * pps), p_end = min(n_pages, (split + 1) * pps);
     const int32_t* bt = a.block_table + (size_t)b * a.max_pages;
 
     int* abort_flag = reinterpret_cast<int*>(smem + SMEM_BAR + 2 * NST * 8);
-    Ctx ctx{base + SMEM_BAR, abort_flag, a.status};
+    Ctx ctx{base + SMEM_BAR, abort_flag, a.status, a.wait_limit};
     auto full = [&](int s) { return ctx.bars + (uint32_t)s * 8u; };
     auto empty = [&](int s) { return ctx.bars + (uint32_t)(NST + s) * 8u; };
     if (tid == 0) {
@@ -181,7 +182,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             if (*ctx.abort) {   // copies already issued must land before the shared memory is released
                 const long long t0 = clock64();
                 for (int i = max(0, issued - NST); i < issued; ++i)
-                    while (!mbar_try_wait(full(i % NST), (i / NST) & 1) && clock64() - t0 < kWaitLimitCycles) {}
+                    while (!mbar_try_wait(full(i % NST), (i / NST) & 1) && clock64() - t0 < ctx.limit) {}
             }
         }
     } else {
@@ -379,38 +380,35 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     __syncthreads();
     const PeerExchange& x = a.x;
     const bool exchange = x.world > 1;
-    unsigned int e = 0;
-    int par = 0;
-    if (exchange) { e = *x.seq + 1; par = e & 1; }
-    for (int idx = tid; idx < a.group * D; idx += kThreads) {
-        const int h = idx / D, d = idx % D;
-        float ov = 0.f;
-        const float* col = a.part + (size_t)(row0 + h) * D + d;
-        int s = 0;
-        for (; s + 8 <= a.n_splits; s += 8) {       // eight loads in flight: the chain is latency, not bandwidth
-            float v[8];
+    // Merged un-normalised rows into shared memory.  A thread owns two columns of one head and has the loads of
+    // up to 16 splits in flight: the partials sit in L2, so the chain is latency, not bandwidth.
+    for (int c = tid; c < a.group * (D / 2); c += kThreads) {
+        const int h = c / (D / 2), d2 = c % (D / 2);
+        const float* col = a.part + (size_t)(row0 + h) * D + 2 * d2;     // 8-byte aligned: D and pstride are even
+        float2 acc = make_float2(0.f, 0.f);
+        for (int s0 = 0; s0 < a.n_splits; s0 += 16) {
+            float2 v[16];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __ldcg(col + (size_t)(s + j) * pstride);
+            for (int j = 0; j < 16; ++j)
+                if (s0 + j < a.n_splits) v[j] = __ldcg(reinterpret_cast<const float2*>(col + (size_t)(s0 + j) * pstride));
 #pragma unroll
-            for (int j = 0; j < 8; ++j) ov = fmaf(sm_w[h * kMaxFusedSplits + s + j], v[j], ov);
+            for (int j = 0; j < 16; ++j)
+                if (s0 + j < a.n_splits) {
+                    const float w = sm_w[h * kMaxFusedSplits + s0 + j];
+                    acc.x = fmaf(w, v[j].x, acc.x);
+                    acc.y = fmaf(w, v[j].y, acc.y);
+                }
         }
-        for (; s < a.n_splits; ++s) ov = fmaf(sm_w[h * kMaxFusedSplits + s], __ldcg(col + (size_t)s * pstride), ov);
-        const float lt = sm_mt[8 + h];
-        if (exchange) {
-            // every 8-byte inbox element carries the step number next to the value: a reader that sees the
-            // number sees the value, so there is neither a fence nor a flag between the peers
-            sm_res[idx] = ov;
-            for (int r = 0; r < x.world; ++r)
-                if (r != x.rank)
-                    reinterpret_cast<uint2*>(x.peer_inbox[r])[((size_t)par * x.world + x.rank) * pstride +
-                                                              (size_t)(row0 + h) * D + d] = make_uint2(__float_as_uint(ov), e);
-        } else if (a.partial_out) {
-            a.partial_out[(size_t)(row0 + h) * D + d] = ov;
-        } else {
-            a.out[(size_t)(row0 + h) * D + d] = lt > 0.f ? ov / lt : 0.f;
-        }
+        *reinterpret_cast<float2*>(&sm_res[h * D + 2 * d2]) = acc;
     }
+    __syncthreads();
     if (!exchange) {
+        for (int idx = tid; idx < a.group * D; idx += kThreads) {
+            const int h = idx / D;
+            const float lt = sm_mt[8 + h];
+            if (a.partial_out) a.partial_out[(size_t)row0 * D + idx] = sm_res[idx];
+            else a.out[(size_t)row0 * D + idx] = lt > 0.f ? sm_res[idx] / lt : 0.f;
+        }
         if (a.partial_out && tid < a.group) {
             a.partial_out[(size_t)rows * D + row0 + tid] = sm_mt[tid];
             a.partial_out[(size_t)rows * D + rows + row0 + tid] = sm_mt[8 + tid];
@@ -418,50 +416,91 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         return;
     }
 
-    // ---- cross-GPU exchange of this head's rows: the O rows have gone out above, now m and l
-    if (tid < a.group) {
-        for (int r = 0; r < x.world; ++r) {
-            if (r == x.rank) continue;
-            uint2* dst = reinterpret_cast<uint2*>(x.peer_inbox[r]) + ((size_t)par * x.world + x.rank) * pstride + (size_t)rows * D;
-            dst[row0 + tid] = make_uint2(__float_as_uint(sm_mt[tid]), e);
-            dst[rows + row0 + tid] = make_uint2(__float_as_uint(sm_mt[8 + tid]), e);
-        }
+    // ---- cross-GPU exchange of this head's rows.  An item is one float of the head's part: group*D values of
+    // O, then group maxima, then group sums; every 8-byte inbox element carries the step number next to the
+    // value, so a reader that sees the number sees the value: neither a fence nor a flag between the peers.
+    const unsigned int e = *x.seq + 1;
+    const int par = e & 1;
+    const int n_items = a.group * (D + 2);
+    auto item_off = [&](int i) -> size_t {       // offset of item i inside a part laid out [O | m | l]
+        if (i < a.group * D) return (size_t)row0 * D + i;
+        i -= a.group * D;
+        return i < a.group ? (size_t)rows * D + row0 + i : (size_t)rows * D + rows + row0 + (i - a.group);
+    };
+    auto item_val = [&](int i) -> float {
+        if (i < a.group * D) return sm_res[i];
+        i -= a.group * D;
+        return i < a.group ? sm_mt[i] : sm_mt[8 + (i - a.group)];
+    };
+    const int total = (x.world - 1) * n_items;
+    for (int it = tid; it < total; it += kThreads) {
+        const int pi = it / n_items, i = it - pi * n_items, r = pi + (pi >= x.rank);
+        reinterpret_cast<uint2*>(x.peer_inbox[r])[((size_t)par * x.world + x.rank) * pstride + item_off(i)] =
+            make_uint2(__float_as_uint(item_val(i)), e);
     }
-    __syncthreads();                    // sm_res complete
-    const long long t0 = clock64();
+    // Poll the peers' items of this head, all peers side by side: a thread issues the loads of up to 16 missing
+    // items before it examines any, so a round is one trip to L2 whatever the number of peers.
+    float* sm_in = sm_res + 8 * D;                 // [world-1][n_items]
+    constexpr int kChunk = 16;
     bool ok = true;
-    for (int idx = tid; idx < a.group * D; idx += kThreads) {
-        const int h = idx / D, d = idx % D;
-        float mr[kMaxPeers], lr[kMaxPeers], orow[kMaxPeers];
-        float mt = sm_mt[h];
-#pragma unroll 1
-        for (int r = 0; r < x.world; ++r) {
-            if (r == x.rank) { mr[r] = sm_mt[h]; lr[r] = sm_mt[8 + h]; orow[r] = sm_res[idx]; continue; }
-            const uint2* in = reinterpret_cast<const uint2*>(x.inbox) + ((size_t)par * x.world + r) * pstride;
-            if (!take3(in + (size_t)rows * D + row0 + h, in + (size_t)rows * D + rows + row0 + h,
-                       in + (size_t)(row0 + h) * D + d, e, t0, &mr[r], &lr[r], &orow[r])) {
+    const long long t0 = clock64();
+    for (int base_it = 0; base_it < total && ok; base_it += kChunk * kThreads) {
+        unsigned int pending = 0;
+        unsigned int off[kChunk];                  // element offset inside the local inbox
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j) {
+            const int it = base_it + j * kThreads + tid;
+            off[j] = 0;
+            if (it < total) {
+                const int pi = it / n_items, i = it - pi * n_items, r = pi + (pi >= x.rank);
+                off[j] = (unsigned int)(((size_t)par * x.world + r) * pstride + item_off(i));
+                pending |= 1u << j;
+            }
+        }
+        const uint2* inbox = reinterpret_cast<const uint2*>(x.inbox);
+        while (pending) {
+            uint2 v[kChunk];
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j)
+                if (pending >> j & 1u) v[j] = ld_pair_volatile(inbox + off[j]);
+#pragma unroll
+            for (int j = 0; j < kChunk; ++j)
+                if ((pending >> j & 1u) && v[j].y == e) {
+                    sm_in[base_it + j * kThreads + tid] = __uint_as_float(v[j].x);
+                    pending &= ~(1u << j);
+                }
+            if (pending && clock64() - t0 > x.wait_cycles) {
                 ok = false;
-                mr[r] = kEmpty; lr[r] = 0.f; orow[r] = 0.f;
                 if (a.status && atomicCAS(a.status, 0, GRL_ERR_TIMEOUT) == 0) {
-                    a.status[1] = 0x200 | r;
+                    const int it = base_it + (__ffs(pending) - 1) * kThreads + tid, pi = it / n_items;
+                    a.status[1] = (3 << 28) | (pi + (pi >= x.rank));     // a peer that did not post
                     a.status[2] = (int)e;
                     a.status[3] = x.rank;
                 }
+                break;
             }
-            mt = fmaxf(mt, mr[r]);
         }
-        float ov = 0.f, lt = 0.f;
-#pragma unroll 1
-        for (int r = 0; r < x.world; ++r) {
-            const float w = __expf(mr[r] - mt);
-            ov = fmaf(w, orow[r], ov);
-            lt = fmaf(w, lr[r], lt);
+    }
+    ok = __syncthreads_and(ok);                    // the whole CTA agrees: no row is written after a timeout
+    if (ok) {
+        for (int idx = tid; idx < a.group * D; idx += kThreads) {
+            const int h = idx / D;
+            float mt = sm_mt[h];
+            for (int pi = 0; pi < x.world - 1; ++pi) mt = fmaxf(mt, sm_in[pi * n_items + a.group * D + h]);
+            const float w0 = __expf(sm_mt[h] - mt);
+            float ov = w0 * sm_res[idx], lt = w0 * sm_mt[8 + h];
+            for (int pi = 0; pi < x.world - 1; ++pi) {
+                const float* in = sm_in + pi * n_items;
+                const float w = __expf(in[a.group * D + h] - mt);
+                ov = fmaf(w, in[idx], ov);
+                lt = fmaf(w, in[a.group * D + a.group + h], lt);
+            }
+            a.out[(size_t)row0 * D + idx] = lt > 0.f ? ov / lt : 0.f;
         }
-        if (ok) a.out[(size_t)(row0 + h) * D + d] = lt > 0.f ? ov / lt : 0.f;
     }
     // the head that finishes last advances the step counter for the next launch (every head has read it by
-    // then); after a timeout the counter stays and grl_sync reports the failure
-    __syncthreads();
+    // then); after a timeout the counter stays, grl_sync reports the failure and grl_exchange_reset on every
+    // rank puts the ranks back in step
     if (tid == 0 && ok) {
         const int heads = a.B * a.Hkv;
         if (atomicAdd(&a.counters[kDoneSlot], 1) == heads - 1) {
@@ -471,29 +510,15 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static int make_pool_map(CUtensorMap* tm, const void* pool, uint64_t rows) {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return set_error(GRL_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-        fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    cuuint64_t dims[2] = {(cuuint64_t)D, rows};
-    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)P};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return set_error(GRL_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-    return GRL_OK;
+// The K (or V) pool as a 2-D bf16 tensor (rows = pages * Hkv * page tokens, 128 columns); box = 64 columns x
+// one page of one kv head.
+static int make_pool_map(grl_device* dev, CUtensorMap* tm, const void* pool, uint64_t rows) {
+    TmapKey k{};
+    k.ptr = pool; k.rank = 2; k.swizzle_128b = 1;
+    k.dims[0] = D; k.dims[1] = rows;
+    k.strides[0] = (uint64_t)D * 2;
+    k.box[0] = 64; k.box[1] = P;
+    return get_tensor_map(dev, k, tm);
 }
 
 }  // namespace dmma
@@ -511,8 +536,8 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
     const uint64_t pages = kv.num_pages > 0 ? (uint64_t)kv.num_pages : (uint64_t)kv.batch * kv.max_pages;
     const uint64_t rows = pages * kv.num_kv_heads * P;
     CUtensorMap tk, tv;
-    int rc = make_pool_map(&tk, kv.k_pages, rows);
-    if (!rc) rc = make_pool_map(&tv, kv.v_pages, rows);
+    int rc = make_pool_map(dev, &tk, kv.k_pages, rows);
+    if (!rc) rc = make_pool_map(dev, &tv, kv.v_pages, rows);
     if (rc) return rc;
     Args a{};
     a.block_table = kv.block_table; a.seq_lens = kv.seq_lens; a.q = p->q;
@@ -523,9 +548,10 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
     a.fuse = fuse ? 1 : 0; a.counters = dev->d_counters; a.partial_out = p->partial_out;
     a.scores_out = p->scores_out; a.scores_ld = p->scores_ld;
     a.x.world = 1;
+    a.wait_limit = dev->wait_limit_cycles;
     if (p->exchange) {
         GRL_REQUIRE(fuse && !direct, "the fused cross-GPU merge needs the split-KV path");
-        rc = fill_peer_exchange(p->exchange, &a.x);
+        rc = fill_peer_exchange(dev, p->exchange, &a.x);
         if (rc) return rc;
         const int heads = kv.batch * kv.num_kv_heads;
         GRL_REQUIRE(heads <= dev->prop.multiProcessorCount,

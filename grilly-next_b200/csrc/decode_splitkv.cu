@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(DecodeArgs
     const int qh0 = kvh * a.group + chunk * GC;          // first query head of this CTA
     const int n_heads = min(GC, a.group - chunk * GC);   // live heads in this chunk
 
-    const int len = a.seq_lens[b];
+    const int len = max(0, min(a.seq_lens[b], a.max_pages * a.P));   // never past the block table
     const int n_pages = (len + a.P - 1) / a.P;
     const int pps = (n_pages + a.n_splits - 1) / a.n_splits;  // pages per split
     const int t_begin = min(len, split * pps * a.P);
@@ -400,7 +400,9 @@ int grl_gqa_decode_static(grl_device* dev, const grl_decode_params* p) {
     size_t need = 0;
     rc = grl_decode_workspace_bytes(p, n_splits, &need);
     if (rc) return rc;
-    if (need > kStaticScratchFloats * sizeof(float))
+    // an unsplit launch writes its result directly and touches no scratch, whatever its nominal size
+    const bool unsplit = (n_splits == 1) && !p->partial_out && !p->exchange;
+    if (!unsplit && need > kStaticScratchFloats * sizeof(float))
         return set_error(GRL_ERR_INVALID,
                          "grl_gqa_decode_static: %d splits x %d rows need %zu bytes of scratch, the built-in array holds "
                          "%zu; pass fewer splits (n_splits) or use grl_gqa_decode with a caller workspace",

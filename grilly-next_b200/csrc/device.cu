@@ -44,22 +44,79 @@ int get_rope_table(grl_device* dev, int n_pos, int head_dim, float theta, float 
     uint32_t tb, sb;
     memcpy(&tb, &theta, 4);
     memcpy(&sb, &scaling, 4);
-    auto key = std::make_tuple(n_pos, head_dim, tb, sb);
+    auto key = std::make_tuple(head_dim, tb, sb);
     std::lock_guard<std::mutex> lock(dev->mu);
     auto it = dev->rope_tables.find(key);
-    if (it != dev->rope_tables.end()) {
-        *out = it->second;
+    if (it != dev->rope_tables.end() && it->second.first >= n_pos) {
+        *out = it->second.second;
         return GRL_OK;
     }
+    // Row contents do not depend on the table's length: keep ONE table per (head_dim, theta, scaling), sized to
+    // the next power of two, and replace it when a longer sequence arrives.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(dev->stream, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+        return set_error(GRL_ERR_INVALID,
+                         "the RoPE table for %d positions does not exist yet and cannot be built while the stream is "
+                         "capturing: call grl_rope_table_prepare (or run the op once) before the capture", n_pos);
+    int cap_pos = 256;
+    while (cap_pos < n_pos) cap_pos <<= 1;
     float2* t = nullptr;
     int half = head_dim / 2;
-    GRL_CUDA(cudaMalloc(&t, sizeof(float2) * (size_t)n_pos * half));
-    int n = n_pos * half;
-    rope_table_kernel<<<(n + 255) / 256, 256, 0, dev->stream>>>(t, n_pos, half,
-                                                                 make_rope_freq(head_dim, theta, scaling));
+    GRL_CUDA(cudaMalloc(&t, sizeof(float2) * (size_t)cap_pos * half));
+    const size_t n = (size_t)cap_pos * half;
+    rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, dev->stream>>>(t, cap_pos, half,
+                                                                            make_rope_freq(head_dim, theta, scaling));
     GRL_LAUNCHED("rope_table_kernel");
-    dev->rope_tables[key] = t;
+    if (it != dev->rope_tables.end()) dev->retired_tables.push_back(it->second.second);
+    dev->rope_tables[key] = std::make_pair(cap_pos, t);
     *out = t;
+    return GRL_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static std::once_flag once;
+    static EncodeTiledFn fn = nullptr;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+int get_tensor_map(grl_device* dev, const TmapKey& key, CUtensorMap* out) {
+    constexpr size_t kMaxCached = 64;
+    std::lock_guard<std::mutex> lock(dev->mu);
+    for (auto& e : dev->tmaps)
+        if (memcmp(&e.first, &key, sizeof(TmapKey)) == 0) {
+            *out = e.second;
+            ++dev->tmap_hits;
+            return GRL_OK;
+        }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(GRL_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    cuuint64_t dims[3] = {key.dims[0], key.dims[1], key.dims[2]};
+    cuuint64_t strides[2] = {key.strides[0], key.strides[1]};
+    cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, key.rank, const_cast<void*>(key.ptr), dims, strides, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    key.swizzle_128b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(GRL_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    ++dev->tmap_misses;
+    if (dev->tmaps.size() < kMaxCached) {
+        dev->tmaps.emplace_back(key, *out);
+    } else {
+        dev->tmaps[dev->tmap_next] = std::make_pair(key, *out);   // round robin
+        dev->tmap_next = (dev->tmap_next + 1) % kMaxCached;
+    }
     return GRL_OK;
 }
 
@@ -149,7 +206,8 @@ int grl_device_close(grl_device* dev) {
     if (!dev) return GRL_OK;
     DeviceGuard g(dev->ordinal);
     cudaStreamSynchronize(dev->stream);
-    for (auto& kv : dev->rope_tables) cudaFree(kv.second);
+    for (auto& kv : dev->rope_tables) cudaFree(kv.second.second);
+    for (float2* t : dev->retired_tables) cudaFree(t);
     cudaFree(dev->d_status);
     cudaFreeHost(dev->h_status);
     cudaStreamDestroy(dev->own_stream);
@@ -177,6 +235,33 @@ int grl_device_use_stream(grl_device* dev, void* cuda_stream) {
     return GRL_OK;
 }
 
+int grl_device_set_wait_limits(grl_device* dev, uint64_t barrier_wait_cycles, uint64_t peer_wait_cycles) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    const uint64_t cap = 20000000000ull;   // ~10 s: a wait never becomes unbounded
+    dev->wait_limit_cycles = barrier_wait_cycles ? (long long)(barrier_wait_cycles < cap ? barrier_wait_cycles : cap)
+                                                 : kDefaultWaitLimitCycles;
+    dev->peer_wait_limit_cycles = peer_wait_cycles ? (long long)(peer_wait_cycles < cap ? peer_wait_cycles : cap)
+                                                   : kDefaultPeerWaitLimitCycles;
+    return GRL_OK;
+}
+
+int grl_rope_table_prepare(grl_device* dev, int n_pos, int head_dim, float theta, float scaling) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    GRL_REQUIRE(n_pos > 0 && head_dim > 0 && head_dim % 2 == 0 && head_dim <= 256 && theta > 0.f, "bad RoPE table shape");
+    DeviceGuard g(dev->ordinal);
+    const float2* t = nullptr;
+    return get_rope_table(dev, n_pos, head_dim, theta, scaling == 0.f ? 1.f : scaling, &t);
+}
+
+int grl_tensor_map_cache_stats(grl_device* dev, int64_t* hits, int64_t* misses, int64_t* cached) {
+    GRL_REQUIRE(dev, "dev is NULL");
+    std::lock_guard<std::mutex> lock(dev->mu);
+    if (hits) *hits = dev->tmap_hits;
+    if (misses) *misses = dev->tmap_misses;
+    if (cached) *cached = (int64_t)dev->tmaps.size();
+    return GRL_OK;
+}
+
 int grl_malloc(grl_device* dev, size_t bytes, void** out) {
     GRL_REQUIRE(dev && out, "NULL argument");
     DeviceGuard g(dev->ordinal);
@@ -191,6 +276,14 @@ int grl_free(grl_device* dev, void* ptr) {
     if (!ptr) return GRL_OK;
     DeviceGuard g(dev->ordinal);
     GRL_CUDA(cudaFree(ptr));
+    {   // a later allocation may reuse the address with another shape: forget the maps built on it
+        std::lock_guard<std::mutex> lock(dev->mu);
+        for (size_t i = 0; i < dev->tmaps.size();) {
+            if (dev->tmaps[i].first.ptr == ptr) { dev->tmaps[i] = dev->tmaps.back(); dev->tmaps.pop_back(); }
+            else ++i;
+        }
+        if (dev->tmap_next >= dev->tmaps.size()) dev->tmap_next = 0;
+    }
     return GRL_OK;
 }
 
@@ -248,8 +341,19 @@ static int report_kernel_status(grl_device* dev, bool copied) {
     if (st[0] == 0) return GRL_OK;
     // a kernel that gave up may have left arrival counters half-way: clear them with the status
     GRL_CUDA(cudaMemsetAsync(dev->d_status, 0, (4 + grl_device::kCounterSlots + 1) * sizeof(int32_t), dev->stream));
-    return set_error(st[0] == GRL_ERR_TIMEOUT ? GRL_ERR_TIMEOUT : GRL_ERR_KERNEL,
-                     "kernel reported failure %d (stuck barrier mask 0x%x, first block %d,%d)", st[0], st[1], st[2], st[3]);
+    // [1] = kind << 28 | detail: 1 prefill (mask of the mbarriers that were being waited on; [3] = CTA),
+    // 2 decode (mbarrier index; [2],[3] = CTA), 3 cross-GPU merge (peer that did not post; [2] = step, [3] = rank),
+    // 4 append (a sequence without room; [2] = sequence, [3] = its length)
+    const int code = st[0] == GRL_ERR_TIMEOUT ? GRL_ERR_TIMEOUT : GRL_ERR_KERNEL;
+    const unsigned int kind = (unsigned int)st[1] >> 28, detail = (unsigned int)st[1] & 0x0fffffffu;
+    switch (kind) {
+        case 1: return set_error(code, "prefill kernel: a wait ran out (mbarrier mask 0x%x, CTA %d)", detail, st[3]);
+        case 2: return set_error(code, "decode kernel: a wait ran out (mbarrier %u, CTA %d,%d)", detail, st[2], st[3]);
+        case 3: return set_error(code, "cross-GPU merge on rank %d: peer %u did not post step %d within the wait limit",
+                                 st[3], detail, st[2]);
+        case 4: return set_error(code, "kv append: sequence %d (length %d) has no room for the new tokens", st[2], st[3]);
+        default: return set_error(code, "kernel reported failure %d (detail 0x%x, %d, %d)", st[0], st[1], st[2], st[3]);
+    }
 }
 
 int grl_sync(grl_device* dev, uint64_t timeout_ns) {
@@ -361,6 +465,8 @@ int grl_graph_launch(grl_device* dev, grl_graph* gr) {
     GRL_REQUIRE(dev && gr && gr->exec, "NULL argument");
     DeviceGuard g(dev->ordinal);
     GRL_CUDA(cudaGraphLaunch(gr->exec, dev->stream));
+    // The replayed kernels may write the status word (bounded waits): the next grl_sync must read it.
+    dev->status_dirty = true;
     return GRL_OK;
 }
 

@@ -18,6 +18,7 @@ struct AppendArgs {
     int B, Hkv, Hq, D, P, max_pages, n_new;
     int rope_mode, pos_base, update_lens;
     const int32_t* pos_offsets;
+    int32_t* status;     // device status word: GRL_ERR_INVALID when a sequence has no room for the new tokens
     RopeFreq freq;
 };
 
@@ -31,6 +32,17 @@ __global__ void __launch_bounds__(1024) kv_append_kernel(AppendArgs a) {
     const int b = blockIdx.y;
     const int half = a.D / 2;
     const int len0 = a.seq_lens[b];
+    // A sequence without room for the new tokens is left untouched (no store, no length update): the block
+    // table has no page for them.  The op layer checks this on the host; a direct caller of the C ABI gets
+    // GRL_ERR_KERNEL from the next grl_sync.
+    if (len0 < 0 || len0 + a.n_new > a.max_pages * a.P) {
+        if (threadIdx.x == 0 && blockIdx.x == 0 && a.status && atomicCAS(a.status, 0, GRL_ERR_INVALID) == 0) {
+            a.status[1] = 4 << 28;
+            a.status[2] = b;
+            a.status[3] = len0;
+        }
+        return;
+    }
     const int pos_off = a.pos_offsets ? a.pos_offsets[b] : 0;
     T* kp = reinterpret_cast<T*>(a.k_pages);
     T* vp = reinterpret_cast<T*>(a.v_pages);
@@ -77,9 +89,9 @@ __global__ void __launch_bounds__(1024) kv_append_kernel(AppendArgs a) {
     }
 }
 
-__global__ void advance_lens_kernel(int32_t* seq_lens, int B, int n) {
+__global__ void advance_lens_kernel(int32_t* seq_lens, int B, int n, int capacity) {
     int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b < B) seq_lens[b] += n;
+    if (b < B && seq_lens[b] >= 0 && seq_lens[b] + n <= capacity) seq_lens[b] += n;   // a full sequence was skipped
 }
 
 template <typename T>
@@ -153,6 +165,8 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p) {
     a.B = kv.batch; a.Hkv = kv.num_kv_heads; a.Hq = p->num_q_heads; a.D = kv.head_dim; a.P = kv.page_tokens;
     a.max_pages = kv.max_pages; a.n_new = p->n_new;
     a.rope_mode = p->rope_mode; a.pos_base = p->pos_base; a.pos_offsets = p->pos_offsets;
+    a.status = dev->d_status;
+    dev->status_dirty = true;
     if (p->rope_mode != GRL_ROPE_NONE) a.freq = make_rope_freq(kv.head_dim, p->rope_theta, p->rope_scaling);
     const long long items = (long long)p->n_new * (kv.num_kv_heads + (p->q_in ? p->num_q_heads : 0)) * (kv.head_dim / 2);
     // one CTA per sequence while a CTA has at most 16 items per thread (a decode step), more for bulk appends
@@ -167,7 +181,8 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p) {
     else kv_append_kernel<float><<<grid, threads, 0, dev->stream>>>(a);
     GRL_LAUNCHED("kv_append_kernel");
     if (p->update_lens && !fused_update) {
-        advance_lens_kernel<<<(kv.batch + 127) / 128, 128, 0, dev->stream>>>(kv.seq_lens, kv.batch, p->n_new);
+        advance_lens_kernel<<<(kv.batch + 127) / 128, 128, 0, dev->stream>>>(kv.seq_lens, kv.batch, p->n_new,
+                                                                                 kv.max_pages * kv.page_tokens);
         GRL_LAUNCHED("advance_lens_kernel");
     }
     return GRL_OK;

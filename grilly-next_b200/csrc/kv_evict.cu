@@ -24,7 +24,7 @@ __global__ void score_accumulate_kernel(const float* __restrict__ attn, int q_ro
                                         float* cum, int capacity) {
     const int b = blockIdx.y;
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
-    const int len = seq_lens[b];
+    const int len = max(0, min(seq_lens[b], capacity));   // never past the metadata arrays
     if (t >= len || t >= ld) return;
     const float* col = attn + (size_t)b * q_rows * ld + t;
     float acc = 0.f;
@@ -39,7 +39,7 @@ __global__ void mass_accumulate_kernel(const float* __restrict__ scores, int ld,
                                        int Hq, int D, int rows, const int32_t* seq_lens, float* cum, int capacity) {
     extern __shared__ float s_ml[];          // [Hq] m, [Hq] 1/l
     const int b = blockIdx.y;
-    const int len = seq_lens[b];
+    const int len = max(0, min(seq_lens[b], capacity));   // never past the metadata arrays
     for (int h = threadIdx.x; h < Hq; h += blockDim.x) {
         const int row = b * Hq + h;
         const float l = partial[(size_t)rows * D + rows + row];
@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(kThreads) evict_lowest_kernel(const float* __r
     __shared__ uint32_t s_prefix;
     __shared__ int s_k;
     const int b = blockIdx.x, tid = threadIdx.x;
-    const int len = seq_lens[b];
+    const int len = max(0, min(seq_lens[b], capacity));   // never past the metadata arrays
     int k = num_evict > 0 ? num_evict : len / 4;          // default: a quarter (kv_cache.cpp:598-600)
     if (k <= 0 || k >= len) return;                       // kv_cache.cpp:601
     const float* c = cum + (size_t)b * capacity;
@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(kThreads) evict_heuristic_kernel(const float* 
                                                                   int capacity, float threshold) {
     __shared__ float s_max[32];
     const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int len = seq_lens[b];
+    const int len = max(0, min(seq_lens[b], capacity));   // never past the metadata arrays
     const float* c = cum + (size_t)b * capacity;
     float m = 0.f;
     for (int t = tid; t < len; t += kThreads) m = fmaxf(m, c[t]);
@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(kThreads) compact_scan_kernel(const uint8_t* _
                                                                int32_t* new_pos, int32_t* new_len) {
     __shared__ int s_warp[33];
     const int b = blockIdx.x, tid = threadIdx.x;
-    const int len = seq_lens[b];
+    const int len = max(0, min(seq_lens[b], capacity));   // never past the metadata arrays
     int carried = 0;
     for (int base = 0; base < len; base += kThreads) {
         const int t = base + tid;
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(kMoveThreads, 3) compact_move_kernel(MoveArgs 
     const int h = blockIdx.x, b = blockIdx.y;
     const int parts = gridDim.z / 2, part = blockIdx.z >> 1;
     uint8_t* pool = (blockIdx.z & 1) == 0 ? a.k_pages : a.v_pages;
-    const int len = a.seq_lens[b];
+    const int len = max(0, min(a.seq_lens[b], min(a.capacity, a.max_pages * a.P)));   // never past the block table
     const int32_t* bt_g = a.block_table + (size_t)b * a.max_pages;
     const int32_t* np = a.new_pos + (size_t)b * a.capacity;
     const int n_pages = (len + a.P - 1) / a.P;
@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(kThreads) compact_meta_kernel(float* cum, uint
                                                                const int32_t* new_pos, const int32_t* new_len,
                                                                int capacity) {
     const int b = blockIdx.x, tid = threadIdx.x;
-    const int len = seq_lens[b], nl = new_len[b];
+    const int len = max(0, min(seq_lens[b], capacity)), nl = new_len[b];
     float* c = cum + (size_t)b * capacity;
     float* r = relevance ? relevance + (size_t)b * capacity : nullptr;
     const int32_t* np = new_pos + (size_t)b * capacity;

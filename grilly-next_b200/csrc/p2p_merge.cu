@@ -23,13 +23,14 @@ struct ExchangeArgs {
     int rows, D;
 };
 
-int fill_peer_exchange(const grl_exchange_params* p, PeerExchange* x) {
+int fill_peer_exchange(grl_device* dev, const grl_exchange_params* p, PeerExchange* x) {
     GRL_REQUIRE(p->world >= 1 && p->world <= kMaxPeers && p->rank >= 0 && p->rank < p->world, "bad rank / world");
     GRL_REQUIRE(p->inbox && p->flags && p->seq, "NULL buffer");
     GRL_REQUIRE(p->peer_inbox && p->peer_flags, "NULL peer tables");
     GRL_REQUIRE((uintptr_t)p->inbox % 16 == 0, "inbox must be 16-byte aligned");
     x->inbox = p->inbox; x->flags = p->flags; x->seq = p->seq;
     x->rank = p->rank; x->world = p->world; x->flag_slots = p->flag_slots > 0 ? p->flag_slots : 1;
+    x->wait_cycles = p->wait_cycles > 0 ? (long long)p->wait_cycles : dev->peer_wait_limit_cycles;
     for (int r = 0; r < p->world; ++r) {
         GRL_REQUIRE(r == p->rank || (p->peer_inbox[r] && p->peer_flags[r]), "peer %d has no inbox", r);
         x->peer_inbox[r] = p->peer_inbox[r];
@@ -61,19 +62,19 @@ __global__ void __launch_bounds__(128) exchange_merge_kernel(ExchangeArgs a) {
             __threadfence_system();
         }
     }
-    // wait for every peer's partial of this step
+    // wait for every peer's partial of this step: lane r of the first warp watches peer r, so that the flags
+    // are polled side by side and the wait costs one round trip past the slowest peer
     __shared__ int s_ok;
-    if (tid == 0) {
-        int ok = 1;
-        const long long t0 = clock64();
-        for (int r = 0; r < x.world && ok; ++r) {
-            if (r == x.rank) continue;
-            volatile unsigned int* f = x.flags + (size_t)(par * x.world + r) * x.flag_slots;
+    if (tid < 32) {
+        bool ok = true;
+        if (tid < x.world && tid != x.rank) {
+            const long long t0 = clock64();
+            volatile unsigned int* f = x.flags + (size_t)(par * x.world + tid) * x.flag_slots;
             while (*f != e) {
-                if (clock64() - t0 > kPeerWaitLimitCycles) {
-                    ok = 0;
+                if (clock64() - t0 > x.wait_cycles) {
+                    ok = false;
                     if (a.status && atomicCAS(a.status, 0, GRL_ERR_TIMEOUT) == 0) {
-                        a.status[1] = 0x200 | r;
+                        a.status[1] = (3 << 28) | tid;
                         a.status[2] = (int)e;
                         a.status[3] = x.rank;
                     }
@@ -81,8 +82,9 @@ __global__ void __launch_bounds__(128) exchange_merge_kernel(ExchangeArgs a) {
                 }
             }
         }
+        ok = __all_sync(0xffffffffu, ok);
         __threadfence_system();
-        s_ok = ok;
+        if (tid == 0) s_ok = ok ? 1 : 0;
     }
     __syncthreads();
     if (!s_ok) return;
@@ -129,35 +131,63 @@ __global__ void __launch_bounds__(128) exchange_merge_ll_kernel(ExchangeArgs a) 
             dst[off_l] = make_uint2(__float_as_uint(my_l), e);
         }
     }
+    // All peers are polled side by side: the loads of every missing peer are issued before any is examined, so a
+    // round costs one trip to L2 whatever the number of peers.  The arrays are indexed by unrolled constants
+    // only and stay in registers.
     const long long t0 = clock64();
+    unsigned int peers = 0;
+    for (int r = 0; r < x.world; ++r)
+        if (r != x.rank) peers |= 1u << r;
     for (int d = tid; d < a.D; d += 128) {
-        float mr[kMaxPeers], lr[kMaxPeers], orow[kMaxPeers];
-        float mt = my_m;
+        uint2 vm[kMaxPeers], vl[kMaxPeers], vo[kMaxPeers];
+        unsigned int pending = peers;
         bool ok = true;
-#pragma unroll 1
-        for (int r = 0; r < x.world; ++r) {
-            if (r == x.rank) { mr[r] = my_m; lr[r] = my_l; orow[r] = a.local_part[(size_t)row * a.D + d]; continue; }
-            const uint2* in = reinterpret_cast<const uint2*>(x.inbox) + ((size_t)par * x.world + r) * n;
-            if (!take3(in + off_m, in + off_l, in + (size_t)row * a.D + d, e, t0, &mr[r], &lr[r], &orow[r])) {
+        while (pending) {
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; ++r)
+                if (pending >> r & 1u) {
+                    const uint2* in = reinterpret_cast<const uint2*>(x.inbox) + ((size_t)par * x.world + r) * n;
+                    vm[r] = ld_pair_volatile(in + off_m);
+                    vl[r] = ld_pair_volatile(in + off_l);
+                    vo[r] = ld_pair_volatile(in + (size_t)row * a.D + d);
+                }
+#pragma unroll
+            for (int r = 0; r < kMaxPeers; ++r)
+                if ((pending >> r & 1u) && vm[r].y == e && vl[r].y == e && vo[r].y == e) pending &= ~(1u << r);
+            if (pending && clock64() - t0 > x.wait_cycles) {
                 ok = false;
-                mr[r] = -1e30f; lr[r] = 0.f; orow[r] = 0.f;
                 if (a.status && atomicCAS(a.status, 0, GRL_ERR_TIMEOUT) == 0) {
-                    a.status[1] = 0x300 | r;
+                    a.status[1] = (3 << 28) | (__ffs(pending) - 1);
                     a.status[2] = (int)e;
                     a.status[3] = x.rank;
                 }
+                break;
             }
-            mt = fmaxf(mt, mr[r]);
         }
-        float o = 0.f, lt = 0.f;
-#pragma unroll 1
-        for (int r = 0; r < x.world; ++r) {
-            const float w = __expf(mr[r] - mt);
-            o = fmaf(w, orow[r], o);
-            lt = fmaf(w, lr[r], lt);
-        }
-        if (ok) a.out[(size_t)row * a.D + d] = lt > 0.f ? o / lt : 0.f;
+        if (!ok) continue;
+        float mt = my_m;
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+            if (peers >> r & 1u) mt = fmaxf(mt, __uint_as_float(vm[r].x));
+        const float w0 = __expf(my_m - mt);
+        float o = w0 * a.local_part[(size_t)row * a.D + d], lt = w0 * my_l;
+#pragma unroll
+        for (int r = 0; r < kMaxPeers; ++r)
+            if (peers >> r & 1u) {
+                const float w = __expf(__uint_as_float(vm[r].x) - mt);
+                o = fmaf(w, __uint_as_float(vo[r].x), o);
+                lt = fmaf(w, __uint_as_float(vl[r].x), lt);
+            }
+        a.out[(size_t)row * a.D + d] = lt > 0.f ? o / lt : 0.f;
     }
+}
+
+__global__ void exchange_reset_kernel(uint4* inbox, size_t inbox_vec, unsigned int* flags, size_t n_flags,
+                                      unsigned int* seq) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x, i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (size_t i = i0; i < inbox_vec; i += stride) inbox[i] = make_uint4(0, 0, 0, 0);
+    for (size_t i = i0; i < n_flags; i += stride) flags[i] = 0;
+    if (i0 == 0) *seq = 0;
 }
 
 }  // namespace grl
@@ -198,7 +228,7 @@ int grl_exchange_merge(grl_device* dev, const grl_exchange_params* p) {
     GRL_REQUIRE(((uintptr_t)p->local_partial % 16 == 0) && (((size_t)p->rows * (p->head_dim + 2) * 4) % 16 == 0),
                 "partials must be 16-byte aligned and a multiple of 16 bytes");
     ExchangeArgs a{};
-    int rc = fill_peer_exchange(p, &a.x);
+    int rc = fill_peer_exchange(dev, p, &a.x);
     if (rc) return rc;
     DeviceGuard g(dev->ordinal);
     a.local_part = p->local_partial; a.out = p->out;
@@ -214,6 +244,22 @@ int grl_exchange_merge(grl_device* dev, const grl_exchange_params* p) {
     const int ctas = p->rows > p->world ? p->rows : p->world;
     exchange_merge_kernel<<<ctas, 128, 0, dev->stream>>>(a);
     GRL_LAUNCHED("exchange_merge_kernel");
+    return GRL_OK;
+}
+
+int grl_exchange_reset(grl_device* dev, const grl_exchange_params* p) {
+    GRL_REQUIRE(dev && p, "NULL argument");
+    GRL_REQUIRE(p->inbox && p->flags && p->seq, "NULL buffer");
+    GRL_REQUIRE(p->world >= 1 && p->world <= kMaxPeers && p->rows > 0 && p->head_dim > 0, "bad shape");
+    GRL_REQUIRE((uintptr_t)p->inbox % 16 == 0, "inbox must be 16-byte aligned");
+    DeviceGuard g(dev->ordinal);
+    const size_t n = (size_t)p->rows * (p->head_dim + 2);
+    const size_t inbox_bytes = 2 * (size_t)p->world * n * (p->low_latency ? 8 : 4);
+    const size_t n_flags = 2 * (size_t)p->world * (p->flag_slots > 0 ? p->flag_slots : 1);
+    GRL_REQUIRE(inbox_bytes % 16 == 0, "inbox size must be a multiple of 16 bytes");
+    exchange_reset_kernel<<<64, 256, 0, dev->stream>>>(reinterpret_cast<uint4*>(p->inbox), inbox_bytes / 16, p->flags,
+                                                       n_flags, p->seq);
+    GRL_LAUNCHED("exchange_reset_kernel");
     return GRL_OK;
 }
 

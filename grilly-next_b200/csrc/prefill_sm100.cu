@@ -58,7 +58,6 @@ constexpr uint32_t TMEM_COLS = 512;
 // TMEM columns of query tile t: S half-buffer b at t*256 + b*64 (P overlays its first 32 columns),
 // O at t*256 + 128.
 constexpr uint32_t TMEM_TILE = 256, TMEM_O = 128;
-constexpr long long kWaitLimitCycles = 2000000000LL;  // ~1 s at 2 GHz
 
 enum Bar { Q_FULL = 0, Q_READY = Q_FULL + NQ, K_FULL = Q_READY + NQ, K_READY = K_FULL + NSTAGE,
            K_EMPTY = K_READY + NSTAGE, V_FULL = K_EMPTY + NSTAGE, V_EMPTY = V_FULL + NSTAGE,
@@ -76,6 +75,7 @@ struct Args {
     int B, H, S, n_qp;
     int causal, rope_mode;
     float scale_log2;
+    long long wait_limit;   // cycle budget of every mbarrier wait
 };
 
 // kind::f16 instruction descriptor: D=f32 (bit 4), A=B=bf16 (bits 7,10), N>>3 at bit 17, M>>4 at bit 24;
@@ -199,26 +199,11 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// Optional in-kernel timeline (compile with -DGRL_TIMELINE): one thread per role of CTA (0,0)
-// stamps clock64() at its pipeline events; read back with grl_debug_timeline().
-#ifdef GRL_TIMELINE
-constexpr int TL_ROLES = 5, TL_SLOTS = 512;   // roles: 0 softmax0, 1 softmax1, 2 rope, 3 tma, 4 mma
-__device__ unsigned long long g_timeline[TL_ROLES * TL_SLOTS];
-__device__ unsigned int g_timeline_n[TL_ROLES];
-__device__ int g_dbg_flags;   // experiment switches: 1 = softmax skips its math, 2 = softmax skips only the exp/pack/store phase
-#define DBG_FLAG(x) (g_dbg_flags & (x))
-#define TL_DECL(role, active) const int tl_role = (role); const bool tl_on = (active) && blockIdx.x == GRL_TIMELINE; int tl_i = 0;
-#define TL(tag) do { if (tl_on && tl_i < TL_SLOTS) { g_timeline[tl_role * TL_SLOTS + tl_i] = ((unsigned long long)(tag) << 48) | (clock64() & 0xffffffffffffULL); ++tl_i; g_timeline_n[tl_role] = tl_i; } } while (0)
-#else
-#define DBG_FLAG(x) 0
-#define TL_DECL(role, active)
-#define TL(tag) do {} while (0)
-#endif
-
 struct Ctx {
     uint32_t bars;          // shared address of barrier 0
     volatile int* abort;    // shared abort flag
     int32_t* status;
+    long long limit;        // cycles a wait may take before the CTA gives up
 };
 
 // Bounded wait.  Returns false when the CTA is aborting (this wait or another one ran out).
@@ -231,14 +216,14 @@ __device__ __forceinline__ bool wait_bar(const Ctx& c, int bar, uint32_t parity)
     for (;;) {
         if (mbar_try_wait(addr, parity)) return true;
         if (*c.abort) {
-            if (c.status) atomicOr(reinterpret_cast<unsigned int*>(c.status) + 1, 1u << bar);
+            if (c.status) atomicOr(reinterpret_cast<unsigned int*>(c.status) + 1, (1u << 28) | (1u << bar));
             return false;
         }
-        if (clock64() - t0 > kWaitLimitCycles) {
+        if (clock64() - t0 > c.limit) {
             *c.abort = 1;
             if (c.status) {
                 // [0] error code, [1] bit mask of the barriers that were being waited on, [2],[3] first CTA
-                atomicOr(reinterpret_cast<unsigned int*>(c.status) + 1, 1u << bar);
+                atomicOr(reinterpret_cast<unsigned int*>(c.status) + 1, (1u << 28) | (1u << bar));
                 if (atomicCAS(c.status, 0, GRL_ERR_TIMEOUT) == 0) {
                     c.status[2] = (parity << 16) | (threadIdx.x << 20);
                     c.status[3] = blockIdx.x;
@@ -455,7 +440,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SMEM_BAR + NUM_BARS * 8);
     int* abort_flag = reinterpret_cast<int*>(smem + SMEM_BAR + NUM_BARS * 8 + 4);
-    Ctx ctx{base_addr + SMEM_BAR, abort_flag, a.status};
+    Ctx ctx{base_addr + SMEM_BAR, abort_flag, a.status, a.wait_limit};
     auto bar = [&](int i) { return ctx.bars + (uint32_t)i * 8u; };
 
     auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, int row, int full_bar) {
@@ -513,8 +498,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (warp == WARP_TMA) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            TL_DECL(3, true)
-            TL(1);
             int issued = 2 * min(n_total, NSTAGE);   // K/V tile loads in flight (K_j = 2j, V_j = 2j+1): the first stages
             bool ok = true;
             for (int j = NSTAGE; j < n_total && ok; ++j) {
@@ -522,24 +505,22 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 ok = wait_bar(ctx, K_EMPTY + s, (it - 1) & 1);
                 if (!ok) break;
                 load_tile(base_addr + SMEM_K + s * TILE_BYTES, &tmK, j * BN, K_FULL + s);
-                TL(2);
                 issued = 2 * j + 1;
                 ok = wait_bar(ctx, V_EMPTY + s, (it - 1) & 1);
                 if (!ok) break;
                 load_tile(base_addr + SMEM_V + s * TILE_BYTES, &tmV, j * BN, V_FULL + s);
-                TL(3);
                 issued = 2 * j + 2;
             }
             if (*ctx.abort) {
                 // Drain: copies already issued must land before the CTA's shared memory is released.
                 const long long t0 = clock64();
-                while (!mbar_try_wait(bar(Q_FULL), 0) && clock64() - t0 < kWaitLimitCycles) {}
+                while (!mbar_try_wait(bar(Q_FULL), 0) && clock64() - t0 < ctx.limit) {}
                 if (n_kt[1] > 0)
-                    while (!mbar_try_wait(bar(Q_FULL + 1), 0) && clock64() - t0 < kWaitLimitCycles) {}
+                    while (!mbar_try_wait(bar(Q_FULL + 1), 0) && clock64() - t0 < ctx.limit) {}
                 for (int x = max(0, issued - 2 * NSTAGE); x < issued; ++x) {
                     const int j = x >> 1, s = j % NSTAGE, it = j / NSTAGE;
                     const uint32_t bb = bar(((x & 1) ? V_FULL : K_FULL) + s);
-                    while (!mbar_try_wait(bb, it & 1) && clock64() - t0 < kWaitLimitCycles) {}
+                    while (!mbar_try_wait(bb, it & 1) && clock64() - t0 < ctx.limit) {}
                 }
             }
         }
@@ -550,8 +531,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const int t = (warp == WARP_MMA) ? 0 : 1;
         if (lane == 0 && n_half[t] > 0) {
             bool ok = true;
-            TL_DECL(4, t == 0)
-            TL(1);
             const uint32_t qa = desc_lo(base_addr + SMEM_Q + t * TILE_BYTES, 16);
             const uint32_t k_lo = desc_lo(base_addr + SMEM_K, 16), v_lo = desc_lo(base_addr + SMEM_V, HALF_BYTES);
             const int nh = n_half[t], other_tiles = n_kt[t ^ 1];
@@ -566,7 +545,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             auto issue_qk = [&](int i) -> bool {
                 const int j = i >> 1, s = j % NSTAGE, it = j / NSTAGE;
                 if (!wait_bar(ctx, (use_rope ? K_READY : K_FULL) + s, it & 1)) return false;
-                TL(10);
                 tc_fence_after();
                 const uint32_t d_tmem = s_tmem + (uint32_t)(i & 1) * BH;
                 const uint32_t kb = k_lo + (uint32_t)s * (TILE_BYTES >> 4) + (uint32_t)(i & 1) * ((BH * 128) >> 4);  // rows 64.. of each box
@@ -578,7 +556,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
                 mma_commit(bar(S_FULL + 2 * t + (i & 1)));
                 if ((i & 1) || i + 1 >= nh) release(K_EMPTY + s, j);   // last step of this tile on K tile j
-                TL(12);
                 return true;
             };
             ok = wait_bar(ctx, (use_rope ? Q_READY : Q_FULL) + t, 0);
@@ -586,7 +563,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             for (int i = 0; i < nh && ok; ++i) {
                 const int j = i >> 1, s = j % NSTAGE, it = j / NSTAGE;
                 ok = wait_bar(ctx, P_READY + 2 * t + (i & 1), (i >> 1) & 1);
-                TL(20);
                 if (ok) ok = wait_bar(ctx, V_FULL + s, it & 1);
                 if (!ok) break;
                 tc_fence_after();
@@ -601,7 +577,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     mma_ts2(o_tmem, p_tmem + ks * 8, vb + (uint32_t)ks * (2048 >> 4), IDESC_PV, 1u);
                 mma_commit(bar(O_DONE + t));
                 if ((i & 1) || i + 1 >= nh) release(V_EMPTY + s, j);
-                TL(24);
                 if (i + 2 < nh) ok = issue_qk(i + 2);   // reuses buffer i & 1: in order after PV(t, i)
             }
         }
@@ -614,20 +589,16 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             RopeState st;
             rope_init(st, a.rope, S, a.rope_mode, rt);
             bool ok = true;
-            TL_DECL(2, rt == 0)
-            TL(1);
             RopeStart cur = rope_load_start(0, S, a.rope, a.rope_mode, rt);
             for (int j = 0; j < n_total && ok; ++j) {
                 const int s = j % NSTAGE, it = j / NSTAGE;
                 const RopeStart nxt = rope_load_start((j + 1) * BN, S, a.rope, a.rope_mode, rt);   // for the next tile
                 ok = wait_bar_warp(ctx, K_FULL + s, it & 1);
                 if (!ok) break;
-                TL(2);
                 rope_tile(base_addr + SMEM_K + s * TILE_BYTES, cur, a.rope_mode, rt, st);
                 cur = nxt;
                 fence_async_smem();
                 mbar_arrive(bar(K_READY + s));
-                TL(3);
             }
         }
     } else {
@@ -651,8 +622,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
             const uint32_t s_addr = lane_addr + (uint32_t)t * TMEM_TILE, o_addr = s_addr + TMEM_O;
             bool ok = true;
-            TL_DECL(t, row == 0)
-            TL(1);
             if (use_rope) {   // this warpgroup rotates its own Q tile
                 RopeState st;
                 rope_init(st, a.rope, S, a.rope_mode, row);
@@ -665,7 +634,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
             }
             float m_ref = -INFINITY, l = 0.f;
-            TL(2);
             const int nh = n_half[t];
             // The two softmax warpgroups take turns in the exponential phase (it saturates the MUFU unit they
             // share): a warpgroup starts its exponentials when the other has finished its own, and spends its
@@ -677,7 +645,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 const int bf = i & 1, k0 = i * BH;
                 ok = wait_bar_warp(ctx, S_FULL + 2 * t + bf, (i >> 1) & 1);
                 if (!ok) break;
-                TL(3);
                 tc_fence_after();
                 uint32_t sr[BH];
                 tmem_ld_x64_sync(s_addr + bf * BH, sr);
@@ -696,7 +663,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         mx4[e] = max3(mx4[e], __uint_as_float(sr[c + 2 * e]), __uint_as_float(sr[c + 2 * e + 1]));
                 }
                 const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-                TL(4);
                 const float m_new = fmaxf(m_ref, mx * a.scale_log2);
                 bool o_waited = false;
                 if (i == 0) {
@@ -745,7 +711,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
                 if (t == 0 ? (i < nc) : (i + 1 < nc)) mbar_arrive(bar(EXP_TURN + (t ^ 1)));   // the other tile's turn
                 l += ((rs4[0].x + rs4[0].y) + (rs4[1].x + rs4[1].y)) + ((rs4[2].x + rs4[2].y) + (rs4[3].x + rs4[3].y));
-                TL(5);
                 tmem_st_wait();
                 // Consume the phase of PV(t, i-1) BEFORE arriving: after the arrival PV(t, i) may complete too,
                 // and a waiter that then looks for the parity of phase i-1 would find the barrier two phases
@@ -756,11 +721,9 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
                 tc_fence_before();
                 mbar_arrive(bar(P_READY + 2 * t + bf));
-                TL(6);
             }
             const int n = nh;
             if (ok) ok = wait_bar_warp(ctx, O_DONE + t, (n - 1) & 1);
-            TL(7);
             if (ok) {
                 tc_fence_after();
                 const bool zero = (row_g >= len) || !(l > 0.f);
@@ -806,7 +769,6 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     }
                 }
             }
-            TL(8);
         }
     }
 
@@ -818,53 +780,17 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
 // (B*H, S, 128) bf16 tensor, box = 64 columns x 128 rows x 1, 128-byte swizzle, zero fill out of bounds.
-static int make_map(CUtensorMap* tm, const void* ptr, int BH, int S) {
-    EncodeTiledFn fn = get_encode_fn();
-    if (!fn) return set_error(GRL_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)S, (cuuint64_t)BH};
-    cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)S * HD * 2};
-    cuuint32_t box[3] = {64, (cuuint32_t)BM, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return set_error(GRL_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-    return GRL_OK;
+static int make_map(grl_device* dev, CUtensorMap* tm, const void* ptr, int BH, int S) {
+    TmapKey k{};
+    k.ptr = ptr; k.rank = 3; k.swizzle_128b = 1;
+    k.dims[0] = HD; k.dims[1] = (uint64_t)S; k.dims[2] = (uint64_t)BH;
+    k.strides[0] = (uint64_t)HD * 2; k.strides[1] = (uint64_t)S * HD * 2;
+    k.box[0] = 64; k.box[1] = BM; k.box[2] = 1;
+    return get_tensor_map(dev, k, tm);
 }
 
 }  // namespace sm100
-
-#ifdef GRL_TIMELINE
-// Copies the timeline of the last launch to the host: counts[5], then 5 x 512 stamps (tag << 48 | clock).
-extern "C" int grl_debug_flags(int flags) {
-    return (int)cudaMemcpyToSymbol(sm100::g_dbg_flags, &flags, sizeof(int));
-}
-extern "C" int grl_debug_timeline(unsigned int* counts, unsigned long long* stamps) {
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(counts, sm100::g_timeline_n, sizeof(unsigned int) * sm100::TL_ROLES);
-    cudaMemcpyFromSymbol(stamps, sm100::g_timeline, sizeof(unsigned long long) * sm100::TL_ROLES * sm100::TL_SLOTS);
-    return 0;
-}
-#endif
 
 int flash_fwd_sm100(grl_device* dev, const grl_flash_params* p, float scale, const float2* rope, int32_t* status) {
     using namespace sm100;
@@ -877,26 +803,28 @@ int flash_fwd_sm100(grl_device* dev, const grl_flash_params* p, float scale, con
                 "Q/K/V/O must be 16-byte aligned");
     const int BH = p->batch * p->heads;
     CUtensorMap tq, tk, tv;
-    int rc = make_map(&tq, p->q, BH, p->seq_len);
-    if (!rc) rc = make_map(&tk, p->k, BH, p->seq_len);
-    if (!rc) rc = make_map(&tv, p->v, BH, p->seq_len);
+    int rc = make_map(dev, &tq, p->q, BH, p->seq_len);
+    if (!rc) rc = make_map(dev, &tk, p->k, BH, p->seq_len);
+    if (!rc) rc = make_map(dev, &tv, p->v, BH, p->seq_len);
     if (rc) return rc;
     Args a{};
     a.o = p->o; a.seq_lens = p->seq_lens; a.rope = rope; a.status = status;
     a.B = p->batch; a.H = p->heads; a.S = p->seq_len;
     a.causal = p->causal; a.rope_mode = p->rope_mode;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.wait_limit = dev->wait_limit_cycles;
     a.n_qp = (p->seq_len + NQ * BM - 1) / (NQ * BM);
     dim3 grid((unsigned)BH * a.n_qp);
-    if (p->out_dtype == GRL_F32) {
-        auto kern = flash_fwd_sm100_kernel<float>;
-        GRL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
-        kern<<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
-    } else {
-        auto kern = flash_fwd_sm100_kernel<__nv_bfloat16>;
-        GRL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
-        kern<<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
+    static bool attr_set[64] = {};
+    if (!attr_set[dev->ordinal & 63]) {      // a function attribute belongs to the device that was current
+        GRL_CUDA(cudaFuncSetAttribute(flash_fwd_sm100_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        GRL_CUDA(cudaFuncSetAttribute(flash_fwd_sm100_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        attr_set[dev->ordinal & 63] = true;
     }
+    if (p->out_dtype == GRL_F32)
+        flash_fwd_sm100_kernel<float><<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
+    else
+        flash_fwd_sm100_kernel<__nv_bfloat16><<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
     GRL_LAUNCHED("flash_fwd_sm100_kernel");
     return GRL_OK;
 }

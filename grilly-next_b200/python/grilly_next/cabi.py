@@ -26,7 +26,9 @@ SYMBOLS = [
     "grl_kv_compact_scratch_bytes", "grl_kv_compact", "grl_evict_head_scratch_bytes", "grl_evict_head_train",
     "grl_evict_head_predict", "grl_decode_pick_splits", "grl_decode_workspace_bytes", "grl_gqa_decode",
     "grl_gqa_decode_static", "grl_lse_merge", "grl_ipc_export", "grl_ipc_import", "grl_ipc_release",
-    "grl_exchange_merge",
+    "grl_exchange_merge", "grl_exchange_reset", "grl_device_set_wait_limits", "grl_tensor_map_cache_stats",
+    "grl_rope_table_prepare", "grl_group_unique_id", "grl_group_init_rank", "grl_group_info", "grl_group_allgather",
+    "grl_group_allreduce_max_f64", "grl_group_allgather_merge", "grl_group_sync", "grl_group_destroy",
 ]
 
 
@@ -70,7 +72,7 @@ class ExchangeParams(C.Structure):
                 ("peer_inbox", C.POINTER(C.c_void_p)), ("peer_flags", C.POINTER(C.c_void_p)),
                 ("seq", C.c_void_p), ("out", C.c_void_p),
                 ("rank", C.c_int32), ("world", C.c_int32), ("rows", C.c_int32), ("head_dim", C.c_int32),
-                ("flag_slots", C.c_int32), ("low_latency", C.c_int32)]
+                ("flag_slots", C.c_int32), ("low_latency", C.c_int32), ("wait_cycles", C.c_uint64)]
 
 
 class DecodeParams(C.Structure):
@@ -126,6 +128,19 @@ def lib():
         _lib.grl_ipc_import.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]
         _lib.grl_ipc_release.argtypes = [C.c_void_p, C.c_void_p]
         _lib.grl_exchange_merge.argtypes = [C.c_void_p, C.POINTER(ExchangeParams)]
+        _lib.grl_exchange_reset.argtypes = [C.c_void_p, C.POINTER(ExchangeParams)]
+        _lib.grl_device_set_wait_limits.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64]
+        _lib.grl_tensor_map_cache_stats.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+        _lib.grl_rope_table_prepare.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_float]
+        _lib.grl_group_unique_id.argtypes = [C.c_void_p]
+        _lib.grl_group_init_rank.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
+        _lib.grl_group_info.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]
+        _lib.grl_group_allgather.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
+        _lib.grl_group_allreduce_max_f64.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        _lib.grl_group_allgather_merge.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                                   C.c_uint64]
+        _lib.grl_group_sync.argtypes = [C.c_void_p, C.c_uint64]
+        _lib.grl_group_destroy.argtypes = [C.c_void_p]
         _lib.grl_decode_pick_splits.argtypes = [C.c_void_p, C.POINTER(DecodeParams), C.POINTER(C.c_int)]
         _lib.grl_decode_workspace_bytes.argtypes = [C.POINTER(DecodeParams), C.c_int, C.POINTER(C.c_size_t)]
         _lib.grl_kv_gather.argtypes = [C.c_void_p, C.POINTER(KVLayout), C.c_int, C.c_int, C.c_void_p, C.c_void_p]

@@ -13,7 +13,9 @@
  *  - All launches and copies are asynchronous on the device's stream (grl_device_use_stream
  *    adopts a caller's stream); grl_sync waits for it.
  *  - Callers own every buffer (grl_malloc / grl_free); kernels never allocate.  The library
- *    itself caches only small per-device tables (RoPE cos/sin) that it frees in grl_device_close.
+ *    itself caches only per-device RoPE cos/sin tables (one per (head_dim, theta, scaling), sized to the
+ *    longest sequence seen, rounded up to a power of two) that it frees in grl_device_close, and
+ *    the encoded tensor maps of recent launches (host memory).
  */
 #ifndef GRILLY_CUDA_H
 #define GRILLY_CUDA_H
@@ -28,6 +30,7 @@ extern "C" {
 typedef struct grl_device grl_device;
 typedef struct grl_event grl_event;
 typedef struct grl_graph grl_graph;
+typedef struct grl_group grl_group;
 
 enum {
     GRL_OK = 0,
@@ -69,6 +72,16 @@ int grl_device_get_info(grl_device* dev, grl_device_info* info);
  * stream; to name the legacy default stream pass cudaStreamLegacy ((cudaStream_t)0x1), since its
  * plain handle is NULL too. */
 int grl_device_use_stream(grl_device* dev, void* cuda_stream);
+/* Cycle budgets of the bounded waits inside the kernels; 0 restores a default.  barrier_wait_cycles
+ * (default 2e9, about a second) bounds every mbarrier wait of the prefill and decode kernels;
+ * peer_wait_cycles (default 1e9) bounds the wait for another GPU's partial in the cross-GPU merge
+ * (grl_exchange_params.wait_cycles overrides it per call).  A wait that runs out makes the kernel
+ * return; the next grl_sync reports GRL_ERR_TIMEOUT.  This is the device-side counterpart of the 2 s
+ * fence timeout of cpp/src/command_batch.cpp:16,145-148. */
+int grl_device_set_wait_limits(grl_device* dev, uint64_t barrier_wait_cycles, uint64_t peer_wait_cycles);
+/* Lookups of encoded tensor maps by (pointer, shape, box): the role of the descriptor-set LRU of
+ * PipelineCache (cpp/src/pipeline_cache.cpp:217-305).  Any pointer may be NULL. */
+int grl_tensor_map_cache_stats(grl_device* dev, int64_t* hits, int64_t* misses, int64_t* cached);
 int grl_malloc(grl_device* dev, size_t bytes, void** out);
 int grl_free(grl_device* dev, void* ptr);
 int grl_host_alloc(size_t bytes, void** out); /* pinned host memory for staging */
@@ -128,6 +141,11 @@ typedef struct {
     int32_t* status;    /* optional device int32[4]; [0] != 0 after a kernel-side failure */
 } grl_flash_params;
 int grl_flash_fwd(grl_device* dev, const grl_flash_params* p);
+
+/* Builds (or grows) the device's cos/sin table for positions [0, n_pos) ahead of use.  grl_flash_fwd
+ * does this on demand, which allocates and launches: inside a stream capture that is refused, so call
+ * this first (the precomputed-table mode of shaders/rope.glsl:109-113 made implicit). */
+int grl_rope_table_prepare(grl_device* dev, int n_pos, int head_dim, float theta, float scaling);
 
 /* ---- standalone RoPE: replaces shaders/rope.glsl:32-126 (push block :32-40).
  * x, y: (B,S,H,D) float32, out of place; position = sequence index / scaling;
@@ -299,9 +317,12 @@ int grl_lse_merge(grl_device* dev, const float* parts, int n_parts, size_t part_
  * grl_ipc_export / grl_ipc_import / grl_ipc_release wrap the CUDA IPC handle (64 bytes) of a
  * grl_malloc'ed buffer so that ranks can map one another's inboxes.
  * grl_exchange_merge: stores this rank's partial (layout of grl_gqa_decode's partial_out, n =
- * rows*(head_dim+2) floats) into every peer's inbox, waits -- at most ~0.5 s, then GRL_ERR_TIMEOUT
- * through grl_sync -- for the peers' partials of the same step, and writes the normalised merge to
- * out.  inbox: local float[2][world][n]; flags: local uint32[2][world], zero before the first step;
+ * rows*(head_dim+2) floats) into every peer's inbox, waits -- at most wait_cycles (default ~0.5 s), then
+ * GRL_ERR_TIMEOUT through grl_sync -- for the peers' partials of the same step, and writes the
+ * normalised merge to out.  After a timeout the ranks' step counters may differ (a rank that gave up
+ * has counted the step, the exchange inside the decode kernel has not): every rank then calls
+ * grl_exchange_reset, which zeroes its inbox, flags and step counter, and the ranks meet at a host
+ * barrier before the next step.  inbox: local float[2][world][n]; flags: local uint32[2][world], zero before the first step;
  * seq: local uint32 step counter, zero before the first step (the call increments it on the
  * device, so a captured CUDA graph can be replayed); peer_inbox / peer_flags: HOST arrays of
  * `world` device pointers (imported; the entry of this rank is ignored).  Every rank must make the
@@ -325,11 +346,35 @@ typedef struct grl_exchange_params_s {
     int32_t low_latency;    /* != 0 => every inbox element is 8 bytes {value, step number}
                              * (inbox: uint2[2][world][n], twice the bytes, zero before the first step); the flags
                              * are not used and no fence separates data from flag: one NVLink crossing per step */
+    uint64_t wait_cycles;   /* cycle budget of the wait for the peers; 0 => the device's peer_wait_cycles */
 } grl_exchange_params;
 int grl_ipc_export(grl_device* dev, void* ptr, void* handle_out_64_bytes);
 int grl_ipc_import(grl_device* dev, const void* handle_64_bytes, void** ptr_out);
 int grl_ipc_release(grl_device* dev, void* ptr);
 int grl_exchange_merge(grl_device* dev, const grl_exchange_params* p);
+int grl_exchange_reset(grl_device* dev, const grl_exchange_params* p);
+
+/* ---- NCCL communicator, one process per GPU.  No counterpart in the reference (it has no communication
+ * backend); this is the collective form of the exchange step above: all-gather of the partials over
+ * NVLink/NVSwitch, then the log-sum-exp merge.  libnccl.so.2 is opened at run time; without it these entry
+ * points return GRL_ERR_UNSUPPORTED and everything else works.
+ * grl_group_unique_id: rank 0 makes the 128-byte id and hands it to the other ranks by any host channel.
+ * grl_group_init_rank: collective; the group launches on dev's stream.
+ * grl_group_allgather_merge: partial = this rank's [O | m | l] (rows*(head_dim+2) floats), gather_buf =
+ * world times that, out = (rows, head_dim) normalised.  timeout_ns == 0 only enqueues (stream order; a CUDA
+ * graph can capture it); otherwise the call waits like grl_group_sync.
+ * grl_group_sync: waits for the stream while polling ncclCommGetAsyncError; a remote failure or the time limit
+ * aborts the communicator (ncclCommAbort) and returns an error; the group is then only good for
+ * grl_group_destroy. */
+int grl_group_unique_id(void* id_out_128_bytes);
+int grl_group_init_rank(grl_device* dev, const void* id_128_bytes, int rank, int world, grl_group** out);
+int grl_group_info(grl_group* group, int* rank, int* world, int* nccl_version);
+int grl_group_allgather(grl_group* group, const void* send, void* recv, size_t bytes_per_rank);
+int grl_group_allreduce_max_f64(grl_group* group, double* inout_device, size_t n);
+int grl_group_allgather_merge(grl_group* group, const float* partial, int rows, int head_dim, float* gather_buf,
+                              float* out, uint64_t timeout_ns);
+int grl_group_sync(grl_group* group, uint64_t timeout_ns);
+int grl_group_destroy(grl_group* group);
 
 #ifdef __cplusplus
 }

@@ -12,6 +12,10 @@
  *
  * oracle_gqa_decode_f32 restates shaders/gqa-attention.glsl:52-129 /
  * tests/test_inference_ops.py:64-95 (kv_head = q_head / (Hq/Hkv), softmax over cache_len).
+ *
+ * oracle_rope_interleaved_f32 restates the rotation of shaders/flash-attention2-rope.glsl:74-88,101-141
+ * (pairs (2i, 2i+1), theta = pos * base^(-2i/D) / scaling) in double arithmetic, like the numpy
+ * restatement it is checked against (parity unpinned: the reference holds no vector for RoPE).
  */
 #include <math.h>
 #include <stdint.h>
@@ -119,4 +123,27 @@ void oracle_gqa_decode_f32(const float* q, const float* k_cache, const float* v_
         }
         free(scores);
     }
+}
+
+/* x, y: (rows_outer, S, D), rotated along S (position = index in S) out of place; y may equal x. */
+void oracle_rope_interleaved_f32(const float* x, float* y, long rows_outer, int S, int D, double base,
+                                 double scaling) {
+    int half = D / 2;
+    double* inv = (double*)malloc(sizeof(double) * (size_t)(half > 0 ? half : 1));
+    for (int i = 0; i < half; ++i) inv[i] = pow(base, -2.0 * (double)i / (double)D);
+    long total = rows_outer * S;
+#pragma omp parallel for schedule(static)
+    for (long r = 0; r < total; ++r) {
+        int pos = (int)(r % S);
+        const float* xr = x + (size_t)r * D;
+        float* yr = y + (size_t)r * D;
+        for (int i = 0; i < half; ++i) {
+            double th = (double)pos * inv[i] / scaling;
+            double c = cos(th), s = sin(th);
+            double x0 = xr[2 * i], x1 = xr[2 * i + 1];
+            yr[2 * i] = (float)(x0 * c - x1 * s);
+            yr[2 * i + 1] = (float)(x0 * s + x1 * c);
+        }
+    }
+    free(inv);
 }

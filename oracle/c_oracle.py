@@ -55,5 +55,15 @@ def gqa_decode(q, k_cache, v_cache, cache_lens=None, scale=0.0):
     return out
 
 
+def rope_interleaved(x, base=10000.0, scaling=1.0):
+    """(..., S, D) float32 rotated along S at positions 0..S-1 (the C twin of attention_oracle.rope_interleaved)."""
+    x = np.ascontiguousarray(x, np.float32)
+    S, D = x.shape[-2], x.shape[-1]
+    out = np.empty_like(x)
+    lib().oracle_rope_interleaved_f32(_p(x), _p(out), ctypes.c_long(x.size // (S * D)), S, D,
+                                      ctypes.c_double(base), ctypes.c_double(scaling))
+    return out
+
+
 def num_threads():
     return lib().oracle_num_threads()

@@ -1,5 +1,9 @@
-"""Two-GPU check of the KV-sharded decode: NCCL all-gather + merge against the fused NVLink exchange +
-merge, both against the oracle.  Skipped unless two CUDA devices are visible."""
+"""Two-GPU check of the KV-sharded decode against the oracle, every form of the exchange: NCCL all-gather +
+merge through grl_group_*, the exchange kernel in its flag and {value, step} forms, the exchange inside the
+decode kernel, and the op layer's grilly_core.sharded_decode_step.  One process per GPU, meeting over the
+package's TcpChannel.  Skipped unless two CUDA devices are visible."""
+import ctypes as C
+import multiprocessing
 import os
 import socket
 import sys
@@ -22,19 +26,14 @@ def _free_port():
 def _worker(rank, world, port, result_dir):
     for p in (ROOT, os.path.join(ROOT, "tests"), os.path.join(ROOT, "grilly-next_b200", "python")):
         sys.path.insert(0, p)
-    import ctypes as C
-    import torch
-    import torch.distributed as dist
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["GRILLY_GPU_INDEX"] = str(rank)
     from grilly_next import cabi
-    from grilly_next.parallel import CudaShardOps, ShardedDecoder, shard_range, torch_stream_handle
+    from grilly_next.parallel import CudaShardOps, ShardedDecoder, TcpChannel, shard_range
     from gpu_helpers import PagedCache
     from oracle import attention_oracle as orc
-    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
-    os.environ["NCCL_NVLS_ENABLE"] = "0"
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    ch = TcpChannel(rank, world, "127.0.0.1", port)
     dev = cabi.Device(rank)
-    cabi.check(dev.L.grl_device_use_stream(dev.h, torch_stream_handle(torch)))
     B, Hq, Hkv, D, T = 1, 32, 8, 128, 1000
     rng = np.random.default_rng(7)
     k = rng.standard_normal((B, T, Hkv, D), dtype=np.float32)
@@ -42,45 +41,78 @@ def _worker(rank, world, port, result_dir):
     lo, hi = shard_range(T, world, rank)
     pc = PagedCache(dev, B, Hkv, D, hi - lo + 64, dtype=cabi.BF16)
     pc.append(k[:, lo:hi], v[:, lo:hi])
-    ops = CudaShardOps(cabi, dev, pc.layout(), Hq, hi - lo, torch)
-    dec = ShardedDecoder(dist, ops, lambda n, m: torch.empty((n, m), dtype=torch.float32, device="cuda"))
+    kb, vb = orc.round_bf16(k), orc.round_bf16(v)
     errs = []
-    for step in range(3):                       # NCCL path
-        q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
-        out = dec.step(torch.from_numpy(q).cuda()).cpu().numpy()
-        want = orc.gqa_decode_attention(q, orc.round_bf16(k), orc.round_bf16(v), Hq, Hkv, D)
-        errs.append(float(np.abs(out - want).max()))
-    fused = ops.setup_p2p(dist)
+
+    def run(dec, ops, steps):
+        for _ in range(steps):
+            q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
+            qd = dev.upload(q)
+            out_ptr = dec.step(qd)
+            dev.sync()
+            out = dev.download(out_ptr, (B, 1, Hq, D), np.float32)
+            dev.free(qd)
+            errs.append(float(np.abs(out - orc.gqa_decode_attention(q, kb, vb, Hq, Hkv, D)).max()))
+
+    # NCCL all-gather + merge behind the C ABI
+    ops = CudaShardOps(cabi, dev, pc.layout(), Hq, hi - lo)
+    ops.setup_nccl(ch)
+    dec = ShardedDecoder(ch, ops)
+    run(dec, ops, 3)
+    # the {value, step} pair form: first the exchange + merge kernel, then decode + exchange + merge as one launch;
+    # several steps each (both inbox parities); both share the inboxes and the step counter
+    fused = ops.setup_p2p(ch)
     assert ops.one_launch
-    for step in range(10):
-        # several steps each (both inbox parities): first the exchange fused with the merge kernel, then
-        # decode + exchange + merge as one launch; both share the inboxes and the step counter
-        ops.one_launch = step >= 5
-        q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
-        out = dec.step(torch.from_numpy(q).cuda()).cpu().numpy()
-        want = orc.gqa_decode_attention(q, orc.round_bf16(k), orc.round_bf16(v), Hq, Hkv, D)
-        errs.append(float(np.abs(out - want).max()))
-    # the flag-and-fence form of the exchange kernel (the default above is the {value, step} pair form)
-    ops2 = CudaShardOps(cabi, dev, pc.layout(), Hq, hi - lo, torch)
-    assert ops2.setup_p2p(dist, one_launch=False, low_latency=False) == fused
-    dec2 = ShardedDecoder(dist, ops2, lambda n, m: torch.empty((n, m), dtype=torch.float32, device="cuda"))
-    for step in range(5):
-        q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
-        out = dec2.step(torch.from_numpy(q).cuda()).cpu().numpy()
-        want = orc.gqa_decode_attention(q, orc.round_bf16(k), orc.round_bf16(v), Hq, Hkv, D)
-        errs.append(float(np.abs(out - want).max()))
+    for one_launch in (False, True):
+        ops.one_launch = one_launch
+        run(dec, ops, 5)
+    # the flag-and-fence form of the exchange kernel
+    ops2 = CudaShardOps(cabi, dev, pc.layout(), Hq, hi - lo)
+    assert ops2.setup_p2p(ch, one_launch=False, low_latency=False) == fused
+    run(ShardedDecoder(ch, ops2), ops2, 5)
+    ops.close()
     dev.sync()
+
+    # the op layer: grilly_core.ShardGroup + sharded_decode_step on host arrays
+    import grilly_core
+    ctx = grilly_core.Device()
+    raw = ch.all_gather_bytes(grilly_core.shard_group_unique_id() if rank == 0 else b"")[0]
+    group = grilly_core.ShardGroup(ctx, raw, rank, world)
+    assert (group.rank, group.world) == (rank, world)
+    assert tuple(grilly_core.shard_range(T, world, rank)) == (lo, hi)
+    kv = grilly_core.create_kv_cache(ctx, num_heads=Hkv, head_dim=D, compression_ratio=1, max_cache_tokens=hi - lo + 64,
+                                     use_h2o=False, batch_size=B, page_tokens=64, dtype="bf16")
+    grilly_core.kv_cache_append(ctx, kv, k[:, lo:hi], v[:, lo:hi])
+    for _ in range(2):
+        q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
+        out = grilly_core.sharded_decode_step(ctx, kv, group, q)
+        errs.append(float(np.abs(out - orc.gqa_decode_attention(q, kb, vb, Hq, Hkv, D)).max()))
+    ch.barrier()
+    del group
+    grilly_core.destroy_kv_cache(ctx, kv)
     np.save(os.path.join(result_dir, f"res{rank}.npy"), np.array(errs + [1.0 if fused else 0.0]))
-    dist.barrier()
-    dist.destroy_process_group()
+    ch.barrier()
+    dev.close()
+    ch.close()
 
 
 def test_sharded_decode_two_gpus(tmp_path):
-    import torch
-    if torch.cuda.device_count() < 2:
+    sys.path.insert(0, os.path.join(ROOT, "grilly-next_b200", "python"))
+    from grilly_next import cabi
+    n = C.c_int()
+    cabi.lib().grl_device_count(C.byref(n))
+    if n.value < 2:
         pytest.skip("needs two GPUs")
-    import torch.multiprocessing as mp
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    ctx = multiprocessing.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, str(tmp_path))) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
     for r in range(2):
         res = np.load(tmp_path / f"res{r}.npy")
+        assert len(res) == 3 + 10 + 5 + 2 + 1
+        assert res[-1] == 1.0, "peer inboxes could not be mapped"
         assert np.all(res[:-1] <= 5e-3), res

@@ -111,6 +111,15 @@ def test_rope_forms_are_rotations_and_differ():
     assert abs(d1 - d2) < 1e-4
 
 
+def test_c_rope_matches_the_numpy_restatement():
+    from oracle import c_oracle
+    rng = np.random.default_rng(6)
+    for shape, base, scaling in (((2, 3, 300, 128), 10000.0, 1.0), ((1, 1, 17, 64), 500000.0, 2.0)):
+        x = rng.standard_normal(shape, dtype=np.float32)
+        want = orc.rope_interleaved(x, np.arange(shape[2]), base, scaling)
+        np.testing.assert_allclose(c_oracle.rope_interleaved(x, base, scaling), want, atol=1e-7, rtol=0)
+
+
 def test_attention_mask_op():
     rng = np.random.default_rng(6)
     s = rng.standard_normal((2, 3, 5, 5), dtype=np.float32)
