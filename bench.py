@@ -491,14 +491,22 @@ def bench_prefill_e2e(args, L, steps, dist):
     for _ in range(steps):
         out = grilly_core.flash_attention2(ctx, *arrs, **kw)   # synchronous: returns with the result on the host
     dt = dist.max((time.perf_counter() - t0) / steps)
-    info = grilly_core.last_pipeline_info() if hasattr(grilly_core, "last_pipeline_info") else None
+    info = grilly_core.last_pipeline_info()            # of the last timed call: what crossed the link
+    h2d, d2h = int(info["h2d_bytes"]), int(info["d2h_bytes"])
+    # one more call, untimed, with per-stage event timing on: which stage is the limiter
+    grilly_core.set_pipeline_timing(True)
+    grilly_core.flash_attention2(ctx, *arrs, **kw)
+    stages = grilly_core.last_pipeline_info()
+    grilly_core.set_pipeline_timing(False)
+    busy = {k: stages[k] for k in ("host_round_ms", "h2d_busy_ms", "kernel_busy_ms", "d2h_busy_ms")}
+    stages["limiter"] = max(busy, key=busy.get)
+    stages["note"] = ("busy time per stage of one call (the stages overlap across chunks); host_round = the op's host threads "
+                      "rounding float32 to bf16 into pinned staging, h2d / d2h = copy queues, kernel = device cast + attention")
     del ctx
     for pp in ptrs:
         L.grl_host_free(pp)
-    nbytes = int(np.prod(shape)) * 4
-    pct = info["host_cast_pct"] if info else 100
-    h2d = 3 * (nbytes // 2 * pct + nbytes * (100 - pct)) // 100
-    return dt, h2d, nbytes, par, info
+    info = stages
+    return dt, h2d, d2h, par, info
 
 
 # ------------------------------------------------------------------------------------- decode legs
@@ -1020,7 +1028,8 @@ def main():
             line["e2e"] = {"value": fl / dt / 1e12 * world, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                            "ms_per_step": dt * 1e3, "parity": epar,
                            "api": "grilly_core.flash_attention2(dtype='bf16', out=pinned), pinned fp32 host arrays in and out; "
-                                  "h2d bytes are what crosses the link (the op rounds inputs to bf16 on host threads; 402,653,184 B of fp32 are read)"}
+                                  "h2d bytes are what crosses the link (the op's host threads round a share of every chunk to bf16 "
+                                  "first -- pipeline.host_cast_pct; 402,653,184 B of fp32 are read from the host arrays)"}
             if info:
                 line["e2e"]["pipeline"] = info
         if "e2e" in legs and "decode" in legs:

@@ -33,6 +33,20 @@ struct FlashAttention2Options {
     Precision precision = Precision::FP32;  // BF16: inputs rounded to bf16, tcgen05 kernel
 };
 
+/// What the last chunked (pipelined) flashAttention2 call of this process did: the share of every chunk that
+/// the host threads rounded to bf16 themselves, and the busy time of each stage -- host rounding (wall clock of
+/// the calling thread), upload queue, main queue (device cast + attention kernel), download queue (CUDA events,
+/// summed over the chunks) -- against the wall time of the whole call.  The stages overlap; the longest one
+/// names the limiter.  Queue times are collected only while setPipelineTiming(true) is in force.
+struct PipelineInfo {
+    bool valid = false, timed = false;
+    int hostCastPct = 0, chunks = 0, hostThreads = 0;
+    double hostRoundMs = 0, h2dMs = 0, kernelMs = 0, d2hMs = 0, totalMs = 0;
+    double h2dBytes = 0, d2hBytes = 0, hostRoundBytes = 0;
+};
+PipelineInfo lastPipelineInfo();
+void setPipelineTiming(bool on);
+
 /// Host pointers in, host pointer out, synchronous -- the reference contract
 /// (cpp/src/ops/attention.cpp:45-166).  Q,K,V,output: (B,H,S,D) float32 row-major;
 /// mask: nullptr or (B,H,S,S) floats, > 0 keeps.

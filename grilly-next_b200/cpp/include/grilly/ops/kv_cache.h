@@ -20,9 +20,9 @@ struct KVCacheConfig {
     uint32_t numHeads = 8;            // KV heads
     uint32_t headDim = 64;
     uint32_t numLayers = 12;
-    uint32_t compressionRatio = 1;    // only 1 (no MLA) is built
+    uint32_t compressionRatio = 1;    // > 1: MLA latents of headDim / ratio per (token, head) instead of pages
     uint32_t maxCacheTokens = 2048;   // capacity per sequence
-    bool useAsymmetricQuant = false;  // not built
+    bool useAsymmetricQuant = false;  // FP8-E4M3 keys + INT4 values + float16 group scales (kv_cache.cpp:250-400 there)
     uint32_t valueBits = 4;
     bool crossLayerSharing = false;
     bool useH2O = false;              // append beyond maxCacheTokens evicts the lowest-scoring tokens first
@@ -31,7 +31,7 @@ struct KVCacheConfig {
     // paged-cache additions
     uint32_t batchSize = 1;           // sequences held
     uint32_t pageTokens = 64;
-    int dtype = GRL_BF16;             // storage type of the pages
+    int dtype = GRL_BF16;             // storage type of the pages (useAsymmetricQuant overrides it with GRL_FP8_INT4)
 };
 
 /// Trainable auxiliary head for speculative eviction (the reference's EvictionHead, kv_cache.h:100-121;
@@ -47,6 +47,14 @@ struct EvictionHead {
 
 struct KVCache {
     GrillyBuffer kPages, vPages;      // [numPages][Hkv][pageTokens][D]
+    GrillyBuffer scales;              // quantised cache: float16 bits [numPages][Hkv][pageTokens][D/32]
+    // MLA mode (compressionRatio > 1, single sequence; cpp/src/ops/kv_cache.cpp:64-82,174-248,441-498 there): the
+    // cache keeps latents = [K | V] W_down per (token, head) and decodes [K | V] = latents W_up.  kPages then
+    // aliases `latents` (no pages exist).  The reference never initialises its two matrices; here they start
+    // as zeros and kvCacheSetMLAWeights sets them.
+    GrillyBuffer wDown, wUp, latents; // (2D, L), (L, 2D), (maxCacheTokens, H, L) float32
+    uint32_t latentDim = 0;
+    bool mla() const { return latentDim != 0; }
     GrillyBuffer blockTable;          // int32 [B][maxPages]
     GrillyBuffer seqLens;             // int32 [B]
     std::vector<int32_t> hostBlockTable;
@@ -98,6 +106,9 @@ void kvCacheDecode(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, 
                    float* decodedKeys, float* decodedValues, uint32_t seq = 0);
 
 KVCacheStats kvCacheGetStats(const KVCache& kvCache);
+
+/// MLA projection matrices from the host: wDown (2*headDim, latentDim), wUp (latentDim, 2*headDim), row-major.
+void kvCacheSetMLAWeights(BufferPool& pool, KVCache& kvCache, const float* wDown, const float* wUp);
 
 /// GQA decode attention over the cache (shaders/gqa-attention.glsl:34-130): q, out (B,1,Hq,D)
 /// host float32, already rotated.  accumulateScores: also add the attention mass every cached token

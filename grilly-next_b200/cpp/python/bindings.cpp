@@ -16,6 +16,7 @@
 #include "grilly/device.h"
 #include "grilly/host_workers.h"
 #include "grilly/ops/attention.h"
+#include "grilly/experimental/fused_attention.h"
 #include "grilly/ops/kv_cache.h"
 #include "grilly/ops/sharded_decode.h"
 #include "grilly/ops/rope.h"
@@ -317,6 +318,24 @@ PYBIND11_MODULE(grilly_core, m) {
         py::arg("rope_mode") = "interleaved", py::arg("dtype") = "fp32", py::arg("out") = py::none(),
         "GPU Flash Attention 2 with online softmax tiling");
 
+    m.def("set_pipeline_timing", &ops::setPipelineTiming, py::arg("on"),
+          "Collect per-stage queue times in the chunked flash_attention2 host path (see last_pipeline_info)");
+    m.def("last_pipeline_info", []() -> py::object {
+        const auto i = ops::lastPipelineInfo();
+        if (!i.valid) return py::none();
+        py::dict d;
+        d["host_cast_pct"] = i.hostCastPct; d["chunks"] = i.chunks; d["host_threads"] = i.hostThreads;
+        d["host_round_ms"] = i.hostRoundMs; d["h2d_busy_ms"] = i.h2dMs; d["total_ms"] = i.totalMs;
+        d["h2d_bytes"] = i.h2dBytes; d["d2h_bytes"] = i.d2hBytes;
+        d["host_round_gbs"] = i.hostRoundMs > 0 ? i.hostRoundBytes / i.hostRoundMs * 1e-6 : 0.0;
+        d["h2d_gbs"] = i.h2dMs > 0 ? i.h2dBytes / i.h2dMs * 1e-6 : 0.0;
+        if (i.timed) {
+            d["kernel_busy_ms"] = i.kernelMs; d["d2h_busy_ms"] = i.d2hMs;
+            d["d2h_gbs"] = i.d2hMs > 0 ? i.d2hBytes / i.d2hMs * 1e-6 : 0.0;
+        }
+        return d;
+    }, "Stages of this process's last chunked flash_attention2 call: share rounded on the host, busy time per stage");
+
     // ---- flash attention 2 + RoPE (push block of shaders/flash-attention2-rope.glsl:56-71)
     m.def(
         "flash_attention2_rope",
@@ -429,7 +448,8 @@ PYBIND11_MODULE(grilly_core, m) {
         py::arg("use_asymmetric_quant") = false, py::arg("value_bits") = 4, py::arg("cross_layer_sharing") = false,
         py::arg("use_h2o") = true, py::arg("use_speculative_eviction") = false, py::arg("eviction_threshold") = 0.1f,
         py::arg("batch_size") = 1, py::arg("page_tokens") = 64, py::arg("dtype") = "bf16",
-        "Create a KV cache (compression_ratio=1 selects the paged head-major cache built here)");
+        "Create a KV cache (compression_ratio=1 selects the paged head-major cache built here; with "
+        "use_asymmetric_quant=True its pages hold FP8-E4M3 keys, INT4 values and float16 group scales)");
 
     m.def("destroy_kv_cache",
           [](GrillyCoreContext& ctx, ops::KVCache& kv) { ops::destroyKVCache(ctx.pool, kv); }, py::arg("device"),
@@ -866,5 +886,55 @@ PYBIND11_MODULE(grilly_core, m) {
         const std::string msg = std::string(name) + ": " + what;
         m.def(name, [msg](py::args, py::kwargs) -> py::object { throw std::runtime_error(msg); });
     };
-    notBuilt("fused_attention_cpu", "the MLA latent path (CPU reference of the fused subgroup attention) is not built");
+    // ---- CPU reference of the MLA path (cpp/python/bindings.cpp:838-899 there): same signature, same shape rules
+    m.def(
+        "fused_attention_cpu",
+        [](FArr Q, FArr latents, FArr wUp, std::optional<FArr> mask, uint32_t cachedTokens, uint32_t numHeads,
+           uint32_t headDim, uint32_t latentDim, float scale) {
+            if (Q.ndim() < 2) throw std::runtime_error("Q must be at least 2D");
+            uint32_t B = 1, S = 1;
+            if (Q.ndim() == 4) { B = uint32_t(Q.shape(0)); S = uint32_t(Q.shape(2)); }
+            else if (Q.ndim() == 3) { B = uint32_t(Q.shape(0)); S = uint32_t(Q.shape(1)); }
+            else S = uint32_t(Q.shape(0));
+            if (size_t(Q.size()) != size_t(B) * numHeads * S * headDim)
+                throw std::runtime_error("Q does not hold batch * num_heads * seq_len * head_dim values");
+            if (size_t(latents.size()) < size_t(cachedTokens) * numHeads * latentDim)
+                throw std::runtime_error("latents must hold cached_tokens * num_heads * latent_dim values");
+            if (size_t(wUp.size()) != size_t(latentDim) * 2 * headDim)
+                throw std::runtime_error("w_up must be (latent_dim, 2 * head_dim)");
+            if (mask.has_value() && size_t(mask->size()) != size_t(B) * S * cachedTokens)
+                throw std::runtime_error("mask must be (batch, seq_len, cached_tokens)");
+            py::array_t<float> out({py::ssize_t(B), py::ssize_t(numHeads), py::ssize_t(S), py::ssize_t(headDim)});
+            experimental::fusedAttentionCPU(Q.data(), latents.data(), wUp.data(), mask.has_value() ? mask->data() : nullptr,
+                                            out.mutable_data(), B, S, cachedTokens, numHeads, headDim, latentDim, scale);
+            return out;
+        },
+        py::arg("Q"), py::arg("latents"), py::arg("w_up"), py::arg("mask") = py::none(), py::arg("cached_tokens") = 0,
+        py::arg("num_heads") = 8, py::arg("head_dim") = 64, py::arg("latent_dim") = 16, py::arg("scale") = 0.0f,
+        "CPU reference for fused MLA decompression + attention.\n"
+        "Decompresses latents via W_up matmul, then computes standard attention.");
+    m.def(
+        "kv_cache_set_mla_weights",
+        [](GrillyCoreContext& ctx, ops::KVCache& kv, FArr wDown, FArr wUp) {
+            const size_t n = size_t(2) * kv.config.headDim * kv.latentDim;
+            if (!kv.mla() || size_t(wDown.size()) != n || size_t(wUp.size()) != n)
+                throw std::runtime_error("kv_cache_set_mla_weights: w_down must be (2*head_dim, latent_dim) and w_up "
+                                         "(latent_dim, 2*head_dim) of an MLA cache (compression_ratio > 1)");
+            ops::kvCacheSetMLAWeights(ctx.pool, kv, wDown.data(), wUp.data());
+        },
+        py::arg("device"), py::arg("kv_cache"), py::arg("w_down"), py::arg("w_up"),
+        "Set the MLA projection matrices (they start as zeros; the reference leaves them uninitialised)");
+    m.def("kv_cache_latents", [](GrillyCoreContext& ctx, ops::KVCache& kv) {
+        if (!kv.mla()) throw std::runtime_error("kv_cache_latents: not an MLA cache");
+        const uint32_t T = kv.currentLen;
+        py::array_t<float> out({py::ssize_t(T), py::ssize_t(kv.config.numHeads), py::ssize_t(kv.latentDim)});
+        if (T) {
+            check(grl_memcpy_d2h(ctx.device.handle(), out.mutable_data(), kv.latents.dptr, size_t(out.size()) * 4), "kv_cache_latents");
+            check(grl_sync(ctx.device.handle(), 0), "kv_cache_latents");
+        }
+        return out;
+    }, py::arg("device"), py::arg("kv_cache"), "Latents of an MLA cache: (tokens, heads, latent_dim) float32");
+    for (const char* name : {"linear", "linear_cpu", "relu", "gelu", "silu", "tanh_act", "layernorm", "conv1d", "conv2d",
+                             "hamming_search"})
+        notBuilt(name, "outside the attention / KV-cache path that this CUDA build covers");
 }

@@ -1,6 +1,9 @@
 // Host side of the prefill ops: upload -> (cast) -> one kernel launch -> download.
 #include <algorithm>
+#include <atomic>
+#include <chrono>
 #include <cmath>
+#include <mutex>
 #include <cstdlib>
 #include <exception>
 #include <string>
@@ -33,6 +36,16 @@ struct Scoped {   // releases pooled buffers on every exit path
         return b;
     }
 };
+std::mutex g_infoMu;
+PipelineInfo g_lastInfo;
+std::atomic<bool> g_pipelineTiming{false};
+// Measured by earlier calls of this process: what the host threads round per second (float32 bytes read) and
+// what the link uploads per second.  They set the host-rounded share of a chunk when several processes share
+// the host (one per GPU).
+std::atomic<double> g_hostRoundBps{0.0}, g_linkBps{0.0};
+double nowMs() {
+    return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
 struct Recording {  // begin() now, leave the recording state on every exit path
     CommandBatch& batch;
     explicit Recording(CommandBatch& b) : batch(b) { batch.begin(); }
@@ -41,6 +54,12 @@ struct Recording {  // begin() now, leave the recording state on every exit path
     }
 };
 }  // namespace
+
+PipelineInfo lastPipelineInfo() {
+    std::lock_guard<std::mutex> lock(g_infoMu);
+    return g_lastInfo;
+}
+void setPipelineTiming(bool on) { g_pipelineTiming.store(on); }
 
 void flashAttention2(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* Q, const float* K,
                      const float* V, const float* mask, float* output, uint32_t batchSize, uint32_t seqLen,
@@ -74,7 +93,15 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
     // TFLOP/s in total at 100 / 50 / 25 / 0 %.
     if (const char* e = std::getenv("LOCAL_WORLD_SIZE")) {
         const int lws = std::atoi(e);
-        if (lws > 1) hostPct = size_t(50 / lws);
+        if (lws > 1) {
+            // Per chunk the link is busy for ((1-x)*4 + x*2) bytes per element and the host threads for 4*x bytes
+            // per element; the two overlap, so the best share x makes them equal: x = 2 r_h / (2 r_l + r_h) with
+            // the rounding rate r_h and the link rate r_l this process measured in its earlier calls (the first
+            // call has no measurement yet and starts from 50 % / processes).
+            const double rh = g_hostRoundBps.load(), rl = g_linkBps.load();
+            if (rh > 0.0 && rl > 0.0) hostPct = size_t(std::min(100.0, std::max(0.0, 100.0 * 2.0 * rh / (2.0 * rl + rh))));
+            else hostPct = size_t(50 / lws);
+        }
     }
     if (const char* e = std::getenv("GRILLY_PIPELINE_HOST_CAST_PCT")) hostPct = size_t(std::min(100, std::max(0, std::atoi(e))));
     if (!(pipelined && bf16 && hostPct == 100)) {
@@ -111,13 +138,25 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
         struct Events {   // destroyed on every exit path
             std::vector<grl_event*> v;
             ~Events() { for (auto* e : v) grl_event_destroy(e); }
-            grl_event* make() {
+            grl_event* make(bool timed = false) {
                 grl_event* e = nullptr;
-                check(grl_event_create_untimed(&e), "flashAttention2: event");
+                check(timed ? grl_event_create(&e) : grl_event_create_untimed(&e), "flashAttention2: event");
                 v.push_back(e);
                 return e;
             }
         } events;
+        const bool timing = g_pipelineTiming.load();
+        const double tCall = nowMs();
+        PipelineInfo info;
+        info.valid = true; info.timed = timing; info.hostCastPct = bf16 ? int(hostPct) : 0; info.chunks = int(plan.size());
+        info.hostThreads = HostWorkers::instance().threads();
+        std::vector<std::pair<grl_event*, grl_event*>> upSpans, mainSpans, downSpans;   // (begin, end) per chunk
+        auto mark = [&](grl_device* q, bool on) -> grl_event* {
+            if (!on) return nullptr;
+            grl_event* e = events.make(true);
+            check(grl_event_record(q, e), "flashAttention2: event");
+            return e;
+        };
         Recording rec(batch);
         if (mask) {
             maskBuf = pool.acquire(size_t(B) * S * 4);
@@ -140,6 +179,8 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
             const size_t s1 = s0 + chunk;
             // upload the whole chunk, then launch it piece by piece (one piece unless it crosses a batch row)
             const size_t e0 = s0 * slice, ne = chunk * slice;
+            // the upload queue is always timed (it feeds the share rule): one span per group of copies, so that the
+            // time the queue sits idle while the host threads round is not counted as copy time
             if (bf16) {
                 // Two routes share the chunk so that the host threads and the link finish together: the tail
                 // of the chunk is uploaded as float32 (and cast on the device), the head is rounded to bf16 by
@@ -149,36 +190,49 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
                 const float* src[3] = {Q + e0, K + e0, V + e0};
                 const GrillyBuffer* dst32[3] = {&q32, &k32, &v32};
                 const GrillyBuffer* dst16[3] = {&q16, &k16, &v16};
-                if (eh < ne)
+                if (eh < ne) {
+                    grl_event* b0 = mark(up, true);
                     for (int x = 0; x < 3; ++x)
                         check(grl_memcpy_h2d(up, at(*dst32[x], (e0 + eh) * 4), src[x] + eh, (ne - eh) * 4),
                               "flashAttention2: upload");
+                    upSpans.emplace_back(b0, mark(up, true));
+                }
                 const int set = int(chunkIndex & 1);
                 if (eh > 0) {
                     if (stagingBusy[set]) check(grl_event_sync(stagingBusy[set]), "flashAttention2: staging");
                     for (int x = 0; x < 3; ++x) {
                         auto* st = static_cast<uint16_t*>(pool.device().pinnedStaging(set * 3 + x, big * slice * 2));
+                        const double t0 = nowMs();
                         convertF32ToBF16(src[x], st, eh);
+                        info.hostRoundMs += nowMs() - t0;
+                        info.hostRoundBytes += double(eh) * 4;
+                        grl_event* b0 = mark(up, true);
                         check(grl_memcpy_h2d(up, at(*dst16[x], e0 * 2), st, eh * 2), "flashAttention2: upload");
+                        upSpans.emplace_back(b0, mark(up, true));
                     }
                 }
-                stagingBusy[set] = events.make();
+                stagingBusy[set] = events.make(true);
                 check(grl_event_record(up, stagingBusy[set]), "flashAttention2: event");
                 check(grl_event_wait(dev, stagingBusy[set]), "flashAttention2: event");
+                info.h2dBytes += 3.0 * (double(ne - eh) * 4 + double(eh) * 2);
                 if (eh < ne)
                     for (int x = 0; x < 3; ++x)
                         check(grl_cast(dev, at(*dst32[x], (e0 + eh) * 4), GRL_F32, at(*dst16[x], (e0 + eh) * 2), GRL_BF16,
                                        ne - eh),
                               "flashAttention2: cast");
             } else {
+                grl_event* upBegin = mark(up, true);
                 check(grl_memcpy_h2d(up, at(q32, e0 * 4), Q + e0, ne * 4), "flashAttention2: upload");
                 check(grl_memcpy_h2d(up, at(k32, e0 * 4), K + e0, ne * 4), "flashAttention2: upload");
                 check(grl_memcpy_h2d(up, at(v32, e0 * 4), V + e0, ne * 4), "flashAttention2: upload");
-                grl_event* uploaded = events.make();
+                grl_event* uploaded = events.make(true);
                 check(grl_event_record(up, uploaded), "flashAttention2: event");
                 check(grl_event_wait(dev, uploaded), "flashAttention2: event");
+                upSpans.emplace_back(upBegin, uploaded);
+                info.h2dBytes += 3.0 * double(ne) * 4;
             }
             ++chunkIndex;
+            grl_event* mainBegin = mark(dev, timing);
             for (size_t p0 = s0; p0 < s1;) {
                 const size_t b = p0 / H;
                 const size_t p1 = perBatch ? std::min(s1, (b + 1) * size_t(H)) : s1;
@@ -201,10 +255,16 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
                 check(grl_flash_fwd(dev, &p), "flashAttention2");
                 p0 = p1;
             }
-            grl_event* computed = events.make();
+            grl_event* computed = events.make(timing);
             check(grl_event_record(dev, computed), "flashAttention2: event");
             check(grl_event_wait(down, computed), "flashAttention2: event");
+            grl_event* downBegin = mark(down, timing);
             check(grl_memcpy_d2h(down, output + e0, at(out, e0 * 4), ne * 4), "flashAttention2: download");
+            if (timing) {
+                mainSpans.emplace_back(mainBegin, computed);
+                downSpans.emplace_back(downBegin, mark(down, true));
+            }
+            info.d2hBytes += double(ne) * 4;
             s0 = s1;
         }
         // the main queue outlives the call: make it wait for the copies before its buffers are reused
@@ -212,6 +272,24 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
         check(grl_event_record(down, done), "flashAttention2: event");
         check(grl_event_wait(dev, done), "flashAttention2: event");
         batch.submit();      // waits for the main queue (and so for `done`), reports kernel failures
+        info.totalMs = nowMs() - tCall;
+        auto busy = [](const std::vector<std::pair<grl_event*, grl_event*>>& spans) {
+            double total = 0;
+            for (auto& s : spans) {
+                float ms = 0;
+                if (grl_event_elapsed_ms(s.first, s.second, &ms) == GRL_OK) total += ms;
+            }
+            return total;
+        };
+        info.h2dMs = busy(upSpans);
+        info.kernelMs = busy(mainSpans);
+        info.d2hMs = busy(downSpans);
+        if (info.hostRoundMs > 0.05) g_hostRoundBps.store(info.hostRoundBytes / (info.hostRoundMs * 1e-3));
+        if (info.h2dMs > 0.05) g_linkBps.store(info.h2dBytes / (info.h2dMs * 1e-3));
+        {
+            std::lock_guard<std::mutex> lock(g_infoMu);
+            g_lastInfo = info;
+        }
         return;
     }
 

@@ -64,6 +64,7 @@ grl_kv_layout KVCache::layout() const {
     l.page_tokens = int(config.pageTokens);
     l.max_pages = int(maxPages);
     l.num_pages = int(numPages);
+    l.scales = scales.dptr;
     return l;
 }
 
@@ -78,22 +79,50 @@ grl_kv_meta KVCache::meta() const {
 }
 
 KVCache createKVCache(BufferPool& pool, const KVCacheConfig& cfg) {
-    if (cfg.compressionRatio != 1 || cfg.useAsymmetricQuant)
-        throw std::runtime_error(
-            "createKVCache: only the uncompressed paged cache is built (compression_ratio=1, "
-            "use_asymmetric_quant=False); MLA latents and FP8/INT4 storage are not");
+    if (cfg.compressionRatio == 0) throw std::runtime_error("createKVCache: compression_ratio must be at least 1");
     if (cfg.numHeads == 0 || cfg.headDim == 0 || cfg.batchSize == 0 || cfg.pageTokens == 0 || cfg.maxCacheTokens == 0)
         throw std::runtime_error("createKVCache: empty shape");
     if (cfg.headDim != 32 && cfg.headDim != 64 && cfg.headDim != 128)
         throw std::runtime_error("createKVCache: head_dim must be 32, 64 or 128");
-    if (cfg.dtype != GRL_BF16 && cfg.dtype != GRL_F32) throw std::runtime_error("createKVCache: unknown dtype");
+    if (cfg.dtype != GRL_BF16 && cfg.dtype != GRL_F32 && cfg.dtype != GRL_FP8_INT4)
+        throw std::runtime_error("createKVCache: unknown dtype");
     KVCache kv;
     kv.config = cfg;
+    const bool quant = cfg.useAsymmetricQuant || cfg.dtype == GRL_FP8_INT4;
+    if (quant) {
+        if (cfg.valueBits != 4) throw std::runtime_error("createKVCache: the quantised cache stores 4-bit values (value_bits=4)");
+        kv.config.dtype = GRL_FP8_INT4;
+        kv.config.useAsymmetricQuant = true;
+    }
     kv.maxPages = (cfg.maxCacheTokens + cfg.pageTokens - 1) / cfg.pageTokens;
     kv.numPages = kv.maxPages * cfg.batchSize;
-    const size_t pageBytes = size_t(cfg.numHeads) * cfg.pageTokens * cfg.headDim * elemSize(cfg.dtype);
-    kv.kPages = pool.acquire(pageBytes * kv.numPages);
-    kv.vPages = pool.acquire(pageBytes * kv.numPages);
+    if (cfg.compressionRatio > 1) {
+        // MLA latents (kv_cache.cpp:64-82): one sequence, float32, no pages
+        if (cfg.batchSize != 1) throw std::runtime_error("createKVCache: the MLA latent cache holds one sequence (batch_size=1)");
+        if (cfg.headDim % cfg.compressionRatio != 0)
+            throw std::runtime_error("createKVCache: head_dim must be a multiple of compression_ratio");
+        if (quant) throw std::runtime_error("createKVCache: quantised storage goes with compression_ratio=1");
+        kv.latentDim = cfg.headDim / cfg.compressionRatio;
+        kv.config.dtype = GRL_F32;
+        const size_t w = size_t(2) * cfg.headDim * kv.latentDim * 4;
+        kv.wDown = pool.acquire(w);
+        kv.wUp = pool.acquire(w);
+        kv.latents = pool.acquire(size_t(kv.capacity()) * cfg.numHeads * kv.latentDim * 4);
+        kv.kPages = kv.latents;
+        check(grl_memset(pool.device().handle(), kv.wDown.dptr, 0, w), "createKVCache");
+        check(grl_memset(pool.device().handle(), kv.wUp.dptr, 0, w), "createKVCache");
+        kv.numPages = 0;
+    } else if (quant) {
+        // one key byte and half a value byte per element, one float16 scale per group of 32 key elements
+        const size_t rows = size_t(cfg.numHeads) * cfg.pageTokens * kv.numPages;
+        kv.kPages = pool.acquire(rows * cfg.headDim);
+        kv.vPages = pool.acquire(rows * cfg.headDim / 2);
+        kv.scales = pool.acquire(rows * (cfg.headDim / 32) * 2);
+    } else {
+        const size_t pageBytes = size_t(cfg.numHeads) * cfg.pageTokens * cfg.headDim * elemSize(cfg.dtype);
+        kv.kPages = pool.acquire(pageBytes * kv.numPages);
+        kv.vPages = pool.acquire(pageBytes * kv.numPages);
+    }
     kv.blockTable = pool.acquire(size_t(kv.maxPages) * cfg.batchSize * 4);
     kv.seqLens = pool.acquire(size_t(cfg.batchSize) * 4);
     kv.hostBlockTable.assign(size_t(kv.maxPages) * cfg.batchSize, -1);
@@ -125,8 +154,16 @@ grl_evict_head EvictionHead::view() const {
 
 void destroyKVCache(BufferPool& pool, KVCache& kv) {
     kvCacheDestroyEvictionHead(pool, kv);
+    if (kv.mla()) {
+        kv.kPages = GrillyBuffer{};       // an alias of `latents`
+        pool.release(kv.wDown);
+        pool.release(kv.wUp);
+        pool.release(kv.latents);
+        kv.latentDim = 0;
+    }
     pool.release(kv.kPages);
     pool.release(kv.vPages);
+    pool.release(kv.scales);
     pool.release(kv.blockTable);
     pool.release(kv.seqLens);
     pool.release(kv.cumScore);
@@ -147,6 +184,36 @@ void kvCacheAppendRope(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
     if (n == 0) return;
     const auto& c = kv.config;
     grl_device* dev = pool.device().handle();
+    if (kv.mla()) {
+        // c_t = [k_t | v_t] W_down (kv_cache.cpp:174-248): concatenate, project, store at the current length
+        if (mode != RopeMode::None || qIn) throw std::runtime_error("kvCacheAppend: the MLA latent cache takes plain appends (no RoPE, no queries)");
+        if (uint32_t(kv.hostSeqLens[0]) + n > kv.capacity())
+            throw std::runtime_error("kvCacheAppend: sequence would exceed max_cache_tokens (" + std::to_string(c.maxCacheTokens) + ")");
+        cache.getOrCreate("kv-append-mla/" + std::to_string(c.headDim));
+        const size_t rows = size_t(n) * c.numHeads, D = c.headDim, L = kv.latentDim;
+        GrillyBuffer kb = pool.acquire(rows * D * 4), vb = pool.acquire(rows * D * 4), cat = pool.acquire(rows * 2 * D * 4);
+        try {
+            Recording rec(batch);
+            pool.upload(kb, newKeys, rows * D * 4);
+            pool.upload(vb, newValues, rows * D * 4);
+            check(grl_mla_concat(dev, static_cast<const float*>(kb.dptr), static_cast<const float*>(vb.dptr),
+                                 static_cast<float*>(cat.dptr), rows, int(D)), "kvCacheAppend: concat");
+            float* dst = static_cast<float*>(kv.latents.dptr) + size_t(kv.hostSeqLens[0]) * c.numHeads * L;
+            check(grl_gemm_f32(dev, static_cast<const float*>(cat.dptr), static_cast<const float*>(kv.wDown.dptr), dst,
+                               int(rows), int(2 * D), int(L)), "kvCacheAppend: down-projection");
+            kv.hostSeqLens[0] += int32_t(n);
+            check(grl_memcpy_h2d(dev, kv.seqLens.dptr, kv.hostSeqLens.data(), 4), "kvCacheAppend: length");
+            batch.submit();
+        } catch (...) {
+            pool.device().quiesce();   // nothing in flight may still touch the buffers released below
+            pool.release(kb); pool.release(vb); pool.release(cat);
+            throw;
+        }
+        pool.release(kb); pool.release(vb); pool.release(cat);
+        kv.currentLen = uint32_t(kv.hostSeqLens[0]);
+        kv.totalAppended += n;
+        return;
+    }
     cache.getOrCreate("kv-append/" + std::to_string(c.headDim));
     // Overflow: evict what does not fit (lowest cumulative scores, if H2O is on), then compact
     // (kv_cache.cpp:161-172).
@@ -204,6 +271,28 @@ void kvCacheDecode(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, 
     if (T == 0) return;
     if (!decodedKeys || !decodedValues) throw std::runtime_error("kvCacheDecode: null output");
     grl_device* dev = pool.device().handle();
+    if (kv.mla()) {
+        // [K | V] = c W_up (kv_cache.cpp:441-498), then split
+        cache.getOrCreate("kv-decode-mla/" + std::to_string(c.headDim));
+        const size_t rows = size_t(T) * c.numHeads, D = c.headDim, L = kv.latentDim;
+        GrillyBuffer full = pool.acquire(rows * 2 * D * 4), kb = pool.acquire(rows * D * 4), vb = pool.acquire(rows * D * 4);
+        try {
+            Recording rec(batch);
+            check(grl_gemm_f32(dev, static_cast<const float*>(kv.latents.dptr), static_cast<const float*>(kv.wUp.dptr),
+                               static_cast<float*>(full.dptr), int(rows), int(L), int(2 * D)), "kvCacheDecode: up-projection");
+            check(grl_mla_split(dev, static_cast<const float*>(full.dptr), static_cast<float*>(kb.dptr),
+                                static_cast<float*>(vb.dptr), rows, int(D)), "kvCacheDecode: split");
+            check(grl_memcpy_d2h(dev, decodedKeys, kb.dptr, rows * D * 4), "kvCacheDecode: download");
+            check(grl_memcpy_d2h(dev, decodedValues, vb.dptr, rows * D * 4), "kvCacheDecode: download");
+            batch.submit();
+        } catch (...) {
+            pool.device().quiesce();   // nothing in flight may still touch the buffers released below
+            pool.release(full); pool.release(kb); pool.release(vb);
+            throw;
+        }
+        pool.release(full); pool.release(kb); pool.release(vb);
+        return;
+    }
     cache.getOrCreate("kv-gather/" + std::to_string(c.headDim));
     const size_t n = size_t(T) * c.numHeads * c.headDim;
     GrillyBuffer kb = pool.acquire(n * 4), vb = pool.acquire(n * 4);
@@ -223,13 +312,25 @@ void kvCacheDecode(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, 
     pool.release(kb); pool.release(vb);
 }
 
+void kvCacheSetMLAWeights(BufferPool& pool, KVCache& kv, const float* wDown, const float* wUp) {
+    if (!kv.mla()) throw std::runtime_error("kvCacheSetMLAWeights: not an MLA cache (compression_ratio > 1)");
+    if (!wDown || !wUp) throw std::runtime_error("kvCacheSetMLAWeights: null matrix");
+    grl_device* dev = pool.device().handle();
+    const size_t bytes = size_t(2) * kv.config.headDim * kv.latentDim * 4;
+    check(grl_memcpy_h2d(dev, kv.wDown.dptr, wDown, bytes), "kvCacheSetMLAWeights");
+    check(grl_memcpy_h2d(dev, kv.wUp.dptr, wUp, bytes), "kvCacheSetMLAWeights");
+    check(grl_sync(dev, 0), "kvCacheSetMLAWeights");
+}
+
 KVCacheStats kvCacheGetStats(const KVCache& kv) {
     KVCacheStats s{};
     s.currentTokens = kv.currentLen;
     s.maxTokens = kv.config.maxCacheTokens;
     s.totalEvicted = uint32_t(kv.totalEvicted);
     s.totalAppended = uint32_t(kv.totalAppended);
-    s.compressionRatio = kv.config.dtype == GRL_BF16 ? 2.0f : 1.0f;  // bytes saved against float32 storage
+    // bytes saved against float32 storage
+    s.compressionRatio = kv.config.dtype == GRL_BF16 ? 2.0f : kv.config.dtype == GRL_FP8_INT4 ? 8.0f / 1.5f : 1.0f;   // the scales are not counted (kv_cache.cpp:1024-1027)
+    if (kv.mla()) s.compressionRatio = 2.0f * float(kv.config.headDim) / float(kv.latentDim);   // kv_cache.cpp:1017-1020
     // mean cumulative score of the active tokens of sequence 0, summed in index order (kv_cache.cpp:1004-1015)
     s.avgAttentionScore = 0.0f;
     if (kv.device && kv.cumScore.valid() && kv.currentLen > 0) {
@@ -246,7 +347,7 @@ KVCacheStats kvCacheGetStats(const KVCache& kv) {
     }
     s.pagesTotal = kv.numPages;
     s.pagesUsed = kv.nextFreePage;
-    s.bytes = uint64_t(kv.kPages.bucketSize) + kv.vPages.bucketSize;
+    s.bytes = uint64_t(kv.kPages.bucketSize) + kv.vPages.bucketSize + kv.scales.bucketSize;
     return s;
 }
 
@@ -289,6 +390,7 @@ static void launchDecode(grl_device* dev, BufferPool& pool, const KVCache& kv, c
 void gqaAttention(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const KVCache& kv, const float* q,
                   float* out, uint32_t numQHeads, float scale, int nSplits, bool accumulateScores) {
     if (!kv.kPages.valid()) throw std::runtime_error("gqaAttention: cache was destroyed");
+    if (kv.mla()) throw std::runtime_error("gqaAttention: not built for the MLA latent cache (decode it with kvCacheDecode, or use compression_ratio=1)");
     if (!q || !out) throw std::runtime_error("gqaAttention: null tensor pointer");
     const auto& c = kv.config;
     if (numQHeads == 0 || numQHeads % c.numHeads != 0)
@@ -316,6 +418,7 @@ void decodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVC
                 const float* kNew, const float* vNew, float* out, uint32_t numQHeads, RopeMode mode, float theta,
                 float scaling, float scale, bool accumulateScores) {
     if (!kv.kPages.valid()) throw std::runtime_error("decodeStep: cache was destroyed");
+    if (kv.mla()) throw std::runtime_error("decodeStep: not built for the MLA latent cache (decode it with kvCacheDecode, or use compression_ratio=1)");
     if (!q || !kNew || !vNew || !out) throw std::runtime_error("decodeStep: null tensor pointer");
     const auto& c = kv.config;
     if (numQHeads == 0 || numQHeads % c.numHeads != 0)
@@ -363,6 +466,7 @@ void decodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVC
 void gqaAttentionDevice(BufferPool& pool, PipelineCache& cache, const KVCache& kv, const GrillyBuffer& q,
                         GrillyBuffer& out, uint32_t numQHeads, float scale, int nSplits, GrillyBuffer& ws) {
     if (!kv.kPages.valid()) throw std::runtime_error("gqaAttention: cache was destroyed");
+    if (kv.mla()) throw std::runtime_error("gqaAttention: not built for the MLA latent cache (decode it with kvCacheDecode, or use compression_ratio=1)");
     const auto& c = kv.config;
     if (numQHeads == 0 || numQHeads % c.numHeads != 0)
         throw std::runtime_error("gqaAttention: num_q_heads must be a positive multiple of num_kv_heads");
@@ -377,6 +481,7 @@ void decodeStepDevice(BufferPool& pool, PipelineCache& cache, KVCache& kv, const
                       const GrillyBuffer& kNew, const GrillyBuffer& vNew, GrillyBuffer& qRotated, GrillyBuffer& out,
                       uint32_t numQHeads, RopeMode mode, float theta, float scaling, float scale, GrillyBuffer& ws) {
     if (!kv.kPages.valid()) throw std::runtime_error("decodeStep: cache was destroyed");
+    if (kv.mla()) throw std::runtime_error("decodeStep: not built for the MLA latent cache (decode it with kvCacheDecode, or use compression_ratio=1)");
     const auto& c = kv.config;
     if (numQHeads == 0 || numQHeads % c.numHeads != 0)
         throw std::runtime_error("decodeStep: num_q_heads must be a positive multiple of num_kv_heads");
@@ -547,6 +652,7 @@ void kvCacheEvictSpeculative(CommandBatch& batch, BufferPool& pool, PipelineCach
 
 void kvCacheCompact(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, KVCache& kv) {
     if (!kv.kPages.valid()) throw std::runtime_error("kvCacheCompact: cache was destroyed");
+    if (kv.mla()) throw std::runtime_error("kvCacheCompact: not built for the MLA latent cache (decode it with kvCacheDecode, or use compression_ratio=1)");
     grl_device* dev = pool.device().handle();
     cache.getOrCreate("kv-compact/" + std::to_string(kv.config.headDim));
     grl_kv_layout l = kv.layout();

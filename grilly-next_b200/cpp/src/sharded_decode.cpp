@@ -43,6 +43,7 @@ void shardedDecodeStep(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
                        const float* q, float* out, uint32_t numQHeads, float scale, uint64_t timeoutNs) {
     if (!g.group) throw std::runtime_error("shardedDecodeStep: the group was destroyed");
     if (!kv.kPages.valid()) throw std::runtime_error("shardedDecodeStep: cache was destroyed");
+    if (kv.mla()) throw std::runtime_error("shardedDecodeStep: not built for the MLA latent cache");
     if (!q || !out) throw std::runtime_error("shardedDecodeStep: null tensor pointer");
     const auto& c = kv.config;
     if (numQHeads == 0 || numQHeads % c.numHeads != 0)

@@ -56,7 +56,8 @@ struct grl_device {
     // Arrival counters of the split-KV decode (one per (sequence, kv head), zero between launches: the
     // CTA that brings a counter to its final value resets it) and, last, the count of finished heads.
     static constexpr int kCounterSlots = 4096;
-    int32_t* d_counters = nullptr;   // = d_status + 4, int32[kCounterSlots + 1]
+    static constexpr int kCounterInts = kCounterSlots + 1 + 2;   // + the prefill kernel's work and finished-CTA counters
+    int32_t* d_counters = nullptr;   // = d_status + 4, int32[kCounterInts]
 };
 
 struct grl_event {

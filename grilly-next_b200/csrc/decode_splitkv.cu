@@ -15,6 +15,7 @@ constexpr int kDecodeThreads = 128;
 struct DecodeArgs {
     const void* k_pages;
     const void* v_pages;
+    const uint16_t* scales;   // quantised cache only: float16 bits per (row, group of 32)
     const int32_t* block_table;
     const int32_t* seq_lens;
     const float* q;
@@ -48,10 +49,46 @@ template <> struct Vec16<__nv_bfloat16> {
     }
 };
 
+// How a lane fetches its slice of one cached row (row = (page * Hkv + kv head) * page_tokens + slot) as float32.
+template <typename T> struct KVLoad {
+    static constexpr int VEC = Vec16<T>::N;
+    __device__ static void load(const DecodeArgs& a, size_t row, int D, int li, float* kx, float* vx) {
+        const size_t off = row * D + li * VEC;
+        Vec16<T>::load(reinterpret_cast<const T*>(a.k_pages) + off, kx);
+        Vec16<T>::load(reinterpret_cast<const T*>(a.v_pages) + off, vx);
+    }
+};
+// GRL_FP8_INT4: 8 elements per lane = 8 key bytes, 4 value bytes and the scale of their group of 32; dequantised
+// with the reference's arithmetic (cpp/src/ops/kv_cache.cpp:513-570): code value times 1/scale, the key scale
+// for keys and values alike.
+struct QuantKV {};
+template <> struct KVLoad<QuantKV> {
+    static constexpr int VEC = 8;
+    __device__ static void load(const DecodeArgs& a, size_t row, int D, int li, float* kx, float* vx) {
+        const uint2 kb = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.k_pages) + row * D + li * 8));
+        const uint32_t vb = __ldg(reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.v_pages) + row * (D / 2) + li * 4));
+        const uint16_t hb = __ldg(a.scales + row * (D / 32) + (li >> 2));
+        const uint32_t he = (hb >> 10) & 0x1Fu, hm = hb & 0x03FFu;
+        const float scale = he == 0 ? (float)hm * 5.9604644775390625e-08f
+                                    : __uint_as_float((((uint32_t)hb >> 15) << 31) | ((he + 112u) << 23) | (hm << 13));
+        const float inv = scale > 0.f ? __fdiv_rn(1.0f, scale) : 1.0f;
+        const uint32_t kw[2] = {kb.x, kb.y};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const uint32_t c = (kw[e >> 2] >> ((e & 3) * 8)) & 0xFFu;
+            const uint32_t ce = (c >> 3) & 0x0Fu, cm = c & 7u;
+            float v = ce == 0 ? (float)cm * 0.001953125f : __uint_as_float(((ce + 120u) << 23) | (cm << 20));
+            v = (c & 0x80u) ? -v : v;
+            kx[e] = __fmul_rn(v, inv);
+            vx[e] = __fmul_rn((float)((int)((vb >> (e * 4)) & 0x0Fu) - 8), inv);
+        }
+    }
+};
+
 // grid (n_splits, Hkv*chunks, B); GC = query heads handled per CTA (a chunk of the KV group).
 template <typename T, int D, int GC>
 __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(DecodeArgs a) {
-    constexpr int VEC = Vec16<T>::N;
+    constexpr int VEC = KVLoad<T>::VEC;
     constexpr int LPT = D / VEC;           // lanes per token
     constexpr int TPW = 32 / LPT;          // tokens per warp iteration
     constexpr int NWARP = kDecodeThreads / 32;
@@ -89,8 +126,6 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(DecodeArgs
         }
     }
 
-    const T* kp = reinterpret_cast<const T*>(a.k_pages);
-    const T* vp = reinterpret_cast<const T*>(a.v_pages);
     const int32_t* bt = a.block_table + (size_t)b * a.max_pages;
 
     // The trip count is uniform across the warp (the shuffles below need all 32 lanes); a
@@ -101,9 +136,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_split_kernel(DecodeArgs
         float kx[VEC], vx[VEC];
         if (live) {
             const int page = bt[t / a.P], slot = t % a.P;
-            const size_t off = (((size_t)page * a.Hkv + kvh) * a.P + slot) * D + li * VEC;
-            Vec16<T>::load(kp + off, kx);
-            Vec16<T>::load(vp + off, vx);
+            KVLoad<T>::load(a, ((size_t)page * a.Hkv + kvh) * a.P + slot, D, li, kx, vx);
         } else {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) { kx[e] = 0.f; vx[e] = 0.f; }
@@ -273,7 +306,10 @@ static int check_decode(const grl_decode_params* p, bool need_tensors = true) {
     GRL_REQUIRE(kv.batch > 0 && kv.num_kv_heads > 0 && kv.page_tokens > 0 && kv.max_pages > 0, "bad cache shape");
     GRL_REQUIRE(p->num_q_heads > 0 && p->num_q_heads % kv.num_kv_heads == 0,
                 "num_q_heads (%d) must be a multiple of num_kv_heads (%d)", p->num_q_heads, kv.num_kv_heads);
-    GRL_REQUIRE(kv.cache_dtype == GRL_BF16 || kv.cache_dtype == GRL_F32, "unknown cache dtype");
+    GRL_REQUIRE(kv.cache_dtype == GRL_BF16 || kv.cache_dtype == GRL_F32 || kv.cache_dtype == GRL_FP8_INT4,
+                "unknown cache dtype");
+    GRL_REQUIRE(kv.cache_dtype != GRL_FP8_INT4 || (kv.scales && kv.head_dim % 32 == 0),
+                "the quantised cache needs its scales buffer and a head_dim that is a multiple of 32");
     if (need_tensors) {
         GRL_REQUIRE(p->q, "q is NULL");
         GRL_REQUIRE(p->out || p->partial_out, "out and partial_out are both NULL");
@@ -351,7 +387,7 @@ int grl_gqa_decode(grl_device* dev, const grl_decode_params* p) {
                     p->workspace_bytes, need);
     DeviceGuard g(dev->ordinal);
     DecodeArgs a{};
-    a.k_pages = kv.k_pages; a.v_pages = kv.v_pages; a.block_table = kv.block_table; a.seq_lens = kv.seq_lens;
+    a.k_pages = kv.k_pages; a.v_pages = kv.v_pages; a.scales = static_cast<const uint16_t*>(kv.scales); a.block_table = kv.block_table; a.seq_lens = kv.seq_lens;
     a.q = p->q; a.part = (float*)p->workspace; a.out = p->out;
     a.scores_out = p->scores_out; a.scores_ld = p->scores_ld;
     a.B = kv.batch; a.Hq = p->num_q_heads; a.Hkv = kv.num_kv_heads; a.P = kv.page_tokens;
@@ -367,8 +403,9 @@ int grl_gqa_decode(grl_device* dev, const grl_decode_params* p) {
     if (mma)
         rc = decode_mma_launch(dev, p, n_splits, a.scale, direct, fused);
     else
-        rc = (kv.cache_dtype == GRL_BF16) ? dispatch_decode_d<__nv_bfloat16>(dev, a, D)
-                                          : dispatch_decode_d<float>(dev, a, D);
+        rc = kv.cache_dtype == GRL_BF16       ? dispatch_decode_d<__nv_bfloat16>(dev, a, D)
+             : kv.cache_dtype == GRL_FP8_INT4 ? dispatch_decode_d<QuantKV>(dev, a, D)
+                                              : dispatch_decode_d<float>(dev, a, D);
     if (rc || direct || fused) return rc;
     const int rows = kv.batch * p->num_q_heads;
     const size_t stride = (size_t)rows * (D + 2);

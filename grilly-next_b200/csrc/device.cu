@@ -179,7 +179,7 @@ int grl_device_open(int ordinal, grl_device** out) {
         return set_error(GRL_ERR_CUDA, "device open failed: %s", cudaGetErrorString(e));
     }
     d->stream = d->own_stream;
-    const size_t status_bytes = (4 + grl_device::kCounterSlots + 1) * sizeof(int32_t);
+    const size_t status_bytes = (4 + grl_device::kCounterInts) * sizeof(int32_t);
     if (cudaMalloc(&d->d_status, status_bytes) != cudaSuccess ||
         cudaMemset(d->d_status, 0, status_bytes) != cudaSuccess ||
         cudaHostAlloc(&d->h_status, 4 * sizeof(int32_t), cudaHostAllocDefault) != cudaSuccess) {
@@ -340,14 +340,14 @@ static int report_kernel_status(grl_device* dev, bool copied) {
     const int32_t* st = dev->h_status;
     if (st[0] == 0) return GRL_OK;
     // a kernel that gave up may have left arrival counters half-way: clear them with the status
-    GRL_CUDA(cudaMemsetAsync(dev->d_status, 0, (4 + grl_device::kCounterSlots + 1) * sizeof(int32_t), dev->stream));
-    // [1] = kind << 28 | detail: 1 prefill (mask of the mbarriers that were being waited on; [3] = CTA),
+    GRL_CUDA(cudaMemsetAsync(dev->d_status, 0, (4 + grl_device::kCounterInts) * sizeof(int32_t), dev->stream));
+    // [1] = kind << 28 | detail: 1 prefill (index of the mbarrier whose wait ran out; [3] = CTA),
     // 2 decode (mbarrier index; [2],[3] = CTA), 3 cross-GPU merge (peer that did not post; [2] = step, [3] = rank),
     // 4 append (a sequence without room; [2] = sequence, [3] = its length)
     const int code = st[0] == GRL_ERR_TIMEOUT ? GRL_ERR_TIMEOUT : GRL_ERR_KERNEL;
     const unsigned int kind = (unsigned int)st[1] >> 28, detail = (unsigned int)st[1] & 0x0fffffffu;
     switch (kind) {
-        case 1: return set_error(code, "prefill kernel: a wait ran out (mbarrier mask 0x%x, CTA %d)", detail, st[3]);
+        case 1: return set_error(code, "prefill kernel: a wait ran out (mbarrier %u, CTA %d)", detail, st[3]);
         case 2: return set_error(code, "decode kernel: a wait ran out (mbarrier %u, CTA %d,%d)", detail, st[2], st[3]);
         case 3: return set_error(code, "cross-GPU merge on rank %d: peer %u did not post step %d within the wait limit",
                                  st[3], detail, st[2]);

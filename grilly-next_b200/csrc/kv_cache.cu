@@ -19,6 +19,8 @@ struct AppendArgs {
     int rope_mode, pos_base, update_lens;
     const int32_t* pos_offsets;
     int32_t* status;     // device status word: GRL_ERR_INVALID when a sequence has no room for the new tokens
+    uint16_t* scales;    // quantised cache only
+    int skip_kv;         // rotate the queries only (the quantised append stores K and V with its own kernel)
     RopeFreq freq;
 };
 
@@ -66,6 +68,7 @@ __global__ void __launch_bounds__(1024) kv_append_kernel(AppendArgs a) {
             cached_pos = slot_pos; cached_j = j;
         }
         if (hs < a.Hkv) {
+            if (a.skip_kv) continue;
             const int page = a.block_table[(size_t)b * a.max_pages + slot_pos / a.P];
             const int slot = slot_pos % a.P;
             const size_t src = (((size_t)b * a.n_new + i) * a.Hkv + hs) * a.D;
@@ -135,11 +138,168 @@ __global__ void swizzle_kv_kernel(const float* __restrict__ in, float* __restric
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Quantised storage (GRL_FP8_INT4): the reference's asymmetric quantisation, cpp/src/ops/kv_cache.cpp:272-399,
+// byte for byte.  One warp owns one group of 32 elements of one (token, kv head): lane = element, the group
+// maximum is a warp reduction, every lane encodes its own key byte and value nibble.
+__device__ __forceinline__ uint16_t scale_to_half_bits(float scale) {       // kv_cache.cpp:297-303: bit surgery
+    const uint32_t b = __float_as_uint(scale);
+    return (uint16_t)(((b >> 16) & 0x8000u) | (((b >> 23) - 112u) << 10) | ((b >> 13) & 0x03FFu));
+}
+__device__ __forceinline__ float half_bits_to_scale(uint16_t h) {           // kv_cache.cpp:517-530
+    const uint32_t sign = (h >> 15) & 1u, e = (h >> 10) & 0x1Fu, m = h & 0x03FFu;
+    if (e == 0) return (float)m * 5.9604644775390625e-08f;                  // ldexp(m, -24), exact
+    return __uint_as_float((sign << 31) | ((e + 112u) << 23) | (m << 13));
+}
+// int(log2f(a)) of the reference (kv_cache.cpp:318): the float32 logarithm, truncated toward zero.  The
+// logarithm is taken in double and rounded to float, which is what a correctly rounded log2f returns.
+__device__ __forceinline__ uint8_t fp8_encode(float scaled) {               // kv_cache.cpp:306-327
+    scaled = fmaxf(-448.0f, fminf(448.0f, scaled));
+    const int sign = scaled < 0.f ? 1 : 0;
+    const float a = fabsf(scaled);
+    if (a < 1.0f / 512.0f) return 0;
+    int e = (int)(float)log2((double)a);
+    e = max(0, min(15, e + 7));
+    const float mantissa = __fsub_rn(__fdiv_rn(a, __uint_as_float((uint32_t)(e - 7 + 127) << 23)), 1.0f);
+    // a negative fraction (magnitudes below 1, whose exponent came out one too high) wraps like the reference's
+    // cast does on x86-64: to int32 with truncation, low 8 bits kept
+    const uint8_t mant = (uint8_t)((uint32_t)(int)__fmul_rn(mantissa, 8.0f) & 0xFFu) & 0x07u;
+    return (uint8_t)((sign << 7) | (e << 3) | mant);
+}
+__device__ __forceinline__ float fp8_decode(uint8_t c) {                    // kv_cache.cpp:540-552
+    const uint32_t s = (c >> 7) & 1u, e = (c >> 3) & 0x0Fu, m = c & 7u;
+    const float v = e == 0 ? (float)m * 0.001953125f                         // m * 2^-9
+                           : __uint_as_float(((e - 7u + 127u) << 23) | (m << 20));
+    return s ? -v : v;
+}
+
+// grid (ceil(n_new*Hkv*G / warps per CTA), B), G = D/32 groups per head.
+__global__ void __launch_bounds__(256) kv_append_quant_kernel(AppendArgs a) {
+    const int b = blockIdx.y, lane = threadIdx.x & 31;
+    const int G = a.D / 32;
+    const int len0 = a.seq_lens[b];
+    if (len0 < 0 || len0 + a.n_new > a.max_pages * a.P) {
+        if (threadIdx.x == 0 && blockIdx.x == 0 && a.status && atomicCAS(a.status, 0, GRL_ERR_INVALID) == 0) {
+            a.status[1] = 4 << 28;
+            a.status[2] = b;
+            a.status[3] = len0;
+        }
+        return;
+    }
+    const int pos_off = a.pos_offsets ? a.pos_offsets[b] : 0;
+    const int items = a.n_new * a.Hkv * G;
+    const int half = a.D / 2;
+    uint8_t* kp = reinterpret_cast<uint8_t*>(a.k_pages);
+    uint8_t* vp = reinterpret_cast<uint8_t*>(a.v_pages);
+    for (int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); item < items; item += gridDim.x * (blockDim.x >> 5)) {
+        const int g = item % G, h = (item / G) % a.Hkv, i = item / (G * a.Hkv);
+        const int d = g * 32 + lane;
+        const int slot_pos = len0 + i;
+        const size_t src = (((size_t)b * a.n_new + i) * a.Hkv + h) * a.D;
+        float kx = a.k_new[src + d];
+        if (a.rope_mode != GRL_ROPE_NONE) {
+            int j, d_other;
+            bool first;
+            if (a.rope_mode == GRL_ROPE_INTERLEAVED) { j = d >> 1; first = (d & 1) == 0; d_other = d ^ 1; }
+            else { j = d % half; first = d < half; d_other = first ? d + half : d - half; }
+            float c, s;
+            rope_sincos(a.pos_base + pos_off + slot_pos, a.freq.inv_freq[j], &c, &s);
+            const float other = a.k_new[src + d_other];
+            kx = first ? kx * c - other * s : other * s + kx * c;
+        }
+        const float vx = a.v_new[src + d];
+        float kmax = fabsf(kx), vmax = fabsf(vx);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            kmax = fmaxf(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+            vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+        }
+        const float kscale = kmax > 0.f ? __fdiv_rn(448.0f, kmax) : 1.0f;
+        const float vscale = vmax > 0.f ? __fdiv_rn(7.0f, vmax) : 1.0f;
+        const int page = a.block_table[(size_t)b * a.max_pages + slot_pos / a.P];
+        const size_t row = ((size_t)page * a.Hkv + h) * a.P + slot_pos % a.P;
+        kp[row * a.D + d] = fp8_encode(__fmul_rn(kx, kscale));
+        int q = (int)roundf(__fmul_rn(vx, vscale)) + 8;                       // kv_cache.cpp:363-366
+        q = max(0, min(15, q));
+        const int q_hi = __shfl_down_sync(0xffffffffu, q, 1);
+        if ((lane & 1) == 0) vp[row * half + (d >> 1)] = (uint8_t)((q & 0x0F) | ((q_hi & 0x0F) << 4));
+        if (lane == 0) a.scales[row * G + g] = scale_to_half_bits(kscale);   // the value scale is dropped (:393-398)
+    }
+}
+
+// Dequantise sequence b as token-major float32 (T, Hkv, D): kv_cache.cpp:500-577.  One thread per element.
+__global__ void kv_gather_quant_kernel(const uint8_t* __restrict__ kp, const uint8_t* __restrict__ vp,
+                                       const uint16_t* __restrict__ scales, const int32_t* __restrict__ block_table,
+                                       int b, int n_tokens, int Hkv, int D, int P, int max_pages,
+                                       float* __restrict__ out_k, float* __restrict__ out_v) {
+    const size_t total = (size_t)n_tokens * Hkv * D;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int d = (int)(idx % D);
+        const int h = (int)((idx / D) % Hkv);
+        const int t = (int)(idx / ((size_t)D * Hkv));
+        const int page = block_table[(size_t)b * max_pages + t / P];
+        const size_t row = ((size_t)page * Hkv + h) * P + t % P;
+        const float scale = half_bits_to_scale(scales[row * (D / 32) + d / 32]);
+        const float inv = scale > 0.f ? __fdiv_rn(1.0f, scale) : 1.0f;
+        out_k[idx] = __fmul_rn(fp8_decode(kp[row * D + d]), inv);
+        const uint8_t packed = vp[row * (D / 2) + (d >> 1)];
+        const int q = (d & 1) ? (packed >> 4) & 0x0F : packed & 0x0F;
+        out_v[idx] = __fmul_rn((float)(q - 8), inv);
+    }
+}
+
+// C = A B, all row-major float32: the reference's gemm_mnk shader (shaders/gemm_mnk.glsl:34-80), which the MLA
+// latent path dispatches (cpp/src/ops/kv_cache.cpp:216-234, :441-498): 16 x 16 tiles in shared memory, the sum
+// over k in ascending order with separate multiplies and adds.
+__global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                                                        float* __restrict__ C, int M, int K, int N) {
+    __shared__ float As[16][17], Bs[16][17];
+    const int lx = threadIdx.x & 15, ly = threadIdx.x >> 4;
+    const int m = blockIdx.y * 16 + ly, n = blockIdx.x * 16 + lx;
+    float acc = 0.f;
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        As[ly][lx] = (m < M && k0 + lx < K) ? A[(size_t)m * K + k0 + lx] : 0.f;
+        Bs[ly][lx] = (n < N && k0 + ly < K) ? B[(size_t)(k0 + ly) * N + n] : 0.f;
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) acc = __fadd_rn(acc, __fmul_rn(As[ly][kk], Bs[kk][lx]));
+        __syncthreads();
+    }
+    if (m < M && n < N) C[(size_t)m * N + n] = acc;
+}
+
+// rows x [K (D) | V (D)] <-> separate (rows, D) K and V: the concatenation in front of the MLA down-projection
+// (kv_cache.cpp:190-203) and the split behind the up-projection (:483-494).
+__global__ void mla_concat_kernel(const float* __restrict__ k, const float* __restrict__ v, float* __restrict__ out,
+                                  size_t rows, int D) {
+    const size_t total = rows * 2 * D;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / (2 * D);
+        const int c = (int)(i % (2 * D));
+        out[i] = c < D ? k[r * D + c] : v[r * D + c - D];
+    }
+}
+__global__ void mla_split_kernel(const float* __restrict__ in, float* __restrict__ k, float* __restrict__ v,
+                                 size_t rows, int D) {
+    const size_t total = rows * 2 * D;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / (2 * D);
+        const int c = (int)(i % (2 * D));
+        if (c < D) k[r * D + c] = in[i];
+        else v[r * D + c - D] = in[i];
+    }
+}
+
 static int check_layout(const grl_kv_layout& kv) {
     GRL_REQUIRE(kv.k_pages && kv.v_pages && kv.block_table && kv.seq_lens, "NULL cache pointer");
     GRL_REQUIRE(kv.batch > 0 && kv.num_kv_heads > 0 && kv.page_tokens > 0 && kv.max_pages > 0, "bad cache shape");
     GRL_REQUIRE(kv.head_dim > 0 && kv.head_dim % 2 == 0 && kv.head_dim <= 256, "head_dim must be even and <= 256");
-    GRL_REQUIRE(kv.cache_dtype == GRL_BF16 || kv.cache_dtype == GRL_F32, "unknown cache dtype");
+    GRL_REQUIRE(kv.cache_dtype == GRL_BF16 || kv.cache_dtype == GRL_F32 || kv.cache_dtype == GRL_FP8_INT4,
+                "unknown cache dtype");
+    if (kv.cache_dtype == GRL_FP8_INT4) {
+        GRL_REQUIRE(kv.scales, "the quantised cache needs its scales buffer");
+        GRL_REQUIRE(kv.head_dim % 32 == 0, "the quantised cache needs head_dim to be a multiple of 32 (scale groups)");
+    }
     return GRL_OK;
 }
 
@@ -166,8 +326,32 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p) {
     a.max_pages = kv.max_pages; a.n_new = p->n_new;
     a.rope_mode = p->rope_mode; a.pos_base = p->pos_base; a.pos_offsets = p->pos_offsets;
     a.status = dev->d_status;
+    a.scales = static_cast<uint16_t*>(kv.scales);
     dev->status_dirty = true;
     if (p->rope_mode != GRL_ROPE_NONE) a.freq = make_rope_freq(kv.head_dim, p->rope_theta, p->rope_scaling);
+    if (kv.cache_dtype == GRL_FP8_INT4) {
+        // K and V: one warp per (token, kv head, group of 32); the queries, if any, through the plain kernel
+        const long long warps = (long long)p->n_new * kv.num_kv_heads * (kv.head_dim / 32);
+        int ctas = (int)((warps + 7) / 8);
+        if (ctas > 1024) ctas = 1024;
+        kv_append_quant_kernel<<<dim3(ctas, kv.batch), 256, 0, dev->stream>>>(a);
+        GRL_LAUNCHED("kv_append_quant_kernel");
+        if (p->q_in) {
+            a.skip_kv = 1;
+            a.update_lens = 0;
+            const long long qitems = (long long)p->n_new * (kv.num_kv_heads + p->num_q_heads) * (kv.head_dim / 2);
+            int qchunks = (int)((qitems + 4095) / 4096);
+            if (qchunks > 128) qchunks = 128;
+            kv_append_kernel<float><<<dim3(qchunks, kv.batch), 256, 0, dev->stream>>>(a);
+            GRL_LAUNCHED("kv_append_kernel");
+        }
+        if (p->update_lens) {
+            advance_lens_kernel<<<(kv.batch + 127) / 128, 128, 0, dev->stream>>>(kv.seq_lens, kv.batch, p->n_new,
+                                                                                 kv.max_pages * kv.page_tokens);
+            GRL_LAUNCHED("advance_lens_kernel");
+        }
+        return GRL_OK;
+    }
     const long long items = (long long)p->n_new * (kv.num_kv_heads + (p->q_in ? p->num_q_heads : 0)) * (kv.head_dim / 2);
     // one CTA per sequence while a CTA has at most 16 items per thread (a decode step), more for bulk appends
     int chunks = (int)((items + 4095) / 4096);
@@ -185,6 +369,33 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p) {
                                                                                  kv.max_pages * kv.page_tokens);
         GRL_LAUNCHED("advance_lens_kernel");
     }
+    return GRL_OK;
+}
+
+int grl_gemm_f32(grl_device* dev, const float* a, const float* b, float* c, int m, int k, int n) {
+    GRL_REQUIRE(dev && a && b && c, "NULL argument");
+    GRL_REQUIRE(m > 0 && k > 0 && n > 0, "bad shape (%d,%d,%d)", m, k, n);
+    DeviceGuard g(dev->ordinal);
+    gemm_f32_kernel<<<dim3((n + 15) / 16, (m + 15) / 16), 256, 0, dev->stream>>>(a, b, c, m, k, n);
+    GRL_LAUNCHED("gemm_f32_kernel");
+    return GRL_OK;
+}
+
+int grl_mla_concat(grl_device* dev, const float* k, const float* v, float* out, size_t rows, int head_dim) {
+    GRL_REQUIRE(dev && k && v && out && rows > 0 && head_dim > 0, "bad argument");
+    DeviceGuard g(dev->ordinal);
+    const size_t blocks = (rows * 2 * head_dim + 255) / 256;
+    mla_concat_kernel<<<(unsigned)(blocks < 4096 ? blocks : 4096), 256, 0, dev->stream>>>(k, v, out, rows, head_dim);
+    GRL_LAUNCHED("mla_concat_kernel");
+    return GRL_OK;
+}
+
+int grl_mla_split(grl_device* dev, const float* in, float* k, float* v, size_t rows, int head_dim) {
+    GRL_REQUIRE(dev && k && v && in && rows > 0 && head_dim > 0, "bad argument");
+    DeviceGuard g(dev->ordinal);
+    const size_t blocks = (rows * 2 * head_dim + 255) / 256;
+    mla_split_kernel<<<(unsigned)(blocks < 4096 ? blocks : 4096), 256, 0, dev->stream>>>(in, k, v, rows, head_dim);
+    GRL_LAUNCHED("mla_split_kernel");
     return GRL_OK;
 }
 
@@ -213,7 +424,11 @@ int grl_kv_gather(grl_device* dev, const grl_kv_layout* kv, int b, int n_tokens,
     DeviceGuard g(dev->ordinal);
     const size_t total = (size_t)n_tokens * kv->num_kv_heads * kv->head_dim;
     int blocks = (int)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
-    if (kv->cache_dtype == GRL_BF16)
+    if (kv->cache_dtype == GRL_FP8_INT4)
+        kv_gather_quant_kernel<<<blocks, 256, 0, dev->stream>>>(
+            (const uint8_t*)kv->k_pages, (const uint8_t*)kv->v_pages, (const uint16_t*)kv->scales, kv->block_table, b,
+            n_tokens, kv->num_kv_heads, kv->head_dim, kv->page_tokens, kv->max_pages, out_k, out_v);
+    else if (kv->cache_dtype == GRL_BF16)
         kv_gather_kernel<__nv_bfloat16><<<blocks, 256, 0, dev->stream>>>(
             (const __nv_bfloat16*)kv->k_pages, (const __nv_bfloat16*)kv->v_pages, kv->block_table, b, n_tokens,
             kv->num_kv_heads, kv->head_dim, kv->page_tokens, kv->max_pages, out_k, out_v);

@@ -479,6 +479,9 @@ int grl_kv_compact(grl_device* dev, const grl_kv_layout* kv, const grl_kv_meta* 
     int rc = check_meta(kv, meta);
     if (rc) return rc;
     GRL_REQUIRE(kv->k_pages && kv->v_pages && kv->num_kv_heads > 0 && kv->head_dim > 0, "bad cache layout");
+    if (kv->cache_dtype == GRL_FP8_INT4)
+        return set_error(GRL_ERR_UNSUPPORTED, "compaction of a quantised (FP8 / INT4) cache is not built: its three pools have "
+                                              "rows of different sizes; evict on a bf16 or fp32 cache");
     size_t need = 0;
     grl_kv_compact_scratch_bytes(kv, meta, &need);
     GRL_REQUIRE(scratch && scratch_bytes >= need, "compaction scratch too small: %zu < %zu", scratch_bytes, need);

@@ -90,3 +90,21 @@ Device = getattr(_core, "Device", None)
 
 def swizzle_kv(device, input, wave_size=32, reverse=False):
     return _core.swizzle_kv(device, input, wave_size, reverse)
+
+
+# Names of the reference's bridge (src/grilly_next/backend/_bridge.py:23-145) outside the attention /
+# KV-cache path: present, so that callers written against the reference import cleanly, and every one
+# of them raises RuntimeError saying that this build does not cover it.  There is no CPU fallback.
+def _outside(name):
+    def op(device=None, *args, **kwargs):
+        _require()
+        return getattr(_core, name)(device, *args, **kwargs)
+    op.__name__ = name
+    op.__doc__ = f"{name}: outside the attention / KV-cache path of this build; raises RuntimeError."
+    return op
+
+
+for _name in ("linear", "linear_cpu", "relu", "gelu", "silu", "tanh_act", "layernorm", "conv1d", "conv2d",
+              "hamming_search"):
+    globals()[_name] = _outside(_name)
+del _name

@@ -66,3 +66,33 @@ class VulkanCompute:
 
     def decode_step(self, kv_cache, q, k_new, v_new, **kwargs):
         return _bridge.decode_step(self._device, kv_cache, q, k_new, v_new, **kwargs)
+
+
+    # ---- methods of the reference class outside the attention / KV-cache path (compute.py:56-111 there):
+    # present and callable; each raises RuntimeError saying that this build does not cover it
+    def linear(self, x, weight, bias=None, **kwargs):
+        return _bridge.linear(self._device, x, weight, bias)
+
+    def activation_relu(self, x, **kwargs):
+        return _bridge.relu(self._device, x)
+
+    def activation_gelu(self, x, **kwargs):
+        return _bridge.gelu(self._device, x)
+
+    def activation_silu(self, x, **kwargs):
+        return _bridge.silu(self._device, x)
+
+    def activation_tanh(self, x, **kwargs):
+        return _bridge.tanh_act(self._device, x)
+
+    def layernorm(self, x, gamma, beta, eps=1e-5, **kwargs):
+        return _bridge.layernorm(self._device, x, gamma, beta, eps)
+
+    def conv2d(self, input, weight, bias=None, **kwargs):
+        return _bridge.conv2d(self._device, input, weight, bias, **kwargs)
+
+    def conv1d(self, input, weight, bias=None, **kwargs):
+        return _bridge.conv1d(self._device, input, weight, bias, **kwargs)
+
+    def hamming_search(self, query, cache):
+        return _bridge.hamming_search(self._device, query, cache)

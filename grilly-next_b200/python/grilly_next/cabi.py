@@ -9,7 +9,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.normpath(os.path.join(_HERE, "..", "..", "lib", "libgrilly_cuda.so"))
 
-F32, BF16 = 0, 1
+F32, BF16, FP8_INT4 = 0, 1, 2
 ROPE_NONE, ROPE_INTERLEAVED, ROPE_HALF = 0, 1, 2
 MASK_NONE, MASK_KEY, MASK_BSS, MASK_BHSS = 0, 1, 2, 3
 KERNEL_AUTO, KERNEL_SIMT_F32, KERNEL_TCGEN05 = 0, 1, 2
@@ -28,7 +28,7 @@ SYMBOLS = [
     "grl_gqa_decode_static", "grl_lse_merge", "grl_ipc_export", "grl_ipc_import", "grl_ipc_release",
     "grl_exchange_merge", "grl_exchange_reset", "grl_device_set_wait_limits", "grl_tensor_map_cache_stats",
     "grl_rope_table_prepare", "grl_group_unique_id", "grl_group_init_rank", "grl_group_info", "grl_group_allgather",
-    "grl_group_allreduce_max_f64", "grl_group_allgather_merge", "grl_group_sync", "grl_group_destroy",
+    "grl_gemm_f32", "grl_mla_concat", "grl_mla_split", "grl_group_allreduce_max_f64", "grl_group_allgather_merge", "grl_group_sync", "grl_group_destroy",
 ]
 
 
@@ -52,7 +52,7 @@ class KVLayout(C.Structure):
     _fields_ = [("k_pages", C.c_void_p), ("v_pages", C.c_void_p), ("cache_dtype", C.c_int32),
                 ("block_table", C.c_void_p), ("seq_lens", C.c_void_p),
                 ("batch", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
-                ("page_tokens", C.c_int32), ("max_pages", C.c_int32), ("num_pages", C.c_int32)]
+                ("page_tokens", C.c_int32), ("max_pages", C.c_int32), ("num_pages", C.c_int32), ("scales", C.c_void_p)]
 
 
 class AppendParams(C.Structure):
@@ -132,6 +132,9 @@ def lib():
         _lib.grl_device_set_wait_limits.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64]
         _lib.grl_tensor_map_cache_stats.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         _lib.grl_rope_table_prepare.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_float]
+        _lib.grl_gemm_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+        _lib.grl_mla_concat.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+        _lib.grl_mla_split.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
         _lib.grl_group_unique_id.argtypes = [C.c_void_p]
         _lib.grl_group_init_rank.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
         _lib.grl_group_info.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]

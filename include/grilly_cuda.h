@@ -42,7 +42,8 @@ enum {
     GRL_ERR_KERNEL = -6       /* a kernel reported a failure through its status word */
 };
 
-enum { GRL_F32 = 0, GRL_BF16 = 1 };
+enum { GRL_F32 = 0, GRL_BF16 = 1,
+       GRL_FP8_INT4 = 2 /* KV cache only: FP8-E4M3 keys, INT4 values, one float16 scale per 32 key elements */ };
 enum { GRL_ROPE_NONE = 0, GRL_ROPE_INTERLEAVED = 1, GRL_ROPE_HALF = 2 };
 /* Mask conventions of the reference, selected by the shape the caller holds. Values > 0 keep. */
 enum {
@@ -167,12 +168,20 @@ int grl_attention_mask(grl_device* dev, float* scores, const float* key_mask, in
 typedef struct {
     void* k_pages;
     void* v_pages;
-    int32_t cache_dtype;          /* GRL_BF16 (default) or GRL_F32 */
+    int32_t cache_dtype;          /* GRL_BF16 (default), GRL_F32 or GRL_FP8_INT4 */
     const int32_t* block_table;   /* (B, max_pages) */
     int32_t* seq_lens;            /* (B) */
     int32_t batch, num_kv_heads, head_dim, page_tokens, max_pages;
     int32_t num_pages;            /* pages in each pool; 0 is read as batch * max_pages */
+    void* scales;                 /* GRL_FP8_INT4 only: uint16 [page][Hkv][page_tokens][head_dim/32], see below */
 } grl_kv_layout;
+/* GRL_FP8_INT4 is the asymmetric quantisation of the reference (cpp/src/ops/kv_cache.cpp:272-399, decode
+ * :500-577), byte for byte, on the paged layout: k_pages holds one FP8-E4M3 byte per element
+ * ([page][Hkv][page_tokens][D]), v_pages two INT4 codes per byte ([page][Hkv][page_tokens][D/2], even
+ * element in the low nibble, stored value + 8), scales one float16 bit pattern per group of 32 key elements.
+ * As in the reference only the KEY scales are kept and decode divides keys AND values by them; head_dim
+ * must be a multiple of 32.  grl_kv_append quantises (after the optional RoPE of the keys), grl_kv_gather
+ * dequantises, grl_gqa_decode attends over the dequantised values with the generic kernel. */
 
 /* Append n_new tokens per sequence: replaces ops::kvCacheAppend (cpp/src/ops/kv_cache.cpp:155-419;
  * signature kv_cache.h:163-166) and fuses the RoPE of the new keys and of the step's queries.
@@ -199,6 +208,15 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p);
  * (cpp/src/ops/kv_cache.cpp:435-578; kv_cache.h:175-177). */
 int grl_kv_gather(grl_device* dev, const grl_kv_layout* kv, int b, int n_tokens, float* out_k,
                   float* out_v);
+
+/* ---- MLA latent path of the KV cache (cpp/src/ops/kv_cache.cpp:174-248 compress, :441-498 decode).
+ * grl_gemm_f32: C (m,n) = A (m,k) B (k,n), row-major float32: replaces the gemm_mnk shader those paths dispatch
+ * (shaders/gemm_mnk.glsl:34-80; sum over k ascending, unfused multiply and add).
+ * grl_mla_concat / grl_mla_split: (rows, D) K and V <-> (rows, 2D) [K | V] rows, the host loops around the two
+ * projections (:190-203, :483-494). */
+int grl_gemm_f32(grl_device* dev, const float* a, const float* b, float* c, int m, int k, int n);
+int grl_mla_concat(grl_device* dev, const float* k, const float* v, float* out, size_t rows, int head_dim);
+int grl_mla_split(grl_device* dev, const float* in, float* k, float* v, size_t rows, int head_dim);
 
 /* Block swizzle of a (B,H,S,D) float32 tensor into (B,H,ceil(S/W),ceil(D/W),W,W) with zero padding, or
  * back (reverse != 0): replaces ops::swizzle / swizzleCPU / unswizzleCPU (cpp/src/ops/swizzle.cpp:49-229).

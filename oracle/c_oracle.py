@@ -65,5 +65,30 @@ def rope_interleaved(x, base=10000.0, scaling=1.0):
     return out
 
 
+def kv_quantize(keys, values):
+    """(T,H,D) float32 keys / values -> (keys_q (T,H,D) u8, vals_q (T,H,D/2) u8, scales (T,H,ceil(D/32)) u16):
+    the reference's FP8 / INT4 storage bytes (kv_quant_oracle.c)."""
+    keys = np.ascontiguousarray(keys, np.float32)
+    values = np.ascontiguousarray(values, np.float32)
+    T, H, D = keys.shape
+    G = (D + 31) // 32
+    kq = np.empty((T, H, D), np.uint8)
+    vq = np.empty((T, H, D // 2), np.uint8)
+    sc = np.empty((T, H, G), np.uint16)
+    lib().oracle_kv_quantize(_p(keys), _p(values), T, H, D, _p(kq), _p(vq), _p(sc))
+    return kq, vq, sc
+
+
+def kv_dequantize(keys_q, vals_q, scales):
+    keys_q = np.ascontiguousarray(keys_q, np.uint8)
+    vals_q = np.ascontiguousarray(vals_q, np.uint8)
+    scales = np.ascontiguousarray(scales, np.uint16)
+    T, H, D = keys_q.shape
+    k = np.empty((T, H, D), np.float32)
+    v = np.empty((T, H, D), np.float32)
+    lib().oracle_kv_dequantize(_p(keys_q), _p(vals_q), _p(scales), T, H, D, _p(k), _p(v))
+    return k, v
+
+
 def num_threads():
     return lib().oracle_num_threads()

@@ -48,9 +48,14 @@ class PagedCache:
         self.dev, self.B, self.Hkv, self.D, self.P, self.dtype = dev, B, Hkv, D, page_tokens, dtype
         self.max_pages = (max_tokens + page_tokens - 1) // page_tokens
         n_pages = self.max_pages * B
-        esz = 2 if dtype == cabi.BF16 else 4
-        nbytes = n_pages * Hkv * page_tokens * D * esz
-        self.k_pages, self.v_pages = dev.malloc(nbytes), dev.malloc(nbytes)
+        rows = n_pages * Hkv * page_tokens
+        self.scales = None
+        if dtype == cabi.FP8_INT4:        # one key byte, half a value byte per element, one float16 scale per 32
+            self.k_pages, self.v_pages = dev.malloc(rows * D), dev.malloc(rows * D // 2)
+            self.scales = dev.malloc(rows * (D // 32) * 2)
+        else:
+            esz = 2 if dtype == cabi.BF16 else 4
+            self.k_pages, self.v_pages = dev.malloc(rows * D * esz), dev.malloc(rows * D * esz)
         table = np.arange(n_pages, dtype=np.int32)
         if shuffle_pages:
             np.random.default_rng(seed).shuffle(table)
@@ -65,6 +70,7 @@ class PagedCache:
         l.block_table, l.seq_lens = self.block_table, self.seq_lens
         l.batch, l.num_kv_heads, l.head_dim, l.page_tokens, l.max_pages = self.B, self.Hkv, self.D, self.P, self.max_pages
         l.num_pages = self.max_pages * self.B
+        l.scales = self.scales
         return l
 
     def append(self, k_new, v_new, q=None, rope_mode=cabi.ROPE_NONE, theta=10000.0, scaling=1.0, pos_base=0,

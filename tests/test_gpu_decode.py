@@ -212,8 +212,9 @@ def test_kv_cache_reference_single_sequence_form(gpu):
     assert np.array_equal(d["keys"], np.concatenate([k, k[:3]])) and np.array_equal(d["values"], np.concatenate([v, v[:3]]))
     with pytest.raises(RuntimeError, match="max_cache_tokens"):
         gpu.kv_cache_append(kv, np.zeros((200, 4, 64), np.float32), np.zeros((200, 4, 64), np.float32))
-    with pytest.raises(RuntimeError, match="compression_ratio"):
-        gpu.create_kv_cache()                     # the reference default (MLA, ratio 4) is not built
+    mla = gpu.create_kv_cache()                   # the reference default: MLA latents, ratio 4 (tests/test_mla_latent_path.py)
+    assert mla.stats()["compression_ratio"] == 8.0
+    gpu.destroy_kv_cache(mla)
     # the eviction calls of the reference API: a quarter of the 13 tokens goes (all scores are zero, so the
     # tie rule picks the first three), compaction closes the gaps
     gpu.kv_cache_evict_h2o(kv)
