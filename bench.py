@@ -518,8 +518,9 @@ def kv_layout(cabi, kp, vp, table, seq_lens, B, Hkv, D, P, max_pages, n_pages):
     return lay
 
 
-def bench_decode(dev, cabi, dist, repeats=3, use_graph=True):
-    """cfg3: 256 decode steps (RoPE + append + split-KV attention + merge), graph-replayed."""
+def bench_decode(dev, cabi, dist, repeats=3, use_graph=True, quant=False):
+    """cfg3: 256 decode steps (RoPE + append + split-KV attention + merge), graph-replayed.  quant: the same run over
+    the FP8 / INT4 cache (the prefix is appended through the quantiser, so every stored byte is a real code)."""
     from oracle import c_oracle
     c = CFG3
     B, Hq, Hkv, D, T0, steps, P = c["B"], c["Hq"], c["Hkv"], c["D"], c["T0"], c["steps"], c["page"]
@@ -529,12 +530,29 @@ def bench_decode(dev, cabi, dist, repeats=3, use_graph=True):
     max_pages = (max_tokens + P - 1) // P
     n_pages = max_pages * B
     page_elems = Hkv * P * D
-    kp, vp = dev.malloc(n_pages * page_elems * 2), dev.malloc(n_pages * page_elems * 2)
-    for dst in (kp, vp):      # the prefix is "already rotated" keys: iid N(0,1) bf16
-        fill_random_bf16(dev, cabi, dst, n_pages * page_elems, rng)
     table = dev.upload(np.arange(n_pages, dtype=np.int32).reshape(B, max_pages))
     lens0 = np.full(B, T0, np.int32)
-    seq_lens = dev.upload(lens0)
+    scales = None
+    if quant:
+        kp, vp = dev.malloc(n_pages * page_elems), dev.malloc(n_pages * page_elems // 2)
+        scales = dev.malloc(n_pages * page_elems // 32 * 2)
+        seq_lens = dev.upload(np.zeros(B, np.int32))
+        lay0 = kv_layout(cabi, kp, vp, table, seq_lens, B, Hkv, D, P, max_pages, n_pages)
+        lay0.cache_dtype, lay0.scales = cabi.FP8_INT4, scales
+        blk = 512
+        for _ in range(T0 // blk):          # the prefix goes in through the quantiser
+            kd = dev.upload(rng.standard_normal((B, blk, Hkv, D), dtype=np.float32))
+            vd = dev.upload(rng.standard_normal((B, blk, Hkv, D), dtype=np.float32))
+            ap0 = cabi.AppendParams()
+            ap0.kv, ap0.k_new, ap0.v_new, ap0.n_new, ap0.update_lens = lay0, kd, vd, blk, 1
+            cabi.check(L.grl_kv_append(dev.h, C.byref(ap0)))
+            dev.sync()
+            dev.free(kd); dev.free(vd)
+    else:
+        kp, vp = dev.malloc(n_pages * page_elems * 2), dev.malloc(n_pages * page_elems * 2)
+        for dst in (kp, vp):      # the prefix is "already rotated" keys: iid N(0,1) bf16
+            fill_random_bf16(dev, cabi, dst, n_pages * page_elems, rng)
+        seq_lens = dev.upload(lens0)
     q_host = rng.standard_normal((steps, B, 1, Hq, D), dtype=np.float32)
     k_host = rng.standard_normal((steps, B, 1, Hkv, D), dtype=np.float32)
     qs, ks = dev.upload(q_host), dev.upload(k_host)
@@ -542,6 +560,8 @@ def bench_decode(dev, cabi, dist, repeats=3, use_graph=True):
     q_rot = dev.malloc(B * Hq * D * 4)
     out = dev.malloc(steps * B * Hq * D * 4)
     lay = kv_layout(cabi, kp, vp, table, seq_lens, B, Hkv, D, P, max_pages, n_pages)
+    if quant:
+        lay.cache_dtype, lay.scales = cabi.FP8_INT4, scales
     dp = cabi.DecodeParams()
     dp.kv, dp.num_q_heads, dp.max_seq_len = lay, Hq, max_tokens
     ns = C.c_int()
@@ -569,6 +589,7 @@ def bench_decode(dev, cabi, dist, repeats=3, use_graph=True):
     def reset():
         cabi.check(L.grl_memcpy_h2d(dev.h, seq_lens, lens0.ctypes.data_as(C.c_void_p), lens0.nbytes))
 
+    dev.sync()
     launches0 = L.grl_launch_count()
     g = C.c_void_p()
     if use_graph:
@@ -594,13 +615,20 @@ def bench_decode(dev, cabi, dist, repeats=3, use_graph=True):
     Kc, Vc = dev.download(gk, (1, T, Hkv, D), np.float32), dev.download(gv, (1, T, Hkv, D), np.float32)
     q_last = dev.download(q_rot, (B, 1, Hq, D), np.float32)[sb:sb + 1]
     o_last = dev.download(C.c_void_p(out.value + (steps - 1) * B * Hq * D * 4), (B, 1, Hq, D), np.float32)[sb:sb + 1]
-    par = parity("decode cfg3", np.abs(o_last - c_oracle.gqa_decode(q_last, Kc, Vc)).max(), TOL_DECODE,
-                 sample=f"sequence {sb}, step {steps}: all 32 query heads over its {T} cached tokens")
+    par = parity("decode cfg3" + (" (quantised cache)" if quant else ""), np.abs(o_last - c_oracle.gqa_decode(q_last, Kc, Vc)).max(),
+                 TOL_DECODE, sample=f"sequence {sb}, step {steps}: all 32 query heads over its {T} cached tokens"
+                                    + (" as the cache dequantises them" if quant else ""))
     k_rot = c_oracle.rope_interleaved(np.concatenate([np.zeros((Hkv, T - 1, D), np.float32),
                                                       k_host[steps - 1, sb, 0][:, None, :]], axis=1), c["theta"])[:, -1]
-    par["appended_key_max_abs"] = float(np.abs(Kc[0, T - 1] - round_bf16(k_rot)).max())
-    if par["appended_key_max_abs"] > 2e-2:
-        raise ParityError(f"decode cfg3: appended key differs from RoPE(k) by {par['appended_key_max_abs']}")
+    if quant:     # the stored key is the quantiser's image of RoPE(k): compare with the checker's quantiser
+        kq_want = c_oracle.kv_dequantize(*c_oracle.kv_quantize(k_rot[None], k_rot[None]))[0][0]
+        par["appended_key_codes_differing"] = float(np.mean(Kc[0, T - 1] != kq_want))
+        if par["appended_key_codes_differing"] > 0.02:
+            raise ParityError("decode cfg3 (quantised): appended key differs from quantise(RoPE(k))")
+    else:
+        par["appended_key_max_abs"] = float(np.abs(Kc[0, T - 1] - round_bf16(k_rot)).max())
+        if par["appended_key_max_abs"] > 2e-2:
+            raise ParityError(f"decode cfg3: appended key differs from RoPE(k) by {par['appended_key_max_abs']}")
     q_want = c_oracle.rope_interleaved(np.concatenate([np.zeros((Hq, T - 1, D), np.float32),
                                                        q_host[steps - 1, sb, 0][:, None, :]], axis=1), c["theta"])[:, -1]
     par["rotated_q_max_abs"] = float(np.abs(q_last[0, 0] - q_want).max())
@@ -621,7 +649,7 @@ def bench_decode(dev, cabi, dist, repeats=3, use_graph=True):
         best = ms if best is None else min(best, ms)
     if use_graph:
         L.grl_graph_destroy(g)
-    for x in (kp, vp, table, seq_lens, qs, ks, vs, q_rot, out, ws):
+    for x in (kp, vp, table, seq_lens, qs, ks, vs, q_rot, out, ws) + ((scales,) if quant else ()):
         dev.free(x)
     return best, launches_per_run, ns.value, par
 
@@ -999,6 +1027,21 @@ def main():
                                            "traffic": DECODE_TRAFFIC_BYTES, "peak_source": pk["src"], "frac_of_nominal_8000": gbs / 8000.0,
                                            "note": "achieved = algorithmic bytes of the 256-step run / its time (append + decode + merge per step)",
                                            "kernel": "decode_mma_kernel"}}
+        if "decode" in legs and world == 1:
+            qms, ql, qsplit, qpar = bench_decode(dev, cabi, dist, args.decode_repeats, not args.no_graph, quant=True)
+            c = CFG3
+            per_pos = c["B"] * c["Hkv"] * (c["D"] + c["D"] // 2 + c["D"] // 32 * 2)      # key bytes + value nibbles + scales
+            qbytes = sum(per_pos * (c["T0"] + t + 1) for t in range(c["steps"])) + c["steps"] * c["B"] * c["Hq"] * c["D"] * 8
+            qgbs = qbytes / (qms * 1e-3) / 1e9
+            line["decode_q"] = {"metric": "decode_tokens_per_s", "value": c["B"] * c["steps"] / (qms * 1e-3), "unit": "tokens/s",
+                                "ms_per_step": qms / c["steps"],
+                                "workload": "cfg3 geometry over the quantised cache (FP8-E4M3 keys, INT4 values, float16 scale per 32: "
+                                            "200 B per cached (token, kv head) against 512 B in bf16), decode_split_kernel dequantising in registers",
+                                "gpu_launches": int(ql), "n_splits": qsplit, "parity": qpar,
+                                "roofline": {"bound": "hbm", "achieved": qgbs, "peak": pk["hbm"], "unit": "GB/s", "frac": qgbs / pk["hbm"],
+                                             "peak_source": pk["src"], "kernel": "decode_split_kernel<QuantKV>",
+                                             "note": "achieved = bytes of the quantised cache actually read per step / time; the kernel is "
+                                                     "bound by its dequantising arithmetic, not by HBM"}}
         if "evict" in legs and world == 1:
             sel_us, cmp_us, moved = bench_evict(dev, cabi)
             gbs = moved / (cmp_us * 1e-6) / 1e9

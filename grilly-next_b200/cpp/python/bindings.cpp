@@ -18,6 +18,7 @@
 #include "grilly/ops/attention.h"
 #include "grilly/experimental/fused_attention.h"
 #include "grilly/ops/kv_cache.h"
+#include "grilly/ops/linear.h"
 #include "grilly/ops/sharded_decode.h"
 #include "grilly/ops/rope.h"
 #include "grilly/pipeline_cache.h"
@@ -934,7 +935,63 @@ PYBIND11_MODULE(grilly_core, m) {
         }
         return out;
     }, py::arg("device"), py::arg("kv_cache"), "Latents of an MLA cache: (tokens, heads, latent_dim) float32");
-    for (const char* name : {"linear", "linear_cpu", "relu", "gelu", "silu", "tanh_act", "layernorm", "conv1d", "conv2d",
+    // ---- linear projection (cpp/python/bindings.cpp:241-300 there) and the fused QKV projection
+    m.def(
+        "linear",
+        [](GrillyCoreContext& ctx, FArr x, FArr weights, std::optional<FArr> bias, const std::string& dtype) {
+            if (x.ndim() < 1 || x.ndim() > 3) throw std::runtime_error("x must be 1D, 2D, or 3D (batch, seq, input_dim)");
+            if (weights.ndim() != 2) throw std::runtime_error("weights must be 2D (output_dim, input_dim)");
+            const uint32_t inputDim = uint32_t(x.shape(x.ndim() - 1));
+            const uint32_t batchSeq = uint32_t(size_t(x.size()) / std::max<uint32_t>(inputDim, 1));
+            const uint32_t outputDim = uint32_t(weights.shape(0));
+            if (uint32_t(weights.shape(1)) != inputDim)
+                throw std::runtime_error("Weight input_dim mismatch: " + std::to_string(weights.shape(1)) + " vs " + std::to_string(inputDim));
+            if (bias.has_value() && (bias->ndim() != 1 || uint32_t(bias->shape(0)) != outputDim))
+                throw std::runtime_error("bias must be 1D with size output_dim");
+            std::vector<py::ssize_t> shape;
+            for (int i = 0; i + 1 < x.ndim(); ++i) shape.push_back(x.shape(i));
+            if (x.ndim() == 1) shape.push_back(1);
+            shape.push_back(outputDim);
+            py::array_t<float> out(shape);
+            ops::LinearParams p{batchSeq, inputDim, outputDim, bias.has_value() ? 1u : 0u};
+            const float *xp = x.data(), *wp = weights.data(), *bp = bias.has_value() ? bias->data() : nullptr;
+            float* op = out.mutable_data();
+            const auto prec = parseDtype(dtype) == GRL_BF16 ? ops::Precision::BF16 : ops::Precision::FP32;
+            {
+                py::gil_scoped_release nogil;
+                ops::linearEx(ctx.batch, ctx.pool, ctx.cache, xp, wp, bp, op, p, prec);
+            }
+            return out;
+        },
+        py::arg("device"), py::arg("x"), py::arg("weights"), py::arg("bias") = py::none(), py::arg("dtype") = "fp32",
+        "GPU linear projection: output = x @ W^T + bias");
+    m.def(
+        "fused_qkv_projection",
+        [](GrillyCoreContext& ctx, FArr x, FArr wQKV, std::optional<FArr> bQKV, uint32_t numHeads, uint32_t headDim,
+           const std::string& dtype) {
+            if (x.ndim() < 2 || x.ndim() > 3) throw std::runtime_error("x must be (batch_seq, hidden) or (batch, seq, hidden)");
+            const uint32_t hidden = uint32_t(x.shape(x.ndim() - 1)), rows = uint32_t(size_t(x.size()) / hidden);
+            const uint32_t qkv = 3 * numHeads * headDim;
+            if (wQKV.ndim() != 2 || uint32_t(wQKV.shape(0)) != qkv || uint32_t(wQKV.shape(1)) != hidden)
+                throw std::runtime_error("w_qkv must be (3 * num_heads * head_dim, hidden_dim): [W_q; W_k; W_v]");
+            if (bQKV.has_value() && uint32_t(bQKV->size()) != qkv) throw std::runtime_error("b_qkv must hold 3 * num_heads * head_dim values");
+            std::vector<py::ssize_t> shape;
+            for (int i = 0; i + 1 < x.ndim(); ++i) shape.push_back(x.shape(i));
+            shape.push_back(qkv);
+            py::array_t<float> out(shape);
+            const float *xp = x.data(), *wp = wQKV.data(), *bp = bQKV.has_value() ? bQKV->data() : nullptr;
+            float* op = out.mutable_data();
+            const auto prec = parseDtype(dtype) == GRL_BF16 ? ops::Precision::BF16 : ops::Precision::FP32;
+            {
+                py::gil_scoped_release nogil;
+                ops::fusedQKVProjection(ctx.batch, ctx.pool, ctx.cache, xp, wp, bp, op, rows, hidden, numHeads, headDim, prec);
+            }
+            return out;
+        },
+        py::arg("device"), py::arg("x"), py::arg("w_qkv"), py::arg("b_qkv") = py::none(), py::arg("num_heads") = 8,
+        py::arg("head_dim") = 64, py::arg("dtype") = "fp32",
+        "Fused QKV projection: (batch_seq, hidden) -> (batch_seq, 3 * num_heads * head_dim) with [W_q; W_k; W_v]");
+    for (const char* name : {"linear_cpu", "relu", "gelu", "silu", "tanh_act", "layernorm", "conv1d", "conv2d",
                              "hamming_search"})
         notBuilt(name, "outside the attention / KV-cache path that this CUDA build covers");
 }

@@ -79,7 +79,7 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
     const size_t n = size_t(B) * H * S * D;
     const bool bf16 = opt.precision == Precision::BF16;
     if (bf16 && mask) throw std::runtime_error("flashAttention2: the bf16 path takes causal / seq_lens masks only");
-    if (bf16 && D != 128) throw std::runtime_error("flashAttention2: the bf16 path needs head_dim 128");
+    if (bf16 && D != 128 && D != 64) throw std::runtime_error("flashAttention2: the bf16 path needs head_dim 128 or 64");
     cache.getOrCreate(std::string(bf16 ? "flash-attention2-tcgen05/" : "flash-attention2/") + std::to_string(D));
 
     Scoped scope(pool);

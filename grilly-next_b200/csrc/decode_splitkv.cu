@@ -343,7 +343,10 @@ int grl_decode_pick_splits(grl_device* dev, const grl_decode_params* p, int* n_s
     // heads x 131072 tokens: 87 us with 18 splits (144 CTAs), 94 us with 19 (152), 100 us with 64; B32 x 8
     // heads x 4096 tokens is fastest unsplit.
     const int sms = dev->prop.multiProcessorCount;
-    int s = sms / base_ctas;
+    // The generic kernel (128-thread CTAs, no shared-memory ring) wants several CTAs per SM to hide its loads and,
+    // over a quantised cache, its dequantising arithmetic: aim at eight per SM.
+    const bool generic = !decode_mma_supported(p) || p->force_simt;
+    int s = generic ? (8 * sms + base_ctas - 1) / base_ctas : sms / base_ctas;
     if (s > pages / 2) s = pages / 2;          // every split keeps at least 2 pages
     if (s > 256) s = 256;
     if (s < 1) s = 1;

@@ -343,7 +343,7 @@ static int report_kernel_status(grl_device* dev, bool copied) {
     GRL_CUDA(cudaMemsetAsync(dev->d_status, 0, (4 + grl_device::kCounterInts) * sizeof(int32_t), dev->stream));
     // [1] = kind << 28 | detail: 1 prefill (index of the mbarrier whose wait ran out; [3] = CTA),
     // 2 decode (mbarrier index; [2],[3] = CTA), 3 cross-GPU merge (peer that did not post; [2] = step, [3] = rank),
-    // 4 append (a sequence without room; [2] = sequence, [3] = its length)
+    // 4 append (a sequence without room; [2] = sequence, [3] = its length), 5 linear projection (mbarrier index)
     const int code = st[0] == GRL_ERR_TIMEOUT ? GRL_ERR_TIMEOUT : GRL_ERR_KERNEL;
     const unsigned int kind = (unsigned int)st[1] >> 28, detail = (unsigned int)st[1] & 0x0fffffffu;
     switch (kind) {
@@ -351,6 +351,7 @@ static int report_kernel_status(grl_device* dev, bool copied) {
         case 2: return set_error(code, "decode kernel: a wait ran out (mbarrier %u, CTA %d,%d)", detail, st[2], st[3]);
         case 3: return set_error(code, "cross-GPU merge on rank %d: peer %u did not post step %d within the wait limit",
                                  st[3], detail, st[2]);
+        case 5: return set_error(code, "linear kernel: a wait ran out (mbarrier %u, CTA %d,%d)", detail, st[2], st[3]);
         case 4: return set_error(code, "kv append: sequence %d (length %d) has no room for the new tokens", st[2], st[3]);
         default: return set_error(code, "kernel reported failure %d (detail 0x%x, %d, %d)", st[0], st[1], st[2], st[3]);
     }

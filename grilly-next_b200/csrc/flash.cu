@@ -31,7 +31,7 @@ extern "C" int grl_flash_fwd(grl_device* dev, const grl_flash_params* p) {
 
     int kernel = p->kernel;
     if (kernel == GRL_KERNEL_AUTO)
-        kernel = (p->in_dtype == GRL_BF16 && p->head_dim == 128 && !p->mask && scale > 0.f) ? GRL_KERNEL_TCGEN05
+        kernel = (p->in_dtype == GRL_BF16 && (p->head_dim == 128 || p->head_dim == 64) && !p->mask && scale > 0.f) ? GRL_KERNEL_TCGEN05
                                                                                             : GRL_KERNEL_SIMT_F32;
     if (kernel == GRL_KERNEL_SIMT_F32) return flash_fwd_simt(dev, p, scale, rope);
     if (kernel == GRL_KERNEL_TCGEN05) {

@@ -1,4 +1,4 @@
-// Blackwell (sm_100a) flash-attention forward for bf16 inputs, head_dim 128.
+// Blackwell (sm_100a) flash-attention forward for bf16 inputs, head_dim 128 or 64.
 //
 // Replaces the S^2/(64*64) dispatch+barrier pairs of ops::flashAttention2
 // (cpp/src/ops/attention.cpp:125-141) and the per-(q,k) thread of flash-attention2-rope.glsl
@@ -26,6 +26,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 #include "tmem_ops.cuh"
 
 namespace grl {
@@ -35,10 +36,10 @@ namespace sm100 {
 constexpr int BM = 128;            // query rows per tile (TMEM lanes)
 constexpr int NQ = 2;              // query tiles per CTA
 constexpr int BN = 128;            // keys per tile
-constexpr int HD = 128;            // head_dim
 constexpr int NSTAGE = 2;
 constexpr int HALF_BYTES = BM * 64 * 2;     // one 64-column box: 16 KiB
-constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KiB
+constexpr int TILE_BYTES = 2 * HALF_BYTES;  // 32 KiB: a Q/K/V tile of head_dim 128 (two boxes), and the stride between
+                                            // tile buffers for either head_dim (head_dim 64 fills the first box only)
 constexpr int kThreads = 512;      // four warpgroups: MMA + TMA (+2 idle warps) | softmax 0 | softmax 1 | RoPE
 constexpr int WARP_MMA = 0, WARP_TMA = 1, WARP_MMA1 = 2, WARP_SOFTMAX0 = 4, WARP_ROT0 = 12;   // warp 3 idle
 // Register budget per warpgroup (setmaxnreg); 2*128*160 + 128*112 + 128*80 = 65536.
@@ -80,124 +81,11 @@ struct Args {
 
 // kind::f16 instruction descriptor: D=f32 (bit 4), A=B=bf16 (bits 7,10), N>>3 at bit 17, M>>4 at bit 24;
 // bit 16 set = B operand is MN-major (the V tile, whose contiguous dimension is head_dim = N).
-constexpr uint32_t IDESC_BASE = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                                ((uint32_t)(BM >> 4) << 24);
 constexpr uint32_t IDESC_QK = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);  // N = 64 keys
-constexpr uint32_t IDESC_PV = IDESC_BASE | (1u << 16);                                                                         // N = 128 dims
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
-           ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                       uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Descriptor halves: the high word (stride offset, version, swizzle) is constant per operand kind and
-// the low word is (address >> 4) | (leading offset >> 4) << 16, so stepping through a tile is one
-// 32-bit add.  The single issuing thread must spend only a few instructions per MMA: a 128x128x16
-// MMA occupies the tensor pipe for 64 cycles, and descriptor arithmetic done per instruction in
-// 64-bit was measured to hold the pipe at less than half rate.
-__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
-    return ((saddr & 0x3FFFFu) >> 4) | ((lbo_bytes >> 4) << 16);
-}
-constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1 KiB, version 1, 128-byte swizzle
-template <bool ACC>
-__device__ __forceinline__ void mma_ss2(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "n"(ACC ? 1 : 0)
-        : "memory");
-}
-__device__ __forceinline__ void mma_ts2(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
-        "mov.b64 db, {%2, %3};\n\t"
-        "setp.ne.b32 p, %5, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-template <int N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
-// explicit shared-space accesses (32-bit addresses): the generic-pointer forms cost an address-space check
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ float2 lds64f(uint32_t addr) {
-    float2 v;
-    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
+template <int HD> struct IdescPV {   // N = head_dim output columns, B (the V tile) MN-major
+    static constexpr uint32_t value =
+        (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24) | (1u << 16);
+};
 
 struct Ctx {
     uint32_t bars;          // shared address of barrier 0
@@ -252,13 +140,20 @@ struct RopeState {
     float cd[8], sd[8];   // step rotation; 4 pairs (interleaved) or 8 pairs (rotate_half) per thread
 };
 
+// Thread rt of the 128 owns one 16-byte chunk column and walks down the rows with a fixed stride.  Interleaved
+// pairs: HD/8 chunk columns, stride 1024/HD rows (8 at head_dim 128, 16 at 64); rotate_half: HD/16 chunk columns
+// of the first half, stride 2048/HD rows, the partner chunk HD/16 columns further on.
+template <int HD>
 __device__ __forceinline__ void rope_init(RopeState& st, const float2* __restrict__ rope, int S, int mode, int rt) {
+    constexpr int HALF = HD / 2;
     if (mode == GRL_ROPE_INTERLEAVED) {
-        const float2* t = rope + (size_t)min(8, S - 1) * 64 + (rt & 15) * 4;
+        constexpr int CH = HD / 8, STRIDE = 128 / CH;
+        const float2* t = rope + (size_t)min(STRIDE, S - 1) * HALF + (rt % CH) * 4;
 #pragma unroll
         for (int e = 0; e < 4; ++e) { const float2 v = __ldg(t + e); st.cd[e] = v.x; st.sd[e] = v.y; }
     } else {
-        const float2* t = rope + (size_t)min(16, S - 1) * 64 + (rt & 7) * 8;
+        constexpr int CHH = HD / 16, STRIDE = 128 / CHH;
+        const float2* t = rope + (size_t)min(STRIDE, S - 1) * HALF + (rt % CHH) * 8;
 #pragma unroll
         for (int e = 0; e < 8; ++e) { const float2 v = __ldg(t + e); st.cd[e] = v.x; st.sd[e] = v.y; }
     }
@@ -269,25 +164,31 @@ __device__ __forceinline__ void rope_init(RopeState& st, const float2* __restric
 struct RopeStart {
     float4 v[4];
 };
+template <int HD>
 __device__ __forceinline__ RopeStart rope_load_start(int pos0, int S, const float2* __restrict__ rope, int mode, int rt) {
+    constexpr int HALF = HD / 2;
     RopeStart r;
     if (mode == GRL_ROPE_INTERLEAVED) {
-        const float4* t = reinterpret_cast<const float4*>(rope + (size_t)min(pos0 + (rt >> 4), S - 1) * 64 + (rt & 15) * 4);
+        constexpr int CH = HD / 8;
+        const float4* t = reinterpret_cast<const float4*>(rope + (size_t)min(pos0 + rt / CH, S - 1) * HALF + (rt % CH) * 4);
         r.v[0] = __ldg(t); r.v[1] = __ldg(t + 1);
         r.v[2] = r.v[3] = make_float4(0.f, 0.f, 0.f, 0.f);
     } else {
-        const float4* t = reinterpret_cast<const float4*>(rope + (size_t)min(pos0 + (rt >> 3), S - 1) * 64 + (rt & 7) * 8);
+        constexpr int CHH = HD / 16;
+        const float4* t = reinterpret_cast<const float4*>(rope + (size_t)min(pos0 + rt / CHH, S - 1) * HALF + (rt % CHH) * 8);
 #pragma unroll
         for (int e = 0; e < 4; ++e) r.v[e] = __ldg(t + e);
     }
     return r;
 }
 
+template <int HD>
 __device__ __forceinline__ void rope_tile(uint32_t tile, const RopeStart& start, int mode, int rt, const RopeState& st) {
     if (mode == GRL_ROPE_INTERLEAVED) {
-        // chunk c = 4 adjacent pairs (2i, 2i+1); rows r0, r0+8, ... : r % 8 == r0, so the swizzle term is fixed
-        const int c = rt & 15, r0 = rt >> 4;
-        uint32_t p = tile + (c >> 3) * HALF_BYTES + r0 * 128 + (((c & 7) ^ r0) << 4);
+        // chunk c = 4 adjacent pairs (2i, 2i+1); rows r0, r0+STRIDE, ... : r % 8 stays r0 % 8, so the swizzle term is fixed
+        constexpr int CH = HD / 8, STRIDE = 128 / CH;
+        const int c = rt % CH, r0 = rt / CH;
+        uint32_t p = tile + (c >> 3) * HALF_BYTES + r0 * 128 + (((c & 7) ^ (r0 & 7)) << 4);
         const float4 t0 = start.v[0], t1 = start.v[1];
         // two pairs per packed operation: C = (c_e, c_e+1), S = (s_e, s_e+1)
         float2 C[2] = {make_float2(t0.x, t0.z), make_float2(t1.x, t1.z)};
@@ -296,7 +197,7 @@ __device__ __forceinline__ void rope_tile(uint32_t tile, const RopeStart& start,
         const float2 Sd[2] = {make_float2(st.sd[0], st.sd[1]), make_float2(st.sd[2], st.sd[3])};
         const float2 Sdn[2] = {make_float2(-st.sd[0], -st.sd[1]), make_float2(-st.sd[2], -st.sd[3])};
 #pragma unroll 4
-        for (int k = 0; k < 16; ++k, p += 1024) {
+        for (int k = 0; k < 128 / STRIDE; ++k, p += STRIDE * 128) {
             uint4 v = lds128(p);
             uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -316,9 +217,12 @@ __device__ __forceinline__ void rope_tile(uint32_t tile, const RopeStart& start,
             sts128(p, make_uint4(w[0], w[1], w[2], w[3]));
         }
     } else {
-        // rotate_half: pairs (d, d+64) sit at the same offset of the two boxes; rows r0, r0+16, ...
-        const int cc = rt & 7, r0 = rt >> 3;
+        // rotate_half: pairs (d, d + HD/2); the partner chunk lies HD/16 chunk columns further on (the same offset of
+        // the second box at head_dim 128, four chunks along the row at 64); rows r0, r0+STRIDE, ...
+        constexpr int CHH = HD / 16, STRIDE = 128 / CHH;
+        const int cc = rt % CHH, r0 = rt / CHH, cb = cc + CHH;
         uint32_t p = tile + r0 * 128 + ((cc ^ (r0 & 7)) << 4);
+        const uint32_t pb_off = (uint32_t)((cb >> 3) * HALF_BYTES + (((cb & 7) ^ (r0 & 7)) << 4)) - (uint32_t)((cc ^ (r0 & 7)) << 4);
         float cs[8], sn[8];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -326,8 +230,8 @@ __device__ __forceinline__ void rope_tile(uint32_t tile, const RopeStart& start,
             cs[2 * e] = v.x; sn[2 * e] = v.y; cs[2 * e + 1] = v.z; sn[2 * e + 1] = v.w;
         }
 #pragma unroll 2
-        for (int k = 0; k < 8; ++k, p += 2048) {
-            uint4 a = lds128(p), b = lds128(p + HALF_BYTES);
+        for (int k = 0; k < 128 / STRIDE; ++k, p += STRIDE * 128) {
+            uint4 a = lds128(p), b = lds128(p + pb_off);
             uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -346,7 +250,7 @@ __device__ __forceinline__ void rope_tile(uint32_t tile, const RopeStart& start,
                 cs[e] = nc;
             }
             sts128(p, make_uint4(wa[0], wa[1], wa[2], wa[3]));
-            sts128(p + HALF_BYTES, make_uint4(wb[0], wb[1], wb[2], wb[3]));
+            sts128(p + pb_off, make_uint4(wb[0], wb[1], wb[2], wb[3]));
         }
     }
 }
@@ -376,7 +280,7 @@ __device__ __forceinline__ void store_row_chunk<__nv_bfloat16>(__nv_bfloat16* ds
     }
 }
 
-template <typename TOut>
+template <typename TOut, int HD>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const Args a) {
@@ -444,9 +348,9 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     auto bar = [&](int i) { return ctx.bars + (uint32_t)i * 8u; };
 
     auto load_tile = [&](uint32_t dst, const CUtensorMap* tm, int row, int full_bar) {
-        mbar_expect_tx(bar(full_bar), TILE_BYTES);
+        mbar_expect_tx(bar(full_bar), (HD / 64) * HALF_BYTES);
         tma_load_3d(dst, tm, 0, row, bh, bar(full_bar));
-        tma_load_3d(dst + HALF_BYTES, tm, 64, row, bh, bar(full_bar));
+        if (HD == 128) tma_load_3d(dst + HALF_BYTES, tm, 64, row, bh, bar(full_bar));
     };
     if (warp == WARP_TMA && lane == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmQ)) : "memory");
@@ -571,10 +475,10 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 // 1 KiB apart = SBO).
                 const uint32_t p_tmem = s_tmem + (uint32_t)(i & 1) * BH;
                 const uint32_t vb = v_lo + (uint32_t)s * (TILE_BYTES >> 4) + (uint32_t)(i & 1) * ((BH * 128) >> 4);
-                mma_ts2(o_tmem, p_tmem, vb, IDESC_PV, i > 0);
+                mma_ts2(o_tmem, p_tmem, vb, IdescPV<HD>::value, i > 0);
 #pragma unroll
                 for (int ks = 1; ks < BH / 16; ++ks)
-                    mma_ts2(o_tmem, p_tmem + ks * 8, vb + (uint32_t)ks * (2048 >> 4), IDESC_PV, 1u);
+                    mma_ts2(o_tmem, p_tmem + ks * 8, vb + (uint32_t)ks * (2048 >> 4), IdescPV<HD>::value, 1u);
                 mma_commit(bar(O_DONE + t));
                 if ((i & 1) || i + 1 >= nh) release(V_EMPTY + s, j);
                 if (i + 2 < nh) ok = issue_qk(i + 2);   // reuses buffer i & 1: in order after PV(t, i)
@@ -587,15 +491,15 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         if (use_rope) {
             const int rt = tid - WARP_ROT0 * 32;
             RopeState st;
-            rope_init(st, a.rope, S, a.rope_mode, rt);
+            rope_init<HD>(st, a.rope, S, a.rope_mode, rt);
             bool ok = true;
-            RopeStart cur = rope_load_start(0, S, a.rope, a.rope_mode, rt);
+            RopeStart cur = rope_load_start<HD>(0, S, a.rope, a.rope_mode, rt);
             for (int j = 0; j < n_total && ok; ++j) {
                 const int s = j % NSTAGE, it = j / NSTAGE;
-                const RopeStart nxt = rope_load_start((j + 1) * BN, S, a.rope, a.rope_mode, rt);   // for the next tile
+                const RopeStart nxt = rope_load_start<HD>((j + 1) * BN, S, a.rope, a.rope_mode, rt);   // for the next tile
                 ok = wait_bar_warp(ctx, K_FULL + s, it & 1);
                 if (!ok) break;
-                rope_tile(base_addr + SMEM_K + s * TILE_BYTES, cur, a.rope_mode, rt, st);
+                rope_tile<HD>(base_addr + SMEM_K + s * TILE_BYTES, cur, a.rope_mode, rt, st);
                 cur = nxt;
                 fence_async_smem();
                 mbar_arrive(bar(K_READY + s));
@@ -616,7 +520,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll
                 for (int i = 0; i < 32; ++i) z[i] = 0u;
 #pragma unroll
-                for (int ch = 0; ch < 4; ++ch) store_row_chunk<TOut>(O + (size_t)row_g * HD + ch * 32, z, 0.f);
+                for (int ch = 0; ch < HD / 32; ++ch) store_row_chunk<TOut>(O + (size_t)row_g * HD + ch * 32, z, 0.f);
             }
         } else {
             const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
@@ -624,11 +528,11 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             bool ok = true;
             if (use_rope) {   // this warpgroup rotates its own Q tile
                 RopeState st;
-                rope_init(st, a.rope, S, a.rope_mode, row);
-                const RopeStart start = rope_load_start(qt0, S, a.rope, a.rope_mode, row);
+                rope_init<HD>(st, a.rope, S, a.rope_mode, row);
+                const RopeStart start = rope_load_start<HD>(qt0, S, a.rope, a.rope_mode, row);
                 ok = wait_bar_warp(ctx, Q_FULL + t, 0);
                 if (ok) {
-                    rope_tile(base_addr + SMEM_Q + t * TILE_BYTES, start, a.rope_mode, row, st);
+                    rope_tile<HD>(base_addr + SMEM_Q + t * TILE_BYTES, start, a.rope_mode, row, st);
                     fence_async_smem();
                     mbar_arrive(bar(Q_READY + t));
                 }
@@ -678,7 +582,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         if (need) m_ref = m_new;
                         l *= f;
 #pragma unroll
-                        for (int ch = 0; ch < 4; ++ch) {
+                        for (int ch = 0; ch < HD / 32; ++ch) {
                             uint32_t orow[32];
                             tmem_ld_x32_sync(o_addr + ch * 32, orow);
 #pragma unroll
@@ -736,7 +640,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     const uint32_t stage = base_addr + SMEM_Q + t * TILE_BYTES + (warp & 3) * 8192;
                     const int row_w0 = qt0 + (warp & 3) * 32;
 #pragma unroll
-                    for (int pass = 0; pass < 2; ++pass) {
+                    for (int pass = 0; pass < HD / 64; ++pass) {
 #pragma unroll
                         for (int ch = 0; ch < 2; ++ch) {
                             uint32_t orow[32];
@@ -762,7 +666,7 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     }
                 } else {
 #pragma unroll
-                    for (int ch = 0; ch < 4; ++ch) {
+                    for (int ch = 0; ch < HD / 32; ++ch) {
                         uint32_t orow[32];
                         tmem_ld_x32_sync(o_addr + ch * 32, orow);   // warp-collective: no divergence here
                         if (row_g < S) store_row_chunk<TOut>(O + (size_t)row_g * HD + ch * 32, orow, inv);
@@ -780,8 +684,8 @@ flash_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
 }
 
-// (B*H, S, 128) bf16 tensor, box = 64 columns x 128 rows x 1, 128-byte swizzle, zero fill out of bounds.
-static int make_map(grl_device* dev, CUtensorMap* tm, const void* ptr, int BH, int S) {
+// (B*H, S, head_dim) bf16 tensor, box = 64 columns x 128 rows x 1, 128-byte swizzle, zero fill out of bounds.
+static int make_map(grl_device* dev, CUtensorMap* tm, const void* ptr, int BH, int S, int HD) {
     TmapKey k{};
     k.ptr = ptr; k.rank = 3; k.swizzle_128b = 1;
     k.dims[0] = HD; k.dims[1] = (uint64_t)S; k.dims[2] = (uint64_t)BH;
@@ -794,7 +698,7 @@ static int make_map(grl_device* dev, CUtensorMap* tm, const void* ptr, int BH, i
 
 int flash_fwd_sm100(grl_device* dev, const grl_flash_params* p, float scale, const float2* rope, int32_t* status) {
     using namespace sm100;
-    GRL_REQUIRE(p->head_dim == HD, "the tcgen05 prefill kernel needs head_dim 128 (got %d)", p->head_dim);
+    GRL_REQUIRE(p->head_dim == 128 || p->head_dim == 64, "the tcgen05 prefill kernel needs head_dim 128 or 64 (got %d)", p->head_dim);
     GRL_REQUIRE(p->in_dtype == GRL_BF16, "the tcgen05 prefill kernel takes bf16 Q/K/V (cast with grl_cast first)");
     GRL_REQUIRE(!p->mask, "the tcgen05 prefill kernel takes causal / seq_lens masks only");
     GRL_REQUIRE(scale > 0.f, "scale must be positive");
@@ -803,9 +707,10 @@ int flash_fwd_sm100(grl_device* dev, const grl_flash_params* p, float scale, con
                 "Q/K/V/O must be 16-byte aligned");
     const int BH = p->batch * p->heads;
     CUtensorMap tq, tk, tv;
-    int rc = make_map(dev, &tq, p->q, BH, p->seq_len);
-    if (!rc) rc = make_map(dev, &tk, p->k, BH, p->seq_len);
-    if (!rc) rc = make_map(dev, &tv, p->v, BH, p->seq_len);
+    const int HD = p->head_dim;
+    int rc = make_map(dev, &tq, p->q, BH, p->seq_len, HD);
+    if (!rc) rc = make_map(dev, &tk, p->k, BH, p->seq_len, HD);
+    if (!rc) rc = make_map(dev, &tv, p->v, BH, p->seq_len, HD);
     if (rc) return rc;
     Args a{};
     a.o = p->o; a.seq_lens = p->seq_lens; a.rope = rope; a.status = status;
@@ -817,14 +722,20 @@ int flash_fwd_sm100(grl_device* dev, const grl_flash_params* p, float scale, con
     dim3 grid((unsigned)BH * a.n_qp);
     static bool attr_set[64] = {};
     if (!attr_set[dev->ordinal & 63]) {      // a function attribute belongs to the device that was current
-        GRL_CUDA(cudaFuncSetAttribute(flash_fwd_sm100_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
-        GRL_CUDA(cudaFuncSetAttribute(flash_fwd_sm100_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        GRL_CUDA(cudaFuncSetAttribute(flash_fwd_sm100_kernel<float, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        GRL_CUDA(cudaFuncSetAttribute(flash_fwd_sm100_kernel<__nv_bfloat16, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        GRL_CUDA(cudaFuncSetAttribute(flash_fwd_sm100_kernel<float, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        GRL_CUDA(cudaFuncSetAttribute(flash_fwd_sm100_kernel<__nv_bfloat16, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
         attr_set[dev->ordinal & 63] = true;
     }
-    if (p->out_dtype == GRL_F32)
-        flash_fwd_sm100_kernel<float><<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
-    else
-        flash_fwd_sm100_kernel<__nv_bfloat16><<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
+    const bool f32 = p->out_dtype == GRL_F32;
+    if (HD == 128) {
+        if (f32) flash_fwd_sm100_kernel<float, 128><<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
+        else flash_fwd_sm100_kernel<__nv_bfloat16, 128><<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
+    } else {
+        if (f32) flash_fwd_sm100_kernel<float, 64><<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
+        else flash_fwd_sm100_kernel<__nv_bfloat16, 64><<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tq, tk, tv, a);
+    }
     GRL_LAUNCHED("flash_fwd_sm100_kernel");
     return GRL_OK;
 }

@@ -104,7 +104,16 @@ def _outside(name):
     return op
 
 
-for _name in ("linear", "linear_cpu", "relu", "gelu", "silu", "tanh_act", "layernorm", "conv1d", "conv2d",
+def linear(device, x, weight, bias=None, **kwargs):
+    """GPU linear projection: output = x @ W^T + bias (dtype="bf16" selects the tensor-core kernel)."""
+    return _core.linear(device, x, weight, bias, **kwargs)
+
+
+def fused_qkv_projection(device, x, w_qkv, b_qkv=None, num_heads=8, head_dim=64, **kwargs):
+    return _core.fused_qkv_projection(device, x, w_qkv, b_qkv, num_heads, head_dim, **kwargs)
+
+
+for _name in ("linear_cpu", "relu", "gelu", "silu", "tanh_act", "layernorm", "conv1d", "conv2d",
               "hamming_search"):
     globals()[_name] = _outside(_name)
 del _name

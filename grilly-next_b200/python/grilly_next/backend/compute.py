@@ -68,11 +68,15 @@ class VulkanCompute:
         return _bridge.decode_step(self._device, kv_cache, q, k_new, v_new, **kwargs)
 
 
+    # ---- the projections on either side of attention
+    def linear(self, x, weight, bias=None, **kwargs):
+        return _bridge.linear(self._device, x, weight, bias, **kwargs)
+
+    def fused_qkv_projection(self, x, w_qkv, b_qkv=None, **kwargs):
+        return _bridge.fused_qkv_projection(self._device, x, w_qkv, b_qkv, **kwargs)
+
     # ---- methods of the reference class outside the attention / KV-cache path (compute.py:56-111 there):
     # present and callable; each raises RuntimeError saying that this build does not cover it
-    def linear(self, x, weight, bias=None, **kwargs):
-        return _bridge.linear(self._device, x, weight, bias)
-
     def activation_relu(self, x, **kwargs):
         return _bridge.relu(self._device, x)
 

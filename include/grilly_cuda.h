@@ -138,7 +138,7 @@ typedef struct {
     int32_t rope_mode;  /* GRL_ROPE_*; position = sequence index (flash-attention2-rope.glsl:101-141) */
     float rope_theta;   /* base, e.g. 10000 */
     float rope_scaling; /* theta / scaling; 0 is read as 1 */
-    int32_t kernel;     /* GRL_KERNEL_*; AUTO picks tcgen05 for bf16 input with D=128 */
+    int32_t kernel;     /* GRL_KERNEL_*; AUTO picks tcgen05 for bf16 input with D=128 or 64 */
     int32_t* status;    /* optional device int32[4]; [0] != 0 after a kernel-side failure */
 } grl_flash_params;
 int grl_flash_fwd(grl_device* dev, const grl_flash_params* p);
@@ -147,6 +147,14 @@ int grl_flash_fwd(grl_device* dev, const grl_flash_params* p);
  * does this on demand, which allocates and launches: inside a stream capture that is refused, so call
  * this first (the precomputed-table mode of shaders/rope.glsl:109-113 made implicit). */
 int grl_rope_table_prepare(grl_device* dev, int n_pos, int head_dim, float theta, float scaling);
+
+/* ---- linear projection, the step on either side of attention: replaces ops::linear (cpp/src/ops/linear.cpp:20-82,
+ * shader fnn-linear) and shaders/fused-qkv-projection.glsl:40-74 (the same product with the packed
+ * [W_q; W_k; W_v] weight and bias).  y (m,n) float32 = x (m,k) w^T + bias, w (n,k) row-major, bias (n) or NULL.
+ * in_dtype GRL_F32: exact float32 dot products; GRL_BF16: x and w are bf16 (grl_cast) and the product runs on the
+ * tcgen05 tensor cores with float32 accumulation (k must be a multiple of 8). */
+int grl_linear(grl_device* dev, const void* x, const void* w, const float* bias, float* y, int m, int k, int n,
+               int in_dtype);
 
 /* ---- standalone RoPE: replaces shaders/rope.glsl:32-126 (push block :32-40).
  * x, y: (B,S,H,D) float32, out of place; position = sequence index / scaling;

@@ -106,6 +106,6 @@ def test_device_group_splits_heads(core, ctx):
 
 
 def test_names_outside_this_build_say_so(core, ctx):
-    for name in ("linear", "relu", "gelu", "layernorm", "conv2d", "hamming_search"):
+    for name in ("relu", "gelu", "layernorm", "conv2d", "hamming_search"):
         with pytest.raises(RuntimeError, match="outside the attention"):
             getattr(core, name)(ctx)

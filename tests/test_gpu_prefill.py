@@ -157,9 +157,9 @@ def test_error_behaviour(gpu):
     q = np.zeros((1, 1, 8, 48), np.float32)
     with pytest.raises(RuntimeError, match="head_dim"):
         gpu.flash_attention2(q, q, q)
-    q = np.zeros((1, 1, 8, 64), np.float32)
+    q = np.zeros((1, 1, 8, 32), np.float32)
     with pytest.raises(RuntimeError, match="bf16 path"):
-        gpu.flash_attention2(q, q, q, dtype="bf16")
+        gpu.flash_attention2(q, q, q, dtype="bf16")          # the tensor-core kernel takes head_dim 128 and 64
     stats = gpu.device.pool_stats()
     assert set(stats) == {"hits", "misses", "allocations", "total_acquired", "total_released"}
     assert set(gpu.device.cache_stats()) == {"hits", "misses", "evictions", "cached_sets"}
@@ -167,7 +167,7 @@ def test_error_behaviour(gpu):
 
 
 # --------------------------------------------------------------------------- bf16 tensor-core path
-@pytest.mark.parametrize("name", ["cfg2_small", "ragged_d128", "noncausal_d128"])
+@pytest.mark.parametrize("name", ["cfg2_small", "ragged_d128", "noncausal_d128", "cfg1", "odd_s_d64", "tiny_s8_d64", "s1_d64"])
 def test_tcgen05_kernel_small_cases(dev, name):
     from grilly_next import cabi
     from gpu_helpers import flash_cabi
@@ -193,6 +193,31 @@ def test_tcgen05_kernel_rope_half_and_bf16_out(dev):
     assert np.abs(got - want).max() <= TOL_BF16
     got16 = flash_cabi(dev, Q, K, V, causal=True, rope_mode=cabi.ROPE_HALF, bf16=True, kernel=cabi.KERNEL_TCGEN05,
                        out_bf16=True)
+    assert np.abs(got16 - want).max() <= 3e-2   # + one bf16 rounding of O
+
+
+@pytest.mark.parametrize("mode", ["interleaved", "half"])
+def test_tcgen05_kernel_head_dim_64_with_rope(dev, mode):
+    """head_dim 64 (the shape of the reference's own tests) on the tensor-core kernel: both RoPE pairings, ragged
+    lengths, float32 and bf16 output, a sequence long enough for several K tiles."""
+    from grilly_next import cabi
+    from gpu_helpers import flash_cabi
+    rng = np.random.default_rng(80)
+    B, H, S, D = 2, 3, 700, 64
+    lens = np.array([700, 333], np.int32)
+    Q, K, V = (rng.standard_normal((B, H, S, D), dtype=np.float32) for _ in range(3))
+    pos = np.arange(S)
+    if mode == "interleaved":
+        q, k = orc.rope_interleaved(Q, pos, 10000.0), orc.rope_interleaved(K, pos, 10000.0)
+    else:
+        q = orc.rope_half(Q.transpose(0, 2, 1, 3), 10000.0).transpose(0, 2, 1, 3)
+        k = orc.rope_half(K.transpose(0, 2, 1, 3), 10000.0).transpose(0, 2, 1, 3)
+    want = orc.attention_4d(q, k, V, mask=orc.causal_length_mask(B, H, S, lens, True))
+    want[1, :, 333:] = 0.0
+    rm = cabi.ROPE_INTERLEAVED if mode == "interleaved" else cabi.ROPE_HALF
+    got = flash_cabi(dev, Q, K, V, causal=True, seq_lens=lens, rope_mode=rm, bf16=True, kernel=cabi.KERNEL_TCGEN05)
+    assert np.abs(got - want).max() <= TOL_BF16
+    got16 = flash_cabi(dev, Q, K, V, causal=True, seq_lens=lens, rope_mode=rm, bf16=True, kernel=cabi.KERNEL_AUTO, out_bf16=True)
     assert np.abs(got16 - want).max() <= 3e-2   # + one bf16 rounding of O
 
 
