@@ -25,7 +25,7 @@ CUDA_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
               "-Xcompiler", "-fPIC", "-ccbin", HOST_CXX, "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
 CU_SOURCES = ["device.cu", "flash.cu", "prefill_fp32.cu", "prefill_sm100.cu", "decode_splitkv.cu", "decode_mma.cu", "p2p_merge.cu", "kv_evict.cu",
-              "kv_cache.cu", "rope_mask.cu", "nccl_group.cu", "linear_sm100.cu"]
+              "kv_cache.cu", "rope_mask.cu", "nccl_group.cu", "linear_sm100.cu", "attention_unfused.cu"]
 HEADERS = ["common.cuh", "tmem_ops.cuh", "sm100_ptx.cuh", os.path.join(ROOT, "include", "grilly_cuda.h")]
 
 

@@ -74,5 +74,26 @@ void swizzle(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const 
              uint32_t batchSize, uint32_t numHeads, uint32_t seqLen, uint32_t headDim, uint32_t waveSize = 32,
              bool reverse = false);
 
+/// The unfused attention pieces, host pointers, synchronous (upload, one launch sequence, download); float32.
+/// attentionScores: Q, K (B,S,H,D) -> scores (B,H,S,S) = scale Q K^T (shaders/attention-scores.glsl:33-65);
+/// scale 0 means 1/sqrt(headDim).
+void attentionScores(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* Q, const float* K,
+                     float* scores, uint32_t batchSize, uint32_t seqLen, uint32_t numHeads, uint32_t headDim,
+                     float scale = 0.0f);
+/// Softmax over the last axis of (rows, features) (shaders/activation-softmax.glsl:34-84).
+void softmax(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* input, float* output,
+             size_t rows, uint32_t features);
+/// weights (B,H,S,S) . V (B,S,H,D) -> (B,S,H,D); causal sums over k <= q only
+/// (shaders/attention-output.glsl:28-70, attention-output-gpt.glsl:29-72).
+void attentionOutput(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* weights, const float* V,
+                     float* output, uint32_t batchSize, uint32_t seqLen, uint32_t numHeads, uint32_t headDim,
+                     bool causal = false);
+/// Backward of softmax(scale Q K^T) V: every tensor (B,H,S,D), attnWeights (B,H,S,S)
+/// (shaders/attention-backward.glsl:73-195).
+void attentionBackward(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* gradOutput,
+                       const float* Q, const float* K, const float* V, const float* attnWeights, float* gradQ,
+                       float* gradK, float* gradV, uint32_t batchSize, uint32_t numHeads, uint32_t seqLen,
+                       uint32_t headDim, float scale = 0.0f);
+
 }  // namespace ops
 }  // namespace grilly

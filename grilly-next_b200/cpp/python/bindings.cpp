@@ -412,6 +412,69 @@ PYBIND11_MODULE(grilly_core, m) {
         py::arg("device"), py::arg("input"), py::arg("wave_size") = 32, py::arg("reverse") = false,
         "Swizzle/unswizzle KV tensor: [B,H,S,D] -> [B,H,S/W,D/W,W,W] (flat, zero padded) and back");
 
+    // ---- the unfused attention pieces and the attention backward pass.  The reference dispatches these as shaders
+    // from its Python backend (attention-scores, activation-softmax, attention-output(-gpt), attention-backward) and
+    // has no pybind entry for them; the names follow VulkanBackwardOps.attention_backward
+    // (src/grilly_next/backend/autograd_core.py:617-655) and the shader names.
+    m.def(
+        "attention_scores",
+        [](GrillyCoreContext& ctx, FArr q, FArr k, float scale) -> py::array_t<float> {
+            if (q.ndim() != 4 || k.ndim() != 4) throw std::runtime_error("q and k must be 4D (batch, seq_len, heads, head_dim)");
+            for (int i = 0; i < 4; ++i)
+                if (q.shape(i) != k.shape(i)) throw std::runtime_error("q and k shapes differ");
+            const uint32_t B = uint32_t(q.shape(0)), S = uint32_t(q.shape(1)), H = uint32_t(q.shape(2)), D = uint32_t(q.shape(3));
+            py::array_t<float> out({py::ssize_t(B), py::ssize_t(H), py::ssize_t(S), py::ssize_t(S)});
+            ops::attentionScores(ctx.batch, ctx.pool, ctx.cache, q.data(), k.data(), out.mutable_data(), B, S, H, D, scale);
+            return out;
+        },
+        py::arg("device"), py::arg("q"), py::arg("k"), py::arg("scale") = 0.0f,
+        "scores (B,H,S,S) = scale * Q K^T for Q, K laid out (B,S,H,D); scale 0 means 1/sqrt(head_dim)");
+    m.def(
+        "softmax",
+        [](GrillyCoreContext& ctx, FArr x) -> py::array_t<float> {
+            if (x.ndim() < 1 || x.size() == 0) throw std::runtime_error("softmax: empty input");
+            const uint32_t F = uint32_t(x.shape(x.ndim() - 1));
+            std::vector<py::ssize_t> shape(x.shape(), x.shape() + x.ndim());
+            py::array_t<float> out(shape);
+            ops::softmax(ctx.batch, ctx.pool, ctx.cache, x.data(), out.mutable_data(), size_t(x.size()) / F, F);
+            return out;
+        },
+        py::arg("device"), py::arg("x"), "Softmax over the last axis");
+    m.def(
+        "attention_output",
+        [](GrillyCoreContext& ctx, FArr weights, FArr v, bool causal) -> py::array_t<float> {
+            if (weights.ndim() != 4 || v.ndim() != 4)
+                throw std::runtime_error("weights must be (batch, heads, seq_len, seq_len) and v (batch, seq_len, heads, head_dim)");
+            const uint32_t B = uint32_t(v.shape(0)), S = uint32_t(v.shape(1)), H = uint32_t(v.shape(2)), D = uint32_t(v.shape(3));
+            if (weights.shape(0) != B || weights.shape(1) != H || weights.shape(2) != S || weights.shape(3) != S)
+                throw std::runtime_error("weights shape does not match v");
+            py::array_t<float> out({py::ssize_t(B), py::ssize_t(S), py::ssize_t(H), py::ssize_t(D)});
+            ops::attentionOutput(ctx.batch, ctx.pool, ctx.cache, weights.data(), v.data(), out.mutable_data(), B, S, H, D, causal);
+            return out;
+        },
+        py::arg("device"), py::arg("weights"), py::arg("v"), py::arg("causal") = false,
+        "out (B,S,H,D) = weights (B,H,S,S) . V (B,S,H,D); causal=True is the GPT form (sum over k <= q)");
+    m.def(
+        "attention_backward",
+        [](GrillyCoreContext& ctx, FArr gradOutput, FArr q, FArr k, FArr v, FArr attn, float scale) -> py::tuple {
+            if (q.ndim() != 4) throw std::runtime_error("q must be 4D (batch, heads, seq_len, head_dim)");
+            const uint32_t B = uint32_t(q.shape(0)), H = uint32_t(q.shape(1)), S = uint32_t(q.shape(2)), D = uint32_t(q.shape(3));
+            for (const FArr* t : {&gradOutput, &k, &v}) {
+                if (t->ndim() != 4) throw std::runtime_error("grad_output, k and v must be 4D like q");
+                for (int i = 0; i < 4; ++i)
+                    if (t->shape(i) != q.shape(i)) throw std::runtime_error("grad_output, k and v must have the shape of q");
+            }
+            if (attn.ndim() != 4 || attn.shape(0) != B || attn.shape(1) != H || attn.shape(2) != S || attn.shape(3) != S)
+                throw std::runtime_error("attn_weights must be (batch, heads, seq_len, seq_len)");
+            std::vector<py::ssize_t> shape{py::ssize_t(B), py::ssize_t(H), py::ssize_t(S), py::ssize_t(D)};
+            py::array_t<float> gq(shape), gk(shape), gv(shape);
+            ops::attentionBackward(ctx.batch, ctx.pool, ctx.cache, gradOutput.data(), q.data(), k.data(), v.data(), attn.data(),
+                                   gq.mutable_data(), gk.mutable_data(), gv.mutable_data(), B, H, S, D, scale);
+            return py::make_tuple(gq, gk, gv);
+        },
+        py::arg("device"), py::arg("grad_output"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("attn_weights"),
+        py::arg("scale") = 0.0f, "(grad_q, grad_k, grad_v) of softmax(scale Q K^T) V; all tensors (B,H,S,D)");
+
     // ---- KV cache (reference: bindings.cpp:592-694)
     py::class_<ops::KVCache>(m, "KVCache")
         .def_readonly("current_len", &ops::KVCache::currentLen)

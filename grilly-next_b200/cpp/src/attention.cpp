@@ -424,5 +424,92 @@ void swizzle(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const 
     batch.submit();
 }
 
+void attentionScores(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* Q, const float* K,
+                     float* scores, uint32_t B, uint32_t S, uint32_t H, uint32_t D, float scale) {
+    if (!Q || !K || !scores) throw std::runtime_error("attentionScores: null tensor pointer");
+    if (B == 0 || S == 0 || H == 0 || D == 0) throw std::runtime_error("attentionScores: empty shape");
+    cache.getOrCreate("attention-scores");
+    const size_t qBytes = size_t(B) * S * H * D * 4, sBytes = size_t(B) * H * S * S * 4;
+    Scoped scope(pool);
+    GrillyBuffer q = pool.acquire(qBytes), k = pool.acquire(qBytes), sc = pool.acquire(sBytes);
+    scope.add(q); scope.add(k); scope.add(sc);
+    grl_device* dev = pool.device().handle();
+    Recording rec(batch);
+    pool.upload(q, Q, qBytes);
+    pool.upload(k, K, qBytes);
+    check(grl_attention_scores(dev, static_cast<const float*>(q.dptr), static_cast<const float*>(k.dptr),
+                               static_cast<float*>(sc.dptr), int(B), int(S), int(H), int(D), scale),
+          "attentionScores");
+    check(grl_memcpy_d2h(dev, scores, sc.dptr, sBytes), "attentionScores: download");
+    batch.submit();
+}
+
+void softmax(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* input, float* output, size_t rows,
+             uint32_t features) {
+    if (!input || !output) throw std::runtime_error("softmax: null tensor pointer");
+    if (rows == 0 || features == 0) throw std::runtime_error("softmax: empty shape");
+    cache.getOrCreate("activation-softmax");
+    const size_t bytes = rows * features * 4;
+    Scoped scope(pool);
+    GrillyBuffer in = pool.acquire(bytes), out = pool.acquire(bytes);
+    scope.add(in); scope.add(out);
+    grl_device* dev = pool.device().handle();
+    Recording rec(batch);
+    pool.upload(in, input, bytes);
+    check(grl_softmax(dev, static_cast<const float*>(in.dptr), static_cast<float*>(out.dptr), rows, int(features)), "softmax");
+    check(grl_memcpy_d2h(dev, output, out.dptr, bytes), "softmax: download");
+    batch.submit();
+}
+
+void attentionOutput(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* weights, const float* V,
+                     float* output, uint32_t B, uint32_t S, uint32_t H, uint32_t D, bool causal) {
+    if (!weights || !V || !output) throw std::runtime_error("attentionOutput: null tensor pointer");
+    if (B == 0 || S == 0 || H == 0 || D == 0) throw std::runtime_error("attentionOutput: empty shape");
+    cache.getOrCreate(causal ? "attention-output-gpt" : "attention-output");
+    const size_t vBytes = size_t(B) * S * H * D * 4, wBytes = size_t(B) * H * S * S * 4;
+    Scoped scope(pool);
+    GrillyBuffer w = pool.acquire(wBytes), v = pool.acquire(vBytes), o = pool.acquire(vBytes);
+    scope.add(w); scope.add(v); scope.add(o);
+    grl_device* dev = pool.device().handle();
+    Recording rec(batch);
+    pool.upload(w, weights, wBytes);
+    pool.upload(v, V, vBytes);
+    check(grl_attention_output(dev, static_cast<const float*>(w.dptr), static_cast<const float*>(v.dptr),
+                               static_cast<float*>(o.dptr), int(B), int(S), int(H), int(D), causal ? 1 : 0),
+          "attentionOutput");
+    check(grl_memcpy_d2h(dev, output, o.dptr, vBytes), "attentionOutput: download");
+    batch.submit();
+}
+
+void attentionBackward(CommandBatch& batch, BufferPool& pool, PipelineCache& cache, const float* gradOutput, const float* Q,
+                       const float* K, const float* V, const float* attnWeights, float* gradQ, float* gradK, float* gradV,
+                       uint32_t B, uint32_t H, uint32_t S, uint32_t D, float scale) {
+    if (!gradOutput || !Q || !K || !V || !attnWeights || !gradQ || !gradK || !gradV)
+        throw std::runtime_error("attentionBackward: null tensor pointer");
+    if (B == 0 || S == 0 || H == 0 || D == 0) throw std::runtime_error("attentionBackward: empty shape");
+    cache.getOrCreate("attention-backward");
+    const size_t tBytes = size_t(B) * H * S * D * 4, aBytes = size_t(B) * H * S * S * 4;
+    Scoped scope(pool);
+    GrillyBuffer go = pool.acquire(tBytes), q = pool.acquire(tBytes), k = pool.acquire(tBytes), v = pool.acquire(tBytes),
+                 a = pool.acquire(aBytes), scratch = pool.acquire(aBytes), gq = pool.acquire(tBytes), gk = pool.acquire(tBytes),
+                 gv = pool.acquire(tBytes);
+    for (GrillyBuffer* b : {&go, &q, &k, &v, &a, &scratch, &gq, &gk, &gv}) scope.add(*b);
+    grl_device* dev = pool.device().handle();
+    Recording rec(batch);
+    pool.upload(go, gradOutput, tBytes);
+    pool.upload(q, Q, tBytes);
+    pool.upload(k, K, tBytes);
+    pool.upload(v, V, tBytes);
+    pool.upload(a, attnWeights, aBytes);
+    auto f = [](const GrillyBuffer& b) { return static_cast<float*>(b.dptr); };
+    check(grl_attention_backward(dev, f(go), f(q), f(k), f(v), f(a), f(gq), f(gk), f(gv), f(scratch), int(B), int(H), int(S),
+                                 int(D), scale),
+          "attentionBackward");
+    check(grl_memcpy_d2h(dev, gradQ, gq.dptr, tBytes), "attentionBackward: download");
+    check(grl_memcpy_d2h(dev, gradK, gk.dptr, tBytes), "attentionBackward: download");
+    check(grl_memcpy_d2h(dev, gradV, gv.dptr, tBytes), "attentionBackward: download");
+    batch.submit();
+}
+
 }  // namespace ops
 }  // namespace grilly

@@ -24,7 +24,7 @@ struct TmapKey {
     uint64_t dims[3];
     uint64_t strides[2];       // bytes, dimensions 1..rank-1
     uint32_t box[3];
-    uint32_t pad;
+    uint32_t bytes;            // 1: uint8 elements; 0: bf16 (two bytes)
 };
 constexpr long long kDefaultWaitLimitCycles = 2000000000LL;       // ~1 s at 2 GHz: mbarrier waits inside a kernel
 constexpr long long kDefaultPeerWaitLimitCycles = 1000000000LL;   // ~0.5 s: a peer GPU that never posts
@@ -180,6 +180,19 @@ template <> __device__ __forceinline__ float load_as_float<float>(const float* p
 template <> __device__ __forceinline__ float load_as_float<__nv_bfloat16>(const __nv_bfloat16* p) {
     return __bfloat162float(*p);
 }
+// Where the packed value bytes of the quantised cache (GRL_FP8_INT4) live inside the value block of one
+// (page, kv head), which holds page_tokens * D/2 bytes.  Byte j of a token packs elements 2j (low nibble) and 2j+1
+// (high nibble) exactly as the reference packs them; only the ADDRESS of the byte is this library's choice.  Tokens
+// are stored in pairs (2i, 2i+1), D bytes per pair, as D/4 words of [even token: bytes 2w, 2w+1 | odd token: bytes
+// 2w, 2w+1]: one 32-bit word then holds the same four elements of two consecutive tokens, which is the pairing a
+// tensor-core operand over the token axis needs, with no transpose.  The words of a pair are ordered [w % 8][w / 8]
+// so that one 16-byte load brings the same word of every scale group (32 elements = 8 words).
+__host__ __device__ __forceinline__ size_t quant_v_off(int token_in_page, int j, int D) {
+    const int w = j >> 1, G = D >> 5;
+    const int pw = (w & 7) * G + (w >> 3);
+    return (size_t)(token_in_page >> 1) * D + pw * 4 + (token_in_page & 1) * 2 + (j & 1);
+}
+
 template <typename T> __device__ __forceinline__ void store_from_float(T* p, float v);
 template <> __device__ __forceinline__ void store_from_float<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_from_float<__nv_bfloat16>(__nv_bfloat16* p, float v) {

@@ -9,27 +9,56 @@
 // bf16 hi+lo so that its fp32 precision survives), with a private fp32 online softmax in the
 // exp2 domain.  K and V cross HBM -> SM exactly once; the four warps' partials are merged in
 // shared memory and leave the CTA as (O un-normalised, m, l), the layout lse_merge_kernel reads.
+//
+// The same kernel, instantiated for the quantised cache (GRL_FP8_INT4: FP8-E4M3 keys, INT4 values, one float16 scale
+// per 32 key elements, cpp/src/ops/kv_cache.cpp:272-399 and :500-577), streams 12.5 KiB per (page, kv head) instead
+// of 32 and dequantises in registers: key bytes become f16 with one conversion per pair (every code the quantiser can
+// emit is an exact f16), the four scale groups of a head accumulate separately and are combined with 1/scale per
+// token; value nibbles become f16 by one logic operation and one subtraction per pair (1024 + n or 64 + n in the
+// mantissa, minus the offset and the code's bias), with 1/scale folded into P.  The contraction indices of both
+// products are permuted so that every operand register is a plain 32-bit piece of what was loaded.
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 #include "common.cuh"
 
+#ifndef GRL_DQ_CTAS
+#define GRL_DQ_CTAS 3
+#define GRL_DQ_NST 4
+#endif
 namespace grl {
 namespace dmma {
 
 constexpr int P = 64;               // tokens per page
 constexpr int D = 128;              // head_dim
-constexpr int NST = 3;              // ring stages
 constexpr int SLAB = P * D * 2;     // 16 KiB: one page of K (or V) for one kv head
 constexpr int STAGE = 2 * SLAB;     // K then V
 constexpr int kThreads = 160;       // 4 compute warps + 1 producer warp
-constexpr int SMEM_BAR = NST * STAGE;
-constexpr int SMEM_TOTAL = SMEM_BAR + 128 + 1024;
+// The shared-memory ring of the two instances.  After the ring: 128 bytes of barriers and flags, 1 KiB of per-warp
+// scratch (1/scale of a warp's 16 tokens x 4 groups), 1 KiB of slack for the 1024-byte alignment of the ring.
+template <bool QUANT> struct Ring {
+    static constexpr int NST = 3;            // ring stages
+    static constexpr int STAGE = dmma::STAGE;
+};
+constexpr int QK_BYTES = P * D;          // 8 KiB of key bytes per (page, kv head)
+constexpr int QV_BYTES = P * D / 2;      // 4 KiB of packed value nibbles
+constexpr int QS_BYTES = P * (D / 32) * 2;   // 512 B of float16 scales
+template <> struct Ring<true> {
+    static constexpr int NST = GRL_DQ_NST;
+    static constexpr int STAGE = 13 * 1024;  // keys at 0, values at 8 KiB, scales at 12 KiB
+};
+template <bool QUANT> struct Smem {
+    static constexpr int BAR = Ring<QUANT>::NST * Ring<QUANT>::STAGE;
+    static constexpr int TOTAL = BAR + 128 + 1024 + 1024;
+};
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kEmpty = -1e30f;
 
 struct Args {
     const int32_t* block_table;
     const int32_t* seq_lens;
+    const uint8_t* v_q;         // quantised cache: the value pool (plain bulk copies; the key pool goes through tmK)
+    const uint16_t* scales;     // quantised cache: float16 bit patterns, (rows, D/32)
     const float* q;
     float* part;
     float* out;
@@ -88,6 +117,49 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
 }
+// Plain (untiled) bulk copy global -> shared, 16-byte aligned on both sides, completing on an mbarrier.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar) : "memory");
+}
+// f16 form of the same product, keeping only rows 0..7 of the accumulator (c0, c1); rows 8..15 are discarded.
+__device__ __forceinline__ void mma_f16_top(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float x2, x3;   // rows 8..15: written by the instruction, never read
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%9,%9};"
+        : "+f"(d0), "+f"(d1), "=f"(x2), "=f"(x3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// Two FP8-E4M3 codes (low byte -> low half) as f16x2.  The reference's decoder (kv_cache.cpp:540-552) and the
+// hardware conversion agree on every code except 0x7F / 0xFF, which the reference's encoder cannot produce.
+__device__ __forceinline__ uint32_t fp8x2_to_f16x2(uint32_t two_codes) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"((unsigned short)two_codes));
+    return r;
+}
+// Value codes to f16x2 (low half: even token of the pair, high half: odd token): the nibble is placed in the mantissa of
+// 1024 (bits 0-3) or of 64 (bits 4-7), and the offset plus the code's bias of 8 is subtracted, which is exact in f16.
+__device__ __forceinline__ uint32_t nib_lo(uint32_t w) {
+    const uint32_t v = (w & 0x000F000Fu) | 0x64006400u, off = 0x64086408u;    // 1032, 1032
+    __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&v), *reinterpret_cast<const __half2*>(&off));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t nib_hi(uint32_t w) {
+    const uint32_t v = (w & 0x00F000F0u) | 0x54005400u, off = 0x54805480u;    // 72, 72
+    __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&v), *reinterpret_cast<const __half2*>(&off));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+// 1/scale from the stored float16 bit pattern, as the reference's decode forms it (kv_cache.cpp:517-533): bits moved
+// into a float32, not converted; a scale that is not positive gives 1.
+__device__ __forceinline__ float inv_scale_bits(uint32_t h) {
+    const uint32_t e = (h >> 10) & 0x1Fu, m = h & 0x03FFu;
+    const float sc = e == 0 ? (float)m * 5.9604644775390625e-08f
+                            : __uint_as_float(((h & 0x8000u) << 16) | ((e + 112u) << 23) | (m << 13));
+    return sc > 0.f ? __fdiv_rn(1.0f, sc) : 1.0f;
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -128,8 +200,10 @@ __device__ __forceinline__ uint32_t slab_off(int row, int d) {
     return (uint32_t)((d >> 6) * (P * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4));
 }
 
-__global__ void __launch_bounds__(kThreads, 2)
+template <bool QUANT>
+__global__ void __launch_bounds__(kThreads, QUANT ? GRL_DQ_CTAS : 2)
 decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const Args a) {
+    constexpr int NST = Ring<QUANT>::NST, STAGE = Ring<QUANT>::STAGE, SMEM_BAR = Smem<QUANT>::BAR;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -170,13 +244,20 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             for (int p = p_begin; p < p_end; ++p) {
                 const int i = p - p_begin, s = i % NST, it = i / NST;
                 if (it > 0 && !wait_bar(ctx, NST + s, (it - 1) & 1)) break;
-                const int row0 = (bt[p] * a.Hkv + kvh) * P;
+                const int blk = bt[p] * a.Hkv + kvh, row0 = blk * P;
                 const uint32_t dst = base + (uint32_t)s * STAGE;
-                mbar_expect_tx(full(s), STAGE);
-                tma_load_2d(dst, &tmK, 0, row0, full(s));
-                tma_load_2d(dst + SLAB / 2, &tmK, 64, row0, full(s));
-                tma_load_2d(dst + SLAB, &tmV, 0, row0, full(s));
-                tma_load_2d(dst + SLAB + SLAB / 2, &tmV, 64, row0, full(s));
+                if constexpr (QUANT) {
+                    mbar_expect_tx(full(s), QK_BYTES + QV_BYTES + QS_BYTES);
+                    tma_load_2d(dst, &tmK, 0, row0, full(s));          // 64 rows of 128 key bytes, 128-byte swizzle
+                    bulk_load(dst + QK_BYTES, a.v_q + (size_t)blk * QV_BYTES, QV_BYTES, full(s));
+                    bulk_load(dst + QK_BYTES + QV_BYTES, a.scales + (size_t)blk * (QS_BYTES / 2), QS_BYTES, full(s));
+                } else {
+                    mbar_expect_tx(full(s), STAGE);
+                    tma_load_2d(dst, &tmK, 0, row0, full(s));
+                    tma_load_2d(dst + SLAB / 2, &tmK, 64, row0, full(s));
+                    tma_load_2d(dst + SLAB, &tmV, 0, row0, full(s));
+                    tma_load_2d(dst + SLAB + SLAB / 2, &tmV, 64, row0, full(s));
+                }
                 issued = i + 1;
             }
             if (*ctx.abort) {   // copies already issued must land before the shared memory is released
@@ -185,6 +266,127 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                     while (!mbar_try_wait(full(i % NST), (i / NST) & 1) && clock64() - t0 < ctx.limit) {}
             }
         }
+    } else if constexpr (QUANT) {
+        // ------------------------------------------------------------------ compute over the quantised cache
+        // Element permutation of the two products.  QK^T: k-step (grp, w) of lane (g, t4) covers elements
+        // 32 grp + 8 t4 + 4 w + {0,1 | 2,3} = one 32-bit word of key bytes.  PV: output tile (grp, e), column n
+        // is element 32 grp + 4 n + e, and the k index pairs (2 t4, 2 t4 + 1 | + 8) are the token pairs
+        // (8 warp + t4 | + 4) of the value block (quant_v_off).
+        const int qh0 = kvh * a.group;
+        uint32_t qf[8][2];
+        {
+            const float sc = a.scale * kLog2e;
+            const float* qrow = a.q + ((size_t)b * a.Hq + qh0 + g) * D;
+            const bool live = g < a.group;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (live) v = *reinterpret_cast<const float4*>(qrow + 32 * (ks >> 1) + 8 * t4 + 4 * (ks & 1));
+                qf[ks][0] = pack_f16(v.x * sc, v.y * sc);
+                qf[ks][1] = pack_f16(v.z * sc, v.w * sc);
+            }
+        }
+        float* inv_w = reinterpret_cast<float*>(smem + SMEM_BAR + 128) + warp * 64;   // [16 tokens][4 groups]
+        bool ok = true;
+        for (int p = p_begin; p < p_end && ok; ++p) {
+            const int i = p - p_begin, s = i % NST, it = i / NST;
+            ok = __all_sync(0xffffffffu, wait_bar(ctx, s, it & 1));
+            if (!ok) break;
+            const uint8_t* kst = smem + s * STAGE;
+            const uint8_t* vst = kst + QK_BYTES;
+            const uint8_t* sst = vst + QV_BYTES;
+            const int tok0 = p * P + 16 * warp;
+            if (tok0 < len) {
+                {   // 1/scale of this warp's tokens: lane -> token lane/2, groups 2*(lane&1) and the next; 0 past the end
+                    const int tl = lane >> 1, g2 = (lane & 1) * 2;
+                    const uint32_t hh = *reinterpret_cast<const uint32_t*>(sst + ((16 * warp + tl) * 4 + g2) * 2);
+                    const bool live_t = tok0 + tl < len;
+                    *reinterpret_cast<float2*>(inv_w + tl * 4 + g2) =
+                        make_float2(live_t ? inv_scale_bits(hh & 0xFFFFu) : 0.f, live_t ? inv_scale_bits(hh >> 16) : 0.f);
+                }
+                __syncwarp();
+                float inv[2][2][4];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float4 v = *reinterpret_cast<const float4*>(inv_w + (8 * nt + 2 * t4 + e) * 4);
+                        inv[nt][e][0] = v.x; inv[nt][e][1] = v.y; inv[nt][e][2] = v.z; inv[nt][e][3] = v.w;
+                    }
+                // ---- S = q K^T for 16 tokens, one accumulator per scale group, combined with 1/scale
+                float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int row = 16 * warp + 8 * nt + g;
+#pragma unroll
+                    for (int grp = 0; grp < 4; ++grp) {
+                        const int chunk = (2 * grp + (t4 >> 1)) ^ (row & 7);
+                        const uint2 kb = *reinterpret_cast<const uint2*>(kst + row * 128 + chunk * 16 + (t4 & 1) * 8);
+                        float c0 = 0.f, c1 = 0.f;
+                        mma_f16_top(c0, c1, qf[2 * grp][0], qf[2 * grp][1], fp8x2_to_f16x2(kb.x), fp8x2_to_f16x2(kb.x >> 16));
+                        mma_f16_top(c0, c1, qf[2 * grp + 1][0], qf[2 * grp + 1][1], fp8x2_to_f16x2(kb.y), fp8x2_to_f16x2(kb.y >> 16));
+                        sacc[nt][0] = fmaf(c0, inv[nt][0][grp], sacc[nt][0]);
+                        sacc[nt][1] = fmaf(c1, inv[nt][1][grp], sacc[nt][1]);
+                    }
+                }
+                // ---- online softmax for head row g
+                float mx = kEmpty;
+                bool valid[2][2];
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        valid[nt][e] = tok0 + nt * 8 + 2 * t4 + e < len;
+                        if (valid[nt][e]) mx = fmaxf(mx, sacc[nt][e]);
+                    }
+                if (a.scores_out && g < a.group) {
+                    float* srow = a.scores_out + ((size_t)b * a.Hq + qh0 + g) * a.scores_ld + tok0 + 2 * t4;
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e)
+                            if (valid[nt][e]) srow[nt * 8 + e] = sacc[nt][e] * 0.6931471805599453f;
+                }
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_new = fmaxf(m_run, mx);
+                const float corr = ex2(m_run - m_new);
+                float pv[2][2], ps = 0.f;
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        pv[nt][e] = valid[nt][e] ? ex2(sacc[nt][e] - m_new) : 0.f;
+                        ps += pv[nt][e];
+                    }
+                l_run = l_run * corr + ps;
+                m_run = m_new;
+                if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+                    for (int n = 0; n < 16; ++n) { o[n][0] *= corr; o[n][1] *= corr; }
+                }
+                // ---- O += (P / scale) V: the two token pairs of this lane, 16 value bytes (all four groups) each
+                const uint4 va = *reinterpret_cast<const uint4*>(vst + (8 * warp + t4) * 128 + g * 16);
+                const uint4 vb = *reinterpret_cast<const uint4*>(vst + (8 * warp + 4 + t4) * 128 + g * 16);
+                const uint32_t xa[4] = {va.x, va.y, va.z, va.w}, xb[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+                for (int grp = 0; grp < 4; ++grp) {
+                    const uint32_t pa0 = pack_f16(pv[0][0] * inv[0][0][grp], pv[0][1] * inv[0][1][grp]);
+                    const uint32_t pa2 = pack_f16(pv[1][0] * inv[1][0][grp], pv[1][1] * inv[1][1][grp]);
+                    const uint32_t x = xa[grp], y = xb[grp], xs = x >> 8, ys = y >> 8;
+                    // nibble n of the even | odd token of a pair as f16x2: 1024 + n (low nibble) or 64 + n (high
+                    // nibble) by one logic operation, then n - 8 exactly by one subtraction
+                    mma_f16_top(o[4 * grp][0], o[4 * grp][1], pa0, pa2, nib_lo(x), nib_lo(y));
+                    mma_f16_top(o[4 * grp + 1][0], o[4 * grp + 1][1], pa0, pa2, nib_hi(x), nib_hi(y));
+                    mma_f16_top(o[4 * grp + 2][0], o[4 * grp + 2][1], pa0, pa2, nib_lo(xs), nib_lo(ys));
+                    mma_f16_top(o[4 * grp + 3][0], o[4 * grp + 3][1], pa0, pa2, nib_hi(xs), nib_hi(ys));
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty(s));
+        }
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
     } else {
         // ------------------------------------------------------------------ compute: tokens [16*warp, 16*warp+16) of every page
         const int qh0 = kvh * a.group;
@@ -302,9 +504,18 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     float* sm_m = sm_o + 4 * 8 * D;                               // [4][8]
     float* sm_l = sm_m + 32;
     if (warp < 4) {
+        if constexpr (QUANT) {
 #pragma unroll
-        for (int n = 0; n < 16; ++n)
-            *reinterpret_cast<float2*>(&sm_o[(warp * 8 + g) * D + n * 8 + 2 * t4]) = make_float2(o[n][0], o[n][1]);
+            for (int grp = 0; grp < 4; ++grp)
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+                    *reinterpret_cast<float4*>(&sm_o[(warp * 8 + g) * D + 32 * grp + 8 * t4 + 4 * c]) =
+                        make_float4(o[4 * grp][c], o[4 * grp + 1][c], o[4 * grp + 2][c], o[4 * grp + 3][c]);
+        } else {
+#pragma unroll
+            for (int n = 0; n < 16; ++n)
+                *reinterpret_cast<float2*>(&sm_o[(warp * 8 + g) * D + n * 8 + 2 * t4]) = make_float2(o[n][0], o[n][1]);
+        }
         if (t4 == 0) { sm_m[warp * 8 + g] = m_run; sm_l[warp * 8 + g] = l_run; }
     }
     __syncthreads();
@@ -526,8 +737,24 @@ static int make_pool_map(grl_device* dev, CUtensorMap* tm, const void* pool, uin
 bool decode_mma_supported(const grl_decode_params* p) {
     const grl_kv_layout& kv = p->kv;
     const int group = p->num_q_heads / kv.num_kv_heads;
-    return kv.cache_dtype == GRL_BF16 && kv.head_dim == dmma::D && kv.page_tokens == dmma::P && group >= 1 && group <= 8 &&
-           ((uintptr_t)kv.k_pages % 16 == 0) && ((uintptr_t)kv.v_pages % 16 == 0) && ((uintptr_t)p->q % 8 == 0);
+    const bool geometry = kv.head_dim == dmma::D && kv.page_tokens == dmma::P && group >= 1 && group <= 8 &&
+                          ((uintptr_t)kv.k_pages % 16 == 0) && ((uintptr_t)kv.v_pages % 16 == 0);
+    if (kv.cache_dtype == GRL_FP8_INT4)
+        return geometry && kv.scales && ((uintptr_t)kv.scales % 16 == 0) && ((uintptr_t)p->q % 16 == 0);
+    return kv.cache_dtype == GRL_BF16 && geometry && ((uintptr_t)p->q % 8 == 0);
+}
+
+template <bool QUANT>
+static int launch_instance(grl_device* dev, const CUtensorMap& tk, const CUtensorMap& tv, const dmma::Args& a, dim3 grid) {
+    using namespace dmma;
+    static bool attr_set[64] = {};
+    if (!attr_set[dev->ordinal & 63]) {      // a function attribute belongs to the device that was current
+        GRL_CUDA(cudaFuncSetAttribute(decode_mma_kernel<QUANT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<QUANT>::TOTAL));
+        attr_set[dev->ordinal & 63] = true;
+    }
+    decode_mma_kernel<QUANT><<<grid, kThreads, Smem<QUANT>::TOTAL, dev->stream>>>(tk, tv, a);
+    GRL_LAUNCHED(QUANT ? "decode_mma_kernel<quantised>" : "decode_mma_kernel");
+    return GRL_OK;
 }
 
 int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits, float scale, bool direct, bool fuse) {
@@ -535,11 +762,26 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
     const grl_kv_layout& kv = p->kv;
     const uint64_t pages = kv.num_pages > 0 ? (uint64_t)kv.num_pages : (uint64_t)kv.batch * kv.max_pages;
     const uint64_t rows = pages * kv.num_kv_heads * P;
+    const bool quant = kv.cache_dtype == GRL_FP8_INT4;
     CUtensorMap tk, tv;
-    int rc = make_pool_map(dev, &tk, kv.k_pages, rows);
-    if (!rc) rc = make_pool_map(dev, &tv, kv.v_pages, rows);
+    int rc;
+    if (quant) {
+        // the key pool as a 2-D byte tensor (rows, 128); box = one page of one kv head; values and scales are
+        // contiguous per (page, kv head) and travel as plain bulk copies
+        TmapKey k{};
+        k.ptr = kv.k_pages; k.rank = 2; k.swizzle_128b = 1; k.bytes = 1;
+        k.dims[0] = D; k.dims[1] = rows;
+        k.strides[0] = (uint64_t)D;
+        k.box[0] = D; k.box[1] = P;
+        rc = get_tensor_map(dev, k, &tk);
+        tv = tk;
+    } else {
+        rc = make_pool_map(dev, &tk, kv.k_pages, rows);
+        if (!rc) rc = make_pool_map(dev, &tv, kv.v_pages, rows);
+    }
     if (rc) return rc;
     Args a{};
+    a.v_q = static_cast<const uint8_t*>(kv.v_pages); a.scales = static_cast<const uint16_t*>(kv.scales);
     a.block_table = kv.block_table; a.seq_lens = kv.seq_lens; a.q = p->q;
     a.part = (float*)p->workspace; a.out = p->out; a.status = dev->d_status;
     a.B = kv.batch; a.Hq = p->num_q_heads; a.Hkv = kv.num_kv_heads; a.max_pages = kv.max_pages;
@@ -562,15 +804,8 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
         GRL_REQUIRE(p->out, "out is NULL");
     }
     dev->status_dirty = true;
-    static bool attr_set[64] = {};
-    if (!attr_set[dev->ordinal & 63]) {      // a function attribute belongs to the device that was current
-        GRL_CUDA(cudaFuncSetAttribute(decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
-        attr_set[dev->ordinal & 63] = true;
-    }
     dim3 grid(n_splits, kv.num_kv_heads, kv.batch);
-    decode_mma_kernel<<<grid, kThreads, SMEM_TOTAL, dev->stream>>>(tk, tv, a);
-    GRL_LAUNCHED("decode_mma_kernel");
-    return GRL_OK;
+    return quant ? launch_instance<true>(dev, tk, tv, a, grid) : launch_instance<false>(dev, tk, tv, a, grid);
 }
 
 }  // namespace grl

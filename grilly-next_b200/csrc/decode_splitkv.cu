@@ -66,7 +66,11 @@ template <> struct KVLoad<QuantKV> {
     static constexpr int VEC = 8;
     __device__ static void load(const DecodeArgs& a, size_t row, int D, int li, float* kx, float* vx) {
         const uint2 kb = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.k_pages) + row * D + li * 8));
-        const uint32_t vb = __ldg(reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.v_pages) + row * (D / 2) + li * 4));
+        // value bytes 4*li .. 4*li+3 of the token: two 16-bit halves of two words of its pair (quant_v_off)
+        const int tok = (int)(row % (size_t)a.P);
+        const uint8_t* vblock = reinterpret_cast<const uint8_t*>(a.v_pages) + (row - tok) * (size_t)(D / 2);
+        const uint32_t vb = (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(vblock + quant_v_off(tok, 4 * li, D))) |
+                            ((uint32_t)__ldg(reinterpret_cast<const uint16_t*>(vblock + quant_v_off(tok, 4 * li + 2, D))) << 16);
         const uint16_t hb = __ldg(a.scales + row * (D / 32) + (li >> 2));
         const uint32_t he = (hb >> 10) & 0x1Fu, hm = hb & 0x03FFu;
         const float scale = he == 0 ? (float)hm * 5.9604644775390625e-08f

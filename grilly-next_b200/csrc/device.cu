@@ -105,7 +105,7 @@ int get_tensor_map(grl_device* dev, const TmapKey& key, CUtensorMap* out) {
     cuuint64_t strides[2] = {key.strides[0], key.strides[1]};
     cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
     cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, key.rank, const_cast<void*>(key.ptr), dims, strides, box,
+    CUresult r = fn(out, key.bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, key.rank, const_cast<void*>(key.ptr), dims, strides, box,
                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     key.swizzle_128b ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

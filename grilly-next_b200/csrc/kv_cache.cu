@@ -222,7 +222,9 @@ __global__ void __launch_bounds__(256) kv_append_quant_kernel(AppendArgs a) {
         int q = (int)roundf(__fmul_rn(vx, vscale)) + 8;                       // kv_cache.cpp:363-366
         q = max(0, min(15, q));
         const int q_hi = __shfl_down_sync(0xffffffffu, q, 1);
-        if ((lane & 1) == 0) vp[row * half + (d >> 1)] = (uint8_t)((q & 0x0F) | ((q_hi & 0x0F) << 4));
+        if ((lane & 1) == 0)
+            vp[((size_t)page * a.Hkv + h) * a.P * half + quant_v_off(slot_pos % a.P, d >> 1, a.D)] =
+                (uint8_t)((q & 0x0F) | ((q_hi & 0x0F) << 4));
         if (lane == 0) a.scales[row * G + g] = scale_to_half_bits(kscale);   // the value scale is dropped (:393-398)
     }
 }
@@ -242,7 +244,7 @@ __global__ void kv_gather_quant_kernel(const uint8_t* __restrict__ kp, const uin
         const float scale = half_bits_to_scale(scales[row * (D / 32) + d / 32]);
         const float inv = scale > 0.f ? __fdiv_rn(1.0f, scale) : 1.0f;
         out_k[idx] = __fmul_rn(fp8_decode(kp[row * D + d]), inv);
-        const uint8_t packed = vp[row * (D / 2) + (d >> 1)];
+        const uint8_t packed = vp[((size_t)page * Hkv + h) * P * (D / 2) + quant_v_off(t % P, d >> 1, D)];
         const int q = (d & 1) ? (packed >> 4) & 0x0F : packed & 0x0F;
         out_v[idx] = __fmul_rn((float)(q - 8), inv);
     }
@@ -299,6 +301,7 @@ static int check_layout(const grl_kv_layout& kv) {
     if (kv.cache_dtype == GRL_FP8_INT4) {
         GRL_REQUIRE(kv.scales, "the quantised cache needs its scales buffer");
         GRL_REQUIRE(kv.head_dim % 32 == 0, "the quantised cache needs head_dim to be a multiple of 32 (scale groups)");
+        GRL_REQUIRE(kv.page_tokens % 2 == 0, "the quantised cache stores value bytes by token pairs: page_tokens must be even");
     }
     return GRL_OK;
 }

@@ -113,6 +113,26 @@ def fused_qkv_projection(device, x, w_qkv, b_qkv=None, num_heads=8, head_dim=64,
     return _core.fused_qkv_projection(device, x, w_qkv, b_qkv, num_heads, head_dim, **kwargs)
 
 
+def attention_scores(device, q, k, scale=0.0):
+    """scores (B,H,S,S) = scale * Q K^T for q, k laid out (B,S,H,D) (shader attention-scores)."""
+    return _core.attention_scores(device, q, k, scale)
+
+
+def softmax(device, x):
+    """Softmax over the last axis (shader activation-softmax)."""
+    return _core.softmax(device, x)
+
+
+def attention_output(device, weights, v, causal=False):
+    """weights (B,H,S,S) . v (B,S,H,D); causal=True is shader attention-output-gpt."""
+    return _core.attention_output(device, weights, v, causal)
+
+
+def attention_backward(device, grad_output, q, k, v, attn_weights, scale=0.0):
+    """(grad_q, grad_k, grad_v), all (B,H,S,D) (shader attention-backward)."""
+    return _core.attention_backward(device, grad_output, q, k, v, attn_weights, scale)
+
+
 for _name in ("linear_cpu", "relu", "gelu", "silu", "tanh_act", "layernorm", "conv1d", "conv2d",
               "hamming_search"):
     globals()[_name] = _outside(_name)

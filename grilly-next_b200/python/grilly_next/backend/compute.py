@@ -75,6 +75,19 @@ class VulkanCompute:
     def fused_qkv_projection(self, x, w_qkv, b_qkv=None, **kwargs):
         return _bridge.fused_qkv_projection(self._device, x, w_qkv, b_qkv, **kwargs)
 
+    # ---- the unfused attention pieces and the backward pass
+    def attention_scores(self, q, k, scale=0.0):
+        return _bridge.attention_scores(self._device, q, k, scale)
+
+    def activation_softmax(self, x):
+        return _bridge.softmax(self._device, x)
+
+    def attention_output(self, weights, v, causal=False):
+        return _bridge.attention_output(self._device, weights, v, causal)
+
+    def attention_backward(self, grad_output, q, k, v, attn_weights, scale=0.0):
+        return _bridge.attention_backward(self._device, grad_output, q, k, v, attn_weights, scale)
+
     # ---- methods of the reference class outside the attention / KV-cache path (compute.py:56-111 there):
     # present and callable; each raises RuntimeError saying that this build does not cover it
     def activation_relu(self, x, **kwargs):

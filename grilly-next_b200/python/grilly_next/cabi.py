@@ -29,6 +29,7 @@ SYMBOLS = [
     "grl_exchange_merge", "grl_exchange_reset", "grl_device_set_wait_limits", "grl_tensor_map_cache_stats",
     "grl_rope_table_prepare", "grl_group_unique_id", "grl_group_init_rank", "grl_group_info", "grl_group_allgather",
     "grl_linear", "grl_gemm_f32", "grl_mla_concat", "grl_mla_split", "grl_group_allreduce_max_f64", "grl_group_allgather_merge", "grl_group_sync", "grl_group_destroy",
+    "grl_attention_scores", "grl_softmax", "grl_attention_output", "grl_attention_backward",
 ]
 
 
@@ -133,6 +134,10 @@ def lib():
         _lib.grl_tensor_map_cache_stats.argtypes = [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         _lib.grl_rope_table_prepare.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_float]
         _lib.grl_linear.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]
+        _lib.grl_attention_scores.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_float]
+        _lib.grl_softmax.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+        _lib.grl_attention_output.argtypes = [C.c_void_p] * 4 + [C.c_int] * 5
+        _lib.grl_attention_backward.argtypes = [C.c_void_p] * 10 + [C.c_int] * 4 + [C.c_float]
         _lib.grl_gemm_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
         _lib.grl_mla_concat.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
         _lib.grl_mla_split.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]

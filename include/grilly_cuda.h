@@ -232,6 +232,26 @@ int grl_mla_split(grl_device* dev, const float* in, float* k, float* v, size_t r
 int grl_swizzle_kv(grl_device* dev, const float* in, float* out, int batch, int heads, int seq_len, int head_dim,
                    int wave, int reverse);
 
+/* ---- the unfused attention pieces (float32, device pointers), for code written against the separate shaders.
+ * grl_attention_scores: scores (B,H,S,S) = scale * Q K^T with Q, K laid out (B,S,H,D): replaces
+ *   shaders/attention-scores.glsl:33-65.  scale 0 means 1/sqrt(D).
+ * grl_softmax: row-wise softmax over the last axis of (rows, features): replaces shaders/activation-softmax.glsl:34-84
+ *   (its three passes in one launch; the maximum starts from -1e10 as the shader's does).
+ * grl_attention_output: out (B,S,H,D) = weights (B,H,S,S) . V (B,S,H,D): replaces shaders/attention-output.glsl:28-70
+ *   (causal == 0) and shaders/attention-output-gpt.glsl:29-72 (causal != 0: the sum runs over k <= q only).
+ * grl_attention_backward: gradients of softmax(scale Q K^T) V given grad_out and the forward's weights, every
+ *   tensor (B,H,S,D) and attn / scratch (B,H,S,S): replaces the three passes of shaders/attention-backward.glsl:73-195
+ *   (grad_V = A^T gO; grad_A = gO V^T into scratch; softmax backward; grad_Q = scale gS K; grad_K = scale gS^T Q)
+ *   and VulkanBackwardOps.attention_backward (src/grilly_next/backend/autograd_core.py:617-655). */
+int grl_attention_scores(grl_device* dev, const float* q, const float* k, float* scores, int batch, int seq_len, int heads,
+                         int head_dim, float scale);
+int grl_softmax(grl_device* dev, const float* in, float* out, size_t rows, int features);
+int grl_attention_output(grl_device* dev, const float* weights, const float* v, float* out, int batch, int seq_len,
+                         int heads, int head_dim, int causal);
+int grl_attention_backward(grl_device* dev, const float* grad_out, const float* q, const float* k, const float* v,
+                           const float* attn, float* grad_q, float* grad_k, float* grad_v, float* scratch, int batch,
+                           int heads, int seq_len, int head_dim, float scale);
+
 /* ---- eviction on the paged cache: replaces the host loops of kvCacheEvictH2O
  * (cpp/src/ops/kv_cache.cpp:595-634), the untrained-head branch of kvCacheEvictSpeculative (:905-929)
  * and kvCacheCompact (:941-992; signatures kv_cache.h:186-229).  The reference's TokenMeta array

@@ -6,6 +6,8 @@ import ctypes as C
 import numpy as np
 import pytest
 
+from gpu_helpers import quant_v_offsets
+
 pytestmark = pytest.mark.gpu
 
 
@@ -14,10 +16,13 @@ def _stored(dev, pc, b, T):
     H, D, P = pc.Hkv, pc.D, pc.P
     rows = pc.max_pages * pc.B * H * P
     kq = dev.download(pc.k_pages, (rows, D), np.uint8)
-    vq = dev.download(pc.v_pages, (rows, D // 2), np.uint8)
+    vq = dev.download(pc.v_pages, (rows // P, P * D // 2), np.uint8)       # one row per (page, kv head) block
     sc = dev.download(pc.scales, (rows, D // 32), np.uint16)
     idx = np.array([[(pc.table_host[b, t // P] * H + h) * P + t % P for h in range(H)] for t in range(T)])
-    return kq[idx], vq[idx], sc[idx]
+    off = quant_v_offsets(P, D)                                           # where the library keeps each value byte
+    vals = np.array([[vq[(pc.table_host[b, t // P] * H + h), off[t % P]] for h in range(H)] for t in range(T)])
+    assert len(np.unique(off)) == off.size and off.max() == off.size - 1  # a permutation of the block's bytes
+    return kq[idx], vals, sc[idx]
 
 
 @pytest.mark.parametrize("D,P,T", [(128, 64, 150), (64, 16, 37), (32, 64, 5)])
@@ -54,10 +59,18 @@ def test_quantised_append_gather_match_the_oracle_bit_for_bit(D, P, T):
         dev.close()
 
 
+def _dequantised(k, v):
+    from oracle import c_oracle
+    kd = np.stack([c_oracle.kv_dequantize(*c_oracle.kv_quantize(k[b], v[b]))[0] for b in range(k.shape[0])])
+    vd = np.stack([c_oracle.kv_dequantize(*c_oracle.kv_quantize(k[b], v[b]))[1] for b in range(k.shape[0])])
+    return kd, vd
+
+
 def test_decode_over_the_quantised_cache():
+    """The generic kernel dequantises with the reference's float32 arithmetic: 2e-4 of the oracle on the same cache."""
     from grilly_next import cabi
     from gpu_helpers import PagedCache
-    from oracle import attention_oracle as orc, c_oracle
+    from oracle import attention_oracle as orc
     dev = cabi.Device(0)
     try:
         rng = np.random.default_rng(12)
@@ -67,12 +80,48 @@ def test_decode_over_the_quantised_cache():
         q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
         pc = PagedCache(dev, B, Hkv, D, 832, dtype=cabi.FP8_INT4)
         pc.append(k, v)
-        kd = np.stack([c_oracle.kv_dequantize(*c_oracle.kv_quantize(k[b], v[b]))[0] for b in range(B)])
-        vd = np.stack([c_oracle.kv_dequantize(*c_oracle.kv_quantize(k[b], v[b]))[1] for b in range(B)])
+        kd, vd = _dequantised(k, v)
         want = orc.gqa_decode_attention(q, kd, vd, Hq, Hkv, D)
         for splits in (1, 5):
-            got = pc.decode(q, n_splits=splits)
+            got = pc.decode(q, n_splits=splits, force_simt=True)
             assert np.abs(got - want).max() <= 2e-4, splits
+    finally:
+        dev.close()
+
+
+@pytest.mark.parametrize("Hq,Hkv,lens", [(8, 2, (777, 64)), (8, 8, (130, 1)), (16, 2, (1000, 999)), (3, 1, (65, 447)),
+                                         (32, 8, (4352, 4100))])
+def test_tensor_core_decode_over_the_quantised_cache(Hq, Hkv, lens):
+    """head_dim 128 with 64-token pages runs on the tensor-core kernel (q and P rounded to float16, the cache
+    dequantised in registers): 1e-3 of the output's scale against the oracle on the same quantised cache, for unsplit,
+    split and kernel-chosen launches, ragged lengths and scattered pages; and it is the kernel that ran."""
+    from grilly_next import cabi
+    from gpu_helpers import PagedCache
+    from oracle import attention_oracle as orc
+    dev = cabi.Device(0)
+    try:
+        rng = np.random.default_rng(Hq * 100 + Hkv)
+        B, D, T = len(lens), 128, max(lens)
+        k = rng.standard_normal((B, T, Hkv, D), dtype=np.float32) * rng.uniform(0.2, 3.0, (B, T, Hkv, 1)).astype(np.float32)
+        v = rng.standard_normal((B, T, Hkv, D), dtype=np.float32)
+        q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
+        pc = PagedCache(dev, B, Hkv, D, T + 64, dtype=cabi.FP8_INT4, shuffle_pages=True, seed=5)
+        pc.append(k, v)
+        cut = np.array(lens, np.int32)                      # shorten the sequences: the pages keep their tails
+        dev.L.grl_memcpy_h2d(dev.h, pc.seq_lens, cut.ctypes.data_as(C.c_void_p), cut.nbytes)
+        dev.sync()
+        pc.lens[:] = cut
+        kd, vd = _dequantised(k, v)
+        want = np.concatenate([orc.gqa_decode_attention(q[b:b + 1], kd[b:b + 1, :lens[b]], vd[b:b + 1, :lens[b]], Hq, Hkv, D)
+                               for b in range(B)])
+        tol = 1e-3 * np.abs(want).max()
+        before = dev.L.grl_launch_count()
+        for splits in (1, 0, 3):
+            got = pc.decode(q, n_splits=splits)
+            assert np.abs(got - want).max() <= tol, (splits, np.abs(got - want).max(), tol)
+        assert dev.L.grl_launch_count() - before == 3        # one launch each: the kernel merges its own splits
+        simt = pc.decode(q, n_splits=2, force_simt=True)
+        assert np.abs(simt - want).max() <= tol
     finally:
         dev.close()
 
