@@ -1036,12 +1036,13 @@ def main():
             line["decode_q"] = {"metric": "decode_tokens_per_s", "value": c["B"] * c["steps"] / (qms * 1e-3), "unit": "tokens/s",
                                 "ms_per_step": qms / c["steps"],
                                 "workload": "cfg3 geometry over the quantised cache (FP8-E4M3 keys, INT4 values, float16 scale per 32: "
-                                            "200 B per cached (token, kv head) against 512 B in bf16), decode_split_kernel dequantising in registers",
+                                            "200 B per cached (token, kv head) against 512 B in bf16), the tensor-core decode kernel dequantising in registers",
                                 "gpu_launches": int(ql), "n_splits": qsplit, "parity": qpar,
                                 "roofline": {"bound": "hbm", "achieved": qgbs, "peak": pk["hbm"], "unit": "GB/s", "frac": qgbs / pk["hbm"],
-                                             "peak_source": pk["src"], "kernel": "decode_split_kernel<QuantKV>",
-                                             "note": "achieved = bytes of the quantised cache actually read per step / time; the kernel is "
-                                                     "bound by its dequantising arithmetic, not by HBM"}}
+                                             "peak_source": pk["src"], "kernel": "decode_mma_kernel<quantised>",
+                                             "note": "achieved = bytes of the quantised cache actually read per step / time (append + decode "
+                                                     "per step); the kernel is bound by its dequantising arithmetic and its dependent chains, "
+                                                     "not by HBM"}}
         if "evict" in legs and world == 1:
             sel_us, cmp_us, moved = bench_evict(dev, cabi)
             gbs = moved / (cmp_us * 1e-6) / 1e9

@@ -186,10 +186,12 @@ template <> __device__ __forceinline__ float load_as_float<__nv_bfloat16>(const 
 // are stored in pairs (2i, 2i+1), D bytes per pair, as D/4 words of [even token: bytes 2w, 2w+1 | odd token: bytes
 // 2w, 2w+1]: one 32-bit word then holds the same four elements of two consecutive tokens, which is the pairing a
 // tensor-core operand over the token axis needs, with no transpose.  The words of a pair are ordered [w % 8][w / 8]
-// so that one 16-byte load brings the same word of every scale group (32 elements = 8 words).
+// so that one load brings the same word of every scale group (32 elements = 8 words), and the eight pieces
+// [w % 8] are XOR-swizzled by the pair index so that lanes reading the same piece of neighbouring pairs use
+// different shared-memory banks.
 __host__ __device__ __forceinline__ size_t quant_v_off(int token_in_page, int j, int D) {
     const int w = j >> 1, G = D >> 5;
-    const int pw = (w & 7) * G + (w >> 3);
+    const int pw = ((w & 7) ^ ((token_in_page >> 1) & 7)) * G + (w >> 3);
     return (size_t)(token_in_page >> 1) * D + pw * 4 + (token_in_page & 1) * 2 + (j & 1);
 }
 

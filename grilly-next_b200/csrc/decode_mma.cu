@@ -12,8 +12,8 @@
 //
 // The same kernel, instantiated for the quantised cache (GRL_FP8_INT4: FP8-E4M3 keys, INT4 values, one float16 scale
 // per 32 key elements, cpp/src/ops/kv_cache.cpp:272-399 and :500-577), streams 12.5 KiB per (page, kv head) instead
-// of 32 and dequantises in registers: key bytes become f16 with one conversion per pair (every code the quantiser can
-// emit is an exact f16), the four scale groups of a head accumulate separately and are combined with 1/scale per
+// of 32 and dequantises in registers: key bytes become f16 by three integer operations per pair (every code is an
+// exact f16 once divided by 256), the four scale groups of a head accumulate separately and are combined with 1/scale per
 // token; value nibbles become f16 by one logic operation and one subtraction per pair (1024 + n or 64 + n in the
 // mantissa, minus the offset and the code's bias), with 1/scale folded into P.  The contraction indices of both
 // products are permuted so that every operand register is a plain 32-bit piece of what was loaded.
@@ -23,8 +23,8 @@
 #include "common.cuh"
 
 #ifndef GRL_DQ_CTAS
-#define GRL_DQ_CTAS 3
-#define GRL_DQ_NST 4
+#define GRL_DQ_CTAS 2
+#define GRL_DQ_NST 6
 #endif
 namespace grl {
 namespace dmma {
@@ -97,6 +97,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// The same test, but the thread may stay suspended in hardware for up to hint_ns while the phase is incomplete: a
+// waiter that is far ahead of what it waits for then takes no issue slots.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tm, int c0, int c1, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -122,24 +133,44 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(__cvta_generic_to_global(src)), "r"(bytes), "r"(bar) : "memory");
 }
-// f16 form of the same product, keeping only rows 0..7 of the accumulator (c0, c1); rows 8..15 are discarded.
-__device__ __forceinline__ void mma_f16_top(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    float x2, x3;   // rows 8..15: written by the instruction, never read
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%9,%9};"
-        : "+f"(d0), "+f"(d1), "=f"(x2), "=f"(x3)
+// f16 form of the same product.  Rows 8..15 of the accumulator (d[2], d[3]) multiply the zero half of A: they stay
+// whatever they were and are never read, but they stay in place -- the instruction wants four consecutive registers,
+// and carving two live ones out of the quad costs a move and a clear around every product.
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
+}
+// All sixteen rows of A live (the transposed value product: rows are head_dim elements, columns query heads).
+__device__ __forceinline__ void mma_f16_full(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// The first product of a chain: C is zero (no register needs clearing for it).
+__device__ __forceinline__ void mma_f16_first(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%9,%9,%9,%9};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
         : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.f));
 }
 __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
-// Two FP8-E4M3 codes (low byte -> low half) as f16x2.  The reference's decoder (kv_cache.cpp:540-552) and the
-// hardware conversion agree on every code except 0x7F / 0xFF, which the reference's encoder cannot produce.
-__device__ __forceinline__ uint32_t fp8x2_to_f16x2(uint32_t two_codes) {
+// FP8-E4M3 codes to f16x2 by integer operations (the conversion instruction runs on the slow special-function
+// pipe).  A code s eeee mmm becomes the f16 s 0eeee mmm0000000, which is the code's value (the reference's decoder,
+// kv_cache.cpp:540-552: 2^(e-7) (1 + m/8), or m 2^-9 for e = 0) divided by 256, denormals included; the factor is
+// folded into q.  Bytes (0, 2) of a word make one register, bytes (1, 3) the other: the byte permute puts each code
+// under a copy of its sign, the shift brings exponent and mantissa into place and the sign to bit 15, the mask
+// clears what the shift dragged along.
+__device__ __forceinline__ uint32_t prmt(uint32_t w, uint32_t selector) {   // a selector digit >= 8 replicates the byte's sign
     uint32_t r;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"((unsigned short)two_codes));
+    asm("prmt.b32 %0, %1, %1, %2;" : "=r"(r) : "r"(w), "r"(selector));
     return r;
 }
+__device__ __forceinline__ uint32_t e4m3_pair02_f16x2(uint32_t w) { return (prmt(w, 0xA280u) << 7) & 0xBF80BF80u; }
+__device__ __forceinline__ uint32_t e4m3_pair13_f16x2(uint32_t w) { return (prmt(w, 0xB391u) << 7) & 0xBF80BF80u; }
 // Value codes to f16x2 (low half: even token of the pair, high half: odd token): the nibble is placed in the mantissa of
 // 1024 (bits 0-3) or of 64 (bits 4-7), and the offset plus the code's bias of 8 is subtracted, which is exact in f16.
 __device__ __forceinline__ uint32_t nib_lo(uint32_t w) {
@@ -158,7 +189,7 @@ __device__ __forceinline__ float inv_scale_bits(uint32_t h) {
     const uint32_t e = (h >> 10) & 0x1Fu, m = h & 0x03FFu;
     const float sc = e == 0 ? (float)m * 5.9604644775390625e-08f
                             : __uint_as_float(((h & 0x8000u) << 16) | ((e + 112u) << 23) | (m << 13));
-    return sc > 0.f ? __fdiv_rn(1.0f, sc) : 1.0f;
+    return sc > 0.f ? __fdividef(1.0f, sc) : 1.0f;     // within an ulp of the reference's quotient
 }
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -176,12 +207,14 @@ struct Ctx {
     int32_t* status;
     long long limit;
 };
-__device__ __forceinline__ bool wait_bar(const Ctx& c, int bar, uint32_t parity) {
+// relaxed: the waiter is ahead of its consumers by the whole ring (the producer lane): it waits suspended instead of
+// competing for issue slots with the compute warp that shares its scheduler.
+__device__ __forceinline__ bool wait_bar(const Ctx& c, int bar, uint32_t parity, bool relaxed = false) {
     const uint32_t addr = c.bars + bar * 8;
     if (mbar_try_wait(addr, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-        if (mbar_try_wait(addr, parity)) return true;
+        if (relaxed ? mbar_try_wait_suspend(addr, parity, 20000u) : mbar_try_wait(addr, parity)) return true;
         if (*c.abort) return false;
         if (clock64() - t0 > c.limit) {
             *c.abort = 1;
@@ -243,7 +276,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             int issued = 0;
             for (int p = p_begin; p < p_end; ++p) {
                 const int i = p - p_begin, s = i % NST, it = i / NST;
-                if (it > 0 && !wait_bar(ctx, NST + s, (it - 1) & 1)) break;
+                if (it > 0 && !wait_bar(ctx, NST + s, (it - 1) & 1, QUANT)) break;
                 const int blk = bt[p] * a.Hkv + kvh, row0 = blk * P;
                 const uint32_t dst = base + (uint32_t)s * STAGE;
                 if constexpr (QUANT) {
@@ -269,21 +302,23 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     } else if constexpr (QUANT) {
         // ------------------------------------------------------------------ compute over the quantised cache
         // Element permutation of the two products.  QK^T: k-step (grp, w) of lane (g, t4) covers elements
-        // 32 grp + 8 t4 + 4 w + {0,1 | 2,3} = one 32-bit word of key bytes.  PV: output tile (grp, e), column n
-        // is element 32 grp + 4 n + e, and the k index pairs (2 t4, 2 t4 + 1 | + 8) are the token pairs
-        // (8 warp + t4 | + 4) of the value block (quant_v_off).
+        // 32 grp + 8 t4 + 4 w + {0,2 | 1,3} = one 32-bit word of key bytes.  PV runs transposed (rows elements,
+        // columns heads): row g | g + 8 of tile (grp, j) is element 32 grp + 4 g + 2 j | + 1, and the k index
+        // pairs (2 t4, 2 t4 + 1 | + 8) are the token pairs (8 warp + 2 t4 | + 1) of the value block (quant_v_off).
+        // Tokens: column n of score tile nt is token 2 n + nt of the warp's 16 (so that a half-warp's key loads hit
+        // all banks once), and a lane's four scores are the four consecutive tokens 4 t4 .. 4 t4 + 3.
         const int qh0 = kvh * a.group;
         uint32_t qf[8][2];
         {
-            const float sc = a.scale * kLog2e;
+            const float sc = a.scale * kLog2e * 256.f;      // the key registers hold code / 256
             const float* qrow = a.q + ((size_t)b * a.Hq + qh0 + g) * D;
             const bool live = g < a.group;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (live) v = *reinterpret_cast<const float4*>(qrow + 32 * (ks >> 1) + 8 * t4 + 4 * (ks & 1));
-                qf[ks][0] = pack_f16(v.x * sc, v.y * sc);
-                qf[ks][1] = pack_f16(v.z * sc, v.w * sc);
+                qf[ks][0] = pack_f16(v.x * sc, v.z * sc);      // with the key codes of bytes 0 and 2 of the word
+                qf[ks][1] = pack_f16(v.y * sc, v.w * sc);      // bytes 1 and 3
             }
         }
         float* inv_w = reinterpret_cast<float*>(smem + SMEM_BAR + 128) + warp * 64;   // [16 tokens][4 groups]
@@ -310,76 +345,82 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
-                        const float4 v = *reinterpret_cast<const float4*>(inv_w + (8 * nt + 2 * t4 + e) * 4);
+                        const float4 v = *reinterpret_cast<const float4*>(inv_w + (4 * t4 + 2 * e + nt) * 4);
                         inv[nt][e][0] = v.x; inv[nt][e][1] = v.y; inv[nt][e][2] = v.z; inv[nt][e][3] = v.w;
                     }
                 // ---- S = q K^T for 16 tokens, one accumulator per scale group, combined with 1/scale
                 float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
-                    const int row = 16 * warp + 8 * nt + g;
+                    const int row = 16 * warp + 2 * g + nt;     // column n of tile nt is token 2 n + nt of the slice
 #pragma unroll
                     for (int grp = 0; grp < 4; ++grp) {
                         const int chunk = (2 * grp + (t4 >> 1)) ^ (row & 7);
                         const uint2 kb = *reinterpret_cast<const uint2*>(kst + row * 128 + chunk * 16 + (t4 & 1) * 8);
-                        float c0 = 0.f, c1 = 0.f;
-                        mma_f16_top(c0, c1, qf[2 * grp][0], qf[2 * grp][1], fp8x2_to_f16x2(kb.x), fp8x2_to_f16x2(kb.x >> 16));
-                        mma_f16_top(c0, c1, qf[2 * grp + 1][0], qf[2 * grp + 1][1], fp8x2_to_f16x2(kb.y), fp8x2_to_f16x2(kb.y >> 16));
-                        sacc[nt][0] = fmaf(c0, inv[nt][0][grp], sacc[nt][0]);
-                        sacc[nt][1] = fmaf(c1, inv[nt][1][grp], sacc[nt][1]);
+                        float c[4];
+                        mma_f16_first(c, qf[2 * grp][0], qf[2 * grp][1], e4m3_pair02_f16x2(kb.x), e4m3_pair13_f16x2(kb.x));
+                        mma_f16(c, qf[2 * grp + 1][0], qf[2 * grp + 1][1], e4m3_pair02_f16x2(kb.y), e4m3_pair13_f16x2(kb.y));
+                        sacc[nt][0] = fmaf(c[0], inv[nt][0][grp], sacc[nt][0]);
+                        sacc[nt][1] = fmaf(c[1], inv[nt][1][grp], sacc[nt][1]);
                     }
                 }
-                // ---- online softmax for head row g
-                float mx = kEmpty;
-                bool valid[2][2];
-#pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        valid[nt][e] = tok0 + nt * 8 + 2 * t4 + e < len;
-                        if (valid[nt][e]) mx = fmaxf(mx, sacc[nt][e]);
-                    }
-                if (a.scores_out && g < a.group) {
-                    float* srow = a.scores_out + ((size_t)b * a.Hq + qh0 + g) * a.scores_ld + tok0 + 2 * t4;
+                // ---- online softmax for head row g.  Only the last tile of a sequence has tokens past its end: they
+                // get the "empty" score there, so the common path carries no per-token predicate
+                if (tok0 + 16 > len) {
 #pragma unroll
                     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                         for (int e = 0; e < 2; ++e)
-                            if (valid[nt][e]) srow[nt * 8 + e] = sacc[nt][e] * 0.6931471805599453f;
+                            if (tok0 + 4 * t4 + 2 * e + nt >= len) sacc[nt][e] = kEmpty;
                 }
+                if (a.scores_out && g < a.group) {
+                    float* srow = a.scores_out + ((size_t)b * a.Hq + qh0 + g) * a.scores_ld + tok0 + 4 * t4;
+#pragma unroll
+                    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e)
+                            if (tok0 + 4 * t4 + 2 * e + nt < len) srow[2 * e + nt] = sacc[nt][e] * 0.6931471805599453f;
+                }
+                float mx = fmaxf(fmaxf(sacc[0][0], sacc[0][1]), fmaxf(sacc[1][0], sacc[1][1]));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                 const float m_new = fmaxf(m_run, mx);
                 const float corr = ex2(m_run - m_new);
-                float pv[2][2], ps = 0.f;
+                float pv[2][2];
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        pv[nt][e] = valid[nt][e] ? ex2(sacc[nt][e] - m_new) : 0.f;
-                        ps += pv[nt][e];
-                    }
+                    for (int e = 0; e < 2; ++e) pv[nt][e] = ex2(sacc[nt][e] - m_new);    // 0 for an "empty" score
+                const float ps = (pv[0][0] + pv[0][1]) + (pv[1][0] + pv[1][1]);
                 l_run = l_run * corr + ps;
                 m_run = m_new;
                 if (__any_sync(0xffffffffu, corr != 1.f)) {
+                    // the accumulator columns of this lane are heads 2 t4 and 2 t4 + 1: their factors live in other lanes
+                    const float ca = __shfl_sync(0xffffffffu, corr, 8 * t4), cb = __shfl_sync(0xffffffffu, corr, 8 * t4 + 4);
 #pragma unroll
-                    for (int n = 0; n < 16; ++n) { o[n][0] *= corr; o[n][1] *= corr; }
+                    for (int n = 0; n < 8; ++n) { o[n][0] *= ca; o[n][2] *= ca; o[n][1] *= cb; o[n][3] *= cb; }
                 }
-                // ---- O += (P / scale) V: the two token pairs of this lane, 16 value bytes (all four groups) each
-                const uint4 va = *reinterpret_cast<const uint4*>(vst + (8 * warp + t4) * 128 + g * 16);
-                const uint4 vb = *reinterpret_cast<const uint4*>(vst + (8 * warp + 4 + t4) * 128 + g * 16);
+                // ---- O^T += V^T (P / scale)^T: rows are head_dim elements, columns heads, so all sixteen rows of the
+                // product work and P is used as it comes out of S (pairs of tokens per head).  The two token pairs of
+                // this lane, 16 value bytes (all four groups) each
+                // (this lane's tokens 4 t4 .. 4 t4 + 3 of the slice: pairs 2 t4 and 2 t4 + 1; the 16-byte pieces of a
+                // pair are stored XOR-swizzled by the pair index, which keeps the eight lanes of a quarter-warp on
+                // different banks)
+                const int pr = 8 * warp + 2 * t4;
+                const uint4 va = *reinterpret_cast<const uint4*>(vst + pr * 128 + ((g ^ (pr & 7)) << 4));
+                const uint4 vb = *reinterpret_cast<const uint4*>(vst + (pr + 1) * 128 + ((g ^ ((pr + 1) & 7)) << 4));
                 const uint32_t xa[4] = {va.x, va.y, va.z, va.w}, xb[4] = {vb.x, vb.y, vb.z, vb.w};
 #pragma unroll
                 for (int grp = 0; grp < 4; ++grp) {
-                    const uint32_t pa0 = pack_f16(pv[0][0] * inv[0][0][grp], pv[0][1] * inv[0][1][grp]);
-                    const uint32_t pa2 = pack_f16(pv[1][0] * inv[1][0][grp], pv[1][1] * inv[1][1][grp]);
+                    // B of the value product: k pairs are (even, odd) tokens of a pair = (tile 0, tile 1) of a column
+                    const uint32_t pa0 = pack_f16(pv[0][0] * inv[0][0][grp], pv[1][0] * inv[1][0][grp]);
+                    const uint32_t pa2 = pack_f16(pv[0][1] * inv[0][1][grp], pv[1][1] * inv[1][1][grp]);
                     const uint32_t x = xa[grp], y = xb[grp], xs = x >> 8, ys = y >> 8;
                     // nibble n of the even | odd token of a pair as f16x2: 1024 + n (low nibble) or 64 + n (high
                     // nibble) by one logic operation, then n - 8 exactly by one subtraction
-                    mma_f16_top(o[4 * grp][0], o[4 * grp][1], pa0, pa2, nib_lo(x), nib_lo(y));
-                    mma_f16_top(o[4 * grp + 1][0], o[4 * grp + 1][1], pa0, pa2, nib_hi(x), nib_hi(y));
-                    mma_f16_top(o[4 * grp + 2][0], o[4 * grp + 2][1], pa0, pa2, nib_lo(xs), nib_lo(ys));
-                    mma_f16_top(o[4 * grp + 3][0], o[4 * grp + 3][1], pa0, pa2, nib_hi(xs), nib_hi(ys));
+                    // rows g | g + 8 of tile (grp, j) are elements 32 grp + 4 g + 2 j | + 1
+                    mma_f16_full(o[2 * grp], nib_lo(x), nib_hi(x), nib_lo(y), nib_hi(y), pa0, pa2);
+                    mma_f16_full(o[2 * grp + 1], nib_lo(xs), nib_hi(xs), nib_lo(ys), nib_hi(ys), pa0, pa2);
                 }
             }
             __syncwarp();
@@ -505,12 +546,13 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     float* sm_l = sm_m + 32;
     if (warp < 4) {
         if constexpr (QUANT) {
+            // tile (grp, j): columns are heads 2 t4 | 2 t4 + 1, rows elements 32 grp + 4 g + 2 j | + 1
 #pragma unroll
-            for (int grp = 0; grp < 4; ++grp)
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-                    *reinterpret_cast<float4*>(&sm_o[(warp * 8 + g) * D + 32 * grp + 8 * t4 + 4 * c]) =
-                        make_float4(o[4 * grp][c], o[4 * grp + 1][c], o[4 * grp + 2][c], o[4 * grp + 3][c]);
+            for (int n = 0; n < 8; ++n) {
+                const int d0 = 32 * (n >> 1) + 4 * g + 2 * (n & 1);
+                *reinterpret_cast<float2*>(&sm_o[(warp * 8 + 2 * t4) * D + d0]) = make_float2(o[n][0], o[n][2]);
+                *reinterpret_cast<float2*>(&sm_o[(warp * 8 + 2 * t4 + 1) * D + d0]) = make_float2(o[n][1], o[n][3]);
+            }
         } else {
 #pragma unroll
             for (int n = 0; n < 16; ++n)

@@ -45,11 +45,11 @@ def flash_cabi(dev, Q, K, V, *, causal=False, seq_lens=None, mask=None, mask_kin
 def quant_v_offsets(P, D):
     """(P, D/2) byte offsets of the packed value bytes inside one (page, kv head) block of the quantised cache: token
     pairs, D bytes per pair, words [even token bytes 2w, 2w+1 | odd token bytes 2w, 2w+1] ordered [w % 8][w // 8]
-    (quant_v_off in csrc/common.cuh)."""
+    with the [w % 8] index XOR-swizzled by the pair index (quant_v_off in csrc/common.cuh)."""
     t = np.arange(P)[:, None]
     j = np.arange(D // 2)[None, :]
     w, G = j >> 1, D // 32
-    pw = (w & 7) * G + (w >> 3)
+    pw = ((w & 7) ^ ((t >> 1) & 7)) * G + (w >> 3)
     return (t >> 1) * D + pw * 4 + (t & 1) * 2 + (j & 1)
 
 
