@@ -1,4 +1,4 @@
-// GQA decode over the paged bf16 cache, head_dim 128, 64-token pages: the fast path.
+// GQA decode over the paged bf16 cache, head_dim 128 or 64, 64-token pages: the fast path.
 //
 // Replaces shaders/gqa-attention.glsl:34-130 like decode_splitkv.cu, for the geometry of the
 // benchmark configurations.  One CTA owns (split, kv head, sequence); a producer warp streams
@@ -22,33 +22,29 @@
 
 #include "common.cuh"
 
-#ifndef GRL_DQ_CTAS
-#define GRL_DQ_CTAS 2
-#define GRL_DQ_NST 6
-#endif
 namespace grl {
 namespace dmma {
 
 constexpr int P = 64;               // tokens per page
-constexpr int D = 128;              // head_dim
-constexpr int SLAB = P * D * 2;     // 16 KiB: one page of K (or V) for one kv head
-constexpr int STAGE = 2 * SLAB;     // K then V
+constexpr int D = 128;              // head_dim of the quantised instance (the bf16 instances carry theirs as HD)
 constexpr int kThreads = 160;       // 4 compute warps + 1 producer warp
 // The shared-memory ring of the two instances.  After the ring: 128 bytes of barriers and flags, 1 KiB of per-warp
 // scratch (1/scale of a warp's 16 tokens x 4 groups), 1 KiB of slack for the 1024-byte alignment of the ring.
-template <bool QUANT> struct Ring {
-    static constexpr int NST = 3;            // ring stages
-    static constexpr int STAGE = dmma::STAGE;
+template <bool QUANT, int HD> struct Ring {
+    static constexpr int SLAB = P * HD * 2;             // one page of K (or V) for one kv head: 16 KiB at head_dim 128
+    static constexpr int STAGE = 2 * SLAB;              // K then V
+    static constexpr int NST = 3 * 128 / HD;            // ring stages: 96 KiB in flight per CTA
 };
 constexpr int QK_BYTES = P * D;          // 8 KiB of key bytes per (page, kv head)
 constexpr int QV_BYTES = P * D / 2;      // 4 KiB of packed value nibbles
 constexpr int QS_BYTES = P * (D / 32) * 2;   // 512 B of float16 scales
-template <> struct Ring<true> {
-    static constexpr int NST = GRL_DQ_NST;
+template <> struct Ring<true, 128> {
+    static constexpr int SLAB = 0;
+    static constexpr int NST = 6;
     static constexpr int STAGE = 13 * 1024;  // keys at 0, values at 8 KiB, scales at 12 KiB
 };
-template <bool QUANT> struct Smem {
-    static constexpr int BAR = Ring<QUANT>::NST * Ring<QUANT>::STAGE;
+template <bool QUANT, int HD> struct Smem {
+    static constexpr int BAR = Ring<QUANT, HD>::NST * Ring<QUANT, HD>::STAGE;
     static constexpr int TOTAL = BAR + 128 + 1024 + 1024;
 };
 constexpr float kLog2e = 1.4426950408889634f;
@@ -233,10 +229,13 @@ __device__ __forceinline__ uint32_t slab_off(int row, int d) {
     return (uint32_t)((d >> 6) * (P * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4));
 }
 
-template <bool QUANT>
-__global__ void __launch_bounds__(kThreads, QUANT ? GRL_DQ_CTAS : 2)
+template <bool QUANT, int HD>
+__global__ void __launch_bounds__(kThreads, 2)
 decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const Args a) {
-    constexpr int NST = Ring<QUANT>::NST, STAGE = Ring<QUANT>::STAGE, SMEM_BAR = Smem<QUANT>::BAR;
+    static_assert(HD == 128 || (HD == 64 && !QUANT), "head_dim 128, or 64 over the bf16 cache");
+    constexpr int D = HD;
+    constexpr int NST = Ring<QUANT, HD>::NST, STAGE = Ring<QUANT, HD>::STAGE, SMEM_BAR = Smem<QUANT, HD>::BAR;
+    constexpr int SLAB = Ring<QUANT, HD>::SLAB;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -263,10 +262,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     __syncthreads();
 
     const int g = lane >> 2, t4 = lane & 3;      // mma row / column-pair index of this lane
-    float o[16][4];
+    float o[D / 8][4];
     float m_run = kEmpty, l_run = 0.f;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
     if (warp == 4) {
         // ------------------------------------------------------------------ producer
@@ -286,10 +285,11 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                     bulk_load(dst + QK_BYTES + QV_BYTES, a.scales + (size_t)blk * (QS_BYTES / 2), QS_BYTES, full(s));
                 } else {
                     mbar_expect_tx(full(s), STAGE);
-                    tma_load_2d(dst, &tmK, 0, row0, full(s));
-                    tma_load_2d(dst + SLAB / 2, &tmK, 64, row0, full(s));
-                    tma_load_2d(dst + SLAB, &tmV, 0, row0, full(s));
-                    tma_load_2d(dst + SLAB + SLAB / 2, &tmV, 64, row0, full(s));
+#pragma unroll
+                    for (int c0 = 0; c0 < D; c0 += 64) {        // 64-column boxes (128 bytes: the swizzle span)
+                        tma_load_2d(dst + (c0 / 64) * (P * 128), &tmK, c0, row0, full(s));
+                        tma_load_2d(dst + SLAB + (c0 / 64) * (P * 128), &tmV, c0, row0, full(s));
+                    }
                 }
                 issued = i + 1;
             }
@@ -432,13 +432,13 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
         // ------------------------------------------------------------------ compute: tokens [16*warp, 16*warp+16) of every page
         const int qh0 = kvh * a.group;
         // A fragments of q (rows = heads of the group, zero beyond), pre-scaled into the exp2 domain, hi + lo bf16
-        uint32_t qhi[8][2], qlo[8][2];
+        uint32_t qhi[D / 16][2], qlo[D / 16][2];
         {
             const float sc = a.scale * kLog2e;
             const float* qrow = a.q + ((size_t)b * a.Hq + qh0 + g) * D;
             const bool live = g < a.group;
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
+            for (int ks = 0; ks < D / 16; ++ks) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int d = 16 * ks + 8 * h + 2 * t4;
@@ -461,8 +461,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 if (tok0 + 16 > len) {
                     // rows past the end of the sequence hold whatever the page held: zero them in V
                     // (their probabilities are zero, but 0 * NaN is not)
-                    for (int c = lane; c < 16 * 16; c += 32) {
-                        const int r = 16 * warp + (c >> 4), ch = c & 15;
+                    for (int c = lane; c < 16 * (D / 8); c += 32) {
+                        const int r = 16 * warp + c / (D / 8), ch = c % (D / 8);
                         if (p * P + r >= len)
                             *reinterpret_cast<uint4*>(smem + s * STAGE + SLAB + slab_off(r, ch * 8)) = make_uint4(0, 0, 0, 0);
                     }
@@ -474,7 +474,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 {
                     const int row = 16 * warp + (lane & 7) + ((mat >> 1) << 3);
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
+                    for (int ks = 0; ks < D / 16; ++ks) {
                         uint32_t kb[4];
                         ldmatrix_x4(kbase + slab_off(row, 16 * ks + ((mat & 1) << 3)), kb);
                         mma_16816(sacc[0], qhi[ks][0], qhi[ks][1], kb[0], kb[1]);
@@ -517,14 +517,14 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
                 m_run = m_new;
                 if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
-                    for (int n = 0; n < 16; ++n) { o[n][0] *= corr; o[n][1] *= corr; }
+                    for (int n = 0; n < D / 8; ++n) { o[n][0] *= corr; o[n][1] *= corr; }
                 }
                 const uint32_t pa0 = pack_bf16(pv[0][0], pv[0][1]), pa2 = pack_bf16(pv[1][0], pv[1][1]);
-                // ---- O += P V: 16 tokens x 128 dims, two 8-wide d n-tiles per ldmatrix
+                // ---- O += P V: 16 tokens x head_dim, two 8-wide d n-tiles per ldmatrix
                 {
                     const int row = 16 * warp + (lane & 7) + ((mat & 1) << 3);
 #pragma unroll
-                    for (int dn = 0; dn < 8; ++dn) {
+                    for (int dn = 0; dn < D / 16; ++dn) {
                         uint32_t vb[4];
                         ldmatrix_x4_trans(vbase + slab_off(row, 16 * dn + ((mat >> 1) << 3)), vb);
                         mma_16816(o[2 * dn], pa0, pa2, vb[0], vb[1]);
@@ -555,7 +555,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             }
         } else {
 #pragma unroll
-            for (int n = 0; n < 16; ++n)
+            for (int n = 0; n < D / 8; ++n)
                 *reinterpret_cast<float2*>(&sm_o[(warp * 8 + g) * D + n * 8 + 2 * t4]) = make_float2(o[n][0], o[n][1]);
         }
         if (t4 == 0) { sm_m[warp * 8 + g] = m_run; sm_l[warp * 8 + g] = l_run; }
@@ -763,13 +763,13 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
     }
 }
 
-// The K (or V) pool as a 2-D bf16 tensor (rows = pages * Hkv * page tokens, 128 columns); box = 64 columns x
+// The K (or V) pool as a 2-D bf16 tensor (rows = pages * Hkv * page tokens, head_dim columns); box = 64 columns x
 // one page of one kv head.
-static int make_pool_map(grl_device* dev, CUtensorMap* tm, const void* pool, uint64_t rows) {
+static int make_pool_map(grl_device* dev, CUtensorMap* tm, const void* pool, uint64_t rows, int head_dim) {
     TmapKey k{};
     k.ptr = pool; k.rank = 2; k.swizzle_128b = 1;
-    k.dims[0] = D; k.dims[1] = rows;
-    k.strides[0] = (uint64_t)D * 2;
+    k.dims[0] = (uint64_t)head_dim; k.dims[1] = rows;
+    k.strides[0] = (uint64_t)head_dim * 2;
     k.box[0] = 64; k.box[1] = P;
     return get_tensor_map(dev, k, tm);
 }
@@ -779,22 +779,23 @@ static int make_pool_map(grl_device* dev, CUtensorMap* tm, const void* pool, uin
 bool decode_mma_supported(const grl_decode_params* p) {
     const grl_kv_layout& kv = p->kv;
     const int group = p->num_q_heads / kv.num_kv_heads;
-    const bool geometry = kv.head_dim == dmma::D && kv.page_tokens == dmma::P && group >= 1 && group <= 8 &&
+    const bool geometry = kv.page_tokens == dmma::P && group >= 1 && group <= 8 &&
                           ((uintptr_t)kv.k_pages % 16 == 0) && ((uintptr_t)kv.v_pages % 16 == 0);
     if (kv.cache_dtype == GRL_FP8_INT4)
-        return geometry && kv.scales && ((uintptr_t)kv.scales % 16 == 0) && ((uintptr_t)p->q % 16 == 0);
-    return kv.cache_dtype == GRL_BF16 && geometry && ((uintptr_t)p->q % 8 == 0);
+        return geometry && kv.head_dim == 128 && kv.scales && ((uintptr_t)kv.scales % 16 == 0) && ((uintptr_t)p->q % 16 == 0);
+    return kv.cache_dtype == GRL_BF16 && geometry && (kv.head_dim == 128 || kv.head_dim == 64) && ((uintptr_t)p->q % 8 == 0);
 }
 
-template <bool QUANT>
+template <bool QUANT, int HD>
 static int launch_instance(grl_device* dev, const CUtensorMap& tk, const CUtensorMap& tv, const dmma::Args& a, dim3 grid) {
     using namespace dmma;
     static bool attr_set[64] = {};
     if (!attr_set[dev->ordinal & 63]) {      // a function attribute belongs to the device that was current
-        GRL_CUDA(cudaFuncSetAttribute(decode_mma_kernel<QUANT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<QUANT>::TOTAL));
+        GRL_CUDA(cudaFuncSetAttribute(decode_mma_kernel<QUANT, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Smem<QUANT, HD>::TOTAL));
         attr_set[dev->ordinal & 63] = true;
     }
-    decode_mma_kernel<QUANT><<<grid, kThreads, Smem<QUANT>::TOTAL, dev->stream>>>(tk, tv, a);
+    decode_mma_kernel<QUANT, HD><<<grid, kThreads, Smem<QUANT, HD>::TOTAL, dev->stream>>>(tk, tv, a);
     GRL_LAUNCHED(QUANT ? "decode_mma_kernel<quantised>" : "decode_mma_kernel");
     return GRL_OK;
 }
@@ -818,8 +819,8 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
         rc = get_tensor_map(dev, k, &tk);
         tv = tk;
     } else {
-        rc = make_pool_map(dev, &tk, kv.k_pages, rows);
-        if (!rc) rc = make_pool_map(dev, &tv, kv.v_pages, rows);
+        rc = make_pool_map(dev, &tk, kv.k_pages, rows, kv.head_dim);
+        if (!rc) rc = make_pool_map(dev, &tv, kv.v_pages, rows, kv.head_dim);
     }
     if (rc) return rc;
     Args a{};
@@ -847,7 +848,8 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
     }
     dev->status_dirty = true;
     dim3 grid(n_splits, kv.num_kv_heads, kv.batch);
-    return quant ? launch_instance<true>(dev, tk, tv, a, grid) : launch_instance<false>(dev, tk, tv, a, grid);
+    if (quant) return launch_instance<true, 128>(dev, tk, tv, a, grid);
+    return kv.head_dim == 64 ? launch_instance<false, 64>(dev, tk, tv, a, grid) : launch_instance<false, 128>(dev, tk, tv, a, grid);
 }
 
 }  // namespace grl

@@ -173,8 +173,9 @@ __device__ __forceinline__ float fp8_decode(uint8_t c) {                    // k
     return s ? -v : v;
 }
 
-// grid (ceil(n_new*Hkv*G / warps per CTA), B), G = D/32 groups per head.
-__global__ void __launch_bounds__(256) kv_append_quant_kernel(AppendArgs a) {
+// grid (ceil(n_new*Hkv*G / warps per CTA), B), G = D/32 groups per head.  With one CTA per sequence (a decode step) the
+// kernel also rotates the step's queries (q_in != NULL) and advances the length (update_lens): one launch per step.
+__global__ void __launch_bounds__(1024) kv_append_quant_kernel(AppendArgs a) {
     const int b = blockIdx.y, lane = threadIdx.x & 31;
     const int G = a.D / 32;
     const int len0 = a.seq_lens[b];
@@ -226,6 +227,24 @@ __global__ void __launch_bounds__(256) kv_append_quant_kernel(AppendArgs a) {
             vp[((size_t)page * a.Hkv + h) * a.P * half + quant_v_off(slot_pos % a.P, d >> 1, a.D)] =
                 (uint8_t)((q & 0x0F) | ((q_hi & 0x0F) << 4));
         if (lane == 0) a.scales[row * G + g] = scale_to_half_bits(kscale);   // the value scale is dropped (:393-398)
+    }
+    if (a.q_in) {           // the queries of the new positions, rotated like the keys (float32 in, float32 out)
+        const int qitems = a.n_new * a.Hq * half;
+        for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < qitems; idx += gridDim.x * blockDim.x) {
+            const int j = idx % half, h = (idx / half) % a.Hq, i = idx / (half * a.Hq);
+            int d0 = 2 * j, d1 = 2 * j + 1;
+            if (a.rope_mode == GRL_ROPE_HALF) { d0 = j; d1 = j + half; }
+            float c = 1.f, s = 0.f;
+            if (a.rope_mode != GRL_ROPE_NONE) rope_sincos(a.pos_base + pos_off + len0 + i, a.freq.inv_freq[j], &c, &s);
+            const size_t qo = (((size_t)b * a.n_new + i) * a.Hq + h) * a.D;
+            const float q0 = a.q_in[qo + d0], q1 = a.q_in[qo + d1];
+            a.q_out[qo + d0] = q0 * c - q1 * s;
+            a.q_out[qo + d1] = q0 * s + q1 * c;
+        }
+    }
+    if (a.update_lens) {    // gridDim.x == 1 here: every warp has read len0
+        __syncthreads();
+        if (threadIdx.x == 0) a.seq_lens[b] = len0 + a.n_new;
     }
 }
 
@@ -335,10 +354,19 @@ int grl_kv_append(grl_device* dev, const grl_append_params* p) {
     if (kv.cache_dtype == GRL_FP8_INT4) {
         // K and V: one warp per (token, kv head, group of 32); the queries, if any, through the plain kernel
         const long long warps = (long long)p->n_new * kv.num_kv_heads * (kv.head_dim / 32);
+        if (warps <= 32) {      // a decode step: one wide CTA per sequence does keys, values, queries and the length
+            a.update_lens = p->update_lens ? 1 : 0;
+            kv_append_quant_kernel<<<dim3(1, kv.batch), 1024, 0, dev->stream>>>(a);
+            GRL_LAUNCHED("kv_append_quant_kernel");
+            return GRL_OK;
+        }
         int ctas = (int)((warps + 7) / 8);
         if (ctas > 1024) ctas = 1024;
+        a.q_in = nullptr;       // bulk append: the queries go through the plain kernel below
+        a.update_lens = 0;
         kv_append_quant_kernel<<<dim3(ctas, kv.batch), 256, 0, dev->stream>>>(a);
         GRL_LAUNCHED("kv_append_quant_kernel");
+        a.q_in = p->q_in;
         if (p->q_in) {
             a.skip_kv = 1;
             a.update_lens = 0;
