@@ -1,4 +1,4 @@
-// GQA decode over the paged bf16 cache, head_dim 128 or 64, 64-token pages: the fast path.
+// GQA decode over the paged bf16 cache, head_dim 128 or 64, pages of 64, 32 or 16 tokens: the fast path.
 //
 // Replaces shaders/gqa-attention.glsl:34-130 like decode_splitkv.cu, for the geometry of the
 // benchmark configurations.  One CTA owns (split, kv head, sequence); a producer warp streams
@@ -25,17 +25,17 @@
 namespace grl {
 namespace dmma {
 
-constexpr int P = 64;               // tokens per page
+constexpr int P = 64;               // tokens per ring stage: one 64-token page, or two / four smaller ones side by side
 constexpr int D = 128;              // head_dim of the quantised instance (the bf16 instances carry theirs as HD)
 constexpr int kThreads = 160;       // 4 compute warps + 1 producer warp
 // The shared-memory ring of the two instances.  After the ring: 128 bytes of barriers and flags, 1 KiB of per-warp
 // scratch (1/scale of a warp's 16 tokens x 4 groups), 1 KiB of slack for the 1024-byte alignment of the ring.
 template <bool QUANT, int HD> struct Ring {
-    static constexpr int SLAB = P * HD * 2;             // one page of K (or V) for one kv head: 16 KiB at head_dim 128
+    static constexpr int SLAB = P * HD * 2;             // 64 tokens of K (or V) for one kv head: 16 KiB at head_dim 128
     static constexpr int STAGE = 2 * SLAB;              // K then V
     static constexpr int NST = 3 * 128 / HD;            // ring stages: 96 KiB in flight per CTA
 };
-constexpr int QK_BYTES = P * D;          // 8 KiB of key bytes per (page, kv head)
+constexpr int QK_BYTES = P * D;          // 8 KiB of key bytes per 64 tokens of a kv head
 constexpr int QV_BYTES = P * D / 2;      // 4 KiB of packed value nibbles
 constexpr int QS_BYTES = P * (D / 32) * 2;   // 512 B of float16 scales
 template <> struct Ring<true, 128> {
@@ -60,6 +60,7 @@ struct Args {
     float* out;
     int32_t* status;
     int B, Hq, Hkv, max_pages, n_splits, group;
+    int page, ppt;          // tokens per page (64, 32 or 16) and pages per 64-token stage
     float scale;
     int direct;
     // fused merge: the last CTA of a (sequence, kv head) to arrive merges the head's splits
@@ -243,8 +244,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int len = max(0, min(a.seq_lens[b], a.max_pages * P));   // never past the block table
-    const int n_pages = (len + P - 1) / P;
+    const int len = max(0, min(a.seq_lens[b], a.max_pages * a.page));   // never past the block table
+    const int n_pages = (len + P - 1) / P;        // 64-token stages ("pages" below)
     const int pps = (n_pages + a.n_splits - 1) / a.n_splits;
     const int p_begin = min(n_pages, split * pps), p_end = min(n_pages, (split + 1) * pps);
     const int32_t* bt = a.block_table + (size_t)b * a.max_pages;
@@ -276,19 +277,29 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             for (int p = p_begin; p < p_end; ++p) {
                 const int i = p - p_begin, s = i % NST, it = i / NST;
                 if (it > 0 && !wait_bar(ctx, NST + s, (it - 1) & 1, QUANT)) break;
-                const int blk = bt[p] * a.Hkv + kvh, row0 = blk * P;
+                // the pages of this stage that hold tokens of the sequence (all of them but in the last stage); rows of
+                // the stage that no copy fills keep what they held: their tokens are past the length and masked
+                const int np = min(a.ppt, (len - p * P + a.page - 1) / a.page);
                 const uint32_t dst = base + (uint32_t)s * STAGE;
                 if constexpr (QUANT) {
-                    mbar_expect_tx(full(s), QK_BYTES + QV_BYTES + QS_BYTES);
-                    tma_load_2d(dst, &tmK, 0, row0, full(s));          // 64 rows of 128 key bytes, 128-byte swizzle
-                    bulk_load(dst + QK_BYTES, a.v_q + (size_t)blk * QV_BYTES, QV_BYTES, full(s));
-                    bulk_load(dst + QK_BYTES + QV_BYTES, a.scales + (size_t)blk * (QS_BYTES / 2), QS_BYTES, full(s));
+                    mbar_expect_tx(full(s), (uint32_t)np * a.page * (D + D / 2 + D / 16));
+                    for (int j = 0; j < np; ++j) {
+                        const int blk = bt[p * a.ppt + j] * a.Hkv + kvh;
+                        // rows of 128 key bytes under the 128-byte swizzle; a page's value and scale blocks are contiguous
+                        tma_load_2d(dst + j * a.page * 128, &tmK, 0, blk * a.page, full(s));
+                        bulk_load(dst + QK_BYTES + j * a.page * (D / 2), a.v_q + (size_t)blk * a.page * (D / 2), a.page * (D / 2), full(s));
+                        bulk_load(dst + QK_BYTES + QV_BYTES + j * a.page * (D / 16), a.scales + (size_t)blk * a.page * (D / 32),
+                                  a.page * (D / 16), full(s));
+                    }
                 } else {
-                    mbar_expect_tx(full(s), STAGE);
+                    mbar_expect_tx(full(s), (uint32_t)np * a.page * D * 4);
+                    for (int j = 0; j < np; ++j) {
+                        const int row0 = (bt[p * a.ppt + j] * a.Hkv + kvh) * a.page;
 #pragma unroll
-                    for (int c0 = 0; c0 < D; c0 += 64) {        // 64-column boxes (128 bytes: the swizzle span)
-                        tma_load_2d(dst + (c0 / 64) * (P * 128), &tmK, c0, row0, full(s));
-                        tma_load_2d(dst + SLAB + (c0 / 64) * (P * 128), &tmV, c0, row0, full(s));
+                        for (int c0 = 0; c0 < D; c0 += 64) {        // 64-column boxes (128 bytes: the swizzle span)
+                            tma_load_2d(dst + (c0 / 64) * (P * 128) + j * a.page * 128, &tmK, c0, row0, full(s));
+                            tma_load_2d(dst + SLAB + (c0 / 64) * (P * 128) + j * a.page * 128, &tmV, c0, row0, full(s));
+                        }
                     }
                 }
                 issued = i + 1;
@@ -765,12 +776,12 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
 
 // The K (or V) pool as a 2-D bf16 tensor (rows = pages * Hkv * page tokens, head_dim columns); box = 64 columns x
 // one page of one kv head.
-static int make_pool_map(grl_device* dev, CUtensorMap* tm, const void* pool, uint64_t rows, int head_dim) {
+static int make_pool_map(grl_device* dev, CUtensorMap* tm, const void* pool, uint64_t rows, int head_dim, int page_tokens) {
     TmapKey k{};
     k.ptr = pool; k.rank = 2; k.swizzle_128b = 1;
     k.dims[0] = (uint64_t)head_dim; k.dims[1] = rows;
     k.strides[0] = (uint64_t)head_dim * 2;
-    k.box[0] = 64; k.box[1] = P;
+    k.box[0] = 64; k.box[1] = (uint32_t)page_tokens;
     return get_tensor_map(dev, k, tm);
 }
 
@@ -779,7 +790,7 @@ static int make_pool_map(grl_device* dev, CUtensorMap* tm, const void* pool, uin
 bool decode_mma_supported(const grl_decode_params* p) {
     const grl_kv_layout& kv = p->kv;
     const int group = p->num_q_heads / kv.num_kv_heads;
-    const bool geometry = kv.page_tokens == dmma::P && group >= 1 && group <= 8 &&
+    const bool geometry = (kv.page_tokens == 64 || kv.page_tokens == 32 || kv.page_tokens == 16) && group >= 1 && group <= 8 &&
                           ((uintptr_t)kv.k_pages % 16 == 0) && ((uintptr_t)kv.v_pages % 16 == 0);
     if (kv.cache_dtype == GRL_FP8_INT4)
         return geometry && kv.head_dim == 128 && kv.scales && ((uintptr_t)kv.scales % 16 == 0) && ((uintptr_t)p->q % 16 == 0);
@@ -804,7 +815,7 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
     using namespace dmma;
     const grl_kv_layout& kv = p->kv;
     const uint64_t pages = kv.num_pages > 0 ? (uint64_t)kv.num_pages : (uint64_t)kv.batch * kv.max_pages;
-    const uint64_t rows = pages * kv.num_kv_heads * P;
+    const uint64_t rows = pages * kv.num_kv_heads * kv.page_tokens;
     const bool quant = kv.cache_dtype == GRL_FP8_INT4;
     CUtensorMap tk, tv;
     int rc;
@@ -815,12 +826,12 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
         k.ptr = kv.k_pages; k.rank = 2; k.swizzle_128b = 1; k.bytes = 1;
         k.dims[0] = D; k.dims[1] = rows;
         k.strides[0] = (uint64_t)D;
-        k.box[0] = D; k.box[1] = P;
+        k.box[0] = D; k.box[1] = (uint32_t)kv.page_tokens;
         rc = get_tensor_map(dev, k, &tk);
         tv = tk;
     } else {
-        rc = make_pool_map(dev, &tk, kv.k_pages, rows, kv.head_dim);
-        if (!rc) rc = make_pool_map(dev, &tv, kv.v_pages, rows, kv.head_dim);
+        rc = make_pool_map(dev, &tk, kv.k_pages, rows, kv.head_dim, kv.page_tokens);
+        if (!rc) rc = make_pool_map(dev, &tv, kv.v_pages, rows, kv.head_dim, kv.page_tokens);
     }
     if (rc) return rc;
     Args a{};
@@ -828,6 +839,7 @@ int decode_mma_launch(grl_device* dev, const grl_decode_params* p, int n_splits,
     a.block_table = kv.block_table; a.seq_lens = kv.seq_lens; a.q = p->q;
     a.part = (float*)p->workspace; a.out = p->out; a.status = dev->d_status;
     a.B = kv.batch; a.Hq = p->num_q_heads; a.Hkv = kv.num_kv_heads; a.max_pages = kv.max_pages;
+    a.page = kv.page_tokens; a.ppt = P / kv.page_tokens;
     a.n_splits = n_splits; a.group = p->num_q_heads / kv.num_kv_heads;
     a.scale = scale; a.direct = direct ? 1 : 0;
     a.fuse = fuse ? 1 : 0; a.counters = dev->d_counters; a.partial_out = p->partial_out;

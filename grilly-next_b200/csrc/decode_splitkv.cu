@@ -340,7 +340,10 @@ int grl_decode_pick_splits(grl_device* dev, const grl_decode_params* p, int* n_s
     }
     const grl_kv_layout& kv = p->kv;
     const int max_len = p->max_seq_len > 0 ? p->max_seq_len : kv.max_pages * kv.page_tokens;
-    const int pages = (max_len + kv.page_tokens - 1) / kv.page_tokens;
+    const bool generic = !decode_mma_supported(p) || p->force_simt;
+    // the tensor-core kernel walks 64-token stages whatever the page size
+    const int unit = generic ? kv.page_tokens : 64;
+    const int pages = (max_len + unit - 1) / unit;
     const int base_ctas = kv.batch * kv.num_kv_heads;
     // At most one CTA per SM: that already keeps HBM saturated (three 32 KB stages in flight each), and one
     // CTA more than there are SMs makes a pair share an SM and finish last.  Measured on B200, B1 x 8 KV
@@ -349,7 +352,6 @@ int grl_decode_pick_splits(grl_device* dev, const grl_decode_params* p, int* n_s
     const int sms = dev->prop.multiProcessorCount;
     // The generic kernel (128-thread CTAs, no shared-memory ring) wants several CTAs per SM to hide its loads and,
     // over a quantised cache, its dequantising arithmetic: aim at eight per SM.
-    const bool generic = !decode_mma_supported(p) || p->force_simt;
     int s = generic ? (8 * sms + base_ctas - 1) / base_ctas : sms / base_ctas;
     if (s > pages / 2) s = pages / 2;          // every split keeps at least 2 pages
     if (s > 256) s = 256;

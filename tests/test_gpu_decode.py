@@ -269,8 +269,9 @@ def test_partial_outputs_merge_across_shards(dev):
     assert np.abs(got - want).max() <= TOL_TC
 
 
-@pytest.mark.parametrize("D,Hq,Hkv", [(128, 16, 4), (64, 12, 4), (64, 8, 1)])
-def test_tensor_core_and_simt_decode_agree(dev, D, Hq, Hkv):
+@pytest.mark.parametrize("D,Hq,Hkv,P", [(128, 16, 4, 64), (64, 12, 4, 64), (64, 8, 1, 64), (128, 16, 4, 16), (128, 8, 2, 32),
+                                        (64, 12, 4, 16)])
+def test_tensor_core_and_simt_decode_agree(dev, D, Hq, Hkv, P):
     """Same bf16 paged cache through both decode kernels: ragged lengths, shuffled pages, a partial
     last page, every split count; the SIMT kernel is the tight one, the tensor-core kernel must stay
     within the rounding of its bf16 probabilities."""
@@ -279,7 +280,7 @@ def test_tensor_core_and_simt_decode_agree(dev, D, Hq, Hkv):
     rng = np.random.default_rng(21)
     B = 3
     lens = [1000, 65, 517]
-    pc = PagedCache(dev, B, Hkv, D, 1024, dtype=cabi.BF16, shuffle_pages=True, seed=9)
+    pc = PagedCache(dev, B, Hkv, D, 1024, page_tokens=P, dtype=cabi.BF16, shuffle_pages=True, seed=9)
     k = rng.standard_normal((B, 1000, Hkv, D), dtype=np.float32)
     v = rng.standard_normal((B, 1000, Hkv, D), dtype=np.float32)
     pc.append(k, v)

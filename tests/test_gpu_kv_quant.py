@@ -89,10 +89,11 @@ def test_decode_over_the_quantised_cache():
         dev.close()
 
 
-@pytest.mark.parametrize("Hq,Hkv,lens", [(8, 2, (777, 64)), (8, 8, (130, 1)), (16, 2, (1000, 999)), (3, 1, (65, 447)),
-                                         (32, 8, (4352, 4100))])
-def test_tensor_core_decode_over_the_quantised_cache(Hq, Hkv, lens):
-    """head_dim 128 with 64-token pages runs on the tensor-core kernel (q and P rounded to float16, the cache
+@pytest.mark.parametrize("Hq,Hkv,lens,P", [(8, 2, (777, 64), 64), (8, 8, (130, 1), 64), (16, 2, (1000, 999), 64),
+                                           (3, 1, (65, 447), 64), (32, 8, (4352, 4100), 64), (8, 2, (777, 49), 16),
+                                           (16, 4, (1000, 33), 32)])
+def test_tensor_core_decode_over_the_quantised_cache(Hq, Hkv, lens, P):
+    """head_dim 128 with pages of 64, 32 or 16 tokens runs on the tensor-core kernel (q and P rounded to float16, the cache
     dequantised in registers): 1e-3 of the output's scale against the oracle on the same quantised cache, for unsplit,
     split and kernel-chosen launches, ragged lengths and scattered pages; and it is the kernel that ran."""
     from grilly_next import cabi
@@ -105,7 +106,7 @@ def test_tensor_core_decode_over_the_quantised_cache(Hq, Hkv, lens):
         k = rng.standard_normal((B, T, Hkv, D), dtype=np.float32) * rng.uniform(0.2, 3.0, (B, T, Hkv, 1)).astype(np.float32)
         v = rng.standard_normal((B, T, Hkv, D), dtype=np.float32)
         q = rng.standard_normal((B, 1, Hq, D), dtype=np.float32)
-        pc = PagedCache(dev, B, Hkv, D, T + 64, dtype=cabi.FP8_INT4, shuffle_pages=True, seed=5)
+        pc = PagedCache(dev, B, Hkv, D, T + 64, page_tokens=P, dtype=cabi.FP8_INT4, shuffle_pages=True, seed=5)
         pc.append(k, v)
         cut = np.array(lens, np.int32)                      # shorten the sequences: the pages keep their tails
         dev.L.grl_memcpy_h2d(dev.h, pc.seq_lens, cut.ctypes.data_as(C.c_void_p), cut.nbytes)
