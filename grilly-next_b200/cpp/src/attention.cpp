@@ -88,20 +88,20 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
     GrillyBuffer q32, k32, v32, out = pool.acquire(n * 4);
     // share of a chunk that the host threads round to bf16 themselves (the rest is cast on the device)
     size_t hostPct = kPipelineHostCastPct;
-    // Several processes of one node (one per GPU) share the host's cores and memory bandwidth, which is what
-    // the rounding costs; every GPU has its own link.  Measured with 2 processes: 22.5 / 26.8 / 27.5 / 26.7
-    // TFLOP/s in total at 100 / 50 / 25 / 0 %.
-    if (const char* e = std::getenv("LOCAL_WORLD_SIZE")) {
-        const int lws = std::atoi(e);
-        if (lws > 1) {
-            // Per chunk the link is busy for ((1-x)*4 + x*2) bytes per element and the host threads for 4*x bytes
-            // per element; the two overlap, so the best share x makes them equal: x = 2 r_h / (2 r_l + r_h) with
-            // the rounding rate r_h and the link rate r_l this process measured in its earlier calls (the first
-            // call has no measurement yet and starts from 50 % / processes).
-            const double rh = g_hostRoundBps.load(), rl = g_linkBps.load();
-            if (rh > 0.0 && rl > 0.0) hostPct = size_t(std::min(100.0, std::max(0.0, 100.0 * 2.0 * rh / (2.0 * rl + rh))));
-            else hostPct = size_t(50 / lws);
-        }
+    // Per chunk the link is busy for ((1-x)*4 + x*2) bytes per element and the host threads for 4*x bytes per
+    // element; the two overlap, so the best share x makes them equal: x = 2 r_h / (2 r_l + r_h) with the rounding
+    // rate r_h and the link rate r_l this process measured in its earlier calls.  Measured on one B200 box (host
+    // rounds at 59 GB/s, link at 45): 8.32 / 7.80 / 7.58 / 7.81 / 7.48 / 7.67 ms per call at 100 / 90 / 80 / 70 / 60 /
+    // 40 %; the rule picks 79 %.  Several processes of one node (one per GPU) share the host's cores and memory
+    // bandwidth, which is what the rounding costs, while every GPU has its own link (2 processes: 22.5 / 26.8 /
+    // 27.5 / 26.7 TFLOP/s in total at 100 / 50 / 25 / 0 %): their measured r_h is lower and the same rule gives them
+    // a smaller share.  The first call has no measurement yet: 100 % alone, 50 % / processes otherwise.
+    {
+        int lws = 1;
+        if (const char* e = std::getenv("LOCAL_WORLD_SIZE")) lws = std::max(1, std::atoi(e));
+        const double rh = g_hostRoundBps.load(), rl = g_linkBps.load();
+        if (rh > 0.0 && rl > 0.0) hostPct = size_t(std::min(100.0, std::max(0.0, 100.0 * 2.0 * rh / (2.0 * rl + rh))));
+        else if (lws > 1) hostPct = size_t(50 / lws);
     }
     if (const char* e = std::getenv("GRILLY_PIPELINE_HOST_CAST_PCT")) hostPct = size_t(std::min(100, std::max(0, std::atoi(e))));
     if (!(pipelined && bf16 && hostPct == 100)) {
