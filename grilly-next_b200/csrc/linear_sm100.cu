@@ -21,7 +21,7 @@ namespace lin {
 using namespace sm100;
 
 constexpr int BM = 128, BN = 128, BK = 64;
-constexpr int NST = 4;
+constexpr int NST = 3;             // 96 KiB of ring: two CTAs per SM, so one CTA's epilogue overlaps the other's products
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE = A_BYTES + B_BYTES;   // 16 + 16 KiB
 constexpr int SMEM_BAR = NST * STAGE;
 constexpr int SMEM_TOTAL = SMEM_BAR + 128 + 1024;
@@ -54,7 +54,7 @@ __device__ __forceinline__ bool wait(uint32_t bar, uint32_t parity, volatile int
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 linear_sm100_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const Args a) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
