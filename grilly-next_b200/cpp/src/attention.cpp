@@ -92,16 +92,18 @@ void flashAttention2Ex(CommandBatch& batch, BufferPool& pool, PipelineCache& cac
     // element; the two overlap, so the best share x makes them equal: x = 2 r_h / (2 r_l + r_h) with the rounding
     // rate r_h and the link rate r_l this process measured in its earlier calls.  Measured on one B200 box (host
     // rounds at 59 GB/s, link at 45): 8.32 / 7.80 / 7.58 / 7.81 / 7.48 / 7.67 ms per call at 100 / 90 / 80 / 70 / 60 /
-    // 40 %; the rule picks 79 %.  Several processes of one node (one per GPU) share the host's cores and memory
-    // bandwidth, which is what the rounding costs, while every GPU has its own link (2 processes: 22.5 / 26.8 /
-    // 27.5 / 26.7 TFLOP/s in total at 100 / 50 / 25 / 0 %): their measured r_h is lower and the same rule gives them
-    // a smaller share.  The first call has no measurement yet: 100 % alone, 50 % / processes otherwise.
+    // 40 %; the rule picks 79 %.  The first call has no measurement yet and rounds everything on the host.
+    // Several processes of one node (one per GPU) share the host's cores and memory: their rounding threads
+    // oversubscribe the cores and take memory bandwidth from the copies, which the two-rate model does not see.
+    // Measured with 4 processes: 15.7 / 16.3 / 19.8 / 24.4 ms per call at 0 / 30 / 62 (the rule) / 100 %; with 8:
+    // 26.8 / 27.7 / 27.4 at 0 / 15 / 33 %; with 2: 22.5 / 26.8 / 27.5 / 26.7 TFLOP/s in total at 100 / 50 / 25 / 0 %.
+    // So a process that shares the host uploads float32 and casts on the device.
     {
         int lws = 1;
         if (const char* e = std::getenv("LOCAL_WORLD_SIZE")) lws = std::max(1, std::atoi(e));
         const double rh = g_hostRoundBps.load(), rl = g_linkBps.load();
-        if (rh > 0.0 && rl > 0.0) hostPct = size_t(std::min(100.0, std::max(0.0, 100.0 * 2.0 * rh / (2.0 * rl + rh))));
-        else if (lws > 1) hostPct = size_t(50 / lws);
+        if (lws > 1) hostPct = 0;
+        else if (rh > 0.0 && rl > 0.0) hostPct = size_t(std::min(100.0, std::max(0.0, 100.0 * 2.0 * rh / (2.0 * rl + rh))));
     }
     if (const char* e = std::getenv("GRILLY_PIPELINE_HOST_CAST_PCT")) hostPct = size_t(std::min(100, std::max(0, std::atoi(e))));
     if (!(pipelined && bf16 && hostPct == 100)) {
