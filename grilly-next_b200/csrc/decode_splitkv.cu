@@ -407,8 +407,9 @@ int grl_gqa_decode(grl_device* dev, const grl_decode_params* p) {
     // the tensor-core kernel merges its own splits (last CTA of a head to arrive) when its counters can hold the heads
     const bool fused = mma && !direct && n_splits <= 256 && kv.batch * kv.num_kv_heads <= grl_device::kCounterSlots;
     GRL_REQUIRE(!p->exchange || fused,
-                "the cross-GPU merge inside the decode needs the tensor-core geometry (bf16 cache, head_dim 128, "
-                "64-token pages); use partial_out and grl_exchange_merge instead");
+                "the cross-GPU merge inside the decode needs the tensor-core geometry (bf16 cache at head_dim 128 / 64 or "
+                "the quantised cache at 128, pages of 64 / 32 / 16 tokens, at most 8 query heads per kv head) and a split "
+                "launch; use partial_out and grl_exchange_merge instead");
     if (mma)
         rc = decode_mma_launch(dev, p, n_splits, a.scale, direct, fused);
     else

@@ -374,8 +374,8 @@ int grl_lse_merge(grl_device* dev, const float* parts, int n_parts, size_t part_
  * `world` device pointers (imported; the entry of this rank is ignored).  Every rank must make the
  * same sequence of calls.
  * With flag_slots = S the flags are uint32[2][world][S]; grl_exchange_merge uses slot 0.
- * grl_decode_params.exchange (tensor-core geometry only: bf16 cache, head_dim 128, 64-token pages,
- * B*Hkv <= the SM count, low_latency inbox format) goes one step further: the CTA that finishes a (sequence, kv
+ * grl_decode_params.exchange (tensor-core geometry only: bf16 cache at head_dim 128 or 64, or the quantised cache
+ * at 128; pages of 64, 32 or 16 tokens; B*Hkv <= the SM count; low_latency inbox format) goes one step further: the CTA that finishes a (sequence, kv
  * head) last merges its splits, stores the head's rows into the peers' inboxes, waits for theirs and
  * writes the final rows -- decode, exchange and merge are ONE launch per step; local_partial, out,
  * rows and head_dim of the exchange struct are then ignored. */
