@@ -276,7 +276,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant
             int issued = 0;
             for (int p = p_begin; p < p_end; ++p) {
                 const int i = p - p_begin, s = i % NST, it = i / NST;
-                if (it > 0 && !wait_bar(ctx, NST + s, (it - 1) & 1, QUANT)) break;
+                if (it > 0 && !wait_bar(ctx, NST + s, (it - 1) & 1, true)) break;
                 // the pages of this stage that hold tokens of the sequence (all of them but in the last stage); rows of
                 // the stage that no copy fills keep what they held: their tokens are past the length and masked
                 const int np = min(a.ppt, (len - p * P + a.page - 1) / a.page);
